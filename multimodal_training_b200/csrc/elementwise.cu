@@ -1,0 +1,657 @@
+// Memory-bound kernels of the training step, written for HBM3e streaming:
+// 16-byte vector accesses, one pass over each tensor, fp32 math, bf16 storage.
+//
+//   RMSNorm fwd/bwd            (reference: HF Qwen2RMSNorm used at modeling_qwen2_5_vl.py:253,771,1302)
+//   rotate-half RoPE, in place (reference: modeling_qwen2_5_vl.py:272-283 vision, 1153-1191 M-RoPE)
+//   SwiGLU / GELU fwd/bwd      (reference: modeling_qwen2_5_vl.py:204,256,1149)
+//   row gather / scatter(-add) (embedding lookup, window permutation, vision->text splice)
+//   column sums                (bias gradients)
+//   vocab-parallel cross-entropy statistics and in-place gradient
+//                              (reference: python/tensor_parallel/cross_entropy.py:41-236)
+//   fused AdamW over a flat parameter shard, sum of squares (grad norm)
+//                              (reference: torch.optim.Adam at python/ray/trainer.py:503-572)
+#include "common.cuh"
+#include "runtime.h"
+
+namespace {
+
+typedef __nv_bfloat16 bf16;
+
+MMT_DEVICE void load8(const bf16* p, float (&v)[8]) {
+  const uint4 u = *reinterpret_cast<const uint4*>(p);
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 f = unpack_bf16x2(w[j]);
+    v[2 * j] = f.x;
+    v[2 * j + 1] = f.y;
+  }
+}
+MMT_DEVICE void store8(bf16* p, const float (&v)[8]) {
+  uint4 o;
+  o.x = pack_bf16x2(v[0], v[1]);
+  o.y = pack_bf16x2(v[2], v[3]);
+  o.z = pack_bf16x2(v[4], v[5]);
+  o.w = pack_bf16x2(v[6], v[7]);
+  *reinterpret_cast<uint4*>(p) = o;
+}
+
+template <int kThreads>
+MMT_DEVICE float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  if (l == 0) red[w] = v;
+  __syncthreads();
+  float t = (threadIdx.x < kThreads / 32) ? red[threadIdx.x] : 0.f;
+  if (w == 0) {
+    t = warp_sum(t);
+    if (l == 0) red[0] = t;
+  }
+  __syncthreads();
+  const float r = red[0];
+  __syncthreads();
+  return r;
+}
+template <int kThreads>
+MMT_DEVICE float block_max(float v, float* red) {
+  v = warp_max(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  if (l == 0) red[w] = v;
+  __syncthreads();
+  float t = (threadIdx.x < kThreads / 32) ? red[threadIdx.x] : -INFINITY;
+  if (w == 0) {
+    t = warp_max(t);
+    if (l == 0) red[0] = t;
+  }
+  __syncthreads();
+  const float r = red[0];
+  __syncthreads();
+  return r;
+}
+
+// ----------------------------------------------------------------------------
+// RMSNorm.  One CTA per row; the row stays in registers between the two passes.
+// cols % 8 == 0, cols <= 8 * kThreads * kVec.
+// ----------------------------------------------------------------------------
+constexpr int kNormThreads = 256;
+constexpr int kNormVec = 4;  // up to 8192 columns
+
+__global__ void __launch_bounds__(kNormThreads) rmsnorm_fwd_kernel(const bf16* __restrict__ x,
+                                                                  const bf16* __restrict__ w, bf16* __restrict__ y,
+                                                                  float* __restrict__ rstd_out, int cols, float eps) {
+  __shared__ float red[32];
+  const long row = blockIdx.x;
+  const bf16* xr = x + row * cols;
+  float v[kNormVec][8];
+  float ss = 0.f;
+  const int nvec = cols >> 3;
+#pragma unroll
+  for (int i = 0; i < kNormVec; ++i) {
+    const int c = threadIdx.x + i * kNormThreads;
+    if (c < nvec) {
+      load8(xr + c * 8, v[i]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += v[i][j] * v[i][j];
+    }
+  }
+  ss = block_sum<kNormThreads>(ss, red);
+  const float rstd = rsqrtf(ss / (float)cols + eps);
+  if (threadIdx.x == 0 && rstd_out) rstd_out[row] = rstd;
+#pragma unroll
+  for (int i = 0; i < kNormVec; ++i) {
+    const int c = threadIdx.x + i * kNormThreads;
+    if (c < nvec) {
+      float wv[8], o[8];
+      load8(w + c * 8, wv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = v[i][j] * rstd * wv[j];
+      store8(y + row * cols + c * 8, o);
+    }
+  }
+}
+
+// dx = rstd * (g - x * rstd^2 * mean(g * x)),  g = dy * w.
+// Each CTA walks rows blockIdx.x, +gridDim.x, ... and keeps its share of
+// dw = sum_rows(dy * x * rstd) in registers; the per-CTA partial sums go to
+// `dw_partial` [gridDim.x, cols] (fp32 scratch) for the second-stage reduction.
+__global__ void __launch_bounds__(kNormThreads) rmsnorm_bwd_kernel(const bf16* __restrict__ dy,
+                                                                  const bf16* __restrict__ x,
+                                                                  const bf16* __restrict__ w,
+                                                                  const float* __restrict__ rstd_in,
+                                                                  bf16* __restrict__ dx, float* __restrict__ dw_partial,
+                                                                  int rows, int cols) {
+  __shared__ float red[32];
+  const int nvec = cols >> 3;
+  float dwacc[kNormVec][8];
+  float wv[kNormVec][8];
+#pragma unroll
+  for (int i = 0; i < kNormVec; ++i) {
+    const int c = threadIdx.x + i * kNormThreads;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dwacc[i][j] = 0.f;
+    if (c < nvec) load8(w + c * 8, wv[i]);
+  }
+  for (long row = blockIdx.x; row < rows; row += gridDim.x) {
+    const float rstd = rstd_in[row];
+    float xv[kNormVec][8], g[kNormVec][8];
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < kNormVec; ++i) {
+      const int c = threadIdx.x + i * kNormThreads;
+      if (c < nvec) {
+        float d[8];
+        load8(x + row * cols + c * 8, xv[i]);
+        load8(dy + row * cols + c * 8, d);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          g[i][j] = d[j] * wv[i][j];
+          dot += g[i][j] * xv[i][j];
+          dwacc[i][j] += d[j] * xv[i][j] * rstd;
+        }
+      }
+    }
+    dot = block_sum<kNormThreads>(dot, red);
+    const float coef = dot * rstd * rstd / (float)cols;
+#pragma unroll
+    for (int i = 0; i < kNormVec; ++i) {
+      const int c = threadIdx.x + i * kNormThreads;
+      if (c < nvec) {
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = rstd * (g[i][j] - xv[i][j] * coef);
+        store8(dx + row * cols + c * 8, o);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < kNormVec; ++i) {
+    const int c = threadIdx.x + i * kNormThreads;
+    if (c < nvec) {
+      float* dst = dw_partial + (long)blockIdx.x * cols + c * 8;
+      *reinterpret_cast<float4*>(dst) = make_float4(dwacc[i][0], dwacc[i][1], dwacc[i][2], dwacc[i][3]);
+      *reinterpret_cast<float4*>(dst + 4) = make_float4(dwacc[i][4], dwacc[i][5], dwacc[i][6], dwacc[i][7]);
+    }
+  }
+}
+
+// out[c] (+)= sum_p partial[p, c]; out is bf16.
+__global__ void reduce_partials_kernel(const float* __restrict__ partial, bf16* __restrict__ out, int parts, int cols,
+                                       int accumulate) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= cols) return;
+  float s = 0.f;
+  for (int p = 0; p < parts; ++p) s += partial[(long)p * cols + c];
+  if (accumulate) s += __bfloat162float(out[c]);
+  out[c] = __float2bfloat16(s);
+}
+
+// ----------------------------------------------------------------------------
+// Rotate-half rotary embedding, in place, over the first `heads` heads of each row.
+// x: [tokens, row_stride] with head h at column h*dim; cs: cos [tokens, dim], sin [tokens, dim] (fp32).
+// sign = +1 forward, -1 backward (the transpose of the rotation).
+// ----------------------------------------------------------------------------
+__global__ void rope_kernel(bf16* __restrict__ x, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                            long tokens, int heads, int dim, long row_stride, float sign) {
+  const int half = dim >> 1;
+  const int pairs_per_head = half >> 1;  // two adjacent columns per thread
+  const long total = tokens * heads * pairs_per_head;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    const int pp = (int)(i % pairs_per_head);
+    const long th = i / pairs_per_head;
+    const int h = (int)(th % heads);
+    const long t = th / heads;
+    const int c = pp * 2;
+    bf16* base = x + t * row_stride + (long)h * dim;
+    const float2 lo = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(base + c));
+    const float2 hi = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(base + c + half));
+    const float2 c_lo = *reinterpret_cast<const float2*>(cos_t + t * dim + c);
+    const float2 c_hi = *reinterpret_cast<const float2*>(cos_t + t * dim + c + half);
+    const float2 s_lo = *reinterpret_cast<const float2*>(sin_t + t * dim + c);
+    const float2 s_hi = *reinterpret_cast<const float2*>(sin_t + t * dim + c + half);
+    float o_lo0, o_lo1, o_hi0, o_hi1;
+    if (sign > 0.f) {
+      // y_lo = x_lo*cos_lo - x_hi*sin_lo ; y_hi = x_hi*cos_hi + x_lo*sin_hi
+      o_lo0 = lo.x * c_lo.x - hi.x * s_lo.x;
+      o_lo1 = lo.y * c_lo.y - hi.y * s_lo.y;
+      o_hi0 = hi.x * c_hi.x + lo.x * s_hi.x;
+      o_hi1 = hi.y * c_hi.y + lo.y * s_hi.y;
+    } else {
+      // transpose: dx_lo = dy_lo*cos_lo + dy_hi*sin_hi ; dx_hi = dy_hi*cos_hi - dy_lo*sin_lo
+      o_lo0 = lo.x * c_lo.x + hi.x * s_hi.x;
+      o_lo1 = lo.y * c_lo.y + hi.y * s_hi.y;
+      o_hi0 = hi.x * c_hi.x - lo.x * s_lo.x;
+      o_hi1 = hi.y * c_hi.y - lo.y * s_lo.y;
+    }
+    *reinterpret_cast<uint32_t*>(base + c) = pack_bf16x2(o_lo0, o_lo1);
+    *reinterpret_cast<uint32_t*>(base + c + half) = pack_bf16x2(o_hi0, o_hi1);
+  }
+}
+
+// ----------------------------------------------------------------------------
+// SwiGLU on a fused [rows, 2*inter] gate|up buffer.
+// ----------------------------------------------------------------------------
+__global__ void swiglu_fwd_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, long rows, int inter) {
+  const int nvec = inter >> 3;
+  const long total = rows * nvec;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    const long r = i / nvec;
+    const int c = (int)(i % nvec) * 8;
+    float g[8], u[8], o[8];
+    load8(gu + r * 2 * inter + c, g);
+    load8(gu + r * 2 * inter + inter + c, u);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = silu(g[j]) * u[j];
+    store8(out + r * inter + c, o);
+  }
+}
+
+__global__ void swiglu_bwd_kernel(const bf16* __restrict__ dout, const bf16* __restrict__ gu, bf16* __restrict__ dgu,
+                                  long rows, int inter) {
+  const int nvec = inter >> 3;
+  const long total = rows * nvec;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    const long r = i / nvec;
+    const int c = (int)(i % nvec) * 8;
+    float g[8], u[8], d[8], dg[8], du[8];
+    load8(gu + r * 2 * inter + c, g);
+    load8(gu + r * 2 * inter + inter + c, u);
+    load8(dout + r * inter + c, d);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float sg = 1.f / (1.f + __expf(-g[j]));
+      const float sl = g[j] * sg;
+      dg[j] = d[j] * u[j] * (sg + sl * (1.f - sg));
+      du[j] = d[j] * sl;
+    }
+    store8(dgu + r * 2 * inter + c, dg);
+    store8(dgu + r * 2 * inter + inter + c, du);
+  }
+}
+
+__global__ void gelu_fwd_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, long n8) {
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n8; i += (long)gridDim.x * blockDim.x) {
+    float v[8];
+    load8(x + i * 8, v);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = gelu_erf(v[j]);
+    store8(y + i * 8, v);
+  }
+}
+__global__ void gelu_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, bf16* __restrict__ dx,
+                                long n8) {
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n8; i += (long)gridDim.x * blockDim.x) {
+    float v[8], d[8];
+    load8(x + i * 8, v);
+    load8(dy + i * 8, d);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) d[j] *= gelu_erf_grad(v[j]);
+    store8(dx + i * 8, d);
+  }
+}
+
+// y = a + b (bf16), used for residual adds outside GEMM epilogues.
+__global__ void add_kernel(const bf16* __restrict__ a, const bf16* __restrict__ b, bf16* __restrict__ y, long n8) {
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n8; i += (long)gridDim.x * blockDim.x) {
+    float u[8], v[8];
+    load8(a + i * 8, u);
+    load8(b + i * 8, v);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) u[j] += v[j];
+    store8(y + i * 8, u);
+  }
+}
+
+// ----------------------------------------------------------------------------
+// Row gather / scatter.  idx[r] < 0 (or outside [lo, hi)) gives a zero row on
+// gather and is skipped on scatter.  One warp per row.
+// ----------------------------------------------------------------------------
+__global__ void gather_rows_kernel(const bf16* __restrict__ src, const long* __restrict__ idx, bf16* __restrict__ dst,
+                                   long rows, int cols, long lo, long hi, long src_ld, long dst_ld) {
+  const long r = blockIdx.x * (long)(blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (r >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const long s = idx[r];
+  const bool valid = s >= lo && s < hi;
+  const uint4 zero = make_uint4(0, 0, 0, 0);
+  for (int c = lane * 8; c < cols; c += 256) {
+    uint4 v = valid ? *reinterpret_cast<const uint4*>(src + (s - lo) * src_ld + c) : zero;
+    *reinterpret_cast<uint4*>(dst + r * dst_ld + c) = v;
+  }
+}
+
+// dst[idx[r]] = src[r]   (add == 0)   or   dst[idx[r]] += src[r]  (add == 1, bf16x2 atomics)
+__global__ void scatter_rows_kernel(const bf16* __restrict__ src, const long* __restrict__ idx, bf16* __restrict__ dst,
+                                    long rows, int cols, long lo, long hi, long src_ld, long dst_ld, int add) {
+  const long r = blockIdx.x * (long)(blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (r >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const long d = idx[r];
+  if (d < lo || d >= hi) return;
+  if (!add) {
+    for (int c = lane * 8; c < cols; c += 256)
+      *reinterpret_cast<uint4*>(dst + (d - lo) * dst_ld + c) = *reinterpret_cast<const uint4*>(src + r * src_ld + c);
+  } else {
+    for (int c = lane * 2; c < cols; c += 64) {
+      const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(src + r * src_ld + c);
+      atomicAdd(reinterpret_cast<__nv_bfloat162*>(dst + (d - lo) * dst_ld + c), v);
+    }
+  }
+}
+
+// ----------------------------------------------------------------------------
+// Column sums: out[c] (+)= sum_r x[r, c].  Stage 1 writes per-CTA partials.
+// ----------------------------------------------------------------------------
+__global__ void colsum_partial_kernel(const bf16* __restrict__ x, float* __restrict__ partial, long rows, int cols,
+                                      long ld) {
+  // blockDim = (32 column-vectors, 8 row lanes); grid = (ceil(cols/256), row splits)
+  __shared__ float red[8][32][8];
+  const int cv = blockIdx.x * 32 + threadIdx.x;
+  const int c = cv * 8;
+  float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  if (c < cols) {
+    for (long r = blockIdx.y * 8 + threadIdx.y; r < rows; r += (long)gridDim.y * 8) {
+      float v[8];
+      load8(x + r * ld + c, v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += v[j];
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) red[threadIdx.y][threadIdx.x][j] = acc[j];
+  __syncthreads();
+  if (threadIdx.y == 0 && c < cols) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float s = 0.f;
+      for (int k = 0; k < 8; ++k) s += red[k][threadIdx.x][j];
+      partial[(long)blockIdx.y * cols + c + j] = s;
+    }
+  }
+}
+
+// ----------------------------------------------------------------------------
+// Vocab-parallel cross-entropy.
+// stats: per row, max over the local vocab shard, sum exp(l - max), and the target logit if the
+// label falls into [vocab_lo, vocab_lo + V) (else 0).
+// grad (in place): l <- (exp(l - gmax) / gsum - [label == col]) * scale for valid rows, 0 otherwise.
+// ----------------------------------------------------------------------------
+constexpr int kCeThreads = 512;
+
+__global__ void __launch_bounds__(kCeThreads) ce_stats_kernel(const bf16* __restrict__ logits,
+                                                             const long* __restrict__ labels, float* __restrict__ omax,
+                                                             float* __restrict__ osum, float* __restrict__ otgt, int V,
+                                                             long ld, long vocab_lo) {
+  __shared__ float red[32];
+  const long row = blockIdx.x;
+  const bf16* l = logits + row * ld;
+  const int nvec = V >> 3;
+  float m = -INFINITY, s = 0.f;
+  for (int c = threadIdx.x; c < nvec; c += kCeThreads) {
+    float v[8];
+    load8(l + c * 8, v);
+    float lm = v[0];
+#pragma unroll
+    for (int j = 1; j < 8; ++j) lm = fmaxf(lm, v[j]);
+    if (lm > m) {
+      s *= __expf(m - lm);
+      m = lm;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) s += __expf(v[j] - m);
+  }
+  const float gm = block_max<kCeThreads>(m, red);
+  s = (m == -INFINITY) ? 0.f : s * __expf(m - gm);
+  s = block_sum<kCeThreads>(s, red);
+  if (threadIdx.x == 0) {
+    omax[row] = gm;
+    osum[row] = s;
+    const long lab = labels[row] - vocab_lo;
+    otgt[row] = (lab >= 0 && lab < V) ? __bfloat162float(l[lab]) : 0.f;
+  }
+}
+
+__global__ void __launch_bounds__(kCeThreads) ce_grad_kernel(bf16* __restrict__ logits, const long* __restrict__ labels,
+                                                            const float* __restrict__ gmax,
+                                                            const float* __restrict__ gsum,
+                                                            const float* __restrict__ scale_ptr, int V, long ld,
+                                                            long vocab_lo) {
+  const long row = blockIdx.x;
+  bf16* l = logits + row * ld;
+  const int nvec = V >> 3;
+  const long lab_g = labels[row];
+  const bool valid = lab_g >= 0;
+  const long lab = lab_g - vocab_lo;
+  const float scale = valid ? *scale_ptr : 0.f;
+  const float m = gmax[row];
+  const float inv = valid ? 1.f / gsum[row] : 0.f;
+  for (int c = threadIdx.x; c < nvec; c += kCeThreads) {
+    float v[8];
+    load8(l + c * 8, v);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float p = __expf(v[j] - m) * inv;
+      if ((long)(c * 8 + j) == lab) p -= 1.f;
+      v[j] = p * scale;
+    }
+    store8(l + c * 8, v);
+  }
+}
+
+// ----------------------------------------------------------------------------
+// Fused AdamW (decoupled weight decay) over a flat shard.
+//   g <- g * gscale;  m,v update;  master -= lr * (mhat / (sqrt(vhat) + eps) + wd * master);  p = bf16(master)
+// Elements [0, n_decay) use `wd`, the rest 0.  gscale_ptr may be null (1.0).
+// ----------------------------------------------------------------------------
+__global__ void adamw_kernel(bf16* __restrict__ p, const bf16* __restrict__ g, float* __restrict__ master,
+                             float* __restrict__ m, float* __restrict__ v, long n, long n_decay, float lr, float b1,
+                             float b2, float eps, float wd, float bc1, float bc2,
+                             const float* __restrict__ gscale_ptr) {
+  const float gs = gscale_ptr ? *gscale_ptr : 1.f;
+  const long n8 = n >> 3;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n8; i += (long)gridDim.x * blockDim.x) {
+    const long e = i * 8;
+    float gv[8], out[8];
+    load8(g + e, gv);
+    float4 w0 = *reinterpret_cast<float4*>(master + e), w1 = *reinterpret_cast<float4*>(master + e + 4);
+    float4 m0 = *reinterpret_cast<float4*>(m + e), m1 = *reinterpret_cast<float4*>(m + e + 4);
+    float4 v0 = *reinterpret_cast<float4*>(v + e), v1 = *reinterpret_cast<float4*>(v + e + 4);
+    float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+    float mv[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
+    float vv[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float gj = gv[j] * gs;
+      mv[j] = b1 * mv[j] + (1.f - b1) * gj;
+      vv[j] = b2 * vv[j] + (1.f - b2) * gj * gj;
+      const float upd = (mv[j] / bc1) / (sqrtf(vv[j] / bc2) + eps);
+      const float decay = (e + j < n_decay) ? wd : 0.f;
+      wv[j] = wv[j] - lr * (upd + decay * wv[j]);
+      out[j] = wv[j];
+    }
+    *reinterpret_cast<float4*>(master + e) = make_float4(wv[0], wv[1], wv[2], wv[3]);
+    *reinterpret_cast<float4*>(master + e + 4) = make_float4(wv[4], wv[5], wv[6], wv[7]);
+    *reinterpret_cast<float4*>(m + e) = make_float4(mv[0], mv[1], mv[2], mv[3]);
+    *reinterpret_cast<float4*>(m + e + 4) = make_float4(mv[4], mv[5], mv[6], mv[7]);
+    *reinterpret_cast<float4*>(v + e) = make_float4(vv[0], vv[1], vv[2], vv[3]);
+    *reinterpret_cast<float4*>(v + e + 4) = make_float4(vv[4], vv[5], vv[6], vv[7]);
+    store8(p + e, out);
+  }
+}
+
+// out[0] += sum(x^2)   (fp32 atomic; caller zeroes out)
+__global__ void sumsq_kernel(const bf16* __restrict__ x, long n8, float* __restrict__ out) {
+  __shared__ float red[32];
+  float s = 0.f;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n8; i += (long)gridDim.x * blockDim.x) {
+    float v[8];
+    load8(x + i * 8, v);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) s += v[j] * v[j];
+  }
+  s = block_sum<256>(s, red);
+  if (threadIdx.x == 0) atomicAdd(out, s);
+}
+
+// coef = min(1, max_norm / (sqrt(normsq) + 1e-6)) * extra
+__global__ void clip_coef_kernel(const float* __restrict__ normsq, float max_norm, float extra,
+                                 float* __restrict__ coef) {
+  const float n = sqrtf(*normsq);
+  float c = max_norm > 0.f ? fminf(1.f, max_norm / (n + 1e-6f)) : 1.f;
+  *coef = c * extra;
+}
+
+inline int grid_for(long work, int threads, int max_blocks) {
+  long b = (work + threads - 1) / threads;
+  if (b < 1) b = 1;
+  if (b > max_blocks) b = max_blocks;
+  return (int)b;
+}
+
+}  // namespace
+
+#define ST(s) reinterpret_cast<cudaStream_t>(s)
+#define BF(p) reinterpret_cast<bf16*>(p)
+#define CBF(p) reinterpret_cast<const bf16*>(p)
+
+extern "C" {
+
+int mmt_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, long rows, int cols, float eps, void* stream) {
+  if (cols % 8 || cols > 8 * kNormThreads * kNormVec) return -2;
+  if (rows == 0) return 0;
+  rmsnorm_fwd_kernel<<<(unsigned)rows, kNormThreads, 0, ST(stream)>>>(CBF(x), CBF(w), BF(y), rstd, cols, eps);
+  return (int)cudaGetLastError();
+}
+
+// Number of per-CTA partial rows that mmt_rmsnorm_bwd writes; scratch must hold parts*cols floats.
+int mmt_rmsnorm_bwd_parts(long rows) {
+  const int cap = mmt_sm_count() * 2;
+  return (int)(rows < cap ? (rows > 0 ? rows : 1) : cap);
+}
+
+// dx and dw (bf16; accumulate_dw adds to the existing dw).  scratch: fp32 [parts, cols].
+int mmt_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx, void* dw,
+                    float* scratch, long rows, int cols, int accumulate_dw, void* stream) {
+  if (cols % 8 || cols > 8 * kNormThreads * kNormVec) return -2;
+  if (rows == 0) return 0;
+  const int parts = mmt_rmsnorm_bwd_parts(rows);
+  rmsnorm_bwd_kernel<<<parts, kNormThreads, 0, ST(stream)>>>(CBF(dy), CBF(x), CBF(w), rstd, BF(dx), scratch, (int)rows,
+                                                            cols);
+  reduce_partials_kernel<<<(cols + 255) / 256, 256, 0, ST(stream)>>>(scratch, BF(dw), parts, cols, accumulate_dw);
+  return (int)cudaGetLastError();
+}
+
+int mmt_rope(void* x, const float* cos_t, const float* sin_t, long tokens, int heads, int dim, long row_stride,
+             int backward, void* stream) {
+  if (dim % 4) return -2;
+  const long work = tokens * heads * (dim / 4);
+  if (work == 0) return 0;
+  rope_kernel<<<grid_for(work, 256, mmt_sm_count() * 8), 256, 0, ST(stream)>>>(BF(x), cos_t, sin_t, tokens, heads, dim,
+                                                                              row_stride, backward ? -1.f : 1.f);
+  return (int)cudaGetLastError();
+}
+
+int mmt_swiglu_fwd(const void* gu, void* out, long rows, int inter, void* stream) {
+  if (inter % 8) return -2;
+  const long work = rows * (inter / 8);
+  if (work == 0) return 0;
+  swiglu_fwd_kernel<<<grid_for(work, 256, mmt_sm_count() * 8), 256, 0, ST(stream)>>>(CBF(gu), BF(out), rows, inter);
+  return (int)cudaGetLastError();
+}
+int mmt_swiglu_bwd(const void* dout, const void* gu, void* dgu, long rows, int inter, void* stream) {
+  if (inter % 8) return -2;
+  const long work = rows * (inter / 8);
+  if (work == 0) return 0;
+  swiglu_bwd_kernel<<<grid_for(work, 256, mmt_sm_count() * 8), 256, 0, ST(stream)>>>(CBF(dout), CBF(gu), BF(dgu), rows,
+                                                                                    inter);
+  return (int)cudaGetLastError();
+}
+int mmt_gelu_fwd(const void* x, void* y, long n, void* stream) {
+  if (n % 8) return -2;
+  if (n == 0) return 0;
+  gelu_fwd_kernel<<<grid_for(n / 8, 256, mmt_sm_count() * 8), 256, 0, ST(stream)>>>(CBF(x), BF(y), n / 8);
+  return (int)cudaGetLastError();
+}
+int mmt_gelu_bwd(const void* dy, const void* x, void* dx, long n, void* stream) {
+  if (n % 8) return -2;
+  if (n == 0) return 0;
+  gelu_bwd_kernel<<<grid_for(n / 8, 256, mmt_sm_count() * 8), 256, 0, ST(stream)>>>(CBF(dy), CBF(x), BF(dx), n / 8);
+  return (int)cudaGetLastError();
+}
+int mmt_add(const void* a, const void* b, void* y, long n, void* stream) {
+  if (n % 8) return -2;
+  if (n == 0) return 0;
+  add_kernel<<<grid_for(n / 8, 256, mmt_sm_count() * 8), 256, 0, ST(stream)>>>(CBF(a), CBF(b), BF(y), n / 8);
+  return (int)cudaGetLastError();
+}
+
+int mmt_gather_rows(const void* src, const long* idx, void* dst, long rows, int cols, long lo, long hi, long src_ld,
+                    long dst_ld, void* stream) {
+  if (cols % 8 || src_ld % 8 || dst_ld % 8) return -2;
+  if (rows == 0) return 0;
+  gather_rows_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, ST(stream)>>>(CBF(src), idx, BF(dst), rows, cols, lo, hi,
+                                                                        src_ld, dst_ld);
+  return (int)cudaGetLastError();
+}
+int mmt_scatter_rows(const void* src, const long* idx, void* dst, long rows, int cols, long lo, long hi, long src_ld,
+                     long dst_ld, int add, void* stream) {
+  if (cols % 8 || src_ld % 8 || dst_ld % 8) return -2;
+  if (rows == 0) return 0;
+  scatter_rows_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, ST(stream)>>>(CBF(src), idx, BF(dst), rows, cols, lo, hi,
+                                                                         src_ld, dst_ld, add);
+  return (int)cudaGetLastError();
+}
+
+int mmt_colsum_parts(long rows) {
+  long p = (rows + 63) / 64;
+  const int cap = 64;
+  return (int)(p < 1 ? 1 : (p > cap ? cap : p));
+}
+// out[c] (+)= sum_r x[r,c]; scratch fp32 [parts, cols].
+int mmt_colsum(const void* x, void* out, float* scratch, long rows, int cols, long ld, int accumulate, void* stream) {
+  if (cols % 8 || ld % 8) return -2;
+  const int parts = mmt_colsum_parts(rows);
+  dim3 grid((cols + 255) / 256, parts), block(32, 8);
+  colsum_partial_kernel<<<grid, block, 0, ST(stream)>>>(CBF(x), scratch, rows, cols, ld);
+  reduce_partials_kernel<<<(cols + 255) / 256, 256, 0, ST(stream)>>>(scratch, BF(out), parts, cols, accumulate);
+  return (int)cudaGetLastError();
+}
+
+int mmt_ce_stats(const void* logits, const long* labels, float* omax, float* osum, float* otgt, long rows, int V,
+                 long ld, long vocab_lo, void* stream) {
+  if (V % 8 || ld % 8) return -2;
+  if (rows == 0) return 0;
+  ce_stats_kernel<<<(unsigned)rows, kCeThreads, 0, ST(stream)>>>(CBF(logits), labels, omax, osum, otgt, V, ld,
+                                                                vocab_lo);
+  return (int)cudaGetLastError();
+}
+int mmt_ce_grad(void* logits, const long* labels, const float* gmax, const float* gsum, const float* scale_ptr,
+                long rows, int V, long ld, long vocab_lo, void* stream) {
+  if (V % 8 || ld % 8) return -2;
+  if (rows == 0) return 0;
+  ce_grad_kernel<<<(unsigned)rows, kCeThreads, 0, ST(stream)>>>(BF(logits), labels, gmax, gsum, scale_ptr, V, ld,
+                                                               vocab_lo);
+  return (int)cudaGetLastError();
+}
+
+int mmt_adamw(void* p, const void* g, float* master, float* m, float* v, long n, long n_decay, float lr, float b1,
+              float b2, float eps, float wd, int step, const float* gscale_ptr, void* stream) {
+  if (n % 8) return -2;
+  if (n == 0) return 0;
+  const float bc1 = 1.f - powf(b1, (float)step), bc2 = 1.f - powf(b2, (float)step);
+  adamw_kernel<<<grid_for(n / 8, 256, mmt_sm_count() * 16), 256, 0, ST(stream)>>>(
+      BF(p), CBF(g), master, m, v, n, n_decay, lr, b1, b2, eps, wd, bc1, bc2, gscale_ptr);
+  return (int)cudaGetLastError();
+}
+
+int mmt_sumsq(const void* x, long n, float* out, void* stream) {
+  if (n % 8) return -2;
+  if (n == 0) return 0;
+  sumsq_kernel<<<grid_for(n / 8, 256, mmt_sm_count() * 8), 256, 0, ST(stream)>>>(CBF(x), n / 8, out);
+  return (int)cudaGetLastError();
+}
+int mmt_clip_coef(const float* normsq, float max_norm, float extra, float* coef, void* stream) {
+  clip_coef_kernel<<<1, 1, 0, ST(stream)>>>(normsq, max_norm, extra, coef);
+  return (int)cudaGetLastError();
+}
+
+}  // extern "C"

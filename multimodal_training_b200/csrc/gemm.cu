@@ -1,0 +1,369 @@
+// bf16 GEMM on the 5th-generation tensor cores (tcgen05) of sm_100a.
+//
+//   C[M,N] = epilogue( alpha * sum_k A[m,k] * B[n,k] )
+//
+// Persistent, warp-specialised kernel, one CTA per SM:
+//   warp 0      TMA producer: global -> 128B-swizzled shared-memory ring
+//   warp 1      MMA issuer: one thread issues tcgen05.mma (cta_group::1) with both
+//               operands in shared memory and the fp32 accumulator in tensor memory;
+//               tcgen05.commit frees ring slots and publishes finished accumulators
+//   warps 2..5  epilogue: tcgen05.ld accumulator rows -> registers -> fused
+//               bias / GELU / residual / accumulate -> bf16 (or fp32) global stores
+// The accumulator is double buffered in tensor memory (2 x BN columns) so the
+// epilogue of tile i overlaps the main loop of tile i+1.
+//
+// Operand layouts.  A is logically [M,K], B is logically [N,K].  Each may be
+// "K-major" (memory [rows][K]) or "MN-major" (memory [K][rows]); the three
+// combinations cover a linear layer's forward (K,K), its input gradient
+// (K,MN) and its weight gradient (MN,MN) without any transpose pass.
+// Tails in M, N and K are handled by TMA zero fill on loads and bounds checks
+// on stores.  Requirements: leading dimensions multiples of 8 elements, N % 8 == 0.
+//
+// Replaces the cuBLAS calls behind nn.Linear in the reference
+// (python/models/qwen2_5_vl/modeling_qwen2_5_vl.py:198-200,334-338,1143-1145,1226-1229).
+#include <cudaTypedefs.h>
+#include <stdio.h>
+
+#include "common.cuh"
+#include "runtime.h"
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64;            // 64 bf16 = one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr int kThreads = 192;
+
+struct GemmParams {
+  int M, N, K;
+  void* C;
+  int ldc;
+  const __nv_bfloat16* bias;      // [N] or nullptr
+  const __nv_bfloat16* residual;  // [M, ldr] or nullptr (added after the activation)
+  int ldr;
+  int act;                        // 0 none, 1 GELU(erf)
+  int accumulate;                 // C += result
+  int out_f32;                    // C is float
+  float alpha;
+  int a_mn, b_mn;                 // operand majors
+  uint32_t mn_lbo, mn_sbo, mn_kstep;  // descriptor constants of MN-major tiles
+  MmtErrorWord* ew;
+};
+
+template <int BN>
+struct Cfg {
+  static constexpr uint32_t A_BYTES = BM * BK * 2;
+  static constexpr uint32_t B_BYTES = BN * BK * 2;
+  static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int kStages = (BN >= 256) ? 4 : (BN >= 192 ? 5 : (BN >= 128 ? 6 : 8));
+  static constexpr uint32_t TMEM_COLS = (2 * BN <= 128) ? 128 : (2 * BN <= 256 ? 256 : 512);
+  static constexpr size_t SMEM = 1024 + (size_t)kStages * STAGE_BYTES + (2 * kStages + 4) * 8 + 16;
+};
+
+template <int BN>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                  const GemmParams p) {
+  using C_ = Cfg<BN>;
+  constexpr int kStages = C_::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)kStages * C_::STAGE_BYTES);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + kStages;
+  uint64_t* tfull = bars + 2 * kStages;
+  uint64_t* tempty = tfull + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int tiles_m = (p.M + BM - 1) / BM;
+  const int tiles_n = (p.N + BN - 1) / BN;
+  const int ntiles = tiles_m * tiles_n;
+  const int KB = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(&tfull[0], 1);
+    mbar_init(&tfull[1], 1);
+    mbar_init(&tempty[0], 4);
+    mbar_init(&tempty[1], 4);
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, C_::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+        const int tm = tile % tiles_m, tn = tile / tiles_m;
+        for (int kb = 0; kb < KB; ++kb) {
+          if (!mbar_wait(&empty[s], ph ^ 1, p.ew, 100)) { ok = false; break; }
+          uint8_t* sA = smem + (size_t)s * C_::STAGE_BYTES;
+          uint8_t* sB = sA + C_::A_BYTES;
+          mbar_expect_tx(&full[s], C_::STAGE_BYTES);
+          if (!p.a_mn) {
+            tma_load_2d(sA, &tmA, &full[s], kb * BK, tm * BM);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BM / 64; ++c) tma_load_2d(sA + c * 8192, &tmA, &full[s], tm * BM + c * 64, kb * BK);
+          }
+          if (!p.b_mn) {
+            tma_load_2d(sB, &tmB, &full[s], kb * BK, tn * BN);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c) tma_load_2d(sB + c * 8192, &tmB, &full[s], tn * BN + c * 64, kb * BK);
+          }
+          if (++s == kStages) { s = 0; ph ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer --------------------------------
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_bf16(BM, BN, p.a_mn, p.b_mn);
+      int s = 0, acc = 0;
+      uint32_t ph = 0, acc_ph = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+        if (!mbar_wait(&tempty[acc], acc_ph ^ 1, p.ew, 200)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+        for (int kb = 0; kb < KB; ++kb) {
+          if (!mbar_wait(&full[s], ph, p.ew, 201)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_base = smem_u32(smem + (size_t)s * C_::STAGE_BYTES);
+          const uint32_t b_base = a_base + C_::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t adesc = p.a_mn ? make_smem_desc(a_base + k * p.mn_kstep, p.mn_lbo, p.mn_sbo)
+                                          : make_smem_desc(a_base + k * (UMMA_K * 2), 16, 1024);
+            const uint64_t bdesc = p.b_mn ? make_smem_desc(b_base + k * p.mn_kstep, p.mn_lbo, p.mn_sbo)
+                                          : make_smem_desc(b_base + k * (UMMA_K * 2), 16, 1024);
+            tc_mma_ss(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          tc_commit(&empty[s]);
+          if (++s == kStages) { s = 0; ph ^= 1; }
+        }
+        if (!ok) break;
+        tc_commit(&tfull[acc]);
+        acc ^= 1;
+        if (acc == 0) acc_ph ^= 1;
+      }
+    }
+  } else {
+    // ------------------------------ epilogue ----------------------------------
+    const int q = warp & 3;  // tensor-memory lane quadrant this warp may read
+    const int row_in_tile = q * 32 + lane;
+    int acc = 0;
+    uint32_t acc_ph = 0;
+    for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+      const int tm = tile % tiles_m, tn = tile / tiles_m;
+      bool ok = mbar_wait(&tfull[acc], acc_ph, p.ew, 300);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const long grow = (long)tm * BM + row_in_tile;
+      const bool row_ok = grow < p.M;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + c * 32);
+        tmem_ld_32x32b_x32(taddr, r);
+        tmem_wait_ld();
+        const int col0 = tn * BN + c * 32;
+        if (row_ok && col0 < p.N) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const int col = col0 + g * 8;
+            if (col >= p.N) break;
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[g * 8 + j]) * p.alpha;
+            if (p.bias) {
+              const uint4 bv = *reinterpret_cast<const uint4*>(p.bias + col);
+              const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                float2 f = unpack_bf16x2(bw[j]);
+                v[2 * j] += f.x;
+                v[2 * j + 1] += f.y;
+              }
+            }
+            if (p.act == 1) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) v[j] = gelu_erf(v[j]);
+            }
+            if (p.residual) {
+              const uint4 rv = *reinterpret_cast<const uint4*>(p.residual + grow * p.ldr + col);
+              const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                float2 f = unpack_bf16x2(rw[j]);
+                v[2 * j] += f.x;
+                v[2 * j + 1] += f.y;
+              }
+            }
+            if (p.out_f32) {
+              float* dst = reinterpret_cast<float*>(p.C) + grow * p.ldc + col;
+              if (p.accumulate) {
+                const float4 o0 = *reinterpret_cast<const float4*>(dst);
+                const float4 o1 = *reinterpret_cast<const float4*>(dst + 4);
+                v[0] += o0.x; v[1] += o0.y; v[2] += o0.z; v[3] += o0.w;
+                v[4] += o1.x; v[5] += o1.y; v[6] += o1.z; v[7] += o1.w;
+              }
+              *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+              *reinterpret_cast<float4*>(dst + 4) = make_float4(v[4], v[5], v[6], v[7]);
+            } else {
+              __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + grow * p.ldc + col;
+              if (p.accumulate) {
+                const uint4 ov = *reinterpret_cast<const uint4*>(dst);
+                const uint32_t ow[4] = {ov.x, ov.y, ov.z, ov.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  float2 f = unpack_bf16x2(ow[j]);
+                  v[2 * j] += f.x;
+                  v[2 * j + 1] += f.y;
+                }
+              }
+              uint4 o;
+              o.x = pack_bf16x2(v[0], v[1]);
+              o.y = pack_bf16x2(v[2], v[3]);
+              o.z = pack_bf16x2(v[4], v[5]);
+              o.w = pack_bf16x2(v[6], v[7]);
+              *reinterpret_cast<uint4*>(dst) = o;
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty[acc]);
+      acc ^= 1;
+      if (acc == 0) acc_ph ^= 1;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, C_::TMEM_COLS);
+}
+
+// ------------------------------------------------------------------------------------
+// Host side
+// ------------------------------------------------------------------------------------
+PFN_cuTensorMapEncodeTiled_v12000 g_encode = nullptr;
+
+bool ensure_encode() {
+  if (g_encode) return true;
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess || !fn)
+    return false;
+  g_encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
+  return true;
+}
+
+uint32_t g_mn_lbo = 8192, g_mn_sbo = 1024, g_mn_kstep = 2048;
+
+template <int BN>
+int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int sms, cudaStream_t st) {
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_tcgen05<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)Cfg<BN>::SMEM);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
+  const int grid = tiles < sms ? tiles : sms;
+  gemm_bf16_tcgen05<BN><<<grid, kThreads, Cfg<BN>::SMEM, st>>>(ta, tb, p);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace
+
+// 2-D bf16 tensor map with 128-byte swizzle.  `inner` elements are contiguous,
+// rows are `ld` elements apart; the box is box_inner x box_outer elements.
+extern "C" int mmt_make_tmap_2d(CUtensorMap* out, const void* ptr, uint64_t inner, uint64_t outer, uint64_t ld,
+                                uint32_t box_inner, uint32_t box_outer) {
+  if (!ensure_encode()) return -1;
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {ld * 2};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = g_encode(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return (int)r;
+}
+
+// Bring-up knob: descriptor constants used for MN-major shared-memory tiles.
+extern "C" void mmt_gemm_set_mn_desc(uint32_t lbo, uint32_t sbo, uint32_t kstep) {
+  g_mn_lbo = lbo;
+  g_mn_sbo = sbo;
+  g_mn_kstep = kstep;
+}
+
+// C = epilogue(alpha * A * B^T).  See the file header for layouts.
+//   a_mn / b_mn : 0 = K-major ([rows][K], ld = row stride), 1 = MN-major ([K][rows], ld = k-row stride)
+//   act         : 0 none, 1 GELU
+//   bn          : 0 = choose, else one of 64/128/192/256
+// Returns 0 or a CUDA / driver error code (negative: argument error).
+extern "C" int mmt_gemm_bf16(const void* A, const void* B, void* C, const void* bias, const void* residual, int M,
+                             int N, int K, int lda, int ldb, int ldc, int ldr, int a_mn, int b_mn, int act,
+                             int accumulate, int out_f32, float alpha, int bn, void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((lda & 7) || (ldb & 7) || (ldc & 7) || (N & 7) || (residual && (ldr & 7))) return -2;
+  if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) ||
+      (reinterpret_cast<uintptr_t>(C) & 15))
+    return -3;
+  const int sms = mmt_sm_count();
+  if (bn == 0) {
+    // Measured on B200: the 256-wide tile has the best bytes-per-flop from L2 and wins even when
+    // it leaves a partial last wave; narrower tiles only for narrow outputs.
+    bn = N > 192 ? 256 : (N > 128 ? 192 : (N > 64 ? 128 : 64));
+  }
+  CUtensorMap ta, tb;
+  int r;
+  if (!a_mn) r = mmt_make_tmap_2d(&ta, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BK, BM);
+  else       r = mmt_make_tmap_2d(&ta, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, 64, BK);
+  if (r) return 1000 + r;
+  if (!b_mn) r = mmt_make_tmap_2d(&tb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BK, (uint32_t)bn);
+  else       r = mmt_make_tmap_2d(&tb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, 64, BK);
+  if (r) return 2000 + r;
+
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K;
+  p.C = C; p.ldc = ldc;
+  p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  p.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
+  p.ldr = ldr;
+  p.act = act; p.accumulate = accumulate; p.out_f32 = out_f32; p.alpha = alpha;
+  p.a_mn = a_mn; p.b_mn = b_mn;
+  p.mn_lbo = g_mn_lbo; p.mn_sbo = g_mn_sbo; p.mn_kstep = g_mn_kstep;
+  p.ew = mmt_error_word();
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  switch (bn) {
+    case 256: return launch<256>(ta, tb, p, sms, st);
+    case 192: return launch<192>(ta, tb, p, sms, st);
+    case 128: return launch<128>(ta, tb, p, sms, st);
+    case 64:  return launch<64>(ta, tb, p, sms, st);
+    default:  return -4;
+  }
+}

@@ -1,0 +1,20 @@
+// Host-side runtime shared by every translation unit of the kernel library.
+#pragma once
+#include <cuda_runtime.h>
+
+struct MmtErrorWord;
+
+// Number of SMs of the current device (cached).
+int mmt_sm_count();
+// Device address of the library's error word for the current device
+// (allocated on first use; kernels record bounded-wait failures there).
+MmtErrorWord* mmt_error_word();
+
+extern "C" {
+// Copies the error word to out[4] = {code, where, block, aux}; synchronises the device.
+int mmt_get_error(int* out);
+// Resets the error word to zero.
+int mmt_clear_error();
+// Library build tag, for tests that check the native path is loaded.
+const char* mmt_version();
+}
