@@ -188,6 +188,21 @@ def trainer_configs(cfg: dict) -> tuple[dict, dict]:
     text["autotp_size"] = cfg["text"].get("autotp_size") or ps
     text["tensor_parallel_size"] = cfg["text"].get("tensor_parallel_size") or ps
     text["dp_size"] = dp
+    # mesh factors: sequence/tensor parallel degrees inside the world of ps*dp ranks
+    sp = ps if cfg["vision"]["parallelism"] in ("sequence", "tensor") else 1
+    if cfg["text"]["parallelism"] == "autotp":
+        tp = text["autotp_size"]
+    elif cfg["text"]["parallelism"] == "tensor":
+        tp = text["tensor_parallel_size"]
+    else:
+        tp = 1
+    for d in (vision, text):
+        d["mesh_sp"], d["mesh_tp"] = int(sp), int(tp)
+        d["world_size"] = int(ps * dp)
+        d["vision_parallelism"] = cfg["vision"]["parallelism"]
+        d["text_parallelism"] = cfg["text"]["parallelism"]
+        d["vision_model_name"] = cfg["vision"]["model_name"]
+        d["text_model_name"] = cfg["text"]["model_name"]
     return vision, text
 
 

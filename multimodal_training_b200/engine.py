@@ -1,0 +1,82 @@
+"""SPMD training engine: one process per GPU runs both halves of the model.
+
+This is the launch mode for ``torchrun``-style jobs (and ``bench.py``): every rank builds a
+:class:`VisionTrainer` and a :class:`TextTrainer` in the same process and calls them in the order
+of the reference's driver loop (python/train_ray.py:315-382): zero_grad, vision forward, text
+forward, text backward, vision backward, gradient norm, two optimizer steps.  The actor runtime in
+``runtime/`` drives the same trainers through ``ActorGroup.execute_all`` instead.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.distributed as dist
+
+from .trainers.text import TextTrainer
+from .trainers.trainer import process_state
+from .trainers.vision import VisionTrainer
+
+
+class HybridEngine:
+    def __init__(self, vision_config: dict, text_config: dict, rank: int | None = None):
+        import os
+        rank = int(os.environ.get("RANK", "0")) if rank is None else rank
+        self.vision = VisionTrainer(vision_config, rank)
+        self.text = TextTrainer(text_config, rank)
+        self.vision.build_model()
+        self.text.build_model()
+        self.vision.initialize_trainer()
+        self.text.initialize_trainer()
+        self.mesh = process_state().mesh
+        self.clip = bool(text_config.get("clip_grad_norm", False))
+        self.max_norm = float(text_config.get("max_grad_norm", 1.0))
+        self.step_index = 0
+        self.last_grad_norm = None
+
+    @classmethod
+    def from_config(cls, cfg: dict) -> "HybridEngine":
+        from .config.loader import trainer_configs
+        v, t = trainer_configs(cfg)
+        return cls(v, t)
+
+    def _global_grad_scale(self):
+        """Device-side global-norm clipping coefficient (no host sync)."""
+        vo, to = self.vision.optimizer, self.text.optimizer
+        vs, ts = vo.reduce_gradients(), to.reduce_gradients()
+        self.vision._reduced_shard, self.text._reduced_shard = vs, ts
+        va, vb = vo.grad_norm_sq_local(vs)
+        ta, tb = to.grad_norm_sq_local(ts)
+        total = va + vb + ta + tb / max(self.mesh.tp, 1)
+        if self.mesh.world > 1:
+            dist.all_reduce(total, group=self.mesh.world_group)
+        norm = total.sqrt()
+        self.last_grad_norm = norm
+        return torch.clamp(self.max_norm / (norm + 1e-6), max=1.0)
+
+    def train_step(self, step: int | None = None) -> torch.Tensor:
+        """One optimisation step on the global batch of ``step``; returns this rank's loss (device scalar)."""
+        step = self.step_index if step is None else step
+        self.vision.zero_grad()
+        self.text.zero_grad()
+        v_out = self.vision.forward_step(step)
+        t_out = self.text.forward_step(v_out, step)
+        g = self.text.backward_step()
+        if g["grad"] is not None:
+            self.vision.backward_step(g)
+        scale = self._global_grad_scale() if self.clip else None
+        for tr in (self.text, self.vision):
+            shard = getattr(tr, "_reduced_shard", None)
+            tr._reduced_shard = None
+            tr.optimizer.step(lr=tr.current_lr(), grad_scale=scale, shard=shard)
+            tr.global_step += 1
+        self.step_index = step + 1
+        return t_out["loss"]
+
+    def mean_loss(self, loss: torch.Tensor) -> float:
+        """Mean over text replicas (every TP rank of a replica holds the same loss)."""
+        t = loss.detach().float().clone().reshape(1)
+        if self.mesh.world > 1:
+            dist.all_reduce(t, group=self.mesh.world_group)
+            t /= self.mesh.world
+        return float(t.item())

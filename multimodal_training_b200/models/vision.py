@@ -1,0 +1,246 @@
+"""Qwen2.5-VL vision encoder with ragged Ulysses sequence parallelism.
+
+Patch embedding (a GEMM: the Conv3d of the reference has kernel = stride), 32 pre-norm blocks with
+2-D rotary attention (window attention everywhere except the full-attention layers) and a gated
+SiLU MLP, then the 2x2 patch merger.  The math follows the reference's
+``Qwen2_5_VisionTransformerPretrainedModel`` (modeling_qwen2_5_vl.py:192-1070).
+
+What differs by design:
+
+* every rank works on its window-aligned slice of every image (``parallel/sp.py``); window layers
+  are purely local;
+* full-attention layers exchange rows so that each rank attends over whole images with its share
+  of the heads.  Rotary embedding is applied BEFORE the exchange, so cos/sin and masks never travel
+  (the reference ships both through the all-to-all, modeling_qwen2_5_vl.py:632-640);
+* the merger runs on the local slice (cuts are multiples of the 4-token merge unit), so the final
+  all-gather of the reference (modeling_qwen2_5_vl.py:1018-1066) does not exist; merged tokens go
+  straight to their text rows (``parallel/handoff.py``).
+* q|k|v and gate|up are fused projections; the MLP width is zero-padded to a multiple of 8 so that
+  activation rows are 16-byte aligned for TMA.  State dicts convert to the reference/HF layout.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+
+from ..config.model_configs import VisionConfig
+from ..ops import functional as F
+from ..ops.attention import SeqInfo
+from ..parallel import comm
+from ..parallel.sp import VisionPlan
+from ..utils.checkpointing import checkpoint
+
+
+class SPContext:
+    """Sequence-parallel group of the vision encoder (None / size 1 = no exchange)."""
+
+    def __init__(self, group=None, size: int = 1, rank: int = 0, fused=None):
+        self.group, self.size, self.rank, self.fused = group, size, rank, fused
+
+
+class VisionEncoder(nn.Module):
+    def __init__(self, cfg: VisionConfig, sp: SPContext | None = None, dtype=torch.float32, device="cpu",
+                 seed: int = 0, activation_checkpointing: bool = True):
+        super().__init__()
+        self.cfg = cfg
+        self.sp = sp or SPContext()
+        self.ckpt = activation_checkpointing
+        C, I, Ip = cfg.hidden_size, cfg.intermediate_size, cfg.padded_intermediate_size
+        if cfg.num_heads % self.sp.size:
+            raise ValueError(f"num_heads {cfg.num_heads} is not divisible by sequence_parallel_size {self.sp.size}")
+        std = cfg.initializer_range
+        gen = torch.Generator(device=device)
+
+        def full(shape, idx):
+            gen.manual_seed(seed * 1000003 + 7919 + idx)
+            return torch.randn(shape, generator=gen, dtype=torch.float32, device=device) * std
+
+        def P(t):
+            return nn.Parameter(t.to(device=device, dtype=dtype).contiguous())
+
+        def pad_rows(t, n):
+            if t.shape[0] == n:
+                return t
+            return torch.cat([t, t.new_zeros((n - t.shape[0],) + tuple(t.shape[1:]))], dim=0)
+
+        def pad_cols(t, n):
+            if t.shape[1] == n:
+                return t
+            return torch.cat([t, t.new_zeros(t.shape[0], n - t.shape[1])], dim=1)
+
+        z = lambda n: torch.zeros(n, device=device)  # noqa: E731
+        o = lambda n: torch.ones(n, device=device)   # noqa: E731
+        idx = 0
+        self.patch_embed_w = P(full((C, cfg.patch_dim), idx))
+        idx += 1
+        self.blocks = nn.ModuleList()
+        for _ in range(cfg.depth):
+            B = nn.Module()
+            B.norm1_w, B.norm2_w = P(o(C)), P(o(C))
+            B.qkv_w, B.qkv_b = P(full((3 * C, C), idx)), P(z(3 * C))
+            B.proj_w, B.proj_b = P(full((C, C), idx + 1)), P(z(C))
+            B.gate_up_w = P(torch.cat([pad_rows(full((I, C), idx + 2), Ip), pad_rows(full((I, C), idx + 3), Ip)], 0))
+            B.gate_up_b = P(z(2 * Ip))
+            B.down_w, B.down_b = P(pad_cols(full((C, I), idx + 4), Ip)), P(z(C))
+            idx += 5
+            self.blocks.append(B)
+        M = C * cfg.merge_unit
+        self.ln_q_w = P(o(C))
+        self.merger_fc1_w, self.merger_fc1_b = P(full((M, M), idx)), P(z(M))
+        self.merger_fc2_w, self.merger_fc2_b = P(full((cfg.out_hidden_size, M), idx + 1)), P(z(cfg.out_hidden_size))
+
+    # ------------------------------------------------------------------ attention variants
+    def _full_attention(self, qkv: torch.Tensor, plan: VisionPlan, full_seq: SeqInfo) -> torch.Tensor:
+        """Ulysses: rows x all heads -> all rows x heads/sp, attention per image, and back."""
+        cfg, sp = self.cfg, self.sp
+        nh, d = cfg.num_heads, cfg.head_dim
+        if sp.size == 1:
+            return F.attention(qkv, nh, nh, d, full_seq, causal=False)
+        if sp.fused is not None and qkv.is_cuda:
+            return sp.fused.ulysses_attention(qkv, plan, full_seq, nh, d)
+        T = qkv.shape[0]
+        hl = nh // sp.size
+        # [T, 3, sp, hl, d] -> [sp, T, 3*hl*d]: peer p gets head group p of q, k and v for all my rows
+        send = qkv.view(T, 3, sp.size, hl, d).permute(2, 0, 1, 3, 4).reshape(sp.size * T, 3 * hl * d)
+        recv = comm.all_to_all_rows(send, [T] * sp.size, plan.rank_tokens, sp.group)
+        gathered = F.gather_rows(recv, plan.to_image_major_dev)          # (rank, image) -> (image, rank)
+        a = F.attention(gathered, hl, hl, d, full_seq, causal=False)    # [T_all, hl*d]
+        a = F.gather_rows(a, plan.to_rank_major_dev)
+        back = comm.all_to_all_rows(a, plan.rank_tokens, [T] * sp.size, sp.group)   # [sp*T, hl*d]
+        return back.view(sp.size, T, hl * d).permute(1, 0, 2).reshape(T, nh * d)
+
+    def _block(self, x, B, cos, sin, plan, win_seq, full_seq, is_full: bool):
+        cfg = self.cfg
+        nh, d = cfg.num_heads, cfg.head_dim
+        h = F.rmsnorm(x, B.norm1_w, cfg.rms_norm_eps)
+        qkv = F.linear(h, B.qkv_w, B.qkv_b)
+        qkv = F.rope(qkv, cos, sin, 2 * nh, d)
+        if is_full:
+            a = self._full_attention(qkv, plan, full_seq)
+        else:
+            a = F.attention(qkv, nh, nh, d, win_seq, causal=False)
+        x = F.linear(a, B.proj_w, B.proj_b, x)
+        h = F.rmsnorm(x, B.norm2_w, cfg.rms_norm_eps)
+        m = F.swiglu(F.linear(h, B.gate_up_w, B.gate_up_b))
+        return F.linear(m, B.down_w, B.down_b, x)
+
+    # ------------------------------------------------------------------ forward
+    def forward(self, local_patches: torch.Tensor, plan: VisionPlan) -> torch.Tensor:
+        """[T_loc, patch_dim] patches of this rank in local window order -> merged tokens [T_loc/4, out_hidden]."""
+        cfg = self.cfg
+        dev = local_patches.device
+        prepare_plan(plan, dev)
+        cos, sin = plan.cos_dev, plan.sin_dev
+        win_seq = plan.win_seq
+        full_seq = plan.full_seq if self.sp.size > 1 else plan.local_image_seq
+        x = F.linear(local_patches, self.patch_embed_w)
+        for i, B in enumerate(self.blocks):
+            is_full = i in cfg.fullatt_block_indexes
+            x = checkpoint(lambda t, B=B, f=is_full: self._block(t, B, cos, sin, plan, win_seq, full_seq, f), (x,),
+                           enabled=self.ckpt)
+        h = F.rmsnorm(x, self.ln_q_w, cfg.rms_norm_eps)
+        h = h.view(-1, cfg.hidden_size * cfg.merge_unit)
+        h = F.gelu(F.linear(h, self.merger_fc1_w, self.merger_fc1_b))
+        return F.linear(h, self.merger_fc2_w, self.merger_fc2_b)
+
+    # ------------------------------------------------------------------ state dict in the reference/HF key layout
+    def reference_state_dict(self, fused_qkv: bool = False) -> dict[str, torch.Tensor]:
+        """Keys of the reference's vision model: ``blocks.N.attn.{q,k,v,proj}``, ``mlp.{gate,up,down}_proj``,
+        ``merger.{ln_q,mlp.0,mlp.2}``, ``patch_embed.proj.weight`` [C,3,2,14,14].  ``fused_qkv`` emits HF's
+        ``attn.qkv`` instead of the reference's split q/k/v (python/ray/vision.py:322-345)."""
+        cfg = self.cfg
+        C, I, Ip = cfg.hidden_size, cfg.intermediate_size, cfg.padded_intermediate_size
+        out = {"patch_embed.proj.weight": self.patch_embed_w.detach().view(
+            C, cfg.in_channels, cfg.temporal_patch_size, cfg.patch_size, cfg.patch_size)}
+        for i, B in enumerate(self.blocks):
+            p = f"blocks.{i}."
+            out[p + "norm1.weight"] = B.norm1_w.detach()
+            out[p + "norm2.weight"] = B.norm2_w.detach()
+            if fused_qkv:
+                out[p + "attn.qkv.weight"] = B.qkv_w.detach()
+                out[p + "attn.qkv.bias"] = B.qkv_b.detach()
+            else:
+                for j, n in enumerate("qkv"):
+                    out[p + f"attn.{n}.weight"] = B.qkv_w.detach()[j * C:(j + 1) * C]
+                    out[p + f"attn.{n}.bias"] = B.qkv_b.detach()[j * C:(j + 1) * C]
+            out[p + "attn.proj.weight"] = B.proj_w.detach()
+            out[p + "attn.proj.bias"] = B.proj_b.detach()
+            out[p + "mlp.gate_proj.weight"] = B.gate_up_w.detach()[:I]
+            out[p + "mlp.up_proj.weight"] = B.gate_up_w.detach()[Ip:Ip + I]
+            out[p + "mlp.gate_proj.bias"] = B.gate_up_b.detach()[:I]
+            out[p + "mlp.up_proj.bias"] = B.gate_up_b.detach()[Ip:Ip + I]
+            out[p + "mlp.down_proj.weight"] = B.down_w.detach()[:, :I]
+            out[p + "mlp.down_proj.bias"] = B.down_b.detach()
+        out["merger.ln_q.weight"] = self.ln_q_w.detach()
+        out["merger.mlp.0.weight"] = self.merger_fc1_w.detach()
+        out["merger.mlp.0.bias"] = self.merger_fc1_b.detach()
+        out["merger.mlp.2.weight"] = self.merger_fc2_w.detach()
+        out["merger.mlp.2.bias"] = self.merger_fc2_b.detach()
+        return {k: v.clone() for k, v in out.items()}
+
+    @torch.no_grad()
+    def load_reference_state_dict(self, sd: dict[str, torch.Tensor]) -> list[str]:
+        """Accepts split q/k/v (reference) or fused ``attn.qkv`` (HF); prefixes ``visual.`` / ``model.visual.``."""
+        cfg = self.cfg
+        C, I, Ip = cfg.hidden_size, cfg.intermediate_size, cfg.padded_intermediate_size
+        clean = {}
+        for k, v in sd.items():
+            for pre in ("model.visual.", "visual."):
+                if k.startswith(pre):
+                    k = k[len(pre):]
+                    break
+            clean[k] = v
+        used = set()
+
+        def get(k):
+            used.add(k)
+            return clean[k]
+
+        self.patch_embed_w.copy_(get("patch_embed.proj.weight").reshape(C, -1))
+        for i, B in enumerate(self.blocks):
+            p = f"blocks.{i}."
+            B.norm1_w.copy_(get(p + "norm1.weight"))
+            B.norm2_w.copy_(get(p + "norm2.weight"))
+            if p + "attn.qkv.weight" in clean:
+                B.qkv_w.copy_(get(p + "attn.qkv.weight"))
+                B.qkv_b.copy_(get(p + "attn.qkv.bias"))
+            else:
+                B.qkv_w.copy_(torch.cat([get(p + f"attn.{n}.weight") for n in "qkv"], 0))
+                B.qkv_b.copy_(torch.cat([get(p + f"attn.{n}.bias") for n in "qkv"], 0))
+            B.proj_w.copy_(get(p + "attn.proj.weight"))
+            B.proj_b.copy_(get(p + "attn.proj.bias"))
+            B.gate_up_w.zero_()
+            B.gate_up_b.zero_()
+            B.down_w.zero_()
+            B.gate_up_w[:I].copy_(get(p + "mlp.gate_proj.weight"))
+            B.gate_up_w[Ip:Ip + I].copy_(get(p + "mlp.up_proj.weight"))
+            B.gate_up_b[:I].copy_(get(p + "mlp.gate_proj.bias"))
+            B.gate_up_b[Ip:Ip + I].copy_(get(p + "mlp.up_proj.bias"))
+            B.down_w[:, :I].copy_(get(p + "mlp.down_proj.weight"))
+            B.down_b.copy_(get(p + "mlp.down_proj.bias"))
+        self.ln_q_w.copy_(get("merger.ln_q.weight"))
+        self.merger_fc1_w.copy_(get("merger.mlp.0.weight"))
+        self.merger_fc1_b.copy_(get("merger.mlp.0.bias"))
+        self.merger_fc2_w.copy_(get("merger.mlp.2.weight"))
+        self.merger_fc2_b.copy_(get("merger.mlp.2.bias"))
+        return [k for k in clean if k not in used]
+
+
+def prepare_plan(plan: VisionPlan, device) -> VisionPlan:
+    """Attach device tensors and sequence descriptors to a host plan (idempotent)."""
+    if getattr(plan, "_prepared", None) == str(device):
+        return plan
+    plan.cos_dev = plan.local_cos.to(device, non_blocking=True)
+    plan.sin_dev = plan.local_sin.to(device, non_blocking=True)
+    plan.win_seq = SeqInfo.from_list(plan.win_cu, device)
+    plan.full_seq = SeqInfo.from_list(plan.full_cu, device)
+    cu = [0]
+    for _, n in plan.per_image_local:
+        if n:
+            cu.append(cu[-1] + n)
+    plan.local_image_seq = SeqInfo.from_list(cu, device)
+    if plan.to_image_major is not None:
+        plan.to_image_major_dev = plan.to_image_major.to(device, non_blocking=True)
+        plan.to_rank_major_dev = plan.to_rank_major.to(device, non_blocking=True)
+    plan._prepared = str(device)
+    return plan

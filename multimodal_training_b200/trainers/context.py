@@ -1,0 +1,101 @@
+"""Per-step host context shared by the vision and text trainers of one process.
+
+The global batch of a step is known to every rank (deterministic synthetic data, or dataloaders
+with a common seed as in the reference, python/ray/trainer.py:69-104).  From it each rank derives,
+without communication: which images its vision replica encodes and how they are split over the
+sequence-parallel ranks, which samples its text replica packs, and the routes of the merged vision
+tokens between the two (``parallel/handoff.py``).  Unlike the reference, data-parallel replicas get
+DIFFERENT samples: replica d of R takes samples [d*B/R, (d+1)*B/R) of the global batch.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from ..config.model_configs import VLConfig
+from ..parallel.handoff import HandoffPlan, TextBatch, build_handoff_plan, pack_text_batch
+from ..parallel.mesh import Mesh
+from ..parallel.sp import Geometry, VisionPlan, build_vision_plan, compute_geometry
+
+
+@dataclass
+class StepContext:
+    step: int
+    samples: list                       # global batch (list of data.synthetic.Sample-like objects)
+    vision_samples: list[int]           # indices (into samples) encoded by this rank's vision replica
+    vision_plan: VisionPlan | None
+    text_batch: TextBatch | None
+    handoff: HandoffPlan | None
+    n_vision_patches_global: int
+    n_text_tokens_global: int
+
+
+def _slice(n: int, parts: int, i: int) -> range:
+    if n % parts:
+        raise ValueError(f"global batch of {n} samples is not divisible by {parts} data-parallel replicas")
+    per = n // parts
+    return range(i * per, (i + 1) * per)
+
+
+def build_step_context(step: int, samples: list, cfg: VLConfig, mesh: Mesh, *, pad_multiple: int | None = None,
+                       window_aligned: bool = True) -> StepContext:
+    v = cfg.vision
+    B = len(samples)
+    # ---------------- vision side: geometry of every replica (needed for routing), plan of mine
+    geoms: list[Geometry] = []
+    images_per_vreplica: list[list[int]] = []
+    image_ids: dict[tuple[int, int], int] = {}
+    gid = 0
+    for si, s in enumerate(samples):
+        for k in range(len(s.grid_thw)):
+            image_ids[(si, k)] = gid
+            gid += 1
+    for r in range(mesh.vdp):
+        grids, ids = [], []
+        for si in _slice(B, mesh.vdp, r):
+            for k, g in enumerate(samples[si].grid_thw):
+                grids.append(g)
+                ids.append(image_ids[(si, k)])
+        images_per_vreplica.append(ids)
+        geoms.append(compute_geometry(grids, sp=mesh.sp, spatial_merge_size=v.spatial_merge_size,
+                                      window_size=v.window_size, patch_size=v.patch_size,
+                                      window_aligned=window_aligned) if grids else None)
+    my_geom = geoms[mesh.vdp_rank]
+    vplan = None
+    if my_geom is not None:
+        vplan = build_vision_plan(None, sp=mesh.sp, rank=mesh.sp_rank, head_dim=v.head_dim, geom=my_geom)
+
+    # ---------------- text side: every replica's packed batch (rows of the placeholders are needed for routing)
+    pad = pad_multiple or max(8, mesh.tp * 8)
+    text_rows, text_len, image_owner = [], [], {}
+    my_tb = None
+    for d in range(mesh.tdp):
+        sl = [samples[i] for i in _slice(B, mesh.tdp, d)]
+        tb = pack_text_batch(sl, image_token_id=cfg.image_token_id, vision_start_token_id=cfg.vision_start_token_id,
+                             spatial_merge_size=v.spatial_merge_size, pad_multiple=pad, pad_token_id=cfg.pad_token_id)
+        text_rows.append(tb.image_rows)
+        text_len.append(tb.input_ids.numel())
+        k = 0
+        for si in _slice(B, mesh.tdp, d):
+            for kk in range(len(samples[si].grid_thw)):
+                image_owner[image_ids[(si, kk)]] = (d, k)
+                k += 1
+        if d == mesh.tdp_rank:
+            my_tb = tb
+    handoff = build_handoff_plan(mesh, [g for g in geoms], images_per_vreplica, text_rows, text_len, image_owner) \
+        if gid > 0 else None
+    n_patches = sum(t * h * w for s in samples for (t, h, w) in s.grid_thw)
+    n_text = sum(s.input_ids.numel() for s in samples)
+    return StepContext(step, samples, list(_slice(B, mesh.vdp, mesh.vdp_rank)), vplan, my_tb, handoff, n_patches,
+                       n_text)
+
+
+def local_pixels(ctx: StepContext, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Host gather of this rank's patches (local window order) from the samples' pixel arrays."""
+    plan = ctx.vision_plan
+    pix = [ctx.samples[i].pixel_values for i in ctx.vision_samples]
+    allpix = pix[0] if len(pix) == 1 else torch.cat(pix, dim=0)
+    if out is not None:
+        return torch.index_select(allpix, 0, plan.local_patch_index, out=out)
+    return allpix.index_select(0, plan.local_patch_index)

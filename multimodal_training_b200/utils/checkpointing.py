@@ -1,0 +1,46 @@
+"""Activation checkpointing for blocks built from this package's ops.
+
+The reference turns on HF ``gradient_checkpointing_enable()`` per block
+(python/ray/trainer.py:257-267).  Here a block is a plain function of tensors; the
+forward pass runs without a graph and keeps only the block inputs, the backward pass
+recomputes the block and back-propagates through the recomputed graph.  Weight gradients
+are written by the ops themselves (``main_grad``) or accumulate into ``.grad`` as usual.
+"""
+from __future__ import annotations
+
+import torch
+
+
+class _Checkpoint(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, fn, n_tensors, *args):
+        ctx.fn = fn
+        tensors = args[:n_tensors]
+        ctx.extra = args[n_tensors:]
+        ctx.save_for_backward(*tensors)
+        ctx.req = [t.requires_grad for t in tensors]
+        with torch.no_grad():
+            out = fn(*tensors, *ctx.extra)
+        return out
+
+    @staticmethod
+    def backward(ctx, *douts):
+        tensors = [t.detach().requires_grad_(r) for t, r in zip(ctx.saved_tensors, ctx.req)]
+        with torch.enable_grad():
+            out = ctx.fn(*tensors, *ctx.extra)
+        outs = out if isinstance(out, tuple) else (out,)
+        pairs = [(o, g) for o, g in zip(outs, douts) if isinstance(o, torch.Tensor) and o.requires_grad]
+        torch.autograd.backward([o for o, _ in pairs], [g for _, g in pairs])
+        grads = tuple(t.grad if r else None for t, r in zip(tensors, ctx.req))
+        return (None, None) + grads + (None,) * len(ctx.extra)
+
+
+def checkpoint(fn, tensors: tuple, extra: tuple = (), enabled: bool = True):
+    """``fn(*tensors, *extra)`` with recomputation in backward.
+
+    ``tensors`` are the differentiable inputs (saved); ``extra`` are non-tensor or constant
+    arguments; parameters are reached through ``fn``'s closure and receive gradients in backward.
+    """
+    if not enabled or not torch.is_grad_enabled():
+        return fn(*tensors, *extra)
+    return _Checkpoint.apply(fn, len(tensors), *tensors, *extra)

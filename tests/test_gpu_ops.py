@@ -1,0 +1,205 @@
+"""Numerics of every sm_100a kernel against a plain PyTorch fp32 reference of the same op."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+
+
+def _F():
+    from multimodal_training_b200.ops import functional as F
+    from multimodal_training_b200.ops import native as nv
+    assert nv.available(), "libmmt_b200.so must be built: the GPU path has no fallback"
+    nv.lib()
+    return F, nv
+
+
+def rel_err(a, b):
+    return ((a.float() - b.float()).abs().max() / (b.float().abs().max() + 1e-9)).item()
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (304, 1288, 1176), (2048, 3584, 3584), (77, 3840, 1280),
+                                   (4096, 1280, 3424)])
+@pytest.mark.parametrize("layout", ["kk", "k_mn", "mn_mn"])
+def test_gemm_layouts(M, N, K, layout):
+    F, nv = _F()
+    torch.manual_seed(0)
+    A = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    B = torch.randn(N, K, device=DEV, dtype=torch.bfloat16) * 0.05
+    ref = A.float() @ B.float().t()
+    a_mn = layout == "mn_mn"
+    b_mn = layout != "kk"
+    out = F.gemm(A.t().contiguous() if a_mn else A, B.t().contiguous() if b_mn else B, a_mn=a_mn, b_mn=b_mn)
+    assert rel_err(out, ref) < 8e-3
+    assert nv.get_error()[0] == 0
+
+
+def test_gemm_epilogue_bias_residual_accumulate_f32():
+    F, nv = _F()
+    torch.manual_seed(1)
+    M, N, K = 520, 1280, 1024
+    A = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    B = torch.randn(N, K, device=DEV, dtype=torch.bfloat16) * 0.05
+    bias = torch.randn(N, device=DEV, dtype=torch.bfloat16)
+    res = torch.randn(M, N, device=DEV, dtype=torch.bfloat16)
+    ref = A.float() @ B.float().t() + bias.float() + res.float()
+    out = F.gemm(A, B, bias=bias, residual=res)
+    assert rel_err(out, ref) < 8e-3
+    acc = torch.ones(M, N, device=DEV, dtype=torch.float32)
+    F.gemm(A, B, out=acc, accumulate=True, out_f32=True)
+    assert rel_err(acc, A.float() @ B.float().t() + 1.0) < 2e-3
+    g = F.gemm(A, B, act=1)
+    assert rel_err(g, torch.nn.functional.gelu(A.float() @ B.float().t())) < 8e-3
+
+
+def test_linear_autograd_matches_reference():
+    F, nv = _F()
+    torch.manual_seed(2)
+    T, K, N = 640, 512, 768
+    x = torch.randn(T, K, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    w = (torch.randn(N, K, device=DEV, dtype=torch.bfloat16) * 0.05).requires_grad_()
+    b = torch.randn(N, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    r = torch.randn(T, N, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    y = F.linear(x, w, b, r)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    xf, wf, bf, rf = (t.detach().float().requires_grad_() for t in (x, w, b, r))
+    yr = torch.nn.functional.linear(xf, wf, bf) + rf
+    yr.backward(dy.float())
+    assert rel_err(y, yr) < 8e-3
+    assert rel_err(x.grad, xf.grad) < 8e-3
+    assert rel_err(w.grad, wf.grad) < 8e-3
+    assert rel_err(b.grad, bf.grad) < 8e-3
+    assert rel_err(r.grad, rf.grad) < 1e-6
+
+
+@pytest.mark.parametrize("rows,cols", [(1000, 1280), (333, 3584), (64, 5120), (17, 256)])
+def test_rmsnorm(rows, cols):
+    F, nv = _F()
+    torch.manual_seed(3)
+    x = torch.randn(rows, cols, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    w = (1 + 0.1 * torch.randn(cols, device=DEV)).to(torch.bfloat16).requires_grad_()
+    y = F.rmsnorm(x, w, 1e-6)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    xf, wf = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    yr = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-6) * wf
+    yr.backward(dy.float())
+    assert rel_err(y, yr) < 1e-2
+    assert rel_err(x.grad, xf.grad) < 1e-2
+    assert rel_err(w.grad, wf.grad) < 1e-2
+
+
+@pytest.mark.parametrize("heads,dim,extra", [(32, 80, 1280), (8, 128, 512)])
+def test_rope(heads, dim, extra):
+    F, nv = _F()
+    torch.manual_seed(4)
+    T = 300
+    x = torch.randn(T, heads * dim + extra, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    ang = torch.rand(T, dim // 2, device=DEV) * 6.28
+    ang = torch.cat([ang, ang], -1)
+    cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+    y = F.rope(x, cos, sin, heads, dim)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    xc = x.detach().cpu().float().requires_grad_()
+    yr = F.rope(xc, cos.cpu(), sin.cpu(), heads, dim)
+    yr.backward(dy.cpu().float())
+    assert rel_err(y.cpu(), yr) < 1e-2
+    assert rel_err(x.grad.cpu(), xc.grad) < 1e-2
+
+
+def test_swiglu_gelu():
+    F, nv = _F()
+    torch.manual_seed(5)
+    gu = torch.randn(500, 2 * 3424, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    y = F.swiglu(gu)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    gf = gu.detach().float().requires_grad_()
+    g, u = gf.chunk(2, -1)
+    yr = torch.nn.functional.silu(g) * u
+    yr.backward(dy.float())
+    assert rel_err(y, yr) < 1e-2 and rel_err(gu.grad, gf.grad) < 1e-2
+    x = torch.randn(300, 5120, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    z = F.gelu(x)
+    z.backward(dy[:300, :5120].contiguous() if dy.shape[1] >= 5120 else torch.ones_like(z))
+    xf = x.detach().float().requires_grad_()
+    zr = torch.nn.functional.gelu(xf)
+    zr.backward(torch.ones_like(zr) if dy.shape[1] < 5120 else dy[:300, :5120].float())
+    assert rel_err(z, zr) < 1e-2 and rel_err(x.grad, xf.grad) < 1e-2
+
+
+def test_gather_scatter_embedding():
+    F, nv = _F()
+    torch.manual_seed(6)
+    table = torch.randn(1000, 512, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    ids = torch.randint(0, 2000, (777,), device=DEV)
+    out = F.embedding(ids, table, vocab_lo=500)
+    ref = torch.zeros(777, 512, device=DEV)
+    ok = (ids >= 500) & (ids < 1500)
+    ref[ok] = table.detach().float()[ids[ok] - 500]
+    assert torch.equal(out.float(), ref)
+    dy = torch.randn_like(out)
+    out.backward(dy)
+    gref = torch.zeros(1000, 512, device=DEV)
+    gref.index_add_(0, ids[ok] - 500, dy.float()[ok])
+    assert rel_err(table.grad, gref) < 2e-2
+    perm = torch.randperm(777, device=DEV)
+    src = torch.randn(777, 256, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    g = F.gather_rows(src, perm)
+    assert torch.equal(g, src.detach()[perm])
+    g.backward(torch.ones_like(g))
+    assert torch.equal(src.grad, torch.ones_like(src))
+
+
+@pytest.mark.parametrize("T,V,H", [(300, 4096, 512), (1000, 38016, 256)])
+def test_lm_head_cross_entropy(T, V, H):
+    F, nv = _F()
+    torch.manual_seed(7)
+    h = torch.randn(T, H, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    w = (torch.randn(V, H, device=DEV, dtype=torch.bfloat16) * 0.05).requires_grad_()
+    labels = torch.randint(0, V, (T,), device=DEV)
+    labels[::7] = -100
+    loss = F.lm_head_cross_entropy(h, w, labels, chunk_rows=256)
+    loss.backward()
+    hf, wf = h.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    lr = torch.nn.functional.cross_entropy(hf @ wf.t(), labels, ignore_index=-100)
+    lr.backward()
+    assert abs(loss.item() - lr.item()) < 2e-2 * abs(lr.item())
+    assert rel_err(h.grad, hf.grad) < 3e-2
+    assert rel_err(w.grad, wf.grad) < 3e-2
+
+
+def test_adamw_and_sumsq():
+    F, nv = _F()
+    torch.manual_seed(8)
+    n = 8 * 12345
+    p = torch.randn(n, device=DEV, dtype=torch.bfloat16)
+    g = torch.randn(n, device=DEV, dtype=torch.bfloat16) * 0.1
+    master = p.float().clone()
+    m, v = torch.zeros(n, device=DEV), torch.zeros(n, device=DEV)
+    pc, gc = p.cpu().float(), g.cpu()
+    mc, vc, wc = torch.zeros(n), torch.zeros(n), pc.clone()
+    pcb = p.cpu().clone()
+    scale = torch.tensor([0.5], device=DEV)
+    for step in (1, 2, 3):
+        F.adamw_step(p, g, master, m, v, n_decay=n // 2, lr=1e-2, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.1,
+                     step=step, grad_scale=scale)
+        F.adamw_step(pcb, gc, wc, mc, vc, n_decay=n // 2, lr=1e-2, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.1,
+                     step=step, grad_scale=torch.tensor([0.5]))
+    assert rel_err(master.cpu(), wc) < 1e-5
+    assert torch.equal(p.cpu(), wc.to(torch.bfloat16))
+    out = torch.zeros(1, device=DEV)
+    F.sum_squares(g, out)
+    assert abs(out.item() - g.float().pow(2).sum().item()) < 1e-3 * out.item()
+
+
+def test_native_library_is_loaded():
+    import ctypes
+    F, nv = _F()
+    assert isinstance(nv.lib(), ctypes.CDLL)
+    assert nv.lib().mmt_version().decode().startswith("mmt_b200")
