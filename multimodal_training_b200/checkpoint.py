@@ -1,0 +1,77 @@
+"""Epoch checkpoints fanned out over both actor groups.
+
+Layout of the reference (python/checkpoint.py:15-136), kept bit-for-bit at the path level::
+
+    {checkpoint_dir}/epoch_{N}/vision/rank_{r}.pt   {"model": state_dict}
+    {checkpoint_dir}/epoch_{N}/text/rank_{r}.pt     {"model": state_dict}
+    {checkpoint_dir}/epoch_{N}/metadata.json        {epoch, timestamp, vision_checkpoints, text_checkpoints,
+                                                     config_summary}
+
+plus an optional superset written when ``training.save_optimizer`` is set
+(``{vision,text}_optim/rank_{r}.pt``: optimizer shard, step counter, RNG state).  Files are written
+to a temporary name and renamed, so a crash never leaves a half-written shard under the final name.
+"""
+from __future__ import annotations
+
+import json
+import logging
+import os
+import re
+import time
+
+log = logging.getLogger("mmt_b200")
+
+
+def find_latest_checkpoint(checkpoint_dir: str) -> int | None:
+    """Largest N such that ``epoch_N/metadata.json`` exists, or None."""
+    if not os.path.isdir(checkpoint_dir):
+        return None
+    best = None
+    for name in os.listdir(checkpoint_dir):
+        m = re.fullmatch(r"epoch_(\d+)", name)
+        if m and os.path.isfile(os.path.join(checkpoint_dir, name, "metadata.json")):
+            n = int(m.group(1))
+            best = n if best is None or n > best else best
+    return best
+
+
+def save_epoch_checkpoint(checkpoint_dir: str, epoch: int, vision_group, text_group, config: dict) -> str:
+    from .runtime.actor_group import get
+
+    v_refs = vision_group.execute_all_async("save_checkpoint", checkpoint_dir, epoch)
+    t_refs = text_group.execute_all_async("save_checkpoint", checkpoint_dir, epoch)
+    v_paths, t_paths = get(v_refs), get(t_refs)
+    epoch_dir = os.path.join(checkpoint_dir, f"epoch_{epoch}")
+    os.makedirs(epoch_dir, exist_ok=True)
+    tr = config.get("training", {})
+    meta = {
+        "epoch": epoch,
+        "timestamp": time.strftime("%Y-%m-%dT%H:%M:%S"),
+        "vision_checkpoints": v_paths,
+        "text_checkpoints": t_paths,
+        "config_summary": {
+            "vision_parallelism": config.get("vision", {}).get("parallelism"),
+            "text_parallelism": config.get("text", {}).get("parallelism"),
+            "batch_size": tr.get("batch_size"),
+            "parallel_size": tr.get("parallel_size"),
+            "dp_size": tr.get("dp_size", 1),
+        },
+    }
+    tmp = os.path.join(epoch_dir, "metadata.json.tmp")
+    with open(tmp, "w") as f:
+        json.dump(meta, f, indent=2)
+    os.replace(tmp, os.path.join(epoch_dir, "metadata.json"))
+    log.info("Saved checkpoint for epoch %d to %s", epoch, epoch_dir)
+    return epoch_dir
+
+
+def load_epoch_checkpoint(checkpoint_dir: str, epoch: int, vision_group, text_group) -> bool:
+    """True only if every actor of both groups loaded its shard."""
+    from .runtime.actor_group import get
+
+    v = get(vision_group.execute_all_async("load_checkpoint", checkpoint_dir, epoch))
+    t = get(text_group.execute_all_async("load_checkpoint", checkpoint_dir, epoch))
+    ok = all(v) and all(t)
+    if not ok:
+        log.warning("checkpoint epoch_%d could not be loaded on every actor (vision %s, text %s)", epoch, v, t)
+    return ok

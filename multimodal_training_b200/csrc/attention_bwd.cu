@@ -1,0 +1,501 @@
+// Backward of the packed variable-length flash attention (see attention.cu for the layout).
+//
+// Three launches, no atomics, deterministic:
+//   1. delta[h, t] = sum_d out[t,h,d] * dout[t,h,d]
+//   2. dK/dV: one CTA per (128-row KV tile, kv head).  For every q head of the GQA group and every
+//      128-row query tile that can see the KV tile:
+//         S  = Q K^T,  dP = dO V^T                (tcgen05, operands K-major, results in tensor memory)
+//         P  = exp(S*scale - lse),  dS = P * (dP - delta) * scale      (one thread per query row)
+//         dV += P^T dO,  dK += dS^T Q             (P/dS in shared memory as MN-major A operands,
+//                                                  dO/Q as MN-major B operands; accumulators stay in
+//                                                  tensor memory across the whole loop)
+//   3. dQ: one CTA per (128-row query tile, q head), looping over KV tiles:
+//         S, dP, P, dS as above;  dQ += dS K      (dS K-major A operand, K MN-major B operand)
+// Every tile is two 64-column TMA boxes, usable as a K-major or an MN-major operand, so Q, K, V and
+// dO are fetched once per use with no transposes.
+#include "attention_common.cuh"
+
+namespace {
+using namespace attn;
+
+// ----------------------------------------------------------------------------------------------
+// 1. delta
+// ----------------------------------------------------------------------------------------------
+__global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ dout,
+                                  float* __restrict__ delta, int T, int n_q, int dim) {
+  const long w = (blockIdx.x * (long)blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (w >= (long)T * n_q) return;
+  const long t = w / n_q;
+  const int h = (int)(w % n_q);
+  const __nv_bfloat16* o = out + t * (long)(n_q * dim) + h * dim;
+  const __nv_bfloat16* d = dout + t * (long)(n_q * dim) + h * dim;
+  float s = 0.f;
+  for (int c = lane * 2; c < dim; c += 64) {
+    const float2 a = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(o + c));
+    const float2 b = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(d + c));
+    s += a.x * b.x + a.y * b.y;
+  }
+  s = warp_sum(s);
+  if (lane == 0) delta[(long)h * T + t] = s;
+}
+
+// P and dS of one 32-column chunk for query row `qrow` (lo <= kv < hi is the row's visible range).
+// r_s / r_dp hold raw S and dP; on return pk_p / pk_ds hold the bf16 pairs.
+MMT_DEVICE void p_ds_chunk(const uint32_t (&r_s)[32], const uint32_t (&r_dp)[32], int kv_base, int lo, int hi,
+                           float sl2, float lse_l2, float delta, float scale, uint32_t (&pk_p)[16],
+                           uint32_t (&pk_ds)[16]) {
+#pragma unroll
+  for (int i = 0; i < 32; i += 2) {
+    const int kv = kv_base + i;
+    const float p0 = (kv >= lo && kv < hi) ? exp2f(__uint_as_float(r_s[i]) * sl2 - lse_l2) : 0.f;
+    const float p1 = (kv + 1 >= lo && kv + 1 < hi) ? exp2f(__uint_as_float(r_s[i + 1]) * sl2 - lse_l2) : 0.f;
+    const float d0 = p0 * (__uint_as_float(r_dp[i]) - delta) * scale;
+    const float d1 = p1 * (__uint_as_float(r_dp[i + 1]) - delta) * scale;
+    pk_p[i >> 1] = pack_bf16x2(p0, p1);
+    pk_ds[i >> 1] = pack_bf16x2(d0, d1);
+  }
+}
+
+MMT_DEVICE void store_chunk(uint8_t* tile, int row, int c, const uint32_t (&pk)[16]) {
+  uint8_t* dst = tile + (c >> 1) * CHUNK;
+  const int col0 = (c & 1) * 32;
+#pragma unroll
+  for (int g = 0; g < 4; ++g)
+    *reinterpret_cast<uint4*>(dst + sw128_offset(row, col0 + g * 8)) =
+        make_uint4(pk[g * 4], pk[g * 4 + 1], pk[g * 4 + 2], pk[g * 4 + 3]);
+}
+
+// ----------------------------------------------------------------------------------------------
+// 2. dK / dV
+// ----------------------------------------------------------------------------------------------
+template <int DIM>
+__global__ void __launch_bounds__(kThreads, 1)
+attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant__ CUtensorMap tm_do,
+                     const AttnParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = smem;
+  uint8_t* sV = sK + 2 * CHUNK;
+  uint8_t* sQ = sV + 2 * CHUNK;
+  uint8_t* sDO = sQ + 2 * CHUNK;
+  uint8_t* sP = sDO + 2 * CHUNK;
+  uint8_t* sDS = sP + 2 * CHUNK;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sDS + 2 * CHUNK);
+  uint64_t* kv_full = bars;        // K and V landed
+  uint64_t* qdo_full = bars + 1;   // Q_i and dO_i landed
+  uint64_t* sdp_full = bars + 2;   // S and dP are in tensor memory
+  uint64_t* sdp_empty = bars + 3;  // softmax threads have read S and dP (4 warps)
+  uint64_t* pds_full = bars + 4;   // P and dS are in shared memory (4 warps)
+  uint64_t* mma2_done = bars + 5;  // dV / dK MMAs of the iteration finished: Q, dO, P, dS reusable
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kv0 = blockIdx.x * BKV;
+  const int kv_head = blockIdx.y;
+  const int group = p.n_q / p.n_kv;
+  const int kv_last = min(kv0 + BKV, p.T) - 1;
+  const int q_lo = p.causal ? kv0 : p.seq_lo[kv0];
+  const int q_hi = p.seq_hi[kv_last];
+  const int n_qt = (q_hi - q_lo + BQ - 1) / BQ;
+  const int n_iter = n_qt * group;
+  const int xk = (p.n_q + kv_head) * DIM, xv = (p.n_q + p.n_kv + kv_head) * DIM;
+
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&tm_qkv);
+    tma_prefetch_desc(&tm_do);
+    mbar_init(kv_full, 1);
+    mbar_init(qdo_full, 1);
+    mbar_init(sdp_full, 1);
+    mbar_init(sdp_empty, 4);
+    mbar_init(pds_full, 4);
+    mbar_init(mma2_done, 1);
+    mbar_fence_init();
+  }
+  if (warp == 5) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t t_s = tmem_base, t_dp = tmem_base + 128, t_dv = tmem_base + 256, t_dk = tmem_base + 384;
+
+  if (warp == 4) {
+    if (lane == 0) {
+      mbar_expect_tx(kv_full, 4 * CHUNK);
+      tma_load_2d(sK, &tm_qkv, kv_full, xk, kv0);
+      tma_load_2d(sK + CHUNK, &tm_qkv, kv_full, xk + 64, kv0);
+      tma_load_2d(sV, &tm_qkv, kv_full, xv, kv0);
+      tma_load_2d(sV + CHUNK, &tm_qkv, kv_full, xv + 64, kv0);
+      for (int it = 0; it < n_iter; ++it) {
+        const int g = it / n_qt, i = it % n_qt;
+        const int head = kv_head * group + g;
+        const int r0 = q_lo + i * BQ;
+        if (!mbar_wait(mma2_done, (it & 1) ^ 1, p.ew, 700)) break;
+        mbar_expect_tx(qdo_full, 4 * CHUNK);
+        tma_load_2d(sQ, &tm_qkv, qdo_full, head * DIM, r0);
+        tma_load_2d(sQ + CHUNK, &tm_qkv, qdo_full, head * DIM + 64, r0);
+        tma_load_2d(sDO, &tm_do, qdo_full, head * DIM, r0);
+        tma_load_2d(sDO + CHUNK, &tm_do, qdo_full, head * DIM + 64, r0);
+      }
+    }
+  } else if (warp == 5) {
+    if (lane == 0) {
+      const uint32_t idesc_s = make_idesc_bf16(BQ, BKV, 0, 0);
+      const uint32_t idesc_t = make_idesc_bf16(BKV, DIM, 1, 1);
+      const uint32_t k_base = smem_u32(sK), v_base = smem_u32(sV), q_base = smem_u32(sQ), do_base = smem_u32(sDO);
+      const uint32_t p_base = smem_u32(sP), ds_base = smem_u32(sDS);
+      bool ok = mbar_wait(kv_full, 0, p.ew, 710);
+      for (int it = 0; it < n_iter && ok; ++it) {
+        const uint32_t ph = it & 1;
+        if (!mbar_wait(qdo_full, ph, p.ew, 711)) break;
+        if (!mbar_wait(sdp_empty, ph ^ 1, p.ew, 712)) break;
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < DIM / 16; ++k)
+          tc_mma_ss(t_s, desc_kmajor(q_base, k), desc_kmajor(k_base, k), idesc_s, k != 0);
+#pragma unroll
+        for (int k = 0; k < DIM / 16; ++k)
+          tc_mma_ss(t_dp, desc_kmajor(do_base, k), desc_kmajor(v_base, k), idesc_s, k != 0);
+        tc_commit(sdp_full);
+        if (!mbar_wait(pds_full, ph, p.ew, 713)) break;
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < BQ / 16; ++k)
+          tc_mma_ss(t_dv, desc_mnmajor(p_base, k), desc_mnmajor(do_base, k), idesc_t, (it | k) != 0);
+#pragma unroll
+        for (int k = 0; k < BQ / 16; ++k)
+          tc_mma_ss(t_dk, desc_mnmajor(ds_base, k), desc_mnmajor(q_base, k), idesc_t, (it | k) != 0);
+        tc_commit(mma2_done);
+      }
+    }
+  } else {
+    const int row = warp * 32 + lane;
+    const uint32_t lane_addr = ((uint32_t)(warp * 32) << 16);
+    const float sl2 = p.scale * LOG2E;
+    bool ok = true;
+    for (int it = 0; it < n_iter; ++it) {
+      const int g = it / n_qt, i = it % n_qt;
+      const int head = kv_head * group + g;
+      const int qrow = q_lo + i * BQ + row;
+      const bool row_ok = qrow < q_hi;
+      int lo = 0, hi = 0;
+      float lse_l2 = 0.f, delta = 0.f;
+      if (row_ok) {
+        lo = p.seq_lo[qrow];
+        hi = p.seq_hi[qrow];
+        if (p.causal) hi = min(hi, qrow + 1);
+        lse_l2 = p.lse[(long)head * p.T + qrow] * LOG2E;
+        delta = p.delta[(long)head * p.T + qrow];
+      }
+      ok = __all_sync(0xffffffffu, mbar_wait(sdp_full, it & 1, p.ew, 720));
+      if (!ok) break;
+      tc_fence_after();
+      // P / dS of the previous iteration must have been consumed before they are overwritten
+      ok = __all_sync(0xffffffffu, mbar_wait(mma2_done, (it & 1) ^ 1, p.ew, 721));
+      if (!ok) break;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r_s[32], r_dp[32], pk_p[16], pk_ds[16];
+        tmem_ld_32x32b_x32(t_s + lane_addr + c * 32, r_s);
+        tmem_ld_32x32b_x32(t_dp + lane_addr + c * 32, r_dp);
+        tmem_wait_ld();
+        p_ds_chunk(r_s, r_dp, kv0 + c * 32, lo, hi, sl2, lse_l2, delta, p.scale, pk_p, pk_ds);
+        store_chunk(sP, row, c, pk_p);
+        store_chunk(sDS, row, c, pk_ds);
+      }
+      tc_fence_before();
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(sdp_empty);
+        mbar_arrive(pds_full);
+      }
+    }
+    // epilogue: thread = kv row
+    if (ok) {
+      if (n_iter > 0) ok = __all_sync(0xffffffffu, mbar_wait(mma2_done, (n_iter - 1) & 1, p.ew, 722));
+      tc_fence_after();
+      const int kvrow = kv0 + row;
+      __nv_bfloat16* dk_dst = p.dqkv + (long)kvrow * p.ld + xk;
+      __nv_bfloat16* dv_dst = p.dqkv + (long)kvrow * p.ld + xv;
+#pragma unroll 1
+      for (int c = 0; c < DIM / 16; ++c) {
+        uint32_t rk[16], rv[16];
+        if (n_iter > 0 && ok) {
+          tmem_ld_32x32b_x16(t_dk + lane_addr + c * 16, rk);
+          tmem_ld_32x32b_x16(t_dv + lane_addr + c * 16, rv);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) rk[i] = rv[i] = 0u;
+        }
+        if (kvrow < p.T) {
+#pragma unroll
+          for (int h2 = 0; h2 < 2; ++h2) {
+            uint4 a, b;
+            a.x = pack_bf16x2(__uint_as_float(rk[h2 * 8 + 0]), __uint_as_float(rk[h2 * 8 + 1]));
+            a.y = pack_bf16x2(__uint_as_float(rk[h2 * 8 + 2]), __uint_as_float(rk[h2 * 8 + 3]));
+            a.z = pack_bf16x2(__uint_as_float(rk[h2 * 8 + 4]), __uint_as_float(rk[h2 * 8 + 5]));
+            a.w = pack_bf16x2(__uint_as_float(rk[h2 * 8 + 6]), __uint_as_float(rk[h2 * 8 + 7]));
+            b.x = pack_bf16x2(__uint_as_float(rv[h2 * 8 + 0]), __uint_as_float(rv[h2 * 8 + 1]));
+            b.y = pack_bf16x2(__uint_as_float(rv[h2 * 8 + 2]), __uint_as_float(rv[h2 * 8 + 3]));
+            b.z = pack_bf16x2(__uint_as_float(rv[h2 * 8 + 4]), __uint_as_float(rv[h2 * 8 + 5]));
+            b.w = pack_bf16x2(__uint_as_float(rv[h2 * 8 + 6]), __uint_as_float(rv[h2 * 8 + 7]));
+            *reinterpret_cast<uint4*>(dk_dst + c * 16 + h2 * 8) = a;
+            *reinterpret_cast<uint4*>(dv_dst + c * 16 + h2 * 8) = b;
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) tmem_dealloc(tmem_base, 512);
+}
+
+// ----------------------------------------------------------------------------------------------
+// 3. dQ
+// ----------------------------------------------------------------------------------------------
+template <int DIM>
+__global__ void __launch_bounds__(kThreads, 1)
+attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant__ CUtensorMap tm_do,
+                   const AttnParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sDO = sQ + 2 * CHUNK;
+  uint8_t* sK = sDO + 2 * CHUNK;    // 2 stages
+  uint8_t* sV = sK + 4 * CHUNK;     // 1 stage (12 boxes in total: the shared-memory budget of the launch)
+  uint8_t* sDS = sV + 2 * CHUNK;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sDS + 2 * CHUNK);
+  uint64_t* qdo_full = bars;       // 1
+  uint64_t* k_full = bars + 1;     // 2
+  uint64_t* k_empty = bars + 3;    // 2
+  uint64_t* v_full = bars + 5;     // 1 (bars + 6 unused)
+  uint64_t* v_empty = bars + 7;    // 1 (bars + 8 unused)
+  uint64_t* sdp_full = bars + 9;
+  uint64_t* sdp_empty = bars + 10;
+  uint64_t* ds_full = bars + 11;
+  uint64_t* dq_done = bars + 12;   // dQ MMA of the iteration finished: dS reusable
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int q0 = blockIdx.x * BQ;
+  const int head = blockIdx.y;
+  const int kv_head = head / (p.n_q / p.n_kv);
+  const int q_last = min(q0 + BQ, p.T) - 1;
+  const int kv_lo = p.seq_lo[q0];
+  const int kv_hi = p.causal ? min(p.seq_hi[q_last], q_last + 1) : p.seq_hi[q_last];
+  const int n_tiles = (kv_hi - kv_lo + BKV - 1) / BKV;
+  const int xq = head * DIM, xk = (p.n_q + kv_head) * DIM, xv = (p.n_q + p.n_kv + kv_head) * DIM;
+
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&tm_qkv);
+    tma_prefetch_desc(&tm_do);
+    mbar_init(qdo_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&k_full[i], 1);
+      mbar_init(&k_empty[i], 1);
+    }
+    mbar_init(v_full, 1);
+    mbar_init(v_empty, 1);
+    mbar_init(sdp_full, 1);
+    mbar_init(sdp_empty, 4);
+    mbar_init(ds_full, 4);
+    mbar_init(dq_done, 1);
+    mbar_fence_init();
+  }
+  if (warp == 5) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t t_s = tmem_base, t_dp = tmem_base + 128, t_dq = tmem_base + 256;
+
+  if (warp == 4) {
+    if (lane == 0) {
+      mbar_expect_tx(qdo_full, 4 * CHUNK);
+      tma_load_2d(sQ, &tm_qkv, qdo_full, xq, q0);
+      tma_load_2d(sQ + CHUNK, &tm_qkv, qdo_full, xq + 64, q0);
+      tma_load_2d(sDO, &tm_do, qdo_full, xq, q0);
+      tma_load_2d(sDO + CHUNK, &tm_do, qdo_full, xq + 64, q0);
+      for (int j = 0; j < n_tiles; ++j) {
+        const int s = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        const int r0 = kv_lo + j * BKV;
+        if (!mbar_wait(&k_empty[s], ph ^ 1, p.ew, 800)) break;
+        mbar_expect_tx(&k_full[s], 2 * CHUNK);
+        tma_load_2d(sK + s * 2 * CHUNK, &tm_qkv, &k_full[s], xk, r0);
+        tma_load_2d(sK + s * 2 * CHUNK + CHUNK, &tm_qkv, &k_full[s], xk + 64, r0);
+        if (!mbar_wait(v_empty, (j & 1) ^ 1, p.ew, 801)) break;
+        mbar_expect_tx(v_full, 2 * CHUNK);
+        tma_load_2d(sV, &tm_qkv, v_full, xv, r0);
+        tma_load_2d(sV + CHUNK, &tm_qkv, v_full, xv + 64, r0);
+      }
+    }
+  } else if (warp == 5) {
+    if (lane == 0) {
+      const uint32_t idesc_s = make_idesc_bf16(BQ, BKV, 0, 0);
+      const uint32_t idesc_dq = make_idesc_bf16(BQ, DIM, 0, 1);
+      const uint32_t q_base = smem_u32(sQ), do_base = smem_u32(sDO), ds_base = smem_u32(sDS);
+      bool ok = mbar_wait(qdo_full, 0, p.ew, 810);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int s = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        const uint32_t k_base = smem_u32(sK + s * 2 * CHUNK), v_base = smem_u32(sV);
+        if (!mbar_wait(&k_full[s], ph, p.ew, 811)) break;
+        if (!mbar_wait(v_full, j & 1, p.ew, 812)) break;
+        if (!mbar_wait(sdp_empty, (j & 1) ^ 1, p.ew, 813)) break;
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < DIM / 16; ++k)
+          tc_mma_ss(t_s, desc_kmajor(q_base, k), desc_kmajor(k_base, k), idesc_s, k != 0);
+#pragma unroll
+        for (int k = 0; k < DIM / 16; ++k)
+          tc_mma_ss(t_dp, desc_kmajor(do_base, k), desc_kmajor(v_base, k), idesc_s, k != 0);
+        tc_commit(sdp_full);
+        tc_commit(v_empty);
+        if (!mbar_wait(ds_full, j & 1, p.ew, 814)) break;
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < BKV / 16; ++k)
+          tc_mma_ss(t_dq, desc_kmajor(ds_base, k), desc_mnmajor(k_base, k), idesc_dq, (j | k) != 0);
+        tc_commit(dq_done);
+        tc_commit(&k_empty[s]);
+      }
+    }
+  } else {
+    const int row = warp * 32 + lane;
+    const int qrow = q0 + row;
+    const bool row_ok = qrow < p.T;
+    const uint32_t lane_addr = ((uint32_t)(warp * 32) << 16);
+    const float sl2 = p.scale * LOG2E;
+    int lo = 0, hi = 0;
+    float lse_l2 = 0.f, delta = 0.f;
+    if (row_ok) {
+      lo = p.seq_lo[qrow];
+      hi = p.seq_hi[qrow];
+      if (p.causal) hi = min(hi, qrow + 1);
+      lse_l2 = p.lse[(long)head * p.T + qrow] * LOG2E;
+      delta = p.delta[(long)head * p.T + qrow];
+    }
+    bool ok = true;
+    for (int j = 0; j < n_tiles; ++j) {
+      const int kv0 = kv_lo + j * BKV;
+      ok = __all_sync(0xffffffffu, mbar_wait(sdp_full, j & 1, p.ew, 820));
+      if (!ok) break;
+      tc_fence_after();
+      ok = __all_sync(0xffffffffu, mbar_wait(dq_done, (j & 1) ^ 1, p.ew, 821));
+      if (!ok) break;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r_s[32], r_dp[32], pk_p[16], pk_ds[16];
+        tmem_ld_32x32b_x32(t_s + lane_addr + c * 32, r_s);
+        tmem_ld_32x32b_x32(t_dp + lane_addr + c * 32, r_dp);
+        tmem_wait_ld();
+        p_ds_chunk(r_s, r_dp, kv0 + c * 32, lo, hi, sl2, lse_l2, delta, p.scale, pk_p, pk_ds);
+        store_chunk(sDS, row, c, pk_ds);
+      }
+      tc_fence_before();
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(sdp_empty);
+        mbar_arrive(ds_full);
+      }
+    }
+    if (ok) {
+      if (n_tiles > 0) ok = __all_sync(0xffffffffu, mbar_wait(dq_done, (n_tiles - 1) & 1, p.ew, 822));
+      tc_fence_after();
+      __nv_bfloat16* dst = p.dqkv + (long)qrow * p.ld + xq;
+#pragma unroll 1
+      for (int c = 0; c < DIM / 16; ++c) {
+        uint32_t r[16];
+        if (n_tiles > 0 && ok) {
+          tmem_ld_32x32b_x16(t_dq + lane_addr + c * 16, r);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) r[i] = 0u;
+        }
+        if (row_ok) {
+#pragma unroll
+          for (int h2 = 0; h2 < 2; ++h2) {
+            uint4 a;
+            a.x = pack_bf16x2(__uint_as_float(r[h2 * 8 + 0]), __uint_as_float(r[h2 * 8 + 1]));
+            a.y = pack_bf16x2(__uint_as_float(r[h2 * 8 + 2]), __uint_as_float(r[h2 * 8 + 3]));
+            a.z = pack_bf16x2(__uint_as_float(r[h2 * 8 + 4]), __uint_as_float(r[h2 * 8 + 5]));
+            a.w = pack_bf16x2(__uint_as_float(r[h2 * 8 + 6]), __uint_as_float(r[h2 * 8 + 7]));
+            *reinterpret_cast<uint4*>(dst + c * 16 + h2 * 8) = a;
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) tmem_dealloc(tmem_base, 512);
+}
+
+constexpr size_t kBwdSmem = 1024 + 12 * CHUNK + 16 * 8 + 16;
+
+template <int DIM>
+int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tdo, const AttnParams& p, cudaStream_t st) {
+  static bool attr = false;
+  if (!attr) {
+    cudaError_t e = cudaFuncSetAttribute(attn_bwd_dkdv_kernel<DIM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)kBwdSmem);
+    if (e != cudaSuccess) return (int)e;
+    e = cudaFuncSetAttribute(attn_bwd_dq_kernel<DIM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kBwdSmem);
+    if (e != cudaSuccess) return (int)e;
+    attr = true;
+  }
+  const int tiles = (p.T + BQ - 1) / BQ;
+  attn_bwd_dkdv_kernel<DIM><<<dim3(tiles, p.n_kv), kThreads, kBwdSmem, st>>>(tq, tdo, p);
+  attn_bwd_dq_kernel<DIM><<<dim3(tiles, p.n_q), kThreads, kBwdSmem, st>>>(tq, tdo, p);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace
+
+// dqkv [T, ld] receives dq | dk | dv in the layout of qkv.  delta is fp32 scratch [n_q, T].
+extern "C" int mmt_attn_bwd(const void* qkv, const void* out, const void* dout, const float* lse, float* delta,
+                            void* dqkv, const int* seq_lo, const int* seq_hi, long T, int n_q, int n_kv, int dim,
+                            long ld, int causal, float scale, void* stream) {
+  if (T <= 0) return 0;
+  if ((dim != 80 && dim != 128) || n_q % n_kv || (ld & 7)) return -2;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  {
+    const long warps = T * n_q;
+    const int threads = 256;
+    const long blocks = (warps * 32 + threads - 1) / threads;
+    attn_delta_kernel<<<(unsigned)blocks, threads, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(out),
+                                                           reinterpret_cast<const __nv_bfloat16*>(dout), delta,
+                                                           (int)T, n_q, dim);
+  }
+  CUtensorMap tq, tdo;
+  const uint64_t width = (uint64_t)(n_q + 2 * n_kv) * dim;
+  int r = mmt_make_tmap_2d(&tq, qkv, width, (uint64_t)T, (uint64_t)ld, 64, 128);
+  if (r) return 1000 + r;
+  r = mmt_make_tmap_2d(&tdo, dout, (uint64_t)n_q * dim, (uint64_t)T, (uint64_t)n_q * dim, 64, 128);
+  if (r) return 2000 + r;
+  AttnParams p;
+  p.qkv = reinterpret_cast<const __nv_bfloat16*>(qkv);
+  p.out = nullptr;
+  p.lse = const_cast<float*>(lse);
+  p.seq_lo = seq_lo;
+  p.seq_hi = seq_hi;
+  p.T = (int)T; p.n_q = n_q; p.n_kv = n_kv; p.dim = dim; p.ld = ld;
+  p.causal = causal; p.scale = scale;
+  p.ew = mmt_error_word();
+  p.dout = reinterpret_cast<const __nv_bfloat16*>(dout);
+  p.delta = delta;
+  p.dqkv = reinterpret_cast<__nv_bfloat16*>(dqkv);
+  return dim == 80 ? launch_bwd<80>(tq, tdo, p, st) : launch_bwd<128>(tq, tdo, p, st);
+}

@@ -1,0 +1,173 @@
+"""Driver: one process that steers the vision and text actor groups through a training run.
+
+``python -m multimodal_training_b200.train --config-path=configs --config-name=sample key=value ...``
+
+Loop and log lines follow the reference (python/train_ray.py:141-459): per iteration zero_grad on
+both groups, vision ``forward_step`` (async), text ``forward_step`` fed with the vision refs, text
+``backward_step``, vision ``backward_step`` fed with the text refs, optional global-norm clipping,
+two optimizer steps, memory stats, one log line; per epoch a checkpoint; at the end the line
+``Training completed! E epochs, S total steps, M measured steps (avg X.XXXs/step)`` that sweep
+scripts grep.  Differences: the data-parallel replicas see different samples, the LR schedule spans
+all epochs, and there is no hidden 100-iteration cap.
+"""
+from __future__ import annotations
+
+import logging
+import math
+import os
+import sys
+import time
+
+from .checkpoint import find_latest_checkpoint, load_epoch_checkpoint, save_epoch_checkpoint
+from .config.loader import parse_cli, trainer_configs
+from .runtime.actor_group import ActorGroup, get
+from .runtime.logger import setup_logging
+
+log = logging.getLogger("mmt_b200")
+
+
+def get_vision_trainer_class(model_type: str):
+    if model_type == "qwen2_5_vl":
+        from .trainers.vision import QwenVisionTrainer
+        return QwenVisionTrainer
+    raise ValueError(f"Unsupported vision model type: {model_type}")
+
+
+def get_text_trainer_class(model_type: str):
+    if model_type == "qwen2_5_vl":
+        from .trainers.text import QwenTextTrainer
+        return QwenTextTrainer
+    raise ValueError(f"Unsupported text model type: {model_type}")
+
+
+def aggregate_grad_norms(vision_norms: list[dict], text_norms: list[dict], dp_size: int = 1,
+                         parallel_size: int = 1) -> float:
+    """Global gradient norm from the per-actor squared-norm pieces.
+
+    Each piece is ``{"type", "sharded", "replicated", ...}`` computed after gradient reduction on the
+    actor's ZeRO shard.  ZeRO shards are disjoint, so sharded parts add over all actors.  Parameters
+    that are replicated inside a tensor-parallel group (norm weights) appear once per TP rank and are
+    counted once: their part is divided by the TP degree.  (The reference samples actors per replica for
+    the same purpose, python/train_ray.py:37-122.)
+    """
+    total = 0.0
+    for n in vision_norms:
+        total += float(n.get("sharded", 0.0)) + float(n.get("replicated", 0.0))
+    tp = max(1, int(text_norms[0].get("tp_size", parallel_size))) if text_norms else 1
+    for n in text_norms:
+        total += float(n.get("sharded", 0.0)) + float(n.get("replicated", 0.0)) / tp
+    return math.sqrt(max(total, 0.0))
+
+
+def main(cfg: dict) -> dict:
+    setup_logging(force=True)
+    tr = cfg["training"]
+    vision_config, text_config = trainer_configs(cfg)
+    parallel_size, dp_size = int(tr["parallel_size"]), int(tr.get("dp_size", 1))
+    num_actors = parallel_size * dp_size
+    collocate = bool(tr.get("collocate", True))
+    log.info("Creating %d vision and %d text actors (collocate=%s)", num_actors, num_actors, collocate)
+
+    vision_cls = get_vision_trainer_class(cfg["vision"]["model_type"])
+    text_cls = get_text_trainer_class(cfg["text"]["model_type"])
+    vision_group = ActorGroup(vision_config, vision_cls, num_actors, collocate=collocate,
+                              rpc_timeout_s=tr.get("rpc_timeout_s"))
+    # the halves always share hosts: the handoff is an in-process exchange (see runtime/actor_group.py)
+    text_group = ActorGroup(text_config, text_cls, num_actors, collocate=collocate,
+                            placement_group_handle=vision_group.placement_group_handle)
+    try:
+        return _run(cfg, vision_group, text_group, num_actors, parallel_size, dp_size)
+    finally:
+        vision_group.shutdown()
+
+
+def _run(cfg, vision_group, text_group, num_actors, parallel_size, dp_size) -> dict:
+    tr = cfg["training"]
+    vision_group.execute_all("build_model")
+    text_group.execute_all("build_model")
+    vision_group.execute_all("initialize_trainer")
+    text_group.execute_all("initialize_trainer")
+    vision_group.execute_all("set_receiver_info", text_group.execute_all("get_physical_gpu_id"))
+
+    num_epochs, num_iterations = int(tr["num_epochs"]), int(tr["num_iterations"])
+    warmup_steps = int(tr.get("warmup_steps", 0))
+    log_interval = max(1, int(tr.get("log_interval", 1)))
+    clip = bool(tr.get("clip_grad_norm", False))
+    profile_time = bool(tr.get("profile_time", False))
+    checkpoint_dir = tr.get("checkpoint_dir", "/tmp/checkpoints")
+    use_ckpt = not bool(tr.get("no_checkpoint", True))
+
+    start_epoch = 0
+    if use_ckpt:
+        latest = find_latest_checkpoint(checkpoint_dir)
+        if latest is not None:
+            if load_epoch_checkpoint(checkpoint_dir, latest, vision_group, text_group):
+                start_epoch = latest + 1
+                log.info("Resumed from epoch %d", latest)
+            else:
+                log.warning("Failed to load checkpoint of epoch %d; starting from scratch", latest)
+
+    global_step = start_epoch * num_iterations
+    measured, measured_time, losses = 0, 0.0, []
+    for epoch in range(start_epoch, num_epochs):
+        for iteration in range(num_iterations):
+            is_warmup = global_step < warmup_steps
+            t0 = time.perf_counter()
+            vision_group.execute_all("zero_grad")
+            text_group.execute_all("zero_grad")
+            vision_refs = vision_group.execute_all_async("forward_step", global_step)
+            text_refs = text_group.execute_all_async("forward_step", vision_refs, [global_step] * num_actors)
+            text_out = get(text_refs)
+            step_losses = [float(o["loss"]) for o in text_out]
+            loss = sum(step_losses) / len(step_losses)
+            text_bwd_refs = text_group.execute_all_async("backward_step")
+            vision_bwd_refs = vision_group.execute_all_async("backward_step", text_bwd_refs)
+            text_bwd, vision_bwd = get(text_bwd_refs), get(vision_bwd_refs)
+            global_norm = None
+            if clip:
+                vn = vision_group.execute_all("compute_grad_norm_contribution")
+                tn = text_group.execute_all("compute_grad_norm_contribution")
+                global_norm = aggregate_grad_norms(vn, tn, dp_size, parallel_size)
+            text_group.execute_all("optimizer_step", global_norm)
+            vision_group.execute_all("optimizer_step", global_norm)
+            vmem = get(vision_group.execute_all_async("get_memory_stats"))
+            tmem = get(text_group.execute_all_async("get_memory_stats"))
+            dt = time.perf_counter() - t0
+            if not is_warmup:
+                measured += 1
+                measured_time += dt
+            losses.append(loss)
+            if iteration % log_interval == 0:
+                avg = lambda xs, k: sum(x[k] for x in xs) / len(xs)  # noqa: E731
+                line = (f"Epoch {epoch + 1}/{num_epochs}, Iter {iteration + 1}/{num_iterations} "
+                        f"({'warmup' if is_warmup else 'training'}) - Loss: {loss:.4f}, Iteration time: {dt:.3f}s")
+                if profile_time:
+                    vf = avg(get(vision_refs), "forward_time_ms")
+                    line += (f", Vision fwd: {vf:.1f}ms, Vision bwd: {avg(vision_bwd, 'backward_time_ms'):.1f}ms, "
+                             f"Text fwd: {avg(text_out, 'forward_time_ms'):.1f}ms, "
+                             f"Text bwd: {avg(text_bwd, 'backward_time_ms'):.1f}ms")
+                if global_norm is not None:
+                    line += f", Grad norm: {global_norm:.4f}"
+                line += (f", Vision mem: {avg(vmem, 'allocated_mb'):.0f} MB (peak {avg(vmem, 'peak_mb'):.0f}), "
+                         f"Text mem: {avg(tmem, 'allocated_mb'):.0f} MB (peak {avg(tmem, 'peak_mb'):.0f})")
+                log.info(line)
+            vision_group.free(vision_refs + vision_bwd_refs)
+            text_group.free(text_refs + text_bwd_refs)
+            global_step += 1
+        if use_ckpt:
+            save_epoch_checkpoint(checkpoint_dir, epoch, vision_group, text_group, cfg)
+    avg_t = measured_time / measured if measured else float("nan")
+    log.info("Training completed! %d epochs, %d total steps, %d measured steps (avg %.3fs/step)", num_epochs,
+             global_step, measured, avg_t)
+    log.info("Average iteration time: %.3fs", avg_t)
+    return {"losses": losses, "avg_step_s": avg_t, "steps": global_step}
+
+
+def cli(argv: list[str] | None = None) -> int:
+    cfg, _ = parse_cli(argv)
+    main(cfg)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(cli())

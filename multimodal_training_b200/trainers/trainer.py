@@ -23,6 +23,7 @@ from ..data.synthetic import synthetic_global_batch
 from ..parallel import comm
 from ..parallel.mesh import Mesh, build_mesh
 from ..parallel.zero import ZeroAdamW, lr_at
+from ..runtime.actor import RayActor
 from .context import StepContext, build_step_context
 
 log = logging.getLogger("mmt_b200")
@@ -102,10 +103,11 @@ class SyntheticSource:
         return self._cache[key]
 
 
-class Trainer:
+class Trainer(RayActor):
     kind = "base"
 
     def __init__(self, config: dict, rank: int = 0):
+        super().__init__()
         self.config = dict(config)
         self.rank = rank
         self.seed = int(self.config.get("seed", 42))
@@ -218,7 +220,7 @@ class Trainer:
         a, b = opt.grad_norm_sq_local(shard)
         self._last_norm_parts = (a, b)
         return {"type": self.norm_type, "sharded": float(a.item()), "replicated": float(b.item()),
-                "zero_size": opt.gsize, "zero_rank": opt.grank}
+                "zero_size": opt.gsize, "zero_rank": opt.grank, "tp_size": self._ensure_mesh().tp}
 
     def optimizer_step(self, global_grad_norm: float | None = None) -> float:
         """Clip (if configured and a global norm is given) -> fused AdamW on the owned shard -> parameter all-gather."""
