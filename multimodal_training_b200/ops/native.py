@@ -94,10 +94,14 @@ def check(code: int, what: str) -> None:
         raise RuntimeError(f"{what} failed with code {code}")
 
 
+# entry points that launch more than one kernel per call
+_LAUNCHES = {"mmt_rmsnorm_bwd": 2, "mmt_colsum": 2, "mmt_attn_bwd": 3}
+
+
 def call(name: str, *args) -> None:
     """Invoke an int-returning entry point and raise on a non-zero code."""
     global launch_count
-    launch_count += 1
+    launch_count += _LAUNCHES.get(name, 1)
     code = getattr(lib(), name)(*args)
     if code != 0:
         raise RuntimeError(f"{name} failed with code {code}")

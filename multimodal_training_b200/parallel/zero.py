@@ -91,7 +91,7 @@ class ZeroAdamW:
                 p.grad = gview
         lo = self.grank * self.shard
         self.shard_lo = lo
-        self.master = self.flat_param[lo:lo + self.shard].float().clone()
+        self.master = self.flat_param[lo:lo + self.shard].to(torch.float32, copy=True)
         self.exp_avg = torch.zeros_like(self.master)
         self.exp_avg_sq = torch.zeros_like(self.master)
         self._normsq = torch.zeros(1, dtype=torch.float32, device=self.device)

@@ -27,10 +27,12 @@ def rel_err(a, b):
 def test_gemm_layouts(M, N, K, layout):
     F, nv = _F()
     torch.manual_seed(0)
+    a_mn = layout == "mn_mn"
+    if a_mn:
+        M = (M + 7) // 8 * 8     # an MN-major A has leading dimension M: multiple of 8 elements (16 bytes)
     A = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
     B = torch.randn(N, K, device=DEV, dtype=torch.bfloat16) * 0.05
     ref = A.float() @ B.float().t()
-    a_mn = layout == "mn_mn"
     b_mn = layout != "kk"
     out = F.gemm(A.t().contiguous() if a_mn else A, B.t().contiguous() if b_mn else B, a_mn=a_mn, b_mn=b_mn)
     assert rel_err(out, ref) < 8e-3
