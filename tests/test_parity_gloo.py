@@ -1,0 +1,130 @@
+"""Hybrid-parallel training equals single-process training (tiny VLM, fp32, CPU/gloo).
+
+Vision sequence parallel (ragged, window aligned, Ulysses exchange in the full-attention layer) +
+ZeRO-1, text tensor parallel with sequence-parallel activations, vocab-parallel embedding and
+cross-entropy, the vision->text row handoff and real data-parallel sharding are compared against one
+process on the same global batch: losses of 3 AdamW steps and the FULL gradient of every parameter
+at step 0 (the reference's own parity tests compare two LayerNorm vectors and print,
+tests/test_vision_sp.py:350-417, tests/test_text_autotp.py in the reference).
+"""
+import pytest
+import torch
+
+from dist_utils import run_ranks
+
+OV = ["vision.model_name=tiny", "text.model_name=tiny", "vision.dtype=float32", "text.dtype=float32",
+      "training.learning_rate=1e-4", "training.warmup_ratio=0", "training.warmup_steps=0",
+      "training.lr_scheduler_type=constant", "training.weight_decay=0.01", "+training.device=cpu",
+      "+data.synthetic.image_size=224", "+data.synthetic.text_tokens=64", "+data.synthetic.global_batch=2",
+      "vision.activation_checkpointing=true", "text.activation_checkpointing=true"]
+
+
+def _grads_reference_layout(model):
+    saved = [(p, p.data) for p in model.parameters()]
+    try:
+        for p, _ in saved:
+            p.data = p.grad if p.grad is not None else torch.zeros_like(p.data)
+        return {k: v.clone() for k, v in model.reference_state_dict().items()}
+    finally:
+        for p, d in saved:
+            p.data = d
+
+
+def _worker(rank, world, sp, tp, steps):
+    import torch.distributed as dist
+    from multimodal_training_b200.config.loader import load_config
+    from multimodal_training_b200.engine import HybridEngine
+
+    ov = OV + ["vision.parallelism=" + ("sequence" if sp > 1 else "none"),
+               "text.parallelism=" + ("tensor" if tp > 1 else "none"), f"text.tensor_parallel_size={tp}",
+               f"training.parallel_size={world}", f"training.batch_size={2 // (world // tp)}"]
+    cfg = load_config(None, ov)
+    # mesh factors: sp ranks share images, tp ranks share a text replica
+    eng = HybridEngine.from_config(cfg) if (sp == world or world == 1) else None
+    if eng is None:
+        from multimodal_training_b200.config.loader import trainer_configs
+        v, t = trainer_configs(cfg)
+        v["mesh_sp"] = t["mesh_sp"] = sp
+        eng = HybridEngine(v, t)
+    m = eng.mesh
+    # ---- step-0 gradients
+    eng.vision.zero_grad()
+    eng.text.zero_grad()
+    vo = eng.vision.forward_step(0)
+    to = eng.text.forward_step(vo, 0)
+    g = eng.text.backward_step()
+    eng.vision.backward_step(g)
+    # vision: sum over all ranks (they split tokens or samples); the data-parallel mean is the divisor
+    fg = eng.vision.optimizer.flat_grad
+    if world > 1:
+        dist.all_reduce(fg)
+    fg /= eng.vision.optimizer.grad_divisor
+    vgrads = _grads_reference_layout(eng.vision.model)
+    # text: partial sums of sequence-parallel params over tp, then mean over data-parallel replicas
+    to_ = eng.text.optimizer
+    to_._finish_grads()
+    if m.tp > 1 and to_.partial_end > to_.partial_start:
+        dist.all_reduce(to_.flat_grad[to_.partial_start:to_.partial_end], group=m.tp_group)
+    if m.tdp > 1:
+        dist.all_reduce(to_.flat_grad, group=m.tdp_group)
+        to_.flat_grad /= m.tdp
+    tgrads = _grads_reference_layout(eng.text.model)
+    loss0 = eng.mean_loss(to["loss"])
+    # ---- three optimisation steps from the same start
+    losses = []
+    for s in range(steps):
+        losses.append(eng.mean_loss(eng.train_step(s)))
+    return {"loss0": loss0, "losses": losses, "vgrads": vgrads, "tgrads": tgrads, "tp_rank": m.tp_rank,
+            "tdp_rank": m.tdp_rank}
+
+
+def _merge_text(results, tp):
+    from multimodal_training_b200.cli.merge_checkpoint import merge_state_dicts
+    shards = [r["tgrads"] for r in results if r["tdp_rank"] == 0]
+    shards.sort(key=lambda _: 0)
+    by_rank = sorted([r for r in results if r["tdp_rank"] == 0], key=lambda r: r["tp_rank"])
+    return merge_state_dicts([r["tgrads"] for r in by_rank]) if tp > 1 else by_rank[0]["tgrads"]
+
+
+def _compare(single, multi, tp):
+    assert abs(single["loss0"] - multi[0]["loss0"]) < 2e-5 * abs(single["loss0"])
+    for a, b in zip(single["losses"], multi[0]["losses"]):
+        assert abs(a - b) < 5e-5 * abs(a), (single["losses"], multi[0]["losses"])
+    worst = 0.0
+    for k, ref in single["vgrads"].items():
+        got = multi[0]["vgrads"][k]
+        err = (got - ref).abs().max().item() / (ref.abs().max().item() + 1e-12)
+        worst = max(worst, err)
+        assert err < 2e-4, ("vision", k, err)
+    merged = _merge_text(multi, tp)
+    for k, ref in single["tgrads"].items():
+        got = merged[k]
+        assert got.shape == ref.shape, (k, got.shape, ref.shape)
+        err = (got - ref).abs().max().item() / (ref.abs().max().item() + 1e-12)
+        worst = max(worst, err)
+        assert err < 2e-4, ("text", k, err)
+    return worst
+
+
+@pytest.fixture(scope="module")
+def single(tmp_path_factory):
+    return run_ranks(_worker, 1, tmp_path_factory.mktemp("single"), 1, 1, 3)[0]
+
+
+@pytest.mark.integration
+def test_sp2_tp2_matches_single_process(single, tmp_path):
+    multi = run_ranks(_worker, 2, tmp_path, 2, 2, 3)
+    _compare(single, multi, tp=2)
+
+
+@pytest.mark.integration
+def test_sp2_with_text_data_parallel_matches_single_process(single, tmp_path):
+    # vision SP=2 over both ranks, text TP=1 x DP=2: each text replica gets one of the two samples
+    multi = run_ranks(_worker, 2, tmp_path, 2, 1, 3)
+    _compare(single, multi, tp=1)
+
+
+@pytest.mark.integration
+def test_sp4_tp2_dp2_matches_single_process(single, tmp_path):
+    multi = run_ranks(_worker, 4, tmp_path, 4, 2, 3)
+    _compare(single, multi, tp=2)
