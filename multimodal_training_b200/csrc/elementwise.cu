@@ -10,7 +10,10 @@
 //                              (reference: python/tensor_parallel/cross_entropy.py:41-236)
 //   fused AdamW over a flat parameter shard, sum of squares (grad norm)
 //                              (reference: torch.optim.Adam at python/ray/trainer.py:503-572)
+#include <stdio.h>
+
 #include "common.cuh"
+#include "noalloc.h"
 #include "runtime.h"
 
 namespace {
@@ -655,3 +658,54 @@ int mmt_clip_coef(const float* normsq, float max_norm, float extra, float* coef,
 }
 
 }  // extern "C"
+
+// ----------------------------------------------------------------------------
+// Allocation-free RMSNorm backward (declared and documented in noalloc.h).
+// ----------------------------------------------------------------------------
+namespace {
+// Scratch for the per-CTA partial sums of dw.  In host code this name is only a stand-in for the
+// symbol: kernels must be given the device address obtained with cudaGetSymbolAddress.
+static __device__ __align__(256) float g_noalloc_scratch[MMT_NOALLOC_SCRATCH_FLOATS];
+
+constexpr int kMaxDevices = 64;
+float* g_noalloc_ptr[kMaxDevices] = {nullptr};
+
+// Device address of the scratch array on the current device (resolved once per device).
+float* noalloc_scratch_ptr() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+  if (g_noalloc_ptr[dev] == nullptr) {
+    float* ptr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_noalloc_scratch);
+    if (e != cudaSuccess) {
+      fprintf(stderr, "mmt_rmsnorm_bwd_noalloc: cudaGetSymbolAddress failed on device %d: %s\n", dev,
+              cudaGetErrorString(e));
+      return nullptr;
+    }
+    g_noalloc_ptr[dev] = ptr;
+  }
+  return g_noalloc_ptr[dev];
+}
+}  // namespace
+
+extern "C" int mmt_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* w, const float* rstd, void* dx,
+                                       void* dw, long rows, int cols, int accumulate_dw, void* stream) {
+  if (cols % 8) return -2;
+  if (cols <= 0 || cols > MMT_NOALLOC_MAX_COLS || rows < 0 || rows > 0x7fffffffL) {
+    fprintf(stderr,
+            "mmt_rmsnorm_bwd_noalloc: size [%ld, %d] is outside the built-in scratch's limits (cols <= %d, "
+            "rows < 2^31)\n", rows, cols, MMT_NOALLOC_MAX_COLS);
+    return -5;
+  }
+  if (rows == 0) return 0;
+  float* scratch = noalloc_scratch_ptr();
+  if (scratch == nullptr) return -6;
+  // as many per-CTA partial rows as the regular entry point would use, capped by the scratch size
+  int parts = mmt_rmsnorm_bwd_parts(rows);
+  const int cap = MMT_NOALLOC_SCRATCH_FLOATS / cols;
+  if (parts > cap) parts = cap;
+  rmsnorm_bwd_kernel<<<parts, kNormThreads, 0, ST(stream)>>>(CBF(dy), CBF(x), CBF(w), rstd, BF(dx), scratch,
+                                                            (int)rows, cols);
+  reduce_partials_kernel<<<(cols + 255) / 256, 256, 0, ST(stream)>>>(scratch, BF(dw), parts, cols, accumulate_dw);
+  return (int)cudaGetLastError();
+}
