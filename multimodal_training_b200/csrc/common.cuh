@@ -127,7 +127,7 @@ MMT_DEVICE bool mbar_wait(uint64_t* bar, uint32_t parity, MmtErrorWord* ew, int 
 }
 
 // ---------------------------------------------------------------------------
-// TMA (cp.async.bulk.tensor), never with cluster multicast.
+// TMA (cp.async.bulk.tensor): plain per-CTA loads and stores only.
 // ---------------------------------------------------------------------------
 MMT_DEVICE void tma_prefetch_desc(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");

@@ -48,7 +48,26 @@ struct GemmParams {
   int a_mn, b_mn;                 // operand majors
   uint32_t mn_lbo, mn_sbo, mn_kstep;  // descriptor constants of MN-major tiles
   MmtErrorWord* ew;
+  // --- all-gather consumer (A rows arrive from peers): rows [s*ag_rows, (s+1)*ag_rows) come from rank s and
+  //     are complete once ag_flags[s] >= ag_epoch; this rank's own rows need no wait.  ag_flags == nullptr: off.
+  const int* ag_flags;
+  int ag_epoch, ag_rows, ag_self;
+  // --- reduce-scatter producer: row r of C belongs to rank r / rs_rows and is stored to that rank's staging
+  //     slot `rs_self` ([rs_self*rs_rows + r % rs_rows, :] at rs_base[owner]); when the whole GEMM is done,
+  //     rs_flag[p] on every peer receives rs_epoch.  rs_rows == 0: off.
+  unsigned long long rs_base[8];
+  int* rs_flag[8];
+  int* rs_counter;
+  int rs_rows, rs_self, rs_ranks, rs_epoch;
 };
+
+// tile index -> (tile_m, tile_n); with an all-gather consumer the m tiles are rotated so that the CTA wave
+// starts on this rank's own rows while the peers' rows are still in flight.
+MMT_DEVICE void tile_coords(const GemmParams& p, int tile, int tiles_m, int& tm, int& tn) {
+  tm = tile % tiles_m;
+  tn = tile / tiles_m;
+  if (p.ag_flags) tm = (tm + (int)(((long)p.ag_self * p.ag_rows) / BM)) % tiles_m;
+}
 
 template <int BN>
 struct Cfg {
@@ -110,8 +129,20 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
+      uint32_t ag_seen = p.ag_flags ? (1u << p.ag_self) : 0u;
       for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
-        const int tm = tile % tiles_m, tn = tile / tiles_m;
+        int tm, tn;
+        tile_coords(p, tile, tiles_m, tm, tn);
+        if (p.ag_flags) {
+          const int r0 = tm * BM, r1 = min(r0 + BM, p.M) - 1;
+          for (int src = r0 / p.ag_rows; src <= r1 / p.ag_rows && ok; ++src) {
+            if (ag_seen & (1u << src)) continue;
+            ok = flag_wait_ge(&p.ag_flags[src], p.ag_epoch, MMT_WAIT_NS, p.ew, 110);
+            ag_seen |= 1u << src;
+          }
+          if (!ok) break;
+          asm volatile("fence.proxy.async;" ::: "memory");
+        }
         for (int kb = 0; kb < KB; ++kb) {
           if (!mbar_wait(&empty[s], ph ^ 1, p.ew, 100)) { ok = false; break; }
           uint8_t* sA = smem + (size_t)s * C_::STAGE_BYTES;
@@ -173,7 +204,8 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     int acc = 0;
     uint32_t acc_ph = 0;
     for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
-      const int tm = tile % tiles_m, tn = tile / tiles_m;
+      int tm, tn;
+      tile_coords(p, tile, tiles_m, tm, tn);
       bool ok = mbar_wait(&tfull[acc], acc_ph, p.ew, 300);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
@@ -230,7 +262,14 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_constant
               *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
               *reinterpret_cast<float4*>(dst + 4) = make_float4(v[4], v[5], v[6], v[7]);
             } else {
-              __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + grow * p.ldc + col;
+              __nv_bfloat16* dst;
+              if (p.rs_rows) {
+                const int owner = (int)(grow / p.rs_rows);
+                dst = reinterpret_cast<__nv_bfloat16*>(p.rs_base[owner]) +
+                      ((long)p.rs_self * p.rs_rows + (grow - (long)owner * p.rs_rows)) * p.ldc + col;
+              } else {
+                dst = reinterpret_cast<__nv_bfloat16*>(p.C) + grow * p.ldc + col;
+              }
               if (p.accumulate) {
                 const uint4 ov = *reinterpret_cast<const uint4*>(dst);
                 const uint32_t ow[4] = {ov.x, ov.y, ov.z, ov.w};
@@ -259,9 +298,18 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     }
   }
 
+  if (p.rs_rows) __threadfence_system();   // this thread's peer stores are visible system-wide
   tc_fence_before();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_base, C_::TMEM_COLS);
+  if (p.rs_rows && threadIdx.x == 0) {
+    // last CTA to finish publishes "my partial sums have landed" to every peer
+    if (atomicAdd(p.rs_counter, 1) == (int)gridDim.x - 1) {
+      *p.rs_counter = 0;
+      __threadfence_system();
+      for (int r = 0; r < p.rs_ranks; ++r) flag_store_release_sys(p.rs_flag[r], p.rs_epoch);
+    }
+  }
 }
 
 // ------------------------------------------------------------------------------------
@@ -320,6 +368,23 @@ extern "C" void mmt_gemm_set_mn_desc(uint32_t lbo, uint32_t sbo, uint32_t kstep)
   g_mn_kstep = kstep;
 }
 
+// Optional collective roles of a GEMM launch (see GemmParams).
+struct MmtGemmComm {
+  const int* ag_flags;
+  int ag_epoch, ag_rows, ag_self;
+  unsigned long long rs_base[8];
+  int* rs_flag[8];
+  int* rs_counter;
+  int rs_rows, rs_self, rs_ranks, rs_epoch;
+};
+
+namespace {
+const MmtGemmComm* g_comm = nullptr;
+}
+
+// Attach collective roles to the NEXT mmt_gemm_bf16 call of this thread of control (cleared by that call).
+extern "C" void mmt_gemm_set_comm(const MmtGemmComm* c) { g_comm = c; }
+
 // C = epilogue(alpha * A * B^T).  See the file header for layouts.
 //   a_mn / b_mn : 0 = K-major ([rows][K], ld = row stride), 1 = MN-major ([K][rows], ld = k-row stride)
 //   act         : 0 none, 1 GELU
@@ -358,6 +423,20 @@ extern "C" int mmt_gemm_bf16(const void* A, const void* B, void* C, const void* 
   p.a_mn = a_mn; p.b_mn = b_mn;
   p.mn_lbo = g_mn_lbo; p.mn_sbo = g_mn_sbo; p.mn_kstep = g_mn_kstep;
   p.ew = mmt_error_word();
+  p.ag_flags = nullptr;
+  p.ag_epoch = p.ag_rows = p.ag_self = 0;
+  p.rs_rows = p.rs_self = p.rs_ranks = p.rs_epoch = 0;
+  p.rs_counter = nullptr;
+  if (g_comm) {
+    const MmtGemmComm* c = g_comm;
+    g_comm = nullptr;
+    p.ag_flags = c->ag_flags; p.ag_epoch = c->ag_epoch; p.ag_rows = c->ag_rows; p.ag_self = c->ag_self;
+    p.rs_rows = c->rs_rows; p.rs_self = c->rs_self; p.rs_ranks = c->rs_ranks; p.rs_epoch = c->rs_epoch;
+    p.rs_counter = c->rs_counter;
+    for (int i = 0; i < 8; ++i) { p.rs_base[i] = c->rs_base[i]; p.rs_flag[i] = c->rs_flag[i]; }
+    if (p.ag_flags && (p.ag_rows <= 0 || a_mn)) return -5;
+    if (p.rs_rows && (out_f32 || p.rs_ranks > 8 || p.rs_ranks < 1)) return -6;
+  }
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   switch (bn) {
     case 256: return launch<256>(ta, tb, p, sms, st);

@@ -107,15 +107,14 @@ class TextDecoder(nn.Module):
 
     def _layer(self, x, L, cos, sin, seq: SeqInfo):
         d = self.cfg.head_dim
-        h = F.rmsnorm(x, L.ln1_w, self.cfg.rms_norm_eps)
-        qkv = column_parallel_linear(h, L.qkv_w, L.qkv_b, self.tp)
+        eps = self.cfg.rms_norm_eps
+        qkv = column_parallel_linear(x, L.qkv_w, L.qkv_b, self.tp, norm_w=L.ln1_w, eps=eps, role="qkv")
         qkv = F.rope(qkv, cos, sin, self.n_q + self.n_kv, d)
         a = F.attention(qkv, self.n_q, self.n_kv, d, seq, causal=True)
-        x = row_parallel_linear(a, L.o_w, x, self.tp)
-        h = F.rmsnorm(x, L.ln2_w, self.cfg.rms_norm_eps)
-        gu = column_parallel_linear(h, L.gate_up_w, None, self.tp)
+        x = row_parallel_linear(a, L.o_w, x, self.tp, role="o")
+        gu = column_parallel_linear(x, L.gate_up_w, None, self.tp, norm_w=L.ln2_w, eps=eps, role="mlp")
         m = F.swiglu(gu)
-        return row_parallel_linear(m, L.down_w, x, self.tp)
+        return row_parallel_linear(m, L.down_w, x, self.tp, role="down")
 
     def forward(self, x_shard: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, seq: SeqInfo) -> torch.Tensor:
         """[T/tp, H] token shard -> final hidden token shard (before the last norm)."""

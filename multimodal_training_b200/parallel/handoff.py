@@ -83,6 +83,11 @@ class HandoffPlan:
     recv_counts: list[int]         # per world rank
     recv_rows: torch.Tensor        # [sum(recv_counts)] row in this rank's token shard
     shard_rows: int                # rows of the text token shard on this rank
+    # direct routes for the peer-memory path (no sorting by destination needed)
+    dest_rank: torch.Tensor | None = None       # [M_loc] int32 world rank that owns the text row
+    dest_row: torch.Tensor | None = None        # [M_loc] int64 row inside that rank's token shard
+    recv_src_rank: torch.Tensor | None = None   # [R] int32 world rank that produced each received row
+    recv_src_index: torch.Tensor | None = None  # [R] int64 index of the row in the producer's local merged tokens
 
 
 def build_handoff_plan(mesh: Mesh, geoms: list[Geometry], images_per_vreplica: list[list[int]],
@@ -96,8 +101,9 @@ def build_handoff_plan(mesh: Mesh, geoms: list[Geometry], images_per_vreplica: l
     """
     world, sp, tp = mesh.world, mesh.sp, mesh.tp
     me = mesh.rank
-    send_dest, send_row = None, None
+    send_dest, send_row, my_drow = None, None, None
     recv_lists = [[] for _ in range(world)]
+    recv_src_idx = [[] for _ in range(world)]
     send_counts = [0] * world
     for v, geom in enumerate(geoms):
         if geom is None:
@@ -123,18 +129,26 @@ def build_handoff_plan(mesh: Mesh, geoms: list[Geometry], images_per_vreplica: l
                 drow[sel] = r % shard
             order = np.argsort(dest, kind="stable")
             if ws == me:
-                send_dest, send_row = dest, order
+                send_dest, send_row, my_drow = dest, order, drow
                 cnt = np.bincount(dest, minlength=world)
                 send_counts = [int(c) for c in cnt]
             mine = dest[order] == me
             if mine.any():
                 recv_lists[ws] = drow[order][mine]
+                recv_src_idx[ws] = order[mine]
     recv_counts = [len(x) for x in recv_lists]
     recv_rows = np.concatenate([np.asarray(x, np.int64) for x in recv_lists]) if sum(recv_counts) else np.zeros(0,
                                                                                                                  np.int64)
     send_perm = send_row if send_row is not None else np.zeros(0, np.int64)
+    src_rank = np.concatenate([np.full(len(x), w, np.int32) for w, x in enumerate(recv_lists)]) if sum(
+        recv_counts) else np.zeros(0, np.int32)
+    src_idx = np.concatenate([np.asarray(x, np.int64) for x in recv_src_idx]) if sum(recv_counts) else np.zeros(
+        0, np.int64)
     return HandoffPlan(torch.from_numpy(np.ascontiguousarray(send_perm)), send_counts, recv_counts,
-                       torch.from_numpy(recv_rows), text_lengths[mesh.tdp_rank] // tp)
+                       torch.from_numpy(recv_rows), text_lengths[mesh.tdp_rank] // tp,
+                       dest_rank=torch.from_numpy((np.zeros(0) if send_dest is None else send_dest).astype(np.int32)),
+                       dest_row=torch.from_numpy((np.zeros(0) if my_drow is None else my_drow).astype(np.int64)),
+                       recv_src_rank=torch.from_numpy(src_rank), recv_src_index=torch.from_numpy(src_idx))
 
 
 class _Splice(torch.autograd.Function):

@@ -32,23 +32,25 @@ class TPContext:
         return cls()
 
 
-def column_parallel_linear(x_shard: torch.Tensor, w: torch.Tensor, b: torch.Tensor | None,
-                           ctx: TPContext) -> torch.Tensor:
-    """[T/tp, K] token shard -> [T, N/tp]: all-gather rows, then ``x @ w^T + b`` with the local weight slice."""
+def column_parallel_linear(x_shard: torch.Tensor, w: torch.Tensor, b: torch.Tensor | None, ctx: TPContext,
+                           norm_w: torch.Tensor | None = None, eps: float = 1e-6, role: str = "qkv") -> torch.Tensor:
+    """[T/tp, K] token shard -> (RMSNorm with ``norm_w``) -> all-gather rows -> ``x @ w^T + b`` with the local
+    weight slice -> [T, N/tp].  ``role`` names the peer-memory buffers of the fused path."""
+    if ctx.size > 1 and ctx.fused is not None and x_shard.is_cuda:
+        return ctx.fused.ag_linear(x_shard, w, b, norm_w=norm_w, eps=eps, role=role)
+    h = x_shard if norm_w is None else F.rmsnorm(x_shard, norm_w, eps)
     if ctx.size == 1:
-        return F.linear(x_shard, w, b)
-    if ctx.fused is not None and x_shard.is_cuda:
-        return ctx.fused.ag_linear(x_shard, w, b)
-    return F.linear(comm.all_gather(x_shard, ctx.group), w, b)
+        return F.linear(h, w, b)
+    return F.linear(comm.all_gather(h, ctx.group), w, b)
 
 
-def row_parallel_linear(x: torch.Tensor, w: torch.Tensor, residual_shard: torch.Tensor | None,
-                        ctx: TPContext) -> torch.Tensor:
+def row_parallel_linear(x: torch.Tensor, w: torch.Tensor, residual_shard: torch.Tensor | None, ctx: TPContext,
+                        role: str = "o") -> torch.Tensor:
     """[T, K/tp] -> [T/tp, N]: partial ``x @ w^T`` summed over ranks and scattered by token rows (+ residual)."""
     if ctx.size == 1:
         return F.linear(x, w, None, residual_shard)
     if ctx.fused is not None and x.is_cuda:
-        return ctx.fused.linear_rs(x, w, residual_shard)
+        return ctx.fused.linear_rs(x, w, residual_shard, role=role)
     y = comm.reduce_scatter(F.linear(x, w), ctx.group)
     return y if residual_shard is None else y + residual_shard
 

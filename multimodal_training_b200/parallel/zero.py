@@ -77,8 +77,14 @@ class ZeroAdamW:
         self.device, self.dtype = p0.device, p0.dtype
         self.native = p0.is_cuda
 
-        self.flat_param = torch.zeros(self.total, dtype=self.dtype, device=self.device)
-        self.flat_grad = torch.zeros(self.total, dtype=self.dtype, device=self.device)
+        self.fz = None
+        if fused is not None and self.native and self.gsize > 1 and self.gsize <= 8:
+            from .fused import FusedZero
+            self.fz = FusedZero(group, self.total, self.device)
+            self.flat_param, self.flat_grad = self.fz.flat_param, self.fz.flat_grad
+        else:
+            self.flat_param = torch.zeros(self.total, dtype=self.dtype, device=self.device)
+            self.flat_grad = torch.zeros(self.total, dtype=self.dtype, device=self.device)
         for p, o in zip(self.params, offsets):
             n = p.numel()
             self.flat_param[o:o + n].copy_(p.data.reshape(-1))
@@ -163,8 +169,6 @@ class ZeroAdamW:
 
         ``grad_scale`` (device scalar or float) multiplies gradients on the fly (clipping); the
         ``grad_divisor`` (data-parallel mean) is folded into it."""
-        if shard is None:
-            shard = self.reduce_gradients()
         self.step_count += 1
         lr = self.lr if lr is None else lr
         if isinstance(grad_scale, torch.Tensor):
@@ -173,8 +177,19 @@ class ZeroAdamW:
             s = (1.0 if grad_scale is None else float(grad_scale)) / self.grad_divisor
             scale_t = None if s == 1.0 else torch.full((1,), s, dtype=torch.float32, device=self.device)
         lo = self.shard_lo
-        p_shard = self.flat_param[lo:lo + self.shard]
         n_decay_local = min(max(self.n_decay - lo, 0), self.shard)
+        if shard is None and self.fz is not None:
+            # one kernel: pull the peers' gradient shards, AdamW, push the parameters to every peer
+            self._finish_grads()
+            if self.partial_grad_group is not None and self.partial_end > self.partial_start and \
+                    comm.group_size(self.partial_grad_group) > 1:
+                dist.all_reduce(self.flat_grad[self.partial_start:self.partial_end], group=self.partial_grad_group)
+            self.fz.step(self.master, self.exp_avg, self.exp_avg_sq, lo, self.shard, n_decay_local, lr, self.betas[0],
+                         self.betas[1], self.eps, self.weight_decay, self.step_count, scale_t, None)
+            return
+        if shard is None:
+            shard = self.reduce_gradients()
+        p_shard = self.flat_param[lo:lo + self.shard]
         F.adamw_step(p_shard, shard, self.master, self.exp_avg, self.exp_avg_sq, n_decay=n_decay_local, lr=lr,
                      beta1=self.betas[0], beta2=self.betas[1], eps=self.eps, weight_decay=self.weight_decay,
                      step=self.step_count, grad_scale=scale_t)

@@ -1,0 +1,188 @@
+"""Peer-memory kernels on ONE GPU: the ranks of a tensor-parallel group are emulated as separate
+buffers of the same device, producers run to completion before any consumer is launched (so no kernel
+ever waits on a kernel that has not been launched), and results are compared with plain PyTorch.
+The multi-GPU behaviour of the same kernels is covered by ``tests/test_gpu_multi.py``."""
+import ctypes
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _mods():
+    from multimodal_training_b200.ops import functional as F
+    from multimodal_training_b200.ops import native as nv
+    from multimodal_training_b200.parallel import fused
+    nv.lib()
+    return F, nv, fused
+
+
+def rel(a, b):
+    return ((a.float() - b.float()).abs().max() / (b.float().abs().max() + 1e-9)).item()
+
+
+def _peerset(fused, bases, flags, my_index):
+    ps = fused.PeerSetC()
+    ps.n = len(bases)
+    for i, (b, f) in enumerate(zip(bases, flags)):
+        ps.base[i] = b.data_ptr()
+        ps.flag[i] = f.data_ptr() + 4 * my_index
+    return ps
+
+
+def test_allgather_gemm_with_fused_rmsnorm():
+    F, nv, fused = _mods()
+    torch.manual_seed(0)
+    tp, rows, K, N = 2, 256, 512, 384
+    x = [torch.randn(rows, K, device=DEV, dtype=torch.bfloat16) for _ in range(tp)]
+    nw = (1 + 0.1 * torch.randn(K, device=DEV)).to(torch.bfloat16)
+    w = [torch.randn(N, K, device=DEV, dtype=torch.bfloat16) * 0.05 for _ in range(tp)]
+    gather = [torch.zeros(tp * rows, K, device=DEV, dtype=torch.bfloat16) for _ in range(tp)]
+    flags = [torch.zeros(8, device=DEV, dtype=torch.int32) for _ in range(tp)]
+    counters = [torch.zeros(1, device=DEV, dtype=torch.int32) for _ in range(tp)]
+    rstd = [torch.empty(rows, device=DEV, dtype=torch.float32) for _ in range(tp)]
+    for r in range(tp):      # producers
+        ps = _peerset(fused, gather, flags, r)
+        nv.call("mmt_rmsnorm_push", x[r].data_ptr(), nw.data_ptr(), rstd[r].data_ptr(), ctypes.byref(ps),
+                counters[r].data_ptr(), 1, r * rows, rows, K, 1e-6, nv.stream())
+    torch.cuda.synchronize()
+    xf = torch.cat(x).float()
+    href = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-6) * nw.float()
+    for r in range(tp):      # consumers
+        assert flags[r][:tp].tolist() == [1] * tp
+        c = fused.GemmCommC()
+        c.ag_flags, c.ag_epoch, c.ag_rows, c.ag_self, c.rs_rows = flags[r].data_ptr(), 1, rows, r, 0
+        nv.lib().mmt_gemm_set_comm(ctypes.byref(c))
+        y = F.gemm(gather[r], w[r])
+        assert rel(gather[r], href) < 1e-2
+        assert rel(y, href @ w[r].float().t()) < 1e-2
+    assert nv.get_error()[0] == 0
+
+
+def test_gemm_reduce_scatter_with_residual():
+    F, nv, fused = _mods()
+    torch.manual_seed(1)
+    tp, T, Kl, N = 2, 512, 256, 640
+    rows = T // tp
+    a = [torch.randn(T, Kl, device=DEV, dtype=torch.bfloat16) for _ in range(tp)]
+    w = [torch.randn(N, Kl, device=DEV, dtype=torch.bfloat16) * 0.05 for _ in range(tp)]
+    res = [torch.randn(rows, N, device=DEV, dtype=torch.bfloat16) for _ in range(tp)]
+    staging = [torch.zeros(tp * rows, N, device=DEV, dtype=torch.bfloat16) for _ in range(tp)]
+    flags = [torch.zeros(8, device=DEV, dtype=torch.int32) for _ in range(tp)]
+    counters = [torch.zeros(1, device=DEV, dtype=torch.int32) for _ in range(tp)]
+    for r in range(tp):      # producers: GEMM epilogues store partial tiles into the owners' staging slots
+        c = fused.GemmCommC()
+        c.ag_flags = None
+        c.rs_rows, c.rs_self, c.rs_ranks, c.rs_epoch = rows, r, tp, 1
+        c.rs_counter = counters[r].data_ptr()
+        for i in range(tp):
+            c.rs_base[i] = staging[i].data_ptr()
+            c.rs_flag[i] = flags[i].data_ptr() + 4 * r
+        nv.lib().mmt_gemm_set_comm(ctypes.byref(c))
+        F.gemm(a[r], w[r], out=staging[r][:T])
+    torch.cuda.synchronize()
+    full = sum(a[r].float() @ w[r].float().t() for r in range(tp))
+    for r in range(tp):      # owners
+        out = torch.empty(rows, N, device=DEV, dtype=torch.bfloat16)
+        nv.call("mmt_rs_reduce", staging[r].data_ptr(), flags[r].data_ptr(), 1, tp, r, res[r].data_ptr(),
+                out.data_ptr(), rows, N, nv.stream())
+        assert rel(out, full[r * rows:(r + 1) * rows] + res[r].float()) < 1.5e-2
+    assert nv.get_error()[0] == 0
+
+
+def test_route_rows_and_wait():
+    F, nv, fused = _mods()
+    torch.manual_seed(2)
+    world, H = 3, 256
+    src = [torch.randn(40 + 8 * r, H, device=DEV, dtype=torch.bfloat16) for r in range(world)]
+    region = [torch.zeros(200, H, device=DEV, dtype=torch.bfloat16) for _ in range(world)]
+    flags = [torch.zeros(8, device=DEV, dtype=torch.int32) for _ in range(world)]
+    counters = [torch.zeros(1, device=DEV, dtype=torch.int32) for _ in range(world)]
+    expect = [torch.zeros(200, H, device=DEV, dtype=torch.bfloat16) for _ in range(world)]
+    nxt = [0] * world
+    for r in range(world):
+        n = src[r].shape[0]
+        dr = torch.randint(0, world, (n,), dtype=torch.int32)
+        drow = torch.empty(n, dtype=torch.int64)
+        for i in range(n):
+            d = int(dr[i])
+            drow[i] = nxt[d]
+            expect[d][nxt[d]] = src[r][i]
+            nxt[d] += 1
+        ps = _peerset(fused, region, flags, r)
+        nv.call("mmt_route_rows", src[r].data_ptr(), dr.to(DEV).data_ptr(), drow.to(DEV).data_ptr(), ctypes.byref(ps),
+                counters[r].data_ptr(), 1, n, H, H, H, nv.stream())
+    torch.cuda.synchronize()
+    for r in range(world):
+        nv.call("mmt_wait_flags", flags[r].data_ptr(), world, -1, 1, nv.stream())
+        assert torch.equal(region[r], expect[r])
+    assert nv.get_error()[0] == 0
+
+
+def test_zero1_adamw_matches_reduce_then_adamw():
+    F, nv, fused = _mods()
+    torch.manual_seed(3)
+    ranks, n = 2, 8 * 4096
+    total = ranks * n
+    grads = [torch.randn(total, device=DEV, dtype=torch.bfloat16) * 0.1 for _ in range(ranks)]
+    p0 = torch.randn(total, device=DEV, dtype=torch.bfloat16)
+    params = [p0.clone() for _ in range(ranks)]
+    gflags = [torch.zeros(8, device=DEV, dtype=torch.int32) for _ in range(ranks)]
+    pflags = [torch.zeros(8, device=DEV, dtype=torch.int32) for _ in range(ranks)]
+    counters = [torch.zeros(1, device=DEV, dtype=torch.int32) for _ in range(ranks)]
+    for r in range(ranks):           # "backward complete" published by everyone first
+        ps = _peerset(fused, grads, gflags, r)
+        nv.call("mmt_publish", ctypes.byref(ps), 1, nv.stream())
+    torch.cuda.synchronize()
+    gsum = sum(g.float() for g in grads)
+    ref_p = p0.clone()
+    for r in range(ranks):
+        lo = r * n
+        master = p0[lo:lo + n].float().clone()
+        m, v = torch.zeros(n, device=DEV), torch.zeros(n, device=DEV)
+        zp = fused.ZeroPeersC()
+        zp.n = ranks
+        for i in range(ranks):
+            zp.grad[i], zp.param[i] = grads[i].data_ptr(), params[i].data_ptr()
+            zp.param_flag[i] = pflags[i].data_ptr() + 4 * r
+        nv.call("mmt_zero1_adamw", ctypes.byref(zp), gflags[r].data_ptr(), 1, r, counters[r].data_ptr(), 1,
+                master.data_ptr(), m.data_ptr(), v.data_ptr(), lo, n, n // 2, 1e-2, 0.9, 0.999, 1e-8, 0.1, 1, None,
+                None, nv.stream())
+        # reference: reduced gradient (bf16 inputs, fp32 sum) then the plain fused AdamW kernel
+        rm = p0[lo:lo + n].float().clone()
+        rmm, rv = torch.zeros(n, device=DEV), torch.zeros(n, device=DEV)
+        rp = p0[lo:lo + n].clone()
+        gs = gsum[lo:lo + n]
+        rmm.mul_(0.9).add_(gs, alpha=0.1)
+        rv.mul_(0.999).addcmul_(gs, gs, value=0.001)
+        upd = (rmm / 0.1) / ((rv / 0.001).sqrt() + 1e-8)
+        wd = torch.zeros(n, device=DEV)
+        wd[: n // 2] = 0.1
+        rm -= 1e-2 * (upd + wd * rm)
+        ref_p[lo:lo + n] = rm.to(torch.bfloat16)
+        assert rel(master, rm) < 1e-5
+    torch.cuda.synchronize()
+    for r in range(ranks):
+        assert pflags[r][:ranks].tolist() == [1] * ranks
+        assert rel(params[r], ref_p) < 1e-2
+    assert nv.get_error()[0] == 0
+
+
+def test_bounded_wait_reports_instead_of_hanging():
+    """A flag that nothing sets: the kernel gives up at its deadline, records where, and the context stays usable."""
+    F, nv, fused = _mods()
+    flags = torch.zeros(8, device=DEV, dtype=torch.int32)
+    nv.lib().mmt_clear_error()
+    nv.call("mmt_wait_flags", flags.data_ptr(), 2, -1, 5, nv.stream())
+    code, where, _, aux = nv.get_error()
+    assert code == 2 and where == 910 and aux == 5
+    nv.lib().mmt_clear_error()
+    x = torch.ones(16, device=DEV)
+    assert float(x.sum()) == 16.0
+    with pytest.raises(RuntimeError):
+        flags.zero_()
+        nv.call("mmt_wait_flags", flags.data_ptr(), 1, -1, 1, nv.stream())
+        nv.raise_on_device_error()
+    assert nv.get_error()[0] == 0
