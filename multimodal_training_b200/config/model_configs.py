@@ -176,7 +176,7 @@ def get_model_config(name_or_path: str) -> VLConfig:
     p = Path(key)
     if p.is_dir():
         p = p / "config.json"
-    if p.is_file():
+    if p.is_file() and p.suffix == ".json":
         cfg = VLConfig.from_dict(json.loads(p.read_text()))
         cfg.name = key
         return cfg

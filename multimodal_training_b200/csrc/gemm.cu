@@ -23,6 +23,7 @@
 // (python/models/qwen2_5_vl/modeling_qwen2_5_vl.py:198-200,334-338,1143-1145,1226-1229).
 #include <cudaTypedefs.h>
 #include <stdio.h>
+#include <string.h>
 
 #include "common.cuh"
 #include "runtime.h"
@@ -46,6 +47,7 @@ struct GemmParams {
   int out_f32;                    // C is float
   float alpha;
   int a_mn, b_mn;                 // operand majors
+  int tma_store;                  // bf16 output leaves through shared memory + TMA stores
   uint32_t mn_lbo, mn_sbo, mn_kstep;  // descriptor constants of MN-major tiles
   MmtErrorWord* ew;
   // --- all-gather consumer (A rows arrive from peers): rows [s*ag_rows, (s+1)*ag_rows) come from rank s and
@@ -76,18 +78,33 @@ struct Cfg {
   static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int kStages = (BN >= 256) ? 4 : (BN >= 192 ? 5 : (BN >= 128 ? 6 : 8));
   static constexpr uint32_t TMEM_COLS = (2 * BN <= 128) ? 128 : (2 * BN <= 256 ? 256 : 512);
-  static constexpr size_t SMEM = 1024 + (size_t)kStages * STAGE_BYTES + (2 * kStages + 4) * 8 + 16;
+  static constexpr uint32_t STORE_BYTES = 2 * BM * 64 * 2;   // two [128 x 64] bf16 staging boxes for TMA stores
+  static constexpr size_t SMEM = 1024 + (size_t)kStages * STAGE_BYTES + STORE_BYTES + (2 * kStages + 4) * 8 + 16;
 };
+
+// Output tensor maps: index 0 for a plain GEMM; one per owner rank for a reduce-scatter producer.
+struct OutMaps {
+  CUtensorMap m[8];
+};
+
+MMT_DEVICE void epi_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+MMT_DEVICE void tma_store_wait_read1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
+
+// byte offset of (row, col) in a [128 x 64] bf16 box with 128-byte rows and the 128B swizzle
+MMT_DEVICE uint32_t store_box_offset(int row, int col) {
+  return (uint32_t)((row >> 3) * 1024 + (row & 7) * 128 + ((((col >> 3) ^ (row & 7)) & 7) << 4) + (col & 7) * 2);
+}
 
 template <int BN>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                  const GemmParams p) {
+                  const __grid_constant__ OutMaps tmC, const GemmParams p) {
   using C_ = Cfg<BN>;
   constexpr int kStages = C_::kStages;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)kStages * C_::STAGE_BYTES);
+  uint8_t* sStore = smem + (size_t)kStages * C_::STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sStore + C_::STORE_BYTES);
   uint64_t* full = bars;
   uint64_t* empty = bars + kStages;
   uint64_t* tfull = bars + 2 * kStages;
@@ -201,6 +218,11 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     // ------------------------------ epilogue ----------------------------------
     const int q = warp & 3;  // tensor-memory lane quadrant this warp may read
     const int row_in_tile = q * 32 + lane;
+    // bf16 results leave through shared memory and TMA stores (full 128-byte rows per request: this is what
+    // makes stores to a peer GPU efficient); fp32 results and ragged reduce-scatter tiles use direct stores
+    const bool tma_out = !p.out_f32 && p.tma_store;
+    const bool issuer = (warp == 2 && lane == 0);
+    int store_group = 0;   // 64-column groups stored so far; the staging box alternates with it
     int acc = 0;
     uint32_t acc_ph = 0;
     for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
@@ -215,6 +237,11 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
+        uint8_t* sbox = sStore + (store_group & 1) * (BM * 64 * 2);
+        if (tma_out && (c & 1) == 0) {
+          if (issuer) tma_store_wait_read1();   // the store that last used this box has read it
+          epi_bar_sync();
+        }
         const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + c * 32);
         tmem_ld_32x32b_x32(taddr, r);
         tmem_wait_ld();
@@ -285,9 +312,27 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_constant
               o.y = pack_bf16x2(v[2], v[3]);
               o.z = pack_bf16x2(v[4], v[5]);
               o.w = pack_bf16x2(v[6], v[7]);
-              *reinterpret_cast<uint4*>(dst) = o;
+              if (tma_out) *reinterpret_cast<uint4*>(sbox + store_box_offset(row_in_tile, (c & 1) * 32 + g * 8)) = o;
+              else *reinterpret_cast<uint4*>(dst) = o;
             }
           }
+        }
+        if (tma_out && (c & 1) == 1) {
+          fence_proxy_async_smem();
+          epi_bar_sync();
+          if (issuer) {
+            const int x = tn * BN + (c >> 1) * 64;
+            if (x < p.N) {
+              if (p.rs_rows) {
+                const int owner = (tm * BM) / p.rs_rows;
+                tma_store_2d(&tmC.m[owner], sbox, x, tm * BM - owner * p.rs_rows);
+              } else {
+                tma_store_2d(&tmC.m[0], sbox, x, tm * BM);
+              }
+            }
+            tma_store_commit();
+          }
+          ++store_group;
         }
       }
       tc_fence_before();
@@ -295,6 +340,10 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       if (lane == 0) mbar_arrive(&tempty[acc]);
       acc ^= 1;
       if (acc == 0) acc_ph ^= 1;
+    }
+    if (tma_out && issuer) {
+      tma_store_wait_all();                                  // every store has been written out
+      asm volatile("fence.proxy.async;" ::: "memory");
     }
   }
 
@@ -330,7 +379,8 @@ bool ensure_encode() {
 uint32_t g_mn_lbo = 8192, g_mn_sbo = 1024, g_mn_kstep = 2048;
 
 template <int BN>
-int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int sms, cudaStream_t st) {
+int launch(const CUtensorMap& ta, const CUtensorMap& tb, const OutMaps& tc, const GemmParams& p, int sms,
+           cudaStream_t st) {
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(gemm_bf16_tcgen05<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -340,7 +390,7 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, in
   }
   const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
   const int grid = tiles < sms ? tiles : sms;
-  gemm_bf16_tcgen05<BN><<<grid, kThreads, Cfg<BN>::SMEM, st>>>(ta, tb, p);
+  gemm_bf16_tcgen05<BN><<<grid, kThreads, Cfg<BN>::SMEM, st>>>(ta, tb, tc, p);
   return (int)cudaGetLastError();
 }
 
@@ -437,12 +487,33 @@ extern "C" int mmt_gemm_bf16(const void* A, const void* B, void* C, const void* 
     if (p.ag_flags && (p.ag_rows <= 0 || a_mn)) return -5;
     if (p.rs_rows && (out_f32 || p.rs_ranks > 8 || p.rs_ranks < 1)) return -6;
   }
+  // output tensor maps for the TMA-store epilogue
+  OutMaps tc;
+  memset(&tc, 0, sizeof(tc));
+  p.tma_store = 0;
+  if (!out_f32) {
+    if (p.rs_rows) {
+      if (p.rs_rows % BM == 0) {
+        p.tma_store = 1;
+        for (int i = 0; i < p.rs_ranks; ++i) {
+          const __nv_bfloat16* base = reinterpret_cast<const __nv_bfloat16*>(p.rs_base[i]) +
+                                      (long)p.rs_self * p.rs_rows * ldc;
+          r = mmt_make_tmap_2d(&tc.m[i], base, (uint64_t)N, (uint64_t)p.rs_rows, (uint64_t)ldc, 64, BM);
+          if (r) return 3000 + r;
+        }
+      }
+    } else {
+      p.tma_store = 1;
+      r = mmt_make_tmap_2d(&tc.m[0], C, (uint64_t)N, (uint64_t)M, (uint64_t)ldc, 64, BM);
+      if (r) return 3000 + r;
+    }
+  }
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   switch (bn) {
-    case 256: return launch<256>(ta, tb, p, sms, st);
-    case 192: return launch<192>(ta, tb, p, sms, st);
-    case 128: return launch<128>(ta, tb, p, sms, st);
-    case 64:  return launch<64>(ta, tb, p, sms, st);
+    case 256: return launch<256>(ta, tb, tc, p, sms, st);
+    case 192: return launch<192>(ta, tb, tc, p, sms, st);
+    case 128: return launch<128>(ta, tb, tc, p, sms, st);
+    case 64:  return launch<64>(ta, tb, tc, p, sms, st);
     default:  return -4;
   }
 }

@@ -43,6 +43,8 @@ def synthetic_sample(cfg: VLConfig, index: int, *, image_size: int, text_tokens:
     labels = input_ids.clone()
     labels[first:first + n_merged] = IGNORE_INDEX
     pixels = None
+    if n_patches == 0:          # text-only sample
+        return Sample(input_ids, labels, None, [], index)
     if with_pixels:
         pixels = torch.randn(n_patches, v.patch_dim, generator=g).to(dtype)
         if pin and torch.cuda.is_available():

@@ -279,8 +279,12 @@ class ActorGroup:
         self.backend = backend or config.get("backend") or self._default_backend()
         seqs = [self.pool.send(i, ("create", self.gid, actor_cls, config, i)) for i in range(num_actors)]
         for i, s in enumerate(seqs):
-            self.pool.wait(i, s)
-        self._setup_process_group()
+            self.pool.wait(i, s, timeout_s=600.0)     # process start-up and imports, not an RPC
+        saved, self.pool.rpc_timeout_s = self.pool.rpc_timeout_s, None
+        try:
+            self._setup_process_group()
+        finally:
+            self.pool.rpc_timeout_s = saved
 
     @staticmethod
     def _default_backend() -> str:

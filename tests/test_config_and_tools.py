@@ -1,0 +1,142 @@
+"""Config loader / CLI overrides / schema validation, checkpoint split+merge tools, LR schedule, grad-norm
+aggregation, vision token calculator, sweep generator."""
+import json
+import math
+import os
+
+import pytest
+import torch
+
+from multimodal_training_b200.cli import compute_vision_tokens, merge_checkpoint, split_checkpoint
+from multimodal_training_b200.config.loader import ConfigError, load_config, parse_cli, trainer_configs
+from multimodal_training_b200.config.model_configs import VLConfig, get_model_config
+from multimodal_training_b200.parallel.zero import lr_at
+
+pytestmark = pytest.mark.cpu_only
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_sample_yaml_loads_through_the_hydra_style_cli():
+    cfg, ns = parse_cli(["--config-path", os.path.join(ROOT, "configs"), "--config-name", "sample",
+                         "training.batch_size=2", "text.parallelism=autotp", "+data.synthetic.image_size=448"])
+    assert cfg["training"]["batch_size"] == 2 and cfg["text"]["parallelism"] == "autotp"
+    assert cfg["data"]["synthetic"] == {"image_size": 448}
+    v, t = trainer_configs(cfg)
+    assert v["sequence_parallel_size"] == 8 and t["autotp_size"] == 8 and v["mesh_sp"] == 8 and t["mesh_tp"] == 8
+    assert v["learning_rate"] == 5e-5 and "reduce_bucket_size" in v and v["datasets"] == ["laion_pop_train"]
+
+
+@pytest.mark.parametrize("ov", ["vision.parallelism=ring", "text.dtype=int8", "training.batch_size=0",
+                                "training.gradient_accumulation_steps=4", "vision.model_type=llava",
+                                "nosuch.key=1", "justakey"])
+def test_invalid_configs_are_rejected(ov):
+    with pytest.raises(ConfigError):
+        load_config(None, [ov])
+
+
+def test_embedded_model_configs():
+    c7, c32 = get_model_config("Qwen/Qwen2.5-VL-7B-Instruct"), get_model_config("qwen2_5_vl_32b")
+    assert (c7.text.hidden_size, c7.text.num_hidden_layers, c7.text.num_key_value_heads) == (3584, 28, 4)
+    assert (c32.text.hidden_size, c32.text.num_hidden_layers, c32.vision.out_hidden_size) == (5120, 64, 5120)
+    assert c7.vision.fullatt_block_indexes == [7, 15, 23, 31] and c7.vision.head_dim == 80
+    assert c7.vision.padded_intermediate_size % 8 == 0
+    rt = VLConfig.from_dict(json.loads(json.dumps(c7.to_dict())))
+    assert rt.text == c7.text and rt.vision == c7.vision
+    with pytest.raises(KeyError):
+        get_model_config("no-such-model")
+
+
+def test_lr_schedule_matches_warmup_then_cosine():
+    kw = dict(base_lr=1.0, total_steps=100, warmup_steps=10)
+    assert lr_at(0, **kw) == 0 and lr_at(5, **kw) == 0.5 and lr_at(10, **kw) == 1.0
+    assert abs(lr_at(55, **kw) - 0.5) < 1e-9 and lr_at(100, **kw) < 1e-9
+    assert lr_at(50, kind="linear", **kw) == pytest.approx(1 - 40 / 90)
+    assert lr_at(50, kind="constant", **kw) == 1.0
+
+
+def test_aggregate_grad_norms():
+    from multimodal_training_b200.train import aggregate_grad_norms
+    v = [{"type": "sequence", "sharded": 1.0, "replicated": 0.0}, {"type": "sequence", "sharded": 3.0}]
+    t = [{"type": "tensor", "sharded": 2.0, "replicated": 4.0, "tp_size": 2},
+         {"type": "tensor", "sharded": 2.0, "replicated": 4.0, "tp_size": 2}]
+    assert aggregate_grad_norms(v, t) == pytest.approx(math.sqrt(1 + 3 + 2 + 2 + 4))
+
+
+def _fake_text_sd(H=8, I=12, V=16, L=2):
+    g = torch.Generator().manual_seed(0)
+    sd = {"embed_tokens.weight": torch.randn(V, H, generator=g), "norm.weight": torch.ones(H),
+          "lm_head.weight": torch.randn(V, H, generator=g)}
+    for i in range(L):
+        p = f"layers.{i}."
+        for n, shape in [("self_attn.q_proj.weight", (H, H)), ("self_attn.k_proj.weight", (H // 2, H)),
+                         ("self_attn.v_proj.weight", (H // 2, H)), ("self_attn.o_proj.weight", (H, H)),
+                         ("mlp.gate_proj.weight", (I, H)), ("mlp.up_proj.weight", (I, H)),
+                         ("mlp.down_proj.weight", (H, I)), ("self_attn.q_proj.bias", (H,)),
+                         ("self_attn.k_proj.bias", (H // 2,)), ("self_attn.v_proj.bias", (H // 2,))]:
+            sd[p + n] = torch.randn(*shape, generator=g)
+        sd[p + "input_layernorm.weight"] = torch.ones(H)
+        sd[p + "post_attention_layernorm.weight"] = torch.ones(H)
+    return sd
+
+
+def _shard(sd, tp, r):
+    out = {}
+    for k, v in sd.items():
+        if any(s in k for s in ("o_proj.weight", "down_proj.weight")):
+            out[k] = v.chunk(tp, dim=1)[r].clone()
+        elif "layernorm" in k or k == "norm.weight":
+            out[k] = v.clone()
+        else:
+            out[k] = v.chunk(tp, dim=0)[r].clone()
+    return out
+
+
+def test_split_train_merge_round_trip(tmp_path):
+    text = _fake_text_sd()
+    vision = {"patch_embed.proj.weight": torch.randn(4, 3, 2, 2, 2), "merger.ln_q.weight": torch.ones(4)}
+    for n in "qkv":
+        vision[f"blocks.0.attn.{n}.weight"] = torch.randn(4, 4)
+        vision[f"blocks.0.attn.{n}.bias"] = torch.randn(4)
+    full = {**{"model.visual." + k: v for k, v in vision.items()},
+            **{"model.language_model." + k: v for k, v in text.items() if not k.startswith("lm_head")},
+            "lm_head.weight": text["lm_head.weight"]}
+    src = tmp_path / "full.pt"
+    torch.save(full, src)
+    split_dir = split_checkpoint.split_checkpoint(str(src), str(tmp_path / "split"))
+    vs = torch.load(os.path.join(split_dir, "vision_model.pt"))["model"]
+    ts = torch.load(os.path.join(split_dir, "text_model.pt"))["model"]
+    assert set(vs) == set(vision) and set(ts) == set(text)
+    assert os.path.exists(os.path.join(split_dir, "split_metadata.json"))
+    # "training" with tp=2: save per-rank shards in the epoch layout, then merge
+    ck = tmp_path / "ckpt" / "epoch_0"
+    for r in range(2):
+        os.makedirs(ck / "vision", exist_ok=True)
+        os.makedirs(ck / "text", exist_ok=True)
+        torch.save({"model": vs}, ck / "vision" / f"rank_{r}.pt")
+        torch.save({"model": _shard(ts, 2, r)}, ck / "text" / f"rank_{r}.pt")
+    out = merge_checkpoint.merge_checkpoint(str(ck), str(tmp_path / "merged"), "tiny", 2)
+    merged = torch.load(os.path.join(out, "pytorch_model.bin"))
+    for k, v in text.items():
+        key = k if k.startswith("lm_head") else "language_model." + k
+        assert torch.equal(merged[key], v), k
+    qkv = torch.cat([vision[f"blocks.0.attn.{n}.weight"] for n in "qkv"])
+    assert torch.equal(merged["visual.blocks.0.attn.qkv.weight"], qkv)      # re-fused for stock HF
+    assert "visual.blocks.0.attn.q.weight" not in merged
+    assert json.load(open(os.path.join(out, "merge_metadata.json")))["vision_qkv"] == "fused"
+
+
+def test_vision_token_calculator_and_sweep_generator(tmp_path, capsys):
+    assert compute_vision_tokens.vision_tokens(896)["patches"] == 4096
+    assert compute_vision_tokens.vision_tokens(3584)["merged_tokens"] == 16384
+    assert compute_vision_tokens.main([]) == 0 and "65536" in capsys.readouterr().out
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("gen", os.path.join(ROOT, "experiments", "generate_configs.py"))
+    gen = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(gen)
+    assert gen.main(["--output-dir", str(tmp_path / "sweep"), "--synthetic"]) == 0
+    names = (tmp_path / "sweep" / "manifest.txt").read_text().split()
+    assert len(names) == 2 * 6 * 2 * 4
+    cfg = load_config(tmp_path / "sweep" / "configs" / (names[0] + ".yaml"))
+    assert cfg["data"]["force_fixed_size"] and cfg["data"]["synthetic"]["image_size"] == 448
+    big = load_config(tmp_path / "sweep" / "configs" / "32b_64k_tokens_sequence_bs2.yaml")
+    assert big["deepspeed"]["reduce_bucket_size"] == 100000000 and big["training"]["parallel_size"] == 8

@@ -102,6 +102,7 @@ def test_route_rows_and_wait():
     counters = [torch.zeros(1, device=DEV, dtype=torch.int32) for _ in range(world)]
     expect = [torch.zeros(200, H, device=DEV, dtype=torch.bfloat16) for _ in range(world)]
     nxt = [0] * world
+    keep = []
     for r in range(world):
         n = src[r].shape[0]
         dr = torch.randint(0, world, (n,), dtype=torch.int32)
@@ -112,7 +113,9 @@ def test_route_rows_and_wait():
             expect[d][nxt[d]] = src[r][i]
             nxt[d] += 1
         ps = _peerset(fused, region, flags, r)
-        nv.call("mmt_route_rows", src[r].data_ptr(), dr.to(DEV).data_ptr(), drow.to(DEV).data_ptr(), ctypes.byref(ps),
+        dr_d, drow_d = dr.to(DEV), drow.to(DEV)      # keep the device copies alive across the launch
+        keep.append((dr_d, drow_d))
+        nv.call("mmt_route_rows", src[r].data_ptr(), dr_d.data_ptr(), drow_d.data_ptr(), ctypes.byref(ps),
                 counters[r].data_ptr(), 1, n, H, H, H, nv.stream())
     torch.cuda.synchronize()
     for r in range(world):

@@ -1,0 +1,158 @@
+"""Actor runtime: ActorGroup calling convention, collocation on shared hosts, object refs, failure detection
+(host side only: an actor that raises, a host process that exits, an RPC deadline), logging, tensor transfer,
+and the driver loop end to end on CPU (gloo) with checkpoint + resume."""
+import logging
+import os
+import time
+
+import pytest
+import torch
+
+from multimodal_training_b200.runtime.actor import RayActor
+from multimodal_training_b200.runtime.actor_group import (ActorDiedError, ActorGroup, ActorTimeoutError, RemoteError,
+                                                          get)
+
+pytestmark = pytest.mark.integration
+
+
+class Echo(RayActor):
+    def __init__(self, config, rank):
+        super().__init__()
+        self.config, self.rank, self.store = config, rank, {}
+
+    def whoami(self):
+        return {"rank": self.rank, "pid": os.getpid(), "env_rank": os.environ.get("RANK"),
+                "world": os.environ.get("WORLD_SIZE"), "port": os.environ.get("MASTER_PORT")}
+
+    def add(self, a, b=0):
+        return a + b + self.rank
+
+    def make_tensor(self, n):
+        return {"t": torch.full((n,), float(self.rank)), "tag": self.config.get("tag")}
+
+    def consume(self, obj, k):
+        return float(obj["t"].sum()) + k
+
+    def boom(self):
+        raise ValueError("kaboom")
+
+    def die(self):
+        os._exit(3)
+
+    def sleep(self, s):
+        time.sleep(s)
+        return s
+
+
+def test_scatter_broadcast_and_shared_world():
+    g = ActorGroup({"tag": "a", "runtime": "builtin"}, Echo, 2, backend="gloo")
+    try:
+        info = g.execute_all("whoami")
+        assert [i["rank"] for i in info] == [0, 1] and [i["env_rank"] for i in info] == ["0", "1"]
+        assert info[0]["world"] == "2" and info[0]["port"] == info[1]["port"]
+        assert g.execute_all("add", 10, b=1) == [11, 12]                 # broadcast
+        assert g.execute_all("add", [10, 20], b=[1, 2]) == [11, 23]      # every arg is a list of length N: scatter
+        # a list mixed with a scalar is NOT scattered (reference rule): the whole list is broadcast
+        with pytest.raises(RemoteError, match="TypeError"):
+            g.execute_all("add", [10, 20], b=1)
+    finally:
+        g.shutdown()
+
+
+def test_collocated_groups_share_hosts_and_refs_resolve_locally():
+    g1 = ActorGroup({"tag": "vision", "runtime": "builtin"}, Echo, 2, collocate=True, backend="gloo")
+    g2 = ActorGroup({"tag": "text", "runtime": "builtin"}, Echo, 2, collocate=True,
+                    placement_group_handle=g1.placement_group_handle)
+    try:
+        p1, p2 = g1.execute_all("whoami"), g2.execute_all("whoami")
+        assert [a["pid"] for a in p1] == [b["pid"] for b in p2]          # actor i of both groups: one process
+        assert p1[0]["port"] == p2[0]["port"]                            # one torch.distributed world
+        refs = g1.execute_all_async("make_tensor", 4)
+        out = g2.execute_all("consume", refs, [1, 2])                    # refs + list: scattered, resolved on host
+        assert out == [1.0, 6.0]
+        fetched = get(refs)
+        assert fetched[1]["tag"] == "vision" and fetched[1]["t"].tolist() == [1.0] * 4
+    finally:
+        g1.shutdown()
+
+
+def test_actor_exception_is_reported_and_the_group_survives():
+    g = ActorGroup({"runtime": "builtin"}, Echo, 2, backend="gloo")
+    try:
+        with pytest.raises(RemoteError, match="kaboom"):
+            g.execute_all("boom")
+        assert g.execute_all("add", 1) == [1, 2]
+    finally:
+        g.shutdown()
+
+
+def test_dead_host_and_rpc_deadline_are_detected():
+    g = ActorGroup({"runtime": "builtin"}, Echo, 2, backend="gloo", rpc_timeout_s=1.0)
+    try:
+        with pytest.raises(ActorTimeoutError):
+            g.execute_all("sleep", 3.0)
+        time.sleep(2.5)
+        refs = g.execute_all_async("die")
+        with pytest.raises((ActorDiedError, RemoteError)):
+            get(refs, timeout_s=20)
+    finally:
+        g.shutdown()
+
+
+def test_tensor_transfer_local_and_copy():
+    from multimodal_training_b200.runtime.tensor_transfer import (TensorTransferRequest,
+                                                                  prepare_tensor_for_transfer, receive_tensor)
+    t = torch.arange(6.0).reshape(2, 3)
+    req = prepare_tensor_for_transfer(t)
+    assert req.transport == "local" and receive_tensor(req.to_dict()) is t
+    req = prepare_tensor_for_transfer(t, receiver_gpu_ids=["cpu"], same_process=False)
+    assert req.transport == "copy" and torch.equal(receive_tensor(TensorTransferRequest.from_dict(req.to_dict())), t)
+
+
+def test_setup_logging_is_idempotent(tmp_path, monkeypatch):
+    from multimodal_training_b200.runtime import logger
+    monkeypatch.setenv("RAY_TRAIN_LOG_FILE", str(tmp_path / "train.log"))
+    root = logger.setup_logging(force=True)
+    n = len(root.handlers)
+    logger.setup_logging()
+    assert len(root.handlers) == n
+    logging.getLogger("x").info("hello")
+    for h in root.handlers:
+        h.flush()
+    assert "hello" in (tmp_path / "train.log").read_text()
+    logger.setup_logging(force=True, log_file="/tmp/ray_train.log")
+
+
+def _cfg(tmp_path, **over):
+    from multimodal_training_b200.config.loader import load_config
+    ov = ["vision.model_name=tiny", "text.model_name=tiny", "vision.dtype=float32", "text.dtype=float32",
+          "vision.parallelism=sequence", "text.parallelism=tensor", "training.parallel_size=2",
+          "training.batch_size=2", "training.num_iterations=3", "training.num_epochs=1", "training.warmup_steps=1",
+          "training.learning_rate=1e-3", "training.warmup_ratio=0", "training.lr_scheduler_type=constant",
+          "+training.device=cpu", "training.backend=gloo", "training.runtime=builtin", "training.clip_grad_norm=true",
+          "training.no_checkpoint=false", f"training.checkpoint_dir={tmp_path / 'ckpt'}",
+          "+data.synthetic.image_size=224", "+data.synthetic.text_tokens=64", "+data.synthetic.global_batch=2",
+          "+data.synthetic.repeat=1"]
+    return load_config(None, ov + [f"{k}={v}" for k, v in over.items()])
+
+
+def test_driver_trains_checkpoints_and_resumes(tmp_path, caplog):
+    from multimodal_training_b200 import train
+    from multimodal_training_b200.checkpoint import find_latest_checkpoint
+    res = train.main(_cfg(tmp_path))
+    assert res["steps"] == 3 and res["losses"][-1] < res["losses"][0]
+    ck = tmp_path / "ckpt"
+    assert find_latest_checkpoint(str(ck)) == 0
+    for half in ("vision", "text"):
+        for r in range(2):
+            assert (ck / "epoch_0" / half / f"rank_{r}.pt").exists()
+    assert (ck / "epoch_0" / "metadata.json").exists()
+    sd = torch.load(ck / "epoch_0" / "text" / "rank_1.pt")["model"]
+    assert "layers.0.self_attn.q_proj.weight" in sd and sd["layers.0.mlp.down_proj.weight"].shape == (256, 344)
+    # resume: epoch 0 is done, so a 2-epoch run continues at epoch 1 from the saved weights
+    res2 = train.main(_cfg(tmp_path, **{"training.num_epochs": 2}))
+    assert res2["steps"] == 6 and len(res2["losses"]) == 3
+    assert res2["losses"][0] < res["losses"][0]
+    assert find_latest_checkpoint(str(ck)) == 1
+    log = open("/tmp/ray_train.log").read() if os.path.exists("/tmp/ray_train.log") else ""
+    assert "Training completed!" in log and "avg" in log

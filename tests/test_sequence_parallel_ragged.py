@@ -1,0 +1,100 @@
+"""Ragged sequence-parallel utilities: window order, window-aligned cuts, pack/pad round trips, local rope,
+exchange permutations (modelled on the reference's tests/test_sequence_parallel_ragged.py, with asserts)."""
+import numpy as np
+import pytest
+import torch
+
+from multimodal_training_b200.parallel.sp import (RaggedSequenceMeta, build_local_rope, build_vision_plan,
+                                                  compute_geometry, pad_pack_to_batch, rebuild_local_cu_seqlens,
+                                                  split_pack_by_sp, token_cut_positions, unpad_batch_to_pack,
+                                                  window_cut_positions, window_index)
+
+pytestmark = pytest.mark.cpu_only
+
+
+def test_window_index_16x16_has_four_full_windows_and_no_empty_ones():
+    idx, cu = window_index([(1, 16, 16)], 2, 112, 14)
+    assert cu == [0, 64, 128, 192, 256]
+    assert sorted(idx.tolist()) == list(range(64))
+    assert idx[:4].tolist() == [0, 1, 2, 3] and idx[4:8].tolist() == [8, 9, 10, 11]
+
+
+def test_window_index_ragged_grid_keeps_partial_windows():
+    idx, cu = window_index([(1, 20, 12)], 2, 112, 14)      # merged grid 10 x 6 -> windows 4x4, 4x2, ... , 2x2
+    lens = np.diff(cu)
+    assert lens.sum() == 20 * 12 and (lens > 0).all()
+    assert sorted(idx.tolist()) == list(range(60))
+
+
+def test_token_cuts_give_remainder_to_low_ranks():
+    assert token_cut_positions(10, 4) == [0, 3, 6, 8, 10]
+    assert token_cut_positions(8, 4) == [0, 2, 4, 6, 8]
+
+
+def test_window_cuts_fall_on_boundaries_and_leave_no_rank_empty():
+    b = [0, 64, 128, 192, 256, 320]
+    cuts = window_cut_positions(b, 4)
+    assert cuts[0] == 0 and cuts[-1] == 320 and all(c in b for c in cuts)
+    assert all(y > x for x, y in zip(cuts, cuts[1:]))
+    assert window_cut_positions([0, 64, 128, 192, 256], 2) == [0, 128, 256]
+
+
+def test_split_even_uneven_and_windowed():
+    pack = torch.arange(30).float().unsqueeze(1)
+    cu = [0, 10, 30]
+    parts = [split_pack_by_sp(pack, cu, 3, r) for r in range(3)]
+    assert [p[1].local_lengths for p in parts] == [[4, 7], [3, 7], [3, 6]]
+    back = []
+    for s in range(2):
+        for r in range(3):
+            lo = parts[r][1].local_offsets[s]
+            back.append(parts[r][0][lo:lo + parts[r][1].local_lengths[s]])
+    assert torch.equal(torch.cat(back), pack)
+    wl, wm = split_pack_by_sp(torch.arange(256).float().unsqueeze(1), [0, 256], 2, 1, [0, 64, 128, 192, 256])
+    assert wm.local_lengths == [128] and wm.local_starts == [128] and wl[0, 0] == 128
+
+
+def test_pad_unpad_round_trip_and_cu_seqlens():
+    pack = torch.randn(9, 3)
+    lengths = [4, 0, 5]
+    batch, mask = pad_pack_to_batch(pack, lengths)
+    assert batch.shape == (3, 5, 3) and mask.sum() == 9 and not mask[1].any()
+    assert torch.equal(unpad_batch_to_pack(batch, lengths), pack)
+    cu = rebuild_local_cu_seqlens(lengths)
+    assert cu.dtype == torch.int32 and cu.tolist() == [0, 4, 4, 9]
+
+
+def test_build_local_rope_slices_every_sample():
+    cos, sin = torch.arange(20).float().unsqueeze(1), -torch.arange(20).float().unsqueeze(1)
+    meta = RaggedSequenceMeta([3, 4], [8, 12], [5, 0], 2, 1)
+    c, s = build_local_rope(cos, sin, [0, 8, 20], meta)
+    assert c.flatten().tolist() == [5, 6, 7, 8, 9, 10, 11] and torch.equal(s, -c)
+
+
+@pytest.mark.parametrize("grids,sp", [([(1, 16, 16), (1, 32, 24)], 2), ([(1, 64, 64)] * 2, 4), ([(1, 32, 32)], 1)])
+def test_plan_partitions_tokens_and_exchange_is_a_permutation(grids, sp):
+    geom = compute_geometry(grids, sp=sp)
+    plans = [build_vision_plan(None, sp=sp, rank=r, head_dim=32, geom=geom) for r in range(sp)]
+    total = sum(t * h * w for t, h, w in grids)
+    all_patches = torch.cat([p.local_patch_index for p in plans])
+    assert sorted(all_patches.tolist()) == list(range(total))
+    merged = torch.cat([p.local_merged_ids for p in plans])
+    assert sorted(merged.tolist()) == list(range(total // 4))
+    for p in plans:
+        assert p.win_cu[0] == 0 and p.win_cu[-1] == p.local_tokens
+        assert all(b > a for a, b in zip(p.win_cu, p.win_cu[1:]))
+        assert p.local_tokens % 4 == 0 and p.local_cos.shape == (p.local_tokens, 32)
+        if sp > 1:
+            assert sorted(p.to_image_major.tolist()) == list(range(total))
+            assert torch.equal(p.to_image_major[p.to_rank_major], torch.arange(total))
+    if sp > 1:
+        # rows in exchange order are (rank, image); after the permutation every image is contiguous
+        owner_image = torch.cat([torch.cat([torch.full((n,), b) for b, (_, n) in enumerate(p.per_image_local)])
+                                 for p in plans])
+        im = owner_image[plans[0].to_image_major]
+        assert (im[1:] >= im[:-1]).all()
+
+
+def test_rank_without_tokens_is_an_error():
+    with pytest.raises(ValueError):
+        build_vision_plan([(1, 8, 8)], sp=8, rank=0, head_dim=32)
