@@ -256,6 +256,46 @@ __global__ void __launch_bounds__(256) zero1_adamw_kernel(ZeroPeers zp, const in
   publish_when_last(counter, ps, param_epoch);
 }
 
+// ----------------------------------------------------------------------------
+// Ulysses exchange (sequence <-> heads) as direct peer stores.
+//   to_heads:  src [rows, parts, groups, W] (token-major rows of this rank, all heads) ->
+//              peer g's buffer [T_all, parts, W] at row dst_row[r]: group g's heads of every part
+//   to_tokens: src [T_all, parts, W] (all rows, this rank's heads) ->
+//              owner's buffer [rows_owner, parts, groups, W] at (row_local[r], part, my group)
+// One warp per (row, part, group) segment of W elements (W % 8 == 0).
+// ----------------------------------------------------------------------------
+__global__ void ulysses_to_heads_kernel(const bf16* __restrict__ src, const int* __restrict__ dst_row, PeerSet ps,
+                                        int* counter, int epoch, long rows, int parts, int groups, int W) {
+  const long seg = blockIdx.x * (long)(blockDim.x >> 5) + (threadIdx.x >> 5);
+  const long nseg = rows * parts * groups;
+  if (seg < nseg) {
+    const int lane = threadIdx.x & 31;
+    const int g = (int)(seg % groups);
+    const int pt = (int)((seg / groups) % parts);
+    const long r = seg / ((long)groups * parts);
+    const bf16* s = src + ((r * parts + pt) * groups + g) * (long)W;
+    bf16* d = reinterpret_cast<bf16*>(ps.base[g]) + ((long)dst_row[r] * parts + pt) * W;
+    for (int c = lane * 8; c < W; c += 256) *reinterpret_cast<uint4*>(d + c) = *reinterpret_cast<const uint4*>(s + c);
+  }
+  publish_when_last(counter, ps, epoch);
+}
+
+__global__ void ulysses_to_tokens_kernel(const bf16* __restrict__ src, const int* __restrict__ owner,
+                                         const int* __restrict__ row_local, PeerSet ps, int* counter, int epoch,
+                                         long rows, int parts, int groups, int my_group, int W) {
+  const long seg = blockIdx.x * (long)(blockDim.x >> 5) + (threadIdx.x >> 5);
+  const long nseg = rows * parts;
+  if (seg < nseg) {
+    const int lane = threadIdx.x & 31;
+    const int pt = (int)(seg % parts);
+    const long r = seg / parts;
+    const bf16* s = src + (r * parts + pt) * (long)W;
+    bf16* d = reinterpret_cast<bf16*>(ps.base[owner[r]]) + (((long)row_local[r] * parts + pt) * groups + my_group) * W;
+    for (int c = lane * 8; c < W; c += 256) *reinterpret_cast<uint4*>(d + c) = *reinterpret_cast<const uint4*>(s + c);
+  }
+  publish_when_last(counter, ps, epoch);
+}
+
 // Publishes an epoch to all peers (e.g. "my backward pass is complete") without moving data.
 __global__ void publish_kernel(PeerSet ps, int epoch) {
   __threadfence_system();
@@ -326,6 +366,28 @@ int mmt_wait_flags(const int* flags, int n, int self, int epoch, void* stream) {
 
 int mmt_publish(const MmtPeerSet* peers, int epoch, void* stream) {
   publish_kernel<<<1, 32, 0, ST(stream)>>>(to_ps(peers), epoch);
+  return (int)cudaGetLastError();
+}
+
+int mmt_ulysses_to_heads(const void* src, const int* dst_row, const MmtPeerSet* peers, int* counter, int epoch,
+                         long rows, int parts, int groups, int W, void* stream) {
+  if (W % 8 || peers->n != groups) return -2;
+  const long nseg = rows * parts * groups;
+  const long blocks = nseg > 0 ? (nseg + 7) / 8 : 1;
+  ulysses_to_heads_kernel<<<(unsigned)blocks, 256, 0, ST(stream)>>>(reinterpret_cast<const bf16*>(src), dst_row,
+                                                                   to_ps(peers), counter, epoch, rows, parts, groups, W);
+  return (int)cudaGetLastError();
+}
+
+int mmt_ulysses_to_tokens(const void* src, const int* owner, const int* row_local, const MmtPeerSet* peers,
+                          int* counter, int epoch, long rows, int parts, int groups, int my_group, int W,
+                          void* stream) {
+  if (W % 8 || peers->n != groups) return -2;
+  const long nseg = rows * parts;
+  const long blocks = nseg > 0 ? (nseg + 7) / 8 : 1;
+  ulysses_to_tokens_kernel<<<(unsigned)blocks, 256, 0, ST(stream)>>>(reinterpret_cast<const bf16*>(src), owner,
+                                                                    row_local, to_ps(peers), counter, epoch, rows,
+                                                                    parts, groups, my_group, W);
   return (int)cudaGetLastError();
 }
 

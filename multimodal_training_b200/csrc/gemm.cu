@@ -65,21 +65,29 @@ struct GemmParams {
 
 // tile index -> (tile_m, tile_n); with an all-gather consumer the m tiles are rotated so that the CTA wave
 // starts on this rank's own rows while the peers' rows are still in flight.
-MMT_DEVICE void tile_coords(const GemmParams& p, int tile, int tiles_m, int& tm, int& tn) {
+MMT_DEVICE void tile_coords(const GemmParams& p, int tile, int tiles_m, int bmt, int& tm, int& tn) {
   tm = tile % tiles_m;
   tn = tile / tiles_m;
-  if (p.ag_flags) tm = (tm + (int)(((long)p.ag_self * p.ag_rows) / BM)) % tiles_m;
+  if (p.ag_flags) tm = (tm + (int)(((long)p.ag_self * p.ag_rows) / bmt)) % tiles_m;
 }
 
-template <int BN>
+// MT = number of 128-row accumulators per CTA tile.  MT == 1: 128 x BN tile, the accumulator is double
+// buffered in tensor memory (epilogue of tile i overlaps the main loop of tile i+1).  MT == 2: 256 x BN tile,
+// both halves share every B tile in shared memory (a third less L2 -> shared-memory traffic per flop, which is
+// what bounds the MT == 1 kernel); the two halves fill tensor memory, so the epilogue overlaps the next tile
+// half by half.
+template <int BN, int MT>
 struct Cfg {
-  static constexpr uint32_t A_BYTES = BM * BK * 2;
+  static constexpr int BMT = BM * MT;
+  static constexpr uint32_t A_BYTES = BMT * BK * 2;
   static constexpr uint32_t B_BYTES = BN * BK * 2;
   static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int kStages = (BN >= 256) ? 4 : (BN >= 192 ? 5 : (BN >= 128 ? 6 : 8));
-  static constexpr uint32_t TMEM_COLS = (2 * BN <= 128) ? 128 : (2 * BN <= 256 ? 256 : 512);
   static constexpr uint32_t STORE_BYTES = 2 * BM * 64 * 2;   // two [128 x 64] bf16 staging boxes for TMA stores
+  static constexpr int kStages = (int)((227u * 1024u - 2048u - STORE_BYTES) / STAGE_BYTES) > 8
+                                     ? 8 : (int)((227u * 1024u - 2048u - STORE_BYTES) / STAGE_BYTES);
+  static constexpr uint32_t TMEM_COLS = (2 * BN <= 128) ? 128 : (2 * BN <= 256 ? 256 : 512);
   static constexpr size_t SMEM = 1024 + (size_t)kStages * STAGE_BYTES + STORE_BYTES + (2 * kStages + 4) * 8 + 16;
+  static_assert(MT == 1 || 2 * BN <= 512, "two accumulators must fit tensor memory");
 };
 
 // Output tensor maps: index 0 for a plain GEMM; one per owner rank for a reduce-scatter producer.
@@ -95,25 +103,26 @@ MMT_DEVICE uint32_t store_box_offset(int row, int col) {
   return (uint32_t)((row >> 3) * 1024 + (row & 7) * 128 + ((((col >> 3) ^ (row & 7)) & 7) << 4) + (col & 7) * 2);
 }
 
-template <int BN>
+template <int BN, int MT>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                   const __grid_constant__ OutMaps tmC, const GemmParams p) {
-  using C_ = Cfg<BN>;
+  using C_ = Cfg<BN, MT>;
   constexpr int kStages = C_::kStages;
+  constexpr int BMT = C_::BMT;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sStore = smem + (size_t)kStages * C_::STAGE_BYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(sStore + C_::STORE_BYTES);
   uint64_t* full = bars;
   uint64_t* empty = bars + kStages;
-  uint64_t* tfull = bars + 2 * kStages;
-  uint64_t* tempty = tfull + 2;
+  uint64_t* tfull = bars + 2 * kStages;   // [2]: accumulator slot filled
+  uint64_t* tempty = tfull + 2;           // [2]: accumulator slot drained
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int tiles_m = (p.M + BM - 1) / BM;
+  const int tiles_m = (p.M + BMT - 1) / BMT;
   const int tiles_n = (p.N + BN - 1) / BN;
   const int ntiles = tiles_m * tiles_n;
   const int KB = (p.K + BK - 1) / BK;
@@ -149,9 +158,9 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       uint32_t ag_seen = p.ag_flags ? (1u << p.ag_self) : 0u;
       for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
         int tm, tn;
-        tile_coords(p, tile, tiles_m, tm, tn);
+        tile_coords(p, tile, tiles_m, BMT, tm, tn);
         if (p.ag_flags) {
-          const int r0 = tm * BM, r1 = min(r0 + BM, p.M) - 1;
+          const int r0 = tm * BMT, r1 = min(r0 + BMT, p.M) - 1;
           for (int src = r0 / p.ag_rows; src <= r1 / p.ag_rows && ok; ++src) {
             if (ag_seen & (1u << src)) continue;
             ok = flag_wait_ge(&p.ag_flags[src], p.ag_epoch, MMT_WAIT_NS, p.ew, 110);
@@ -166,10 +175,10 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           uint8_t* sB = sA + C_::A_BYTES;
           mbar_expect_tx(&full[s], C_::STAGE_BYTES);
           if (!p.a_mn) {
-            tma_load_2d(sA, &tmA, &full[s], kb * BK, tm * BM);
+            tma_load_2d(sA, &tmA, &full[s], kb * BK, tm * BMT);      // one box of BMT rows
           } else {
 #pragma unroll
-            for (int c = 0; c < BM / 64; ++c) tma_load_2d(sA + c * 8192, &tmA, &full[s], tm * BM + c * 64, kb * BK);
+            for (int c = 0; c < BMT / 64; ++c) tma_load_2d(sA + c * 8192, &tmA, &full[s], tm * BMT + c * 64, kb * BK);
           }
           if (!p.b_mn) {
             tma_load_2d(sB, &tmB, &full[s], kb * BK, tn * BN);
@@ -186,32 +195,51 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     if (lane == 0) {
       const uint32_t idesc = make_idesc_bf16(BM, BN, p.a_mn, p.b_mn);
       int s = 0, acc = 0;
-      uint32_t ph = 0, acc_ph = 0;
+      uint32_t ph = 0, acc_ph = 0;   // MT == 1: acc alternates per tile; MT == 2: slots 0/1 are the halves
       bool ok = true;
       for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
-        if (!mbar_wait(&tempty[acc], acc_ph ^ 1, p.ew, 200)) { ok = false; break; }
-        tc_fence_after();
-        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
-        for (int kb = 0; kb < KB; ++kb) {
+        if (MT == 1) {
+          if (!mbar_wait(&tempty[acc], acc_ph ^ 1, p.ew, 200)) { ok = false; break; }
+          tc_fence_after();
+        }
+        for (int kb = 0; kb < KB && ok; ++kb) {
           if (!mbar_wait(&full[s], ph, p.ew, 201)) { ok = false; break; }
           tc_fence_after();
           const uint32_t a_base = smem_u32(smem + (size_t)s * C_::STAGE_BYTES);
           const uint32_t b_base = a_base + C_::A_BYTES;
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
-            const uint64_t adesc = p.a_mn ? make_smem_desc(a_base + k * p.mn_kstep, p.mn_lbo, p.mn_sbo)
-                                          : make_smem_desc(a_base + k * (UMMA_K * 2), 16, 1024);
             const uint64_t bdesc = p.b_mn ? make_smem_desc(b_base + k * p.mn_kstep, p.mn_lbo, p.mn_sbo)
                                           : make_smem_desc(b_base + k * (UMMA_K * 2), 16, 1024);
-            tc_mma_ss(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+#pragma unroll
+            for (int h = 0; h < MT; ++h) {
+              if (MT == 2 && kb == 0 && k == 0) {
+                // half h of the previous tile must have been drained before it is overwritten
+                if (!mbar_wait(&tempty[h], acc_ph ^ 1, p.ew, 202)) { ok = false; break; }
+                tc_fence_after();
+              }
+              const uint32_t ah = a_base + h * (BM * BK * 2);   // 128 rows (K-major) or two 64-column chunks
+              const uint64_t adesc = p.a_mn ? make_smem_desc(ah + k * p.mn_kstep, p.mn_lbo, p.mn_sbo)
+                                            : make_smem_desc(ah + k * (UMMA_K * 2), 16, 1024);
+              const uint32_t d_tmem = tmem_base + (uint32_t)((MT == 2 ? h : acc) * BN);
+              tc_mma_ss(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+            }
+            if (!ok) break;
           }
+          if (!ok) break;
           tc_commit(&empty[s]);
           if (++s == kStages) { s = 0; ph ^= 1; }
         }
         if (!ok) break;
-        tc_commit(&tfull[acc]);
-        acc ^= 1;
-        if (acc == 0) acc_ph ^= 1;
+        if (MT == 1) {
+          tc_commit(&tfull[acc]);
+          acc ^= 1;
+          if (acc == 0) acc_ph ^= 1;
+        } else {
+          tc_commit(&tfull[0]);
+          tc_commit(&tfull[1]);
+          acc_ph ^= 1;
+        }
       }
     }
   } else {
@@ -225,121 +253,131 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     int store_group = 0;   // 64-column groups stored so far; the staging box alternates with it
     int acc = 0;
     uint32_t acc_ph = 0;
-    for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
       int tm, tn;
-      tile_coords(p, tile, tiles_m, tm, tn);
-      bool ok = mbar_wait(&tfull[acc], acc_ph, p.ew, 300);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      tc_fence_after();
-      const long grow = (long)tm * BM + row_in_tile;
-      const bool row_ok = grow < p.M;
+      tile_coords(p, tile, tiles_m, BMT, tm, tn);
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        uint8_t* sbox = sStore + (store_group & 1) * (BM * 64 * 2);
-        if (tma_out && (c & 1) == 0) {
-          if (issuer) tma_store_wait_read1();   // the store that last used this box has read it
-          epi_bar_sync();
-        }
-        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + c * 32);
-        tmem_ld_32x32b_x32(taddr, r);
-        tmem_wait_ld();
-        const int col0 = tn * BN + c * 32;
-        if (row_ok && col0 < p.N) {
+      for (int h = 0; h < MT; ++h) {
+        const int slot = MT == 2 ? h : acc;
+        ok = mbar_wait(&tfull[slot], acc_ph, p.ew, 300);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        const int row0 = tm * BMT + h * BM;             // first row of this 128-row half
+        const long grow = (long)row0 + row_in_tile;
+        const bool row_ok = grow < p.M;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          uint8_t* sbox = sStore + (store_group & 1) * (BM * 64 * 2);
+          if (tma_out && (c & 1) == 0) {
+            if (issuer) tma_store_wait_read1();   // the store that last used this box has read it
+            epi_bar_sync();
+          }
+          const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(slot * BN + c * 32);
+          tmem_ld_32x32b_x32(taddr, r);
+          tmem_wait_ld();
+          const int col0 = tn * BN + c * 32;
+          if (row_ok && col0 < p.N) {
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            const int col = col0 + g * 8;
-            if (col >= p.N) break;
-            float v[8];
+            for (int g = 0; g < 4; ++g) {
+              const int col = col0 + g * 8;
+              if (col >= p.N) break;
+              float v[8];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[g * 8 + j]) * p.alpha;
-            if (p.bias) {
-              const uint4 bv = *reinterpret_cast<const uint4*>(p.bias + col);
-              const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                float2 f = unpack_bf16x2(bw[j]);
-                v[2 * j] += f.x;
-                v[2 * j + 1] += f.y;
-              }
-            }
-            if (p.act == 1) {
-#pragma unroll
-              for (int j = 0; j < 8; ++j) v[j] = gelu_erf(v[j]);
-            }
-            if (p.residual) {
-              const uint4 rv = *reinterpret_cast<const uint4*>(p.residual + grow * p.ldr + col);
-              const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                float2 f = unpack_bf16x2(rw[j]);
-                v[2 * j] += f.x;
-                v[2 * j + 1] += f.y;
-              }
-            }
-            if (p.out_f32) {
-              float* dst = reinterpret_cast<float*>(p.C) + grow * p.ldc + col;
-              if (p.accumulate) {
-                const float4 o0 = *reinterpret_cast<const float4*>(dst);
-                const float4 o1 = *reinterpret_cast<const float4*>(dst + 4);
-                v[0] += o0.x; v[1] += o0.y; v[2] += o0.z; v[3] += o0.w;
-                v[4] += o1.x; v[5] += o1.y; v[6] += o1.z; v[7] += o1.w;
-              }
-              *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
-              *reinterpret_cast<float4*>(dst + 4) = make_float4(v[4], v[5], v[6], v[7]);
-            } else {
-              __nv_bfloat16* dst;
-              if (p.rs_rows) {
-                const int owner = (int)(grow / p.rs_rows);
-                dst = reinterpret_cast<__nv_bfloat16*>(p.rs_base[owner]) +
-                      ((long)p.rs_self * p.rs_rows + (grow - (long)owner * p.rs_rows)) * p.ldc + col;
-              } else {
-                dst = reinterpret_cast<__nv_bfloat16*>(p.C) + grow * p.ldc + col;
-              }
-              if (p.accumulate) {
-                const uint4 ov = *reinterpret_cast<const uint4*>(dst);
-                const uint32_t ow[4] = {ov.x, ov.y, ov.z, ov.w};
+              for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[g * 8 + j]) * p.alpha;
+              if (p.bias) {
+                const uint4 bv = *reinterpret_cast<const uint4*>(p.bias + col);
+                const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                  float2 f = unpack_bf16x2(ow[j]);
+                  float2 f = unpack_bf16x2(bw[j]);
                   v[2 * j] += f.x;
                   v[2 * j + 1] += f.y;
                 }
               }
-              uint4 o;
-              o.x = pack_bf16x2(v[0], v[1]);
-              o.y = pack_bf16x2(v[2], v[3]);
-              o.z = pack_bf16x2(v[4], v[5]);
-              o.w = pack_bf16x2(v[6], v[7]);
-              if (tma_out) *reinterpret_cast<uint4*>(sbox + store_box_offset(row_in_tile, (c & 1) * 32 + g * 8)) = o;
-              else *reinterpret_cast<uint4*>(dst) = o;
-            }
-          }
-        }
-        if (tma_out && (c & 1) == 1) {
-          fence_proxy_async_smem();
-          epi_bar_sync();
-          if (issuer) {
-            const int x = tn * BN + (c >> 1) * 64;
-            if (x < p.N) {
-              if (p.rs_rows) {
-                const int owner = (tm * BM) / p.rs_rows;
-                tma_store_2d(&tmC.m[owner], sbox, x, tm * BM - owner * p.rs_rows);
+              if (p.act == 1) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] = gelu_erf(v[j]);
+              }
+              if (p.residual) {
+                const uint4 rv = *reinterpret_cast<const uint4*>(p.residual + grow * p.ldr + col);
+                const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  float2 f = unpack_bf16x2(rw[j]);
+                  v[2 * j] += f.x;
+                  v[2 * j + 1] += f.y;
+                }
+              }
+              if (p.out_f32) {
+                float* dst = reinterpret_cast<float*>(p.C) + grow * p.ldc + col;
+                if (p.accumulate) {
+                  const float4 o0 = *reinterpret_cast<const float4*>(dst);
+                  const float4 o1 = *reinterpret_cast<const float4*>(dst + 4);
+                  v[0] += o0.x; v[1] += o0.y; v[2] += o0.z; v[3] += o0.w;
+                  v[4] += o1.x; v[5] += o1.y; v[6] += o1.z; v[7] += o1.w;
+                }
+                *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+                *reinterpret_cast<float4*>(dst + 4) = make_float4(v[4], v[5], v[6], v[7]);
               } else {
-                tma_store_2d(&tmC.m[0], sbox, x, tm * BM);
+                __nv_bfloat16* dst;
+                if (p.rs_rows) {
+                  const int owner = (int)(grow / p.rs_rows);
+                  dst = reinterpret_cast<__nv_bfloat16*>(p.rs_base[owner]) +
+                        ((long)p.rs_self * p.rs_rows + (grow - (long)owner * p.rs_rows)) * p.ldc + col;
+                } else {
+                  dst = reinterpret_cast<__nv_bfloat16*>(p.C) + grow * p.ldc + col;
+                }
+                if (p.accumulate) {
+                  const uint4 ov = *reinterpret_cast<const uint4*>(dst);
+                  const uint32_t ow[4] = {ov.x, ov.y, ov.z, ov.w};
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    float2 f = unpack_bf16x2(ow[j]);
+                    v[2 * j] += f.x;
+                    v[2 * j + 1] += f.y;
+                  }
+                }
+                uint4 o;
+                o.x = pack_bf16x2(v[0], v[1]);
+                o.y = pack_bf16x2(v[2], v[3]);
+                o.z = pack_bf16x2(v[4], v[5]);
+                o.w = pack_bf16x2(v[6], v[7]);
+                if (tma_out) *reinterpret_cast<uint4*>(sbox + store_box_offset(row_in_tile, (c & 1) * 32 + g * 8)) = o;
+                else *reinterpret_cast<uint4*>(dst) = o;
               }
             }
-            tma_store_commit();
           }
-          ++store_group;
+          if (tma_out && (c & 1) == 1) {
+            fence_proxy_async_smem();
+            epi_bar_sync();
+            if (issuer) {
+              const int x = tn * BN + (c >> 1) * 64;
+              if (x < p.N && row0 < p.M) {
+                if (p.rs_rows) {
+                  const int owner = row0 / p.rs_rows;
+                  tma_store_2d(&tmC.m[owner], sbox, x, row0 - owner * p.rs_rows);
+                } else {
+                  tma_store_2d(&tmC.m[0], sbox, x, row0);
+                }
+              }
+              tma_store_commit();
+            }
+            ++store_group;
+          }
         }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tempty[slot]);
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&tempty[acc]);
-      acc ^= 1;
-      if (acc == 0) acc_ph ^= 1;
+      if (MT == 1) {
+        acc ^= 1;
+        if (acc == 0) acc_ph ^= 1;
+      } else {
+        acc_ph ^= 1;
+      }
     }
     if (tma_out && issuer) {
       tma_store_wait_all();                                  // every store has been written out
@@ -378,21 +416,24 @@ bool ensure_encode() {
 
 uint32_t g_mn_lbo = 8192, g_mn_sbo = 1024, g_mn_kstep = 2048;
 
-template <int BN>
+template <int BN, int MT>
 int launch(const CUtensorMap& ta, const CUtensorMap& tb, const OutMaps& tc, const GemmParams& p, int sms,
            cudaStream_t st) {
+  using C_ = Cfg<BN, MT>;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_tcgen05<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)Cfg<BN>::SMEM);
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_tcgen05<BN, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)C_::SMEM);
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
   }
-  const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
+  const int tiles = ((p.M + C_::BMT - 1) / C_::BMT) * ((p.N + BN - 1) / BN);
   const int grid = tiles < sms ? tiles : sms;
-  gemm_bf16_tcgen05<BN><<<grid, kThreads, Cfg<BN>::SMEM, st>>>(ta, tb, tc, p);
+  gemm_bf16_tcgen05<BN, MT><<<grid, kThreads, C_::SMEM, st>>>(ta, tb, tc, p);
   return (int)cudaGetLastError();
 }
+
+int g_force_mt = 0;   // 0 = choose, 1 / 2 = force the number of 128-row accumulators per tile
 
 }  // namespace
 
@@ -410,6 +451,9 @@ extern "C" int mmt_make_tmap_2d(CUtensorMap* out, const void* ptr, uint64_t inne
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return (int)r;
 }
+
+// Tuning knob: 0 = choose the tile height per call, 1 = 128-row tiles, 2 = 256-row tiles.
+extern "C" void mmt_gemm_force_mt(int mt) { g_force_mt = mt; }
 
 // Bring-up knob: descriptor constants used for MN-major shared-memory tiles.
 extern "C" void mmt_gemm_set_mn_desc(uint32_t lbo, uint32_t sbo, uint32_t kstep) {
@@ -454,9 +498,20 @@ extern "C" int mmt_gemm_bf16(const void* A, const void* B, void* C, const void* 
     // it leaves a partial last wave; narrower tiles only for narrow outputs.
     bn = N > 192 ? 256 : (N > 128 ? 192 : (N > 64 ? 128 : 64));
   }
+  // tile height: 256 rows (two accumulators sharing each B tile) when it does not cost a wave
+  int mt = 1;
+  if (bn == 256) {
+    const int tn = (N + 255) / 256;
+    const long w1 = ((long)((M + 127) / 128) * tn + sms - 1) / sms;          // waves of 128-row tiles
+    const long w2 = ((long)((M + 255) / 256) * tn + sms - 1) / sms;          // waves of 256-row tiles
+    if (M >= 256 && 2 * w2 <= w1 && w1 <= 3) mt = 2;   // measured: pays only when it removes a partial wave of a short grid
+    if (g_force_mt) mt = g_force_mt;
+    if (M < 256) mt = 1;
+  }
+  const int bmt = BM * mt;
   CUtensorMap ta, tb;
   int r;
-  if (!a_mn) r = mmt_make_tmap_2d(&ta, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BK, BM);
+  if (!a_mn) r = mmt_make_tmap_2d(&ta, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BK, (uint32_t)bmt);
   else       r = mmt_make_tmap_2d(&ta, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, 64, BK);
   if (r) return 1000 + r;
   if (!b_mn) r = mmt_make_tmap_2d(&tb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BK, (uint32_t)bn);
@@ -510,10 +565,10 @@ extern "C" int mmt_gemm_bf16(const void* A, const void* B, void* C, const void* 
   }
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   switch (bn) {
-    case 256: return launch<256>(ta, tb, tc, p, sms, st);
-    case 192: return launch<192>(ta, tb, tc, p, sms, st);
-    case 128: return launch<128>(ta, tb, tc, p, sms, st);
-    case 64:  return launch<64>(ta, tb, tc, p, sms, st);
+    case 256: return mt == 2 ? launch<256, 2>(ta, tb, tc, p, sms, st) : launch<256, 1>(ta, tb, tc, p, sms, st);
+    case 192: return launch<192, 1>(ta, tb, tc, p, sms, st);
+    case 128: return launch<128, 1>(ta, tb, tc, p, sms, st);
+    case 64:  return launch<64, 1>(ta, tb, tc, p, sms, st);
     default:  return -4;
   }
 }

@@ -28,7 +28,11 @@ class VisionTrainer(Trainer):
         if self.config.get("attention_backend") == "flash_attention_2" and self.config.get("library_attention"):
             attn_mod.set_backend("lib")
         cfg.vision.sequence_parallel = mesh.sp > 1
-        sp = SPContext(mesh.sp_group, mesh.sp, mesh.sp_rank, fused=None)
+        ulysses = None
+        if self.state.fused is not None and mesh.sp > 1 and self.config.get("fused_ulysses", True):
+            from ..parallel.fused_ulysses import UlyssesFused
+            ulysses = UlyssesFused(self.state.fused)
+        sp = SPContext(mesh.sp_group, mesh.sp, mesh.sp_rank, fused=ulysses)
         self.model = VisionEncoder(cfg.vision, sp, dtype=dt, device=dev, seed=self.seed,
                                    activation_checkpointing=bool(self.config.get("activation_checkpointing", True)))
         pre = self.config.get("pretrained_checkpoint_dir")

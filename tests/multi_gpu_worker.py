@@ -1,0 +1,48 @@
+"""Worker of tests/test_gpu_multi.py (run under torch.distributed.run, one rank per GPU):
+trains the small bf16 model for a few steps with the fused peer-memory collectives and again with the
+NCCL collectives from the same initial weights, and prints both loss series as JSON on rank 0."""
+import json
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+import torch  # noqa: E402
+import torch.distributed as dist  # noqa: E402
+
+
+def run(fused: bool, steps: int):
+    from multimodal_training_b200.config.loader import load_config
+    from multimodal_training_b200.engine import HybridEngine
+    from multimodal_training_b200.ops import native as nv
+    from multimodal_training_b200.trainers.trainer import process_state, reset_process_state
+
+    world = dist.get_world_size()
+    cfg = load_config(None, [
+        "vision.model_name=smoke", "text.model_name=smoke", "vision.parallelism=sequence", "text.parallelism=tensor",
+        f"training.parallel_size={world}", f"text.tensor_parallel_size={min(world, 2)}", "training.batch_size=2",
+        "training.learning_rate=1e-3", "training.warmup_ratio=0", "training.warmup_steps=0",
+        "training.lr_scheduler_type=constant", "+data.synthetic.image_size=448", "+data.synthetic.text_tokens=256",
+        f"+data.synthetic.global_batch={2 * (world // min(world, 2))}", "+data.synthetic.repeat=1",
+        f"training.fused_comm={'true' if fused else 'false'}"])
+    reset_process_state()
+    eng = HybridEngine.from_config(cfg)
+    assert (process_state().fused is not None) == fused
+    losses = [eng.mean_loss(eng.train_step(0)) for _ in range(steps)]
+    nv.raise_on_device_error()
+    return losses
+
+
+def main():
+    torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    dist.init_process_group("nccl", device_id=torch.device("cuda", int(os.environ["LOCAL_RANK"])))
+    fused = run(True, 4)
+    lib = run(False, 4)
+    if dist.get_rank() == 0:
+        print("RESULT " + json.dumps({"fused": fused, "lib": lib}))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
