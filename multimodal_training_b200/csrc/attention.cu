@@ -285,6 +285,7 @@ int launch_fwd(const CUtensorMap& tm, const AttnParams& p, cudaStream_t st) {
 extern "C" int mmt_attn_fwd(const void* qkv, void* out, float* lse, const int* seq_lo, const int* seq_hi, long T,
                             int n_q, int n_kv, int dim, long ld, int causal, float scale, void* stream) {
   if (T <= 0) return 0;
+  if (mmt_ensure_context(qkv)) return -7;
   if ((dim != 80 && dim != 128) || n_q % n_kv || (ld & 7)) return -2;
   CUtensorMap tm;
   const uint64_t width = (uint64_t)(n_q + 2 * n_kv) * dim;

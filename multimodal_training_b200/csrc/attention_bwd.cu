@@ -469,6 +469,7 @@ extern "C" int mmt_attn_bwd(const void* qkv, const void* out, const void* dout, 
                             void* dqkv, const int* seq_lo, const int* seq_hi, long T, int n_q, int n_kv, int dim,
                             long ld, int causal, float scale, void* stream) {
   if (T <= 0) return 0;
+  if (mmt_ensure_context(qkv)) return -7;
   if ((dim != 80 && dim != 128) || n_q % n_kv || (ld & 7)) return -2;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   {

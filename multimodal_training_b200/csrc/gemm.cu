@@ -400,6 +400,357 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 }
 
 // ------------------------------------------------------------------------------------
+// 2-CTA kernel (cta_group::2): a pair of CTAs on neighbouring SMs computes one 256 x 256 tile.
+//
+// Each CTA stages its own 128 rows of A and HALF of the B tile (128 of the 256 output columns), the
+// leader CTA issues tcgen05.mma.cta_group::2 with M = 256, and each CTA's tensor memory receives its
+// 128 x 256 half of the accumulator.  Compared with the 1-CTA kernel every B byte is read from
+// shared memory once per 256 rows instead of once per 128, which is what lifts the shared-memory
+// bandwidth bound of 128 x 256 tiles.  No multicast anywhere: every CTA loads exactly what it keeps.
+//
+// Barriers: full[s] lives in the leader and counts the bytes of BOTH CTAs' TMA loads (the follower's
+// loads signal the leader's barrier); empty[s] and tfull[a] exist in both CTAs and the leader's
+// tcgen05.commit arrives on each of them; tempty[a] lives in the leader and collects the epilogue
+// warps of both CTAs.
+// ------------------------------------------------------------------------------------
+MMT_DEVICE uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+MMT_DEVICE void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// shared::cluster address of the same shared-memory location in CTA `rank` of the cluster
+MMT_DEVICE uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+MMT_DEVICE void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+MMT_DEVICE void tma_load_2d_pair(void* smem_dst, const CUtensorMap* m, uint32_t leader_bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(leader_bar), "r"(x), "r"(y)
+      : "memory");
+}
+MMT_DEVICE void tc_commit_pair(uint32_t cluster_bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar)
+               : "memory");
+}
+MMT_DEVICE void tc_mma_ss_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "}\n"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+MMT_DEVICE void tmem_alloc_pair(uint32_t* smem_slot, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+               ::"r"(smem_u32(smem_slot)), "r"(cols) : "memory");
+}
+MMT_DEVICE void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+MMT_DEVICE void tmem_dealloc_pair(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+
+struct PairCfg {
+  static constexpr int BN = 256;                      // tile columns (128 per CTA in shared memory)
+  static constexpr uint32_t A_BYTES = BM * BK * 2;    // this CTA's 128 rows of A
+  static constexpr uint32_t B_BYTES = 128 * BK * 2;   // this CTA's half of the B tile
+  static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr uint32_t STORE_BYTES = 2 * BM * 64 * 2;
+  static constexpr int kStages = 6;
+  static constexpr uint32_t TMEM_COLS = 512;          // two 256-column accumulators
+  static constexpr size_t SMEM = 1024 + (size_t)kStages * STAGE_BYTES + STORE_BYTES + (2 * kStages + 4) * 8 + 16;
+};
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+gemm_bf16_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                       const __grid_constant__ OutMaps tmC, const GemmParams p) {
+  using C_ = PairCfg;
+  constexpr int kStages = C_::kStages;
+  constexpr int BN = C_::BN;
+  constexpr int BMT = 2 * BM;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sStore = smem + (size_t)kStages * C_::STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sStore + C_::STORE_BYTES);
+  uint64_t* full = bars;                  // used in the leader only
+  uint64_t* empty = bars + kStages;       // both CTAs
+  uint64_t* tfull = bars + 2 * kStages;   // both CTAs
+  uint64_t* tempty = tfull + 2;           // used in the leader only
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int pair = blockIdx.x >> 1;
+  const int npairs = gridDim.x >> 1;
+  const int tiles_m = (p.M + BMT - 1) / BMT;
+  const int tiles_n = (p.N + BN - 1) / BN;
+  const int ntiles = tiles_m * tiles_n;
+  const int KB = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(&tfull[0], 1);
+    mbar_init(&tfull[1], 1);
+    mbar_init(&tempty[0], 8);   // 4 epilogue warps of each CTA
+    mbar_init(&tempty[1], 8);
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, C_::TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();          // the peer's barriers are initialised before anybody signals them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer (both CTAs) ------------------------------
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      uint32_t ag_seen = p.ag_flags ? (1u << p.ag_self) : 0u;
+      for (int tile = pair; tile < ntiles && ok; tile += npairs) {
+        int tm, tn;
+        tile_coords(p, tile, tiles_m, BMT, tm, tn);
+        const int row0 = tm * BMT + (int)rank * BM;      // this CTA's rows of A
+        const int col0 = tn * BN + (int)rank * 128;      // this CTA's half of the B tile
+        if (p.ag_flags && row0 < p.M) {
+          const int r1 = min(row0 + BM, p.M) - 1;
+          for (int src = row0 / p.ag_rows; src <= r1 / p.ag_rows && ok; ++src) {
+            if (ag_seen & (1u << src)) continue;
+            ok = flag_wait_ge(&p.ag_flags[src], p.ag_epoch, MMT_WAIT_NS, p.ew, 120);
+            ag_seen |= 1u << src;
+          }
+          if (!ok) break;
+          asm volatile("fence.proxy.async;" ::: "memory");
+        }
+        for (int kb = 0; kb < KB; ++kb) {
+          if (!mbar_wait(&empty[s], ph ^ 1, p.ew, 121)) { ok = false; break; }
+          uint8_t* sA = smem + (size_t)s * C_::STAGE_BYTES;
+          uint8_t* sB = sA + C_::A_BYTES;
+          const uint32_t lbar = map_to_cta(smem_u32(&full[s]), 0);
+          if (leader) mbar_expect_tx(&full[s], 2 * C_::STAGE_BYTES);   // the loads of both CTAs
+          if (!p.a_mn) {
+            tma_load_2d_pair(sA, &tmA, lbar, kb * BK, row0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < 2; ++c) tma_load_2d_pair(sA + c * 8192, &tmA, lbar, row0 + c * 64, kb * BK);
+          }
+          if (!p.b_mn) {
+            tma_load_2d_pair(sB, &tmB, lbar, kb * BK, col0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < 2; ++c) tma_load_2d_pair(sB + c * 8192, &tmB, lbar, col0 + c * 64, kb * BK);
+          }
+          if (++s == kStages) { s = 0; ph ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer (leader CTA only) ------------------------------
+    if (lane == 0 && leader) {
+      const uint32_t idesc = make_idesc_bf16(BMT, BN, p.a_mn, p.b_mn);
+      int s = 0, acc = 0;
+      uint32_t ph = 0, acc_ph = 0;
+      bool ok = true;
+      for (int tile = pair; tile < ntiles && ok; tile += npairs) {
+        if (!mbar_wait(&tempty[acc], acc_ph ^ 1, p.ew, 220)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+        for (int kb = 0; kb < KB; ++kb) {
+          if (!mbar_wait(&full[s], ph, p.ew, 221)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_base = smem_u32(smem + (size_t)s * C_::STAGE_BYTES);
+          const uint32_t b_base = a_base + C_::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t adesc = p.a_mn ? make_smem_desc(a_base + k * p.mn_kstep, p.mn_lbo, p.mn_sbo)
+                                          : make_smem_desc(a_base + k * (UMMA_K * 2), 16, 1024);
+            const uint64_t bdesc = p.b_mn ? make_smem_desc(b_base + k * p.mn_kstep, p.mn_lbo, p.mn_sbo)
+                                          : make_smem_desc(b_base + k * (UMMA_K * 2), 16, 1024);
+            tc_mma_ss_pair(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          const uint32_t e = smem_u32(&empty[s]);
+          tc_commit_pair(map_to_cta(e, 0));     // the stage is free again in both CTAs
+          tc_commit_pair(map_to_cta(e, 1));
+          if (++s == kStages) { s = 0; ph ^= 1; }
+        }
+        if (!ok) break;
+        const uint32_t f = smem_u32(&tfull[acc]);
+        tc_commit_pair(map_to_cta(f, 0));       // both halves of the accumulator are complete
+        tc_commit_pair(map_to_cta(f, 1));
+        acc ^= 1;
+        if (acc == 0) acc_ph ^= 1;
+      }
+    }
+  } else {
+    // ------------------------------ epilogue (both CTAs) ------------------------------
+    const int q = warp & 3;
+    const int row_in_tile = q * 32 + lane;
+    const bool tma_out = !p.out_f32 && p.tma_store;
+    const bool issuer = (warp == 2 && lane == 0);
+    int store_group = 0;
+    int acc = 0;
+    uint32_t acc_ph = 0;
+    for (int tile = pair; tile < ntiles; tile += npairs) {
+      int tm, tn;
+      tile_coords(p, tile, tiles_m, BMT, tm, tn);
+      bool ok = mbar_wait(&tfull[acc], acc_ph, p.ew, 320);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const int row0 = tm * BMT + (int)rank * BM;
+      const long grow = (long)row0 + row_in_tile;
+      const bool row_ok = grow < p.M;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        uint8_t* sbox = sStore + (store_group & 1) * (BM * 64 * 2);
+        if (tma_out && (c & 1) == 0) {
+          if (issuer) tma_store_wait_read1();
+          epi_bar_sync();
+        }
+        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + c * 32);
+        tmem_ld_32x32b_x32(taddr, r);
+        tmem_wait_ld();
+        const int colbase = tn * BN + c * 32;
+        if (row_ok && colbase < p.N) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const int col = colbase + g * 8;
+            if (col >= p.N) break;
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[g * 8 + j]) * p.alpha;
+            if (p.bias) {
+              const uint4 bv = *reinterpret_cast<const uint4*>(p.bias + col);
+              const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                float2 f = unpack_bf16x2(bw[j]);
+                v[2 * j] += f.x;
+                v[2 * j + 1] += f.y;
+              }
+            }
+            if (p.act == 1) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) v[j] = gelu_erf(v[j]);
+            }
+            if (p.residual) {
+              const uint4 rv = *reinterpret_cast<const uint4*>(p.residual + grow * p.ldr + col);
+              const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                float2 f = unpack_bf16x2(rw[j]);
+                v[2 * j] += f.x;
+                v[2 * j + 1] += f.y;
+              }
+            }
+            if (p.out_f32) {
+              float* dst = reinterpret_cast<float*>(p.C) + grow * p.ldc + col;
+              if (p.accumulate) {
+                const float4 o0 = *reinterpret_cast<const float4*>(dst);
+                const float4 o1 = *reinterpret_cast<const float4*>(dst + 4);
+                v[0] += o0.x; v[1] += o0.y; v[2] += o0.z; v[3] += o0.w;
+                v[4] += o1.x; v[5] += o1.y; v[6] += o1.z; v[7] += o1.w;
+              }
+              *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+              *reinterpret_cast<float4*>(dst + 4) = make_float4(v[4], v[5], v[6], v[7]);
+            } else {
+              __nv_bfloat16* dst;
+              if (p.rs_rows) {
+                const int owner = (int)(grow / p.rs_rows);
+                dst = reinterpret_cast<__nv_bfloat16*>(p.rs_base[owner]) +
+                      ((long)p.rs_self * p.rs_rows + (grow - (long)owner * p.rs_rows)) * p.ldc + col;
+              } else {
+                dst = reinterpret_cast<__nv_bfloat16*>(p.C) + grow * p.ldc + col;
+              }
+              if (p.accumulate) {
+                const uint4 ov = *reinterpret_cast<const uint4*>(dst);
+                const uint32_t ow[4] = {ov.x, ov.y, ov.z, ov.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  float2 f = unpack_bf16x2(ow[j]);
+                  v[2 * j] += f.x;
+                  v[2 * j + 1] += f.y;
+                }
+              }
+              uint4 o;
+              o.x = pack_bf16x2(v[0], v[1]);
+              o.y = pack_bf16x2(v[2], v[3]);
+              o.z = pack_bf16x2(v[4], v[5]);
+              o.w = pack_bf16x2(v[6], v[7]);
+              if (tma_out) *reinterpret_cast<uint4*>(sbox + store_box_offset(row_in_tile, (c & 1) * 32 + g * 8)) = o;
+              else *reinterpret_cast<uint4*>(dst) = o;
+            }
+          }
+        }
+        if (tma_out && (c & 1) == 1) {
+          fence_proxy_async_smem();
+          epi_bar_sync();
+          if (issuer) {
+            const int x = tn * BN + (c >> 1) * 64;
+            if (x < p.N && row0 < p.M) {
+              if (p.rs_rows) {
+                const int owner = row0 / p.rs_rows;
+                tma_store_2d(&tmC.m[owner], sbox, x, row0 - owner * p.rs_rows);
+              } else {
+                tma_store_2d(&tmC.m[0], sbox, x, row0);
+              }
+            }
+            tma_store_commit();
+          }
+          ++store_group;
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty[acc]), 0));
+      acc ^= 1;
+      if (acc == 0) acc_ph ^= 1;
+    }
+    if (tma_out && issuer) {
+      tma_store_wait_all();
+      asm volatile("fence.proxy.async;" ::: "memory");
+    }
+  }
+
+  if (p.rs_rows) __threadfence_system();
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();          // nobody leaves (or frees tensor memory) while the peer may still touch it
+  if (warp == 1) tmem_dealloc_pair(tmem_base, C_::TMEM_COLS);
+  if (p.rs_rows && threadIdx.x == 0) {
+    if (atomicAdd(p.rs_counter, 1) == (int)gridDim.x - 1) {
+      *p.rs_counter = 0;
+      __threadfence_system();
+      for (int r = 0; r < p.rs_ranks; ++r) flag_store_release_sys(p.rs_flag[r], p.rs_epoch);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------
 // Host side
 // ------------------------------------------------------------------------------------
 PFN_cuTensorMapEncodeTiled_v12000 g_encode = nullptr;
@@ -433,7 +784,23 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const OutMaps& tc, cons
   return (int)cudaGetLastError();
 }
 
-int g_force_mt = 0;   // 0 = choose, 1 / 2 = force the number of 128-row accumulators per tile
+int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const OutMaps& tc, const GemmParams& p, int sms,
+                cudaStream_t st) {
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_tcgen05_pair, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)PairCfg::SMEM);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  const int tiles = ((p.M + 2 * BM - 1) / (2 * BM)) * ((p.N + PairCfg::BN - 1) / PairCfg::BN);
+  const int pairs = tiles < sms / 2 ? tiles : sms / 2;
+  gemm_bf16_tcgen05_pair<<<2 * pairs, kThreads, PairCfg::SMEM, st>>>(ta, tb, tc, p);
+  return (int)cudaGetLastError();
+}
+
+int g_force_mt = 0;
+int g_use_pair = 0;   // 0 = choose, 1 / 2 = force the number of 128-row accumulators per tile
 
 }  // namespace
 
@@ -452,8 +819,10 @@ extern "C" int mmt_make_tmap_2d(CUtensorMap* out, const void* ptr, uint64_t inne
   return (int)r;
 }
 
-// Tuning knob: 0 = choose the tile height per call, 1 = 128-row tiles, 2 = 256-row tiles.
+// Tuning knob: 0 = choose per call, 1 = 128-row tiles, 2 = 256-row tiles in one CTA, 3 = 2-CTA kernel.
 extern "C" void mmt_gemm_force_mt(int mt) { g_force_mt = mt; }
+// Default kernel for M >= 256 and 256-wide tiles: 1 = the 2-CTA kernel, 0 = the 1-CTA kernels.
+extern "C" void mmt_gemm_use_pair(int on) { g_use_pair = on; }
 
 // Bring-up knob: descriptor constants used for MN-major shared-memory tiles.
 extern "C" void mmt_gemm_set_mn_desc(uint32_t lbo, uint32_t sbo, uint32_t kstep) {
@@ -488,6 +857,7 @@ extern "C" int mmt_gemm_bf16(const void* A, const void* B, void* C, const void* 
                              int N, int K, int lda, int ldb, int ldc, int ldr, int a_mn, int b_mn, int act,
                              int accumulate, int out_f32, float alpha, int bn, void* stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (mmt_ensure_context(A)) return -7;
   if ((lda & 7) || (ldb & 7) || (ldc & 7) || (N & 7) || (residual && (ldr & 7))) return -2;
   if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) ||
       (reinterpret_cast<uintptr_t>(C) & 15))
@@ -505,16 +875,18 @@ extern "C" int mmt_gemm_bf16(const void* A, const void* B, void* C, const void* 
     const long w1 = ((long)((M + 127) / 128) * tn + sms - 1) / sms;          // waves of 128-row tiles
     const long w2 = ((long)((M + 255) / 256) * tn + sms - 1) / sms;          // waves of 256-row tiles
     if (M >= 256 && 2 * w2 <= w1 && w1 <= 3) mt = 2;   // measured: pays only when it removes a partial wave of a short grid
+    if (g_use_pair && M >= 256) mt = 3;                  // 2-CTA kernel: 256 x 256 tile per CTA pair
     if (g_force_mt) mt = g_force_mt;
     if (M < 256) mt = 1;
   }
-  const int bmt = BM * mt;
+  const int bmt = mt == 3 ? BM : BM * mt;              // rows per TMA box of A
+  const int bbox = mt == 3 ? 128 : bn;                 // rows per TMA box of B
   CUtensorMap ta, tb;
   int r;
   if (!a_mn) r = mmt_make_tmap_2d(&ta, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BK, (uint32_t)bmt);
   else       r = mmt_make_tmap_2d(&ta, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, 64, BK);
   if (r) return 1000 + r;
-  if (!b_mn) r = mmt_make_tmap_2d(&tb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BK, (uint32_t)bn);
+  if (!b_mn) r = mmt_make_tmap_2d(&tb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BK, (uint32_t)bbox);
   else       r = mmt_make_tmap_2d(&tb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, 64, BK);
   if (r) return 2000 + r;
 
@@ -565,7 +937,9 @@ extern "C" int mmt_gemm_bf16(const void* A, const void* B, void* C, const void* 
   }
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   switch (bn) {
-    case 256: return mt == 2 ? launch<256, 2>(ta, tb, tc, p, sms, st) : launch<256, 1>(ta, tb, tc, p, sms, st);
+    case 256:
+      if (mt == 3) return launch_pair(ta, tb, tc, p, sms, st);
+      return mt == 2 ? launch<256, 2>(ta, tb, tc, p, sms, st) : launch<256, 1>(ta, tb, tc, p, sms, st);
     case 192: return launch<192, 1>(ta, tb, tc, p, sms, st);
     case 128: return launch<128, 1>(ta, tb, tc, p, sms, st);
     case 64:  return launch<64, 1>(ta, tb, tc, p, sms, st);

@@ -27,6 +27,26 @@ MmtErrorWord* mmt_error_word() {
   return g_err;
 }
 
+// Driver-API calls (tensor-map encoding) need a current context on the calling thread.  Threads that
+// PyTorch creates for backward may not have one yet when our first call arrives, so the first call on
+// each thread binds the primary context of the device that owns `ptr`.
+int mmt_ensure_context(const void* ptr) {
+  thread_local int bound_device = -1;
+  if (bound_device >= 0) return 0;
+  cudaPointerAttributes attr;
+  int dev = -1;
+  if (ptr && cudaPointerGetAttributes(&attr, ptr) == cudaSuccess && attr.type == cudaMemoryTypeDevice)
+    dev = attr.device;
+  else
+    cudaGetLastError();
+  if (dev < 0 && cudaGetDevice(&dev) != cudaSuccess) return -1;
+  cudaError_t e = cudaSetDevice(dev);
+  if (e == cudaSuccess) e = cudaFree(0);
+  if (e != cudaSuccess) return (int)e;
+  bound_device = dev;
+  return 0;
+}
+
 extern "C" int mmt_get_error(int* out) {
   MmtErrorWord* w = mmt_error_word();
   if (!w) return -1;

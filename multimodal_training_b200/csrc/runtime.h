@@ -10,6 +10,9 @@ int mmt_sm_count();
 // (allocated on first use; kernels record bounded-wait failures there).
 MmtErrorWord* mmt_error_word();
 
+// Makes sure the calling thread has the CUDA context of the device that owns `ptr` (first call per thread).
+int mmt_ensure_context(const void* ptr);
+
 extern "C" {
 // Copies the error word to out[4] = {code, where, block, aux}; synchronises the device.
 int mmt_get_error(int* out);

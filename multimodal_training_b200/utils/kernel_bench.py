@@ -1,0 +1,165 @@
+"""Micro-benchmarks of the sm_100a kernels with roofline fractions.
+
+    python -m multimodal_training_b200.utils.kernel_bench gemm --m 8192 --n 8192 --k 8192
+    python -m multimodal_training_b200.utils.kernel_bench attention --tokens 16384 --heads 7 --kv-heads 1 --dim 128 --causal
+    python -m multimodal_training_b200.utils.kernel_bench rmsnorm --rows 65536 --cols 3584
+    python -m multimodal_training_b200.utils.kernel_bench adamw --elems 268435456
+
+Timing: CUDA events on the launching stream, >= 3 warm-up launches, an L2 flush (a 256 MiB write)
+between timed launches, median of the timed launches.  Fractions are relative to the measured peaks in
+``MEASURED_PEAKS.json`` at the repository root when present (copy bandwidth and cuBLAS bf16 burst
+throughput), else to 6.65 TB/s and 1.59 PFLOP/s.  ``--iters 1 --no-flush`` gives a single clean launch
+for profilers.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+
+import torch
+
+from ..ops import functional as F
+from ..ops import native as nv
+from ..ops.attention import SeqInfo
+
+
+def peaks() -> tuple[float, float, str]:
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))),
+                        "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return float(d["hbm_gbs"]) * 1e9, float(d["bf16_tflops"]) * 1e12, "of measured"
+    return 6.65e12, 1.59e15, "of fallback"
+
+
+def timed(fn, iters: int, warmup: int, flush: bool) -> float:
+    buf = torch.empty(256 << 20, device="cuda", dtype=torch.uint8) if flush else None
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        if buf is not None:
+            buf.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1))
+    ts.sort()
+    return ts[len(ts) // 2] * 1e-3
+
+
+def report(name: str, seconds: float, flops: float = 0.0, bytes_: float = 0.0, **extra) -> dict:
+    bw, fl, tag = peaks()
+    out = {"kernel": name, "ms": seconds * 1e3, **extra}
+    if flops:
+        out["tflops"] = flops / seconds / 1e12
+        out["frac_compute"] = flops / seconds / fl
+    if bytes_:
+        out["gbs"] = bytes_ / seconds / 1e9
+        out["frac_hbm"] = bytes_ / seconds / bw
+    out["peaks"] = tag
+    print(json.dumps(out))
+    return out
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("kernel", choices=["gemm", "attention", "attention_bwd", "rmsnorm", "swiglu", "adamw", "ce"])
+    ap.add_argument("--m", type=int, default=8192)
+    ap.add_argument("--n", type=int, default=8192)
+    ap.add_argument("--k", type=int, default=8192)
+    ap.add_argument("--layout", default="kk", choices=["kk", "k_mn", "mn_mn"])
+    ap.add_argument("--tokens", type=int, default=8192)
+    ap.add_argument("--seq", type=int, default=0, help="sequence length inside the packed tokens (0 = one sequence)")
+    ap.add_argument("--heads", type=int, default=16)
+    ap.add_argument("--kv-heads", type=int, default=0)
+    ap.add_argument("--dim", type=int, default=80)
+    ap.add_argument("--causal", action="store_true")
+    ap.add_argument("--rows", type=int, default=65536)
+    ap.add_argument("--cols", type=int, default=3584)
+    ap.add_argument("--elems", type=int, default=1 << 28)
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--no-flush", action="store_true")
+    ap.add_argument("--pair", type=int, default=-1, help="GEMM: 1 = 2-CTA kernel, 0 = 1-CTA kernels, -1 = default")
+    a = ap.parse_args(argv)
+    dev = "cuda"
+    nv.lib()
+    flush = not a.no_flush
+    if a.kernel == "gemm":
+        if a.pair >= 0:
+            nv.lib().mmt_gemm_use_pair(a.pair)
+        a_mn, b_mn = a.layout == "mn_mn", a.layout != "kk"
+        A = torch.randn((a.k, a.m) if a_mn else (a.m, a.k), device=dev, dtype=torch.bfloat16)
+        B = torch.randn((a.k, a.n) if b_mn else (a.n, a.k), device=dev, dtype=torch.bfloat16)
+        C = torch.empty(a.m, a.n, device=dev, dtype=torch.bfloat16)
+        t = timed(lambda: F.gemm(A, B, a_mn=a_mn, b_mn=b_mn, out=C), a.iters, a.warmup, flush)
+        report("gemm_bf16_tcgen05", t, flops=2.0 * a.m * a.n * a.k, bytes_=2.0 * (a.m * a.k + a.n * a.k + a.m * a.n),
+               shape=[a.m, a.n, a.k], layout=a.layout)
+    elif a.kernel in ("attention", "attention_bwd"):
+        nkv = a.kv_heads or a.heads
+        seq = a.seq or a.tokens
+        cu = list(range(0, a.tokens + 1, seq))
+        if cu[-1] != a.tokens:
+            cu.append(a.tokens)
+        info = SeqInfo.from_list(cu, dev)
+        qkv = torch.randn(a.tokens, (a.heads + 2 * nkv) * a.dim, device=dev, dtype=torch.bfloat16,
+                          requires_grad=a.kernel == "attention_bwd")
+        fl = sum(4.0 * (y - x) ** 2 * a.dim * a.heads * (0.5 if a.causal else 1.0) for x, y in zip(cu, cu[1:]))
+        if a.kernel == "attention":
+            with torch.no_grad():
+                t = timed(lambda: F.attention(qkv, a.heads, nkv, a.dim, info, causal=a.causal), a.iters, a.warmup,
+                          flush)
+            report("attn_fwd", t, flops=fl, tokens=a.tokens, seq=seq, heads=[a.heads, nkv], dim=a.dim,
+                   causal=a.causal)
+        else:
+            out = F.attention(qkv, a.heads, nkv, a.dim, info, causal=a.causal)
+            do = torch.randn_like(out)
+
+            def bwd():
+                qkv.grad = None
+                out.backward(do, retain_graph=True)
+
+            t = timed(bwd, a.iters, a.warmup, flush)
+            report("attn_bwd(delta+dkdv+dq)", t, flops=3.5 * fl, tokens=a.tokens, seq=seq, heads=[a.heads, nkv],
+                   dim=a.dim, causal=a.causal, note="3.5x forward flops: the two-kernel backward recomputes S and dP twice")
+    elif a.kernel == "rmsnorm":
+        x = torch.randn(a.rows, a.cols, device=dev, dtype=torch.bfloat16)
+        w = torch.ones(a.cols, device=dev, dtype=torch.bfloat16)
+        with torch.no_grad():
+            t = timed(lambda: F.rmsnorm(x, w), a.iters, a.warmup, flush)
+        report("rmsnorm_fwd", t, bytes_=4.0 * a.rows * a.cols, shape=[a.rows, a.cols])
+    elif a.kernel == "swiglu":
+        gu = torch.randn(a.rows, 2 * a.cols, device=dev, dtype=torch.bfloat16)
+        with torch.no_grad():
+            t = timed(lambda: F.swiglu(gu), a.iters, a.warmup, flush)
+        report("swiglu_fwd", t, bytes_=6.0 * a.rows * a.cols, shape=[a.rows, a.cols])
+    elif a.kernel == "adamw":
+        n = a.elems // 8 * 8
+        p = torch.randn(n, device=dev, dtype=torch.bfloat16)
+        g = torch.randn(n, device=dev, dtype=torch.bfloat16)
+        master, m, v = p.float(), torch.zeros(n, device=dev), torch.zeros(n, device=dev)
+        t = timed(lambda: F.adamw_step(p, g, master, m, v, n_decay=n, lr=1e-4, beta1=0.9, beta2=0.999, eps=1e-8,
+                                       weight_decay=0.01, step=1), a.iters, a.warmup, flush)
+        report("adamw", t, bytes_=28.0 * n, elems=n)
+    elif a.kernel == "ce":
+        T, V, H = a.rows, a.cols, a.k
+        h = torch.randn(T, H, device=dev, dtype=torch.bfloat16, requires_grad=True)
+        w = (torch.randn(V, H, device=dev, dtype=torch.bfloat16) * 0.02).requires_grad_()
+        labels = torch.randint(0, V, (T,), device=dev)
+        t = timed(lambda: F.lm_head_cross_entropy(h, w, labels), a.iters, a.warmup, flush)
+        report("lm_head+ce fwd+bwd", t, flops=6.0 * T * V * H, shape=[T, V, H])
+    code = nv.get_error()
+    if code[0]:
+        print(json.dumps({"device_error": code}))
+        return 1
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())
