@@ -126,6 +126,21 @@ MMT_DEVICE bool mbar_wait(uint64_t* bar, uint32_t parity, MmtErrorWord* ew, int 
   }
 }
 
+// One non-blocking look at an mbarrier phase (true = that phase has completed).
+MMT_DEVICE bool mbar_test(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
 // ---------------------------------------------------------------------------
 // TMA (cp.async.bulk.tensor): plain per-CTA loads and stores only.
 // ---------------------------------------------------------------------------
@@ -233,6 +248,18 @@ MMT_DEVICE uint64_t make_smem_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint3
   d |= (uint64_t)2 << 61;
   return d;
 }
+
+// The same descriptor split into its 32-bit halves.  Only the low half depends on the tile's address, and moving
+// the start address by `bytes` (a multiple of 16) adds bytes >> 4 to it: an MMA issue loop builds both halves
+// once and then spends one integer add per instruction instead of re-encoding the descriptor, which matters
+// because a single thread has to issue an MMA every ~128 cycles.
+MMT_DEVICE uint32_t smem_desc_lo(uint32_t smem_addr, uint32_t lbo_bytes) {
+  return ((smem_addr & 0x3ffff) >> 4) | (((lbo_bytes >> 4) & 0x3fff) << 16);
+}
+MMT_DEVICE uint32_t smem_desc_hi(uint32_t sbo_bytes) {
+  return ((sbo_bytes >> 4) & 0x3fff) | (1u << 14) | (2u << 29);
+}
+MMT_DEVICE uint64_t smem_desc_join(uint32_t hi, uint32_t lo) { return ((uint64_t)hi << 32) | lo; }
 
 // 32 lanes x 32 consecutive fp32 columns: thread i of the warp gets lane
 // (warp%4)*32+i, registers r[0..31] = columns c..c+31.

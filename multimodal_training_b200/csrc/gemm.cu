@@ -7,8 +7,8 @@
 //   warp 1      MMA issuer: one thread issues tcgen05.mma (cta_group::1) with both
 //               operands in shared memory and the fp32 accumulator in tensor memory;
 //               tcgen05.commit frees ring slots and publishes finished accumulators
-//   warps 2..5  epilogue: tcgen05.ld accumulator rows -> registers -> fused
-//               bias / GELU / residual / accumulate -> bf16 (or fp32) global stores
+//   warps 2..9  epilogue: tcgen05.ld accumulator rows -> registers -> fused bias / GELU / residual /
+//               accumulate -> bf16 through per-warp shared-memory slabs and TMA stores (or direct stores)
 // The accumulator is double buffered in tensor memory (2 x BN columns) so the
 // epilogue of tile i overlaps the main loop of tile i+1.
 //
@@ -33,7 +33,9 @@ namespace {
 constexpr int BM = 128;
 constexpr int BK = 64;            // 64 bf16 = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
-constexpr int kThreads = 192;
+constexpr int kEpiWarps = 8;
+constexpr uint32_t kSlabBytes = 32 * 64 * 2;   // one epilogue warp's [32 x 64] bf16 staging slab
+constexpr int kThreads = 64 + kEpiWarps * 32;   // TMA warp, MMA warp, eight epilogue warps
 
 struct GemmParams {
   int M, N, K;
@@ -48,8 +50,12 @@ struct GemmParams {
   float alpha;
   int a_mn, b_mn;                 // operand majors
   int tma_store;                  // bf16 output leaves through shared memory + TMA stores
+  int group_m, tiles_n;           // raster: m-tiles per band (0 = all), number of n-tiles
   uint32_t mn_lbo, mn_sbo, mn_kstep;  // descriptor constants of MN-major tiles
   MmtErrorWord* ew;
+  int dbg;                        // measurement only: bit 0 = operands are loaded once (ring filled, then reused), bit 1 = no
+                                  // per-stage commit, bit 2 = no TMA stores, bit 3 = no epilogue work at all
+  unsigned long long* clk;        // optional: CTA 0 writes {SM cycles, nanoseconds} it spent in the kernel
   // --- all-gather consumer (A rows arrive from peers): rows [s*ag_rows, (s+1)*ag_rows) come from rank s and
   //     are complete once ag_flags[s] >= ag_epoch; this rank's own rows need no wait.  ag_flags == nullptr: off.
   const int* ag_flags;
@@ -66,8 +72,16 @@ struct GemmParams {
 // tile index -> (tile_m, tile_n); with an all-gather consumer the m tiles are rotated so that the CTA wave
 // starts on this rank's own rows while the peers' rows are still in flight.
 MMT_DEVICE void tile_coords(const GemmParams& p, int tile, int tiles_m, int bmt, int& tm, int& tn) {
-  tm = tile % tiles_m;
-  tn = tile / tiles_m;
+  // Grouped raster: tiles are walked in bands of `group_m` m-tiles, n-fastest inside a band... i.e. a wave of
+  // CTAs covers a roughly square block of the output, so every A and B tile it needs is shared by many CTAs
+  // and stays in L2 instead of being re-streamed from DRAM once per n-tile.
+  const int g = p.group_m > 0 ? p.group_m : tiles_m;
+  const int band = tile / (g * p.tiles_n);
+  const int first = band * g;
+  const int rows = min(g, tiles_m - first);
+  const int local = tile - band * g * p.tiles_n;
+  tm = first + local % rows;
+  tn = local / rows;
   if (p.ag_flags) tm = (tm + (int)(((long)p.ag_self * p.ag_rows) / bmt)) % tiles_m;
 }
 
@@ -82,7 +96,7 @@ struct Cfg {
   static constexpr uint32_t A_BYTES = BMT * BK * 2;
   static constexpr uint32_t B_BYTES = BN * BK * 2;
   static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr uint32_t STORE_BYTES = 2 * BM * 64 * 2;   // two [128 x 64] bf16 staging boxes for TMA stores
+  static constexpr uint32_t STORE_BYTES = kEpiWarps * kSlabBytes;   // one [32 x 64] bf16 slab per epilogue warp
   static constexpr int kStages = (int)((227u * 1024u - 2048u - STORE_BYTES) / STAGE_BYTES) > 8
                                      ? 8 : (int)((227u * 1024u - 2048u - STORE_BYTES) / STAGE_BYTES);
   static constexpr uint32_t TMEM_COLS = (2 * BN <= 128) ? 128 : (2 * BN <= 256 ? 256 : 512);
@@ -95,324 +109,12 @@ struct OutMaps {
   CUtensorMap m[8];
 };
 
-MMT_DEVICE void epi_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
-MMT_DEVICE void tma_store_wait_read1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
 
-// byte offset of (row, col) in a [128 x 64] bf16 box with 128-byte rows and the 128B swizzle
+// byte offset of (row, col) in a [rows x 64] bf16 box (1024-byte aligned) with 128-byte rows and the 128B swizzle
 MMT_DEVICE uint32_t store_box_offset(int row, int col) {
   return (uint32_t)((row >> 3) * 1024 + (row & 7) * 128 + ((((col >> 3) ^ (row & 7)) & 7) << 4) + (col & 7) * 2);
 }
 
-template <int BN, int MT>
-__global__ void __launch_bounds__(kThreads, 1)
-gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                  const __grid_constant__ OutMaps tmC, const GemmParams p) {
-  using C_ = Cfg<BN, MT>;
-  constexpr int kStages = C_::kStages;
-  constexpr int BMT = C_::BMT;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* sStore = smem + (size_t)kStages * C_::STAGE_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sStore + C_::STORE_BYTES);
-  uint64_t* full = bars;
-  uint64_t* empty = bars + kStages;
-  uint64_t* tfull = bars + 2 * kStages;   // [2]: accumulator slot filled
-  uint64_t* tempty = tfull + 2;           // [2]: accumulator slot drained
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
-
-  const int warp = threadIdx.x >> 5;
-  const int lane = threadIdx.x & 31;
-  const int tiles_m = (p.M + BMT - 1) / BMT;
-  const int tiles_n = (p.N + BN - 1) / BN;
-  const int ntiles = tiles_m * tiles_n;
-  const int KB = (p.K + BK - 1) / BK;
-
-  if (threadIdx.x == 0) {
-    tma_prefetch_desc(&tmA);
-    tma_prefetch_desc(&tmB);
-    for (int s = 0; s < kStages; ++s) {
-      mbar_init(&full[s], 1);
-      mbar_init(&empty[s], 1);
-    }
-    mbar_init(&tfull[0], 1);
-    mbar_init(&tfull[1], 1);
-    mbar_init(&tempty[0], 4);
-    mbar_init(&tempty[1], 4);
-    mbar_fence_init();
-  }
-  if (warp == 1) {
-    tmem_alloc(tmem_slot, C_::TMEM_COLS);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
-
-  if (warp == 0) {
-    // ------------------------------ TMA producer ------------------------------
-    if (lane == 0) {
-      int s = 0;
-      uint32_t ph = 0;
-      bool ok = true;
-      uint32_t ag_seen = p.ag_flags ? (1u << p.ag_self) : 0u;
-      for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
-        int tm, tn;
-        tile_coords(p, tile, tiles_m, BMT, tm, tn);
-        if (p.ag_flags) {
-          const int r0 = tm * BMT, r1 = min(r0 + BMT, p.M) - 1;
-          for (int src = r0 / p.ag_rows; src <= r1 / p.ag_rows && ok; ++src) {
-            if (ag_seen & (1u << src)) continue;
-            ok = flag_wait_ge(&p.ag_flags[src], p.ag_epoch, MMT_WAIT_NS, p.ew, 110);
-            ag_seen |= 1u << src;
-          }
-          if (!ok) break;
-          asm volatile("fence.proxy.async;" ::: "memory");
-        }
-        for (int kb = 0; kb < KB; ++kb) {
-          if (!mbar_wait(&empty[s], ph ^ 1, p.ew, 100)) { ok = false; break; }
-          uint8_t* sA = smem + (size_t)s * C_::STAGE_BYTES;
-          uint8_t* sB = sA + C_::A_BYTES;
-          mbar_expect_tx(&full[s], C_::STAGE_BYTES);
-          if (!p.a_mn) {
-            tma_load_2d(sA, &tmA, &full[s], kb * BK, tm * BMT);      // one box of BMT rows
-          } else {
-#pragma unroll
-            for (int c = 0; c < BMT / 64; ++c) tma_load_2d(sA + c * 8192, &tmA, &full[s], tm * BMT + c * 64, kb * BK);
-          }
-          if (!p.b_mn) {
-            tma_load_2d(sB, &tmB, &full[s], kb * BK, tn * BN);
-          } else {
-#pragma unroll
-            for (int c = 0; c < BN / 64; ++c) tma_load_2d(sB + c * 8192, &tmB, &full[s], tn * BN + c * 64, kb * BK);
-          }
-          if (++s == kStages) { s = 0; ph ^= 1; }
-        }
-      }
-    }
-  } else if (warp == 1) {
-    // ------------------------------ MMA issuer --------------------------------
-    if (lane == 0) {
-      const uint32_t idesc = make_idesc_bf16(BM, BN, p.a_mn, p.b_mn);
-      int s = 0, acc = 0;
-      uint32_t ph = 0, acc_ph = 0;   // MT == 1: acc alternates per tile; MT == 2: slots 0/1 are the halves
-      bool ok = true;
-      for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
-        if (MT == 1) {
-          if (!mbar_wait(&tempty[acc], acc_ph ^ 1, p.ew, 200)) { ok = false; break; }
-          tc_fence_after();
-        }
-        for (int kb = 0; kb < KB && ok; ++kb) {
-          if (!mbar_wait(&full[s], ph, p.ew, 201)) { ok = false; break; }
-          tc_fence_after();
-          const uint32_t a_base = smem_u32(smem + (size_t)s * C_::STAGE_BYTES);
-          const uint32_t b_base = a_base + C_::A_BYTES;
-#pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) {
-            const uint64_t bdesc = p.b_mn ? make_smem_desc(b_base + k * p.mn_kstep, p.mn_lbo, p.mn_sbo)
-                                          : make_smem_desc(b_base + k * (UMMA_K * 2), 16, 1024);
-#pragma unroll
-            for (int h = 0; h < MT; ++h) {
-              if (MT == 2 && kb == 0 && k == 0) {
-                // half h of the previous tile must have been drained before it is overwritten
-                if (!mbar_wait(&tempty[h], acc_ph ^ 1, p.ew, 202)) { ok = false; break; }
-                tc_fence_after();
-              }
-              const uint32_t ah = a_base + h * (BM * BK * 2);   // 128 rows (K-major) or two 64-column chunks
-              const uint64_t adesc = p.a_mn ? make_smem_desc(ah + k * p.mn_kstep, p.mn_lbo, p.mn_sbo)
-                                            : make_smem_desc(ah + k * (UMMA_K * 2), 16, 1024);
-              const uint32_t d_tmem = tmem_base + (uint32_t)((MT == 2 ? h : acc) * BN);
-              tc_mma_ss(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
-            }
-            if (!ok) break;
-          }
-          if (!ok) break;
-          tc_commit(&empty[s]);
-          if (++s == kStages) { s = 0; ph ^= 1; }
-        }
-        if (!ok) break;
-        if (MT == 1) {
-          tc_commit(&tfull[acc]);
-          acc ^= 1;
-          if (acc == 0) acc_ph ^= 1;
-        } else {
-          tc_commit(&tfull[0]);
-          tc_commit(&tfull[1]);
-          acc_ph ^= 1;
-        }
-      }
-    }
-  } else {
-    // ------------------------------ epilogue ----------------------------------
-    const int q = warp & 3;  // tensor-memory lane quadrant this warp may read
-    const int row_in_tile = q * 32 + lane;
-    // bf16 results leave through shared memory and TMA stores (full 128-byte rows per request: this is what
-    // makes stores to a peer GPU efficient); fp32 results and ragged reduce-scatter tiles use direct stores
-    const bool tma_out = !p.out_f32 && p.tma_store;
-    const bool issuer = (warp == 2 && lane == 0);
-    int store_group = 0;   // 64-column groups stored so far; the staging box alternates with it
-    int acc = 0;
-    uint32_t acc_ph = 0;
-    bool ok = true;
-    for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
-      int tm, tn;
-      tile_coords(p, tile, tiles_m, BMT, tm, tn);
-#pragma unroll 1
-      for (int h = 0; h < MT; ++h) {
-        const int slot = MT == 2 ? h : acc;
-        ok = mbar_wait(&tfull[slot], acc_ph, p.ew, 300);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        tc_fence_after();
-        const int row0 = tm * BMT + h * BM;             // first row of this 128-row half
-        const long grow = (long)row0 + row_in_tile;
-        const bool row_ok = grow < p.M;
-#pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          uint32_t r[32];
-          uint8_t* sbox = sStore + (store_group & 1) * (BM * 64 * 2);
-          if (tma_out && (c & 1) == 0) {
-            if (issuer) tma_store_wait_read1();   // the store that last used this box has read it
-            epi_bar_sync();
-          }
-          const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(slot * BN + c * 32);
-          tmem_ld_32x32b_x32(taddr, r);
-          tmem_wait_ld();
-          const int col0 = tn * BN + c * 32;
-          if (row_ok && col0 < p.N) {
-#pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              const int col = col0 + g * 8;
-              if (col >= p.N) break;
-              float v[8];
-#pragma unroll
-              for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[g * 8 + j]) * p.alpha;
-              if (p.bias) {
-                const uint4 bv = *reinterpret_cast<const uint4*>(p.bias + col);
-                const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  float2 f = unpack_bf16x2(bw[j]);
-                  v[2 * j] += f.x;
-                  v[2 * j + 1] += f.y;
-                }
-              }
-              if (p.act == 1) {
-#pragma unroll
-                for (int j = 0; j < 8; ++j) v[j] = gelu_erf(v[j]);
-              }
-              if (p.residual) {
-                const uint4 rv = *reinterpret_cast<const uint4*>(p.residual + grow * p.ldr + col);
-                const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  float2 f = unpack_bf16x2(rw[j]);
-                  v[2 * j] += f.x;
-                  v[2 * j + 1] += f.y;
-                }
-              }
-              if (p.out_f32) {
-                float* dst = reinterpret_cast<float*>(p.C) + grow * p.ldc + col;
-                if (p.accumulate) {
-                  const float4 o0 = *reinterpret_cast<const float4*>(dst);
-                  const float4 o1 = *reinterpret_cast<const float4*>(dst + 4);
-                  v[0] += o0.x; v[1] += o0.y; v[2] += o0.z; v[3] += o0.w;
-                  v[4] += o1.x; v[5] += o1.y; v[6] += o1.z; v[7] += o1.w;
-                }
-                *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
-                *reinterpret_cast<float4*>(dst + 4) = make_float4(v[4], v[5], v[6], v[7]);
-              } else {
-                __nv_bfloat16* dst;
-                if (p.rs_rows) {
-                  const int owner = (int)(grow / p.rs_rows);
-                  dst = reinterpret_cast<__nv_bfloat16*>(p.rs_base[owner]) +
-                        ((long)p.rs_self * p.rs_rows + (grow - (long)owner * p.rs_rows)) * p.ldc + col;
-                } else {
-                  dst = reinterpret_cast<__nv_bfloat16*>(p.C) + grow * p.ldc + col;
-                }
-                if (p.accumulate) {
-                  const uint4 ov = *reinterpret_cast<const uint4*>(dst);
-                  const uint32_t ow[4] = {ov.x, ov.y, ov.z, ov.w};
-#pragma unroll
-                  for (int j = 0; j < 4; ++j) {
-                    float2 f = unpack_bf16x2(ow[j]);
-                    v[2 * j] += f.x;
-                    v[2 * j + 1] += f.y;
-                  }
-                }
-                uint4 o;
-                o.x = pack_bf16x2(v[0], v[1]);
-                o.y = pack_bf16x2(v[2], v[3]);
-                o.z = pack_bf16x2(v[4], v[5]);
-                o.w = pack_bf16x2(v[6], v[7]);
-                if (tma_out) *reinterpret_cast<uint4*>(sbox + store_box_offset(row_in_tile, (c & 1) * 32 + g * 8)) = o;
-                else *reinterpret_cast<uint4*>(dst) = o;
-              }
-            }
-          }
-          if (tma_out && (c & 1) == 1) {
-            fence_proxy_async_smem();
-            epi_bar_sync();
-            if (issuer) {
-              const int x = tn * BN + (c >> 1) * 64;
-              if (x < p.N && row0 < p.M) {
-                if (p.rs_rows) {
-                  const int owner = row0 / p.rs_rows;
-                  tma_store_2d(&tmC.m[owner], sbox, x, row0 - owner * p.rs_rows);
-                } else {
-                  tma_store_2d(&tmC.m[0], sbox, x, row0);
-                }
-              }
-              tma_store_commit();
-            }
-            ++store_group;
-          }
-        }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&tempty[slot]);
-      }
-      if (MT == 1) {
-        acc ^= 1;
-        if (acc == 0) acc_ph ^= 1;
-      } else {
-        acc_ph ^= 1;
-      }
-    }
-    if (tma_out && issuer) {
-      tma_store_wait_all();                                  // every store has been written out
-      asm volatile("fence.proxy.async;" ::: "memory");
-    }
-  }
-
-  if (p.rs_rows) __threadfence_system();   // this thread's peer stores are visible system-wide
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem_base, C_::TMEM_COLS);
-  if (p.rs_rows && threadIdx.x == 0) {
-    // last CTA to finish publishes "my partial sums have landed" to every peer
-    if (atomicAdd(p.rs_counter, 1) == (int)gridDim.x - 1) {
-      *p.rs_counter = 0;
-      __threadfence_system();
-      for (int r = 0; r < p.rs_ranks; ++r) flag_store_release_sys(p.rs_flag[r], p.rs_epoch);
-    }
-  }
-}
-
-// ------------------------------------------------------------------------------------
-// 2-CTA kernel (cta_group::2): a pair of CTAs on neighbouring SMs computes one 256 x 256 tile.
-//
-// Each CTA stages its own 128 rows of A and HALF of the B tile (128 of the 256 output columns), the
-// leader CTA issues tcgen05.mma.cta_group::2 with M = 256, and each CTA's tensor memory receives its
-// 128 x 256 half of the accumulator.  Compared with the 1-CTA kernel every B byte is read from
-// shared memory once per 256 rows instead of once per 128, which is what lifts the shared-memory
-// bandwidth bound of 128 x 256 tiles.  No multicast anywhere: every CTA loads exactly what it keeps.
-//
-// Barriers: full[s] lives in the leader and counts the bytes of BOTH CTAs' TMA loads (the follower's
-// loads signal the leader's barrier); empty[s] and tfull[a] exist in both CTAs and the leader's
-// tcgen05.commit arrives on each of them; tempty[a] lives in the leader and collects the epilogue
-// warps of both CTAs.
-// ------------------------------------------------------------------------------------
 MMT_DEVICE uint32_t cluster_ctarank() {
   uint32_t r;
   asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
@@ -461,12 +163,373 @@ MMT_DEVICE void tmem_dealloc_pair(uint32_t taddr, uint32_t cols) {
   asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
 }
 
+
+// ------------------------------------------------------------------------------------
+// Epilogue of one 128-row accumulator, shared by both kernels.
+//
+// Eight warps drain an accumulator: warp e owns tensor-memory lanes (rows) 32*(e%4).. and every second group of
+// 64 columns.  A warp never synchronises with another warp: it reads 64 columns of its 32 rows with two
+// tcgen05.ld, converts them, writes its own 32 x 64 bf16 slab of shared memory (128-byte rows, 128B swizzle) and
+// hands that slab to a TMA store of its own (full 128-byte rows per request, also when C is a peer GPU's buffer).
+// The next group's tcgen05.ld is issued before the warp waits for its previous store to have read the slab, and
+// the accumulator is released to the MMA warp as soon as this warp's last tcgen05.ld has completed, i.e. before
+// the conversion and the stores of the last group.
+// fp32 outputs, C += and ragged reduce-scatter rows use direct 16-byte global stores instead of the slab.
+// ------------------------------------------------------------------------------------
+
+template <int BN>
+MMT_DEVICE void epilogue_block(const GemmParams& p, const OutMaps& tmC, uint32_t tmem_acc, int row0, int col_tile0,
+                               int q, int half, int lane, uint8_t* slab, uint32_t release_bar) {
+  constexpr int kGroups = BN / 64;
+  const bool tma_out = !p.out_f32 && p.tma_store;
+  const int srow0 = row0 + q * 32;                 // first row of this warp's slab
+  const long grow = (long)srow0 + lane;
+  const bool row_ok = grow < p.M;
+  const uint32_t taddr0 = tmem_acc + ((uint32_t)(q * 32) << 16);
+  int last_g = -1;
+  for (int g = half; g < kGroups; g += 2) last_g = g;
+  if (last_g < 0) {                                 // no columns for this warp (BN == 64, second half)
+    __syncwarp();
+    if (lane == 0) mbar_arrive_cluster(release_bar);
+    return;
+  }
+#pragma unroll 1
+  for (int g = half; g < kGroups; g += 2) {
+    uint32_t r0[32], r1[32];
+    tmem_ld_32x32b_x32(taddr0 + (uint32_t)(g * 64), r0);
+    tmem_ld_32x32b_x32(taddr0 + (uint32_t)(g * 64 + 32), r1);
+    tmem_wait_ld();
+    if (g == last_g) {
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(release_bar);
+    }
+    const int colg = col_tile0 + g * 64;
+    if (p.dbg & 8) continue;                        // measurement only: drain the accumulator, store nothing
+    if (tma_out) {
+      if (lane == 0) tma_store_wait_read();        // this warp's previous store has read the slab
+      __syncwarp();
+    }
+    if (colg < p.N && (row_ok || tma_out)) {
+#pragma unroll
+      for (int j8 = 0; j8 < 8; ++j8) {
+        const int col = colg + j8 * 8;
+        if (col >= p.N) break;
+        float v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          v[j] = __uint_as_float(j8 < 4 ? r0[j8 * 8 + j] : r1[(j8 - 4) * 8 + j]) * p.alpha;
+        if (p.bias) {
+          const uint4 bv = *reinterpret_cast<const uint4*>(p.bias + col);
+          const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            float2 f = unpack_bf16x2(bw[j]);
+            v[2 * j] += f.x;
+            v[2 * j + 1] += f.y;
+          }
+        }
+        if (p.act == 1) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[j] = gelu_erf(v[j]);
+        }
+        if (p.residual && row_ok) {
+          const uint4 rv = *reinterpret_cast<const uint4*>(p.residual + grow * p.ldr + col);
+          const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            float2 f = unpack_bf16x2(rw[j]);
+            v[2 * j] += f.x;
+            v[2 * j + 1] += f.y;
+          }
+        }
+        if (p.out_f32) {
+          float* dst = reinterpret_cast<float*>(p.C) + grow * p.ldc + col;
+          if (p.accumulate) {
+            const float4 o0 = *reinterpret_cast<const float4*>(dst);
+            const float4 o1 = *reinterpret_cast<const float4*>(dst + 4);
+            v[0] += o0.x; v[1] += o0.y; v[2] += o0.z; v[3] += o0.w;
+            v[4] += o1.x; v[5] += o1.y; v[6] += o1.z; v[7] += o1.w;
+          }
+          *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+          *reinterpret_cast<float4*>(dst + 4) = make_float4(v[4], v[5], v[6], v[7]);
+        } else {
+          __nv_bfloat16* dst = nullptr;
+          if (!tma_out || (p.accumulate && row_ok)) {
+            if (p.rs_rows) {
+              const int owner = (int)(grow / p.rs_rows);
+              dst = reinterpret_cast<__nv_bfloat16*>(p.rs_base[owner]) +
+                    ((long)p.rs_self * p.rs_rows + (grow - (long)owner * p.rs_rows)) * p.ldc + col;
+            } else {
+              dst = reinterpret_cast<__nv_bfloat16*>(p.C) + grow * p.ldc + col;
+            }
+            if (p.accumulate) {       // C += : the old value is read directly, the sum leaves like any other result
+              const uint4 ov = *reinterpret_cast<const uint4*>(dst);
+              const uint32_t ow[4] = {ov.x, ov.y, ov.z, ov.w};
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                float2 f = unpack_bf16x2(ow[j]);
+                v[2 * j] += f.x;
+                v[2 * j + 1] += f.y;
+              }
+            }
+          }
+          uint4 o;
+          o.x = pack_bf16x2(v[0], v[1]);
+          o.y = pack_bf16x2(v[2], v[3]);
+          o.z = pack_bf16x2(v[4], v[5]);
+          o.w = pack_bf16x2(v[6], v[7]);
+          if (tma_out) *reinterpret_cast<uint4*>(slab + store_box_offset(lane, j8 * 8)) = o;
+          else *reinterpret_cast<uint4*>(dst) = o;
+        }
+      }
+    }
+    if (tma_out) {
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        if (colg < p.N && srow0 < p.M && !(p.dbg & 4)) {   // dbg bit 2: everything but the TMA store itself
+          if (p.rs_rows) {
+            const int owner = srow0 / p.rs_rows;
+            tma_store_2d(&tmC.m[owner], slab, colg, srow0 - owner * p.rs_rows);
+          } else {
+            tma_store_2d(&tmC.m[0], slab, colg, srow0);
+          }
+        }
+        tma_store_commit();
+      }
+    }
+  }
+}
+
+template <int BN, int MT>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                  const __grid_constant__ OutMaps tmC, const GemmParams p) {
+  using C_ = Cfg<BN, MT>;
+  constexpr int kStages = C_::kStages;
+  constexpr int BMT = C_::BMT;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sStore = smem + (size_t)kStages * C_::STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sStore + C_::STORE_BYTES);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + kStages;
+  uint64_t* tfull = bars + 2 * kStages;   // [2]: accumulator slot filled
+  uint64_t* tempty = tfull + 2;           // [2]: accumulator slot drained
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  long long clk_c0 = 0;
+  unsigned long long clk_t0 = 0;
+  if (p.clk && blockIdx.x == 0 && threadIdx.x == 0) {
+    clk_c0 = clock64();
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(clk_t0));
+  }
+  const int tiles_m = (p.M + BMT - 1) / BMT;
+  const int tiles_n = (p.N + BN - 1) / BN;
+  const int ntiles = tiles_m * tiles_n;
+  const int KB = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(&tfull[0], 1);
+    mbar_init(&tfull[1], 1);
+    mbar_init(&tempty[0], kEpiWarps);
+    mbar_init(&tempty[1], kEpiWarps);
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, C_::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      uint32_t ag_seen = p.ag_flags ? (1u << p.ag_self) : 0u;
+      int kcount = 0;
+      for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+        int tm, tn;
+        tile_coords(p, tile, tiles_m, BMT, tm, tn);
+        if (p.ag_flags) {
+          const int r0 = tm * BMT, r1 = min(r0 + BMT, p.M) - 1;
+          for (int src = r0 / p.ag_rows; src <= r1 / p.ag_rows && ok; ++src) {
+            if (ag_seen & (1u << src)) continue;
+            ok = flag_wait_ge(&p.ag_flags[src], p.ag_epoch, MMT_WAIT_NS, p.ew, 110);
+            ag_seen |= 1u << src;
+          }
+          if (!ok) break;
+          asm volatile("fence.proxy.async;" ::: "memory");
+        }
+        for (int kb = 0; kb < KB; ++kb) {
+          if ((p.dbg & 1) && kcount++ >= kStages) continue;
+          if (!mbar_wait(&empty[s], ph ^ 1, p.ew, 100)) { ok = false; break; }
+          uint8_t* sA = smem + (size_t)s * C_::STAGE_BYTES;
+          uint8_t* sB = sA + C_::A_BYTES;
+          mbar_expect_tx(&full[s], C_::STAGE_BYTES);
+          if (!p.a_mn) {
+            tma_load_2d(sA, &tmA, &full[s], kb * BK, tm * BMT);      // one box of BMT rows
+          } else {
+#pragma unroll
+            for (int c = 0; c < BMT / 64; ++c) tma_load_2d(sA + c * 8192, &tmA, &full[s], tm * BMT + c * 64, kb * BK);
+          }
+          if (!p.b_mn) {
+            tma_load_2d(sB, &tmB, &full[s], kb * BK, tn * BN);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c) tma_load_2d(sB + c * 8192, &tmB, &full[s], tn * BN + c * 64, kb * BK);
+          }
+          if (++s == kStages) { s = 0; ph ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer --------------------------------
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_bf16(BM, BN, p.a_mn, p.b_mn);
+      // descriptor halves, encoded once: per instruction only the start-address field moves
+      const uint32_t a_hi = smem_desc_hi(p.a_mn ? p.mn_sbo : 1024u), b_hi = smem_desc_hi(p.b_mn ? p.mn_sbo : 1024u);
+      const uint32_t a_lo0 = smem_desc_lo(smem_u32(smem), p.a_mn ? p.mn_lbo : 16u);
+      const uint32_t b_lo0 = smem_desc_lo(smem_u32(smem) + C_::A_BYTES, p.b_mn ? p.mn_lbo : 16u);
+      const uint32_t a_k = (p.a_mn ? p.mn_kstep : (uint32_t)(UMMA_K * 2)) >> 4;
+      const uint32_t b_k = (p.b_mn ? p.mn_kstep : (uint32_t)(UMMA_K * 2)) >> 4;
+      int s = 0, acc = 0;
+      uint32_t ph = 0, acc_ph = 0;   // MT == 1: acc alternates per tile; MT == 2: slots 0/1 are the halves
+      bool ok = true;
+      int kcount = 0;
+      // The issue loop is kept as short as it can be: this one thread has to hand the tensor core an instruction
+      // every ~128 cycles.  Whether the NEXT ring slot is full is looked up (non-blocking) in the shadow of the
+      // current slot's instructions, so the common case never waits for a barrier round trip.
+      bool ready = false;
+      for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+        // the accumulator (MT == 1) or both halves (MT == 2) of an earlier tile must have been drained
+        if (!mbar_wait(&tempty[MT == 2 ? 0 : acc], acc_ph ^ 1, p.ew, 200)) { ok = false; break; }
+        if (MT == 2 && !mbar_wait(&tempty[1], acc_ph ^ 1, p.ew, 202)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d0 = tmem_base + (uint32_t)((MT == 2 ? 0 : acc) * BN);
+        for (int kb = 0; kb < KB; ++kb) {
+          const bool skip = (p.dbg & 1) && kcount++ >= kStages;
+          if (!ready && !skip && !mbar_wait(&full[s], ph, p.ew, 201)) { ok = false; break; }
+          const uint32_t so = (uint32_t)s * (C_::STAGE_BYTES >> 4);
+          int sn = s + 1;
+          uint32_t phn = ph;
+          if (sn == kStages) { sn = 0; phn ^= 1; }
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t bdesc = smem_desc_join(b_hi, b_lo0 + so + (uint32_t)k * b_k);
+#pragma unroll
+            for (int h = 0; h < MT; ++h) {
+              // half h: 128 rows further (K-major) or two 64-column chunks further (MN-major)
+              const uint64_t adesc =
+                  smem_desc_join(a_hi, a_lo0 + so + (uint32_t)h * ((BM * BK * 2) >> 4) + (uint32_t)k * a_k);
+              tc_mma_ss(d0 + (uint32_t)(h * BN), adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+            }
+            if (k == 0) ready = mbar_test(&full[sn], phn);
+          }
+          if (!(p.dbg & 2)) tc_commit(&empty[s]);
+          s = sn;
+          ph = phn;
+        }
+        if (!ok) break;
+        if (MT == 1) {
+          tc_commit(&tfull[acc]);
+          acc ^= 1;
+          if (acc == 0) acc_ph ^= 1;
+        } else {
+          tc_commit(&tfull[0]);
+          tc_commit(&tfull[1]);
+          acc_ph ^= 1;
+        }
+      }
+    }
+  } else {
+    // ------------------------------ epilogue (8 warps) -------------------------
+    const int q = warp & 3;              // tensor-memory lane quadrant this warp may read
+    const int half = (warp - 2) >> 2;    // which groups of 64 columns this warp takes
+    uint8_t* slab = sStore + (size_t)(warp - 2) * kSlabBytes;
+    int acc = 0;
+    uint32_t acc_ph = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+      int tm, tn;
+      tile_coords(p, tile, tiles_m, BMT, tm, tn);
+#pragma unroll 1
+      for (int h = 0; h < MT; ++h) {
+        const int slot = MT == 2 ? h : acc;
+        ok = mbar_wait(&tfull[slot], acc_ph, p.ew, 300);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        epilogue_block<BN>(p, tmC, tmem_base + (uint32_t)(slot * BN), tm * BMT + h * BM, tn * BN, q, half, lane, slab,
+                           smem_u32(&tempty[slot]));
+      }
+      if (MT == 1) {
+        acc ^= 1;
+        if (acc == 0) acc_ph ^= 1;
+      } else {
+        acc_ph ^= 1;
+      }
+    }
+    if (lane == 0) {
+      tma_store_wait_all();                                  // every store of this warp has been written out
+      asm volatile("fence.proxy.async;" ::: "memory");
+    }
+  }
+
+  if (p.rs_rows) __threadfence_system();   // this thread's peer stores are visible system-wide
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, C_::TMEM_COLS);
+  if (p.clk && blockIdx.x == 0 && threadIdx.x == 0) {
+    unsigned long long t1;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+    p.clk[0] = (unsigned long long)(clock64() - clk_c0);
+    p.clk[1] = t1 - clk_t0;
+  }
+  if (p.rs_rows && threadIdx.x == 0) {
+    // last CTA to finish publishes "my partial sums have landed" to every peer
+    if (atomicAdd(p.rs_counter, 1) == (int)gridDim.x - 1) {
+      *p.rs_counter = 0;
+      __threadfence_system();
+      for (int r = 0; r < p.rs_ranks; ++r) flag_store_release_sys(p.rs_flag[r], p.rs_epoch);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------
+// 2-CTA kernel (cta_group::2): a pair of CTAs on neighbouring SMs computes one 256 x 256 tile.
+//
+// Each CTA stages its own 128 rows of A and HALF of the B tile (128 of the 256 output columns), the
+// leader CTA issues tcgen05.mma.cta_group::2 with M = 256, and each CTA's tensor memory receives its
+// 128 x 256 half of the accumulator.  Compared with the 1-CTA kernel every B byte is read from
+// shared memory once per 256 rows instead of once per 128, which is what lifts the shared-memory
+// bandwidth bound of 128 x 256 tiles.  No multicast anywhere: every CTA loads exactly what it keeps.
+//
+// Barriers: full[s] lives in the leader and counts the bytes of BOTH CTAs' TMA loads (the follower's
+// loads signal the leader's barrier); empty[s] and tfull[a] exist in both CTAs and the leader's
+// tcgen05.commit arrives on each of them; tempty[a] lives in the leader and collects the epilogue
+// warps of both CTAs.
+// ------------------------------------------------------------------------------------
 struct PairCfg {
   static constexpr int BN = 256;                      // tile columns (128 per CTA in shared memory)
   static constexpr uint32_t A_BYTES = BM * BK * 2;    // this CTA's 128 rows of A
   static constexpr uint32_t B_BYTES = 128 * BK * 2;   // this CTA's half of the B tile
   static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr uint32_t STORE_BYTES = 2 * BM * 64 * 2;
+  static constexpr uint32_t STORE_BYTES = kEpiWarps * kSlabBytes;
   static constexpr int kStages = 6;
   static constexpr uint32_t TMEM_COLS = 512;          // two 256-column accumulators
   static constexpr size_t SMEM = 1024 + (size_t)kStages * STAGE_BYTES + STORE_BYTES + (2 * kStages + 4) * 8 + 16;
@@ -491,6 +554,12 @@ gemm_bf16_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_con
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  long long clk_c0 = 0;
+  unsigned long long clk_t0 = 0;
+  if (p.clk && blockIdx.x == 0 && threadIdx.x == 0) {
+    clk_c0 = clock64();
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(clk_t0));
+  }
   const uint32_t rank = cluster_ctarank();
   const bool leader = rank == 0;
   const int pair = blockIdx.x >> 1;
@@ -509,8 +578,8 @@ gemm_bf16_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_con
     }
     mbar_init(&tfull[0], 1);
     mbar_init(&tfull[1], 1);
-    mbar_init(&tempty[0], 8);   // 4 epilogue warps of each CTA
-    mbar_init(&tempty[1], 8);
+    mbar_init(&tempty[0], 2 * kEpiWarps);   // the epilogue warps of both CTAs
+    mbar_init(&tempty[1], 2 * kEpiWarps);
     mbar_fence_init();
   }
   if (warp == 1) {
@@ -530,6 +599,7 @@ gemm_bf16_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_con
       uint32_t ph = 0;
       bool ok = true;
       uint32_t ag_seen = p.ag_flags ? (1u << p.ag_self) : 0u;
+      int kcount = 0;
       for (int tile = pair; tile < ntiles && ok; tile += npairs) {
         int tm, tn;
         tile_coords(p, tile, tiles_m, BMT, tm, tn);
@@ -546,6 +616,7 @@ gemm_bf16_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_con
           asm volatile("fence.proxy.async;" ::: "memory");
         }
         for (int kb = 0; kb < KB; ++kb) {
+          if ((p.dbg & 1) && kcount++ >= kStages) continue;
           if (!mbar_wait(&empty[s], ph ^ 1, p.ew, 121)) { ok = false; break; }
           uint8_t* sA = smem + (size_t)s * C_::STAGE_BYTES;
           uint8_t* sB = sA + C_::A_BYTES;
@@ -571,46 +642,55 @@ gemm_bf16_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_con
     // ------------------------------ MMA issuer (leader CTA only) ------------------------------
     if (lane == 0 && leader) {
       const uint32_t idesc = make_idesc_bf16(BMT, BN, p.a_mn, p.b_mn);
+      const uint32_t a_hi = smem_desc_hi(p.a_mn ? p.mn_sbo : 1024u), b_hi = smem_desc_hi(p.b_mn ? p.mn_sbo : 1024u);
+      const uint32_t a_lo0 = smem_desc_lo(smem_u32(smem), p.a_mn ? p.mn_lbo : 16u);
+      const uint32_t b_lo0 = smem_desc_lo(smem_u32(smem) + C_::A_BYTES, p.b_mn ? p.mn_lbo : 16u);
+      const uint32_t a_k = (p.a_mn ? p.mn_kstep : (uint32_t)(UMMA_K * 2)) >> 4;
+      const uint32_t b_k = (p.b_mn ? p.mn_kstep : (uint32_t)(UMMA_K * 2)) >> 4;
+      const uint32_t empty0 = map_to_cta(smem_u32(&empty[0]), 0), empty1 = map_to_cta(smem_u32(&empty[0]), 1);
+      const uint32_t tfull0 = map_to_cta(smem_u32(&tfull[0]), 0), tfull1 = map_to_cta(smem_u32(&tfull[0]), 1);
       int s = 0, acc = 0;
       uint32_t ph = 0, acc_ph = 0;
       bool ok = true;
+      int kcount = 0;
+      bool ready = false;   // see the 1-CTA kernel: the next slot's barrier is probed behind this slot's MMAs
       for (int tile = pair; tile < ntiles && ok; tile += npairs) {
         if (!mbar_wait(&tempty[acc], acc_ph ^ 1, p.ew, 220)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
         for (int kb = 0; kb < KB; ++kb) {
-          if (!mbar_wait(&full[s], ph, p.ew, 221)) { ok = false; break; }
-          tc_fence_after();
-          const uint32_t a_base = smem_u32(smem + (size_t)s * C_::STAGE_BYTES);
-          const uint32_t b_base = a_base + C_::A_BYTES;
+          const bool skip = (p.dbg & 1) && kcount++ >= kStages;
+          if (!ready && !skip && !mbar_wait(&full[s], ph, p.ew, 221)) { ok = false; break; }
+          const uint32_t so = (uint32_t)s * (C_::STAGE_BYTES >> 4);
+          int sn = s + 1;
+          uint32_t phn = ph;
+          if (sn == kStages) { sn = 0; phn ^= 1; }
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
-            const uint64_t adesc = p.a_mn ? make_smem_desc(a_base + k * p.mn_kstep, p.mn_lbo, p.mn_sbo)
-                                          : make_smem_desc(a_base + k * (UMMA_K * 2), 16, 1024);
-            const uint64_t bdesc = p.b_mn ? make_smem_desc(b_base + k * p.mn_kstep, p.mn_lbo, p.mn_sbo)
-                                          : make_smem_desc(b_base + k * (UMMA_K * 2), 16, 1024);
+            const uint64_t adesc = smem_desc_join(a_hi, a_lo0 + so + (uint32_t)k * a_k);
+            const uint64_t bdesc = smem_desc_join(b_hi, b_lo0 + so + (uint32_t)k * b_k);
             tc_mma_ss_pair(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+            if (k == 0) ready = mbar_test(&full[sn], phn);
           }
-          const uint32_t e = smem_u32(&empty[s]);
-          tc_commit_pair(map_to_cta(e, 0));     // the stage is free again in both CTAs
-          tc_commit_pair(map_to_cta(e, 1));
-          if (++s == kStages) { s = 0; ph ^= 1; }
+          if (!(p.dbg & 2)) {
+            tc_commit_pair(empty0 + (uint32_t)s * 8u);     // the stage is free again in both CTAs
+            tc_commit_pair(empty1 + (uint32_t)s * 8u);
+          }
+          s = sn;
+          ph = phn;
         }
         if (!ok) break;
-        const uint32_t f = smem_u32(&tfull[acc]);
-        tc_commit_pair(map_to_cta(f, 0));       // both halves of the accumulator are complete
-        tc_commit_pair(map_to_cta(f, 1));
+        tc_commit_pair(tfull0 + (uint32_t)acc * 8u);       // both halves of the accumulator are complete
+        tc_commit_pair(tfull1 + (uint32_t)acc * 8u);
         acc ^= 1;
         if (acc == 0) acc_ph ^= 1;
       }
     }
   } else {
-    // ------------------------------ epilogue (both CTAs) ------------------------------
+    // ------------------------------ epilogue (both CTAs, 8 warps each) ------------------------------
     const int q = warp & 3;
-    const int row_in_tile = q * 32 + lane;
-    const bool tma_out = !p.out_f32 && p.tma_store;
-    const bool issuer = (warp == 2 && lane == 0);
-    int store_group = 0;
+    const int half = (warp - 2) >> 2;
+    uint8_t* slab = sStore + (size_t)(warp - 2) * kSlabBytes;
     int acc = 0;
     uint32_t acc_ph = 0;
     for (int tile = pair; tile < ntiles; tile += npairs) {
@@ -620,117 +700,12 @@ gemm_bf16_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_con
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      const int row0 = tm * BMT + (int)rank * BM;
-      const long grow = (long)row0 + row_in_tile;
-      const bool row_ok = grow < p.M;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        uint8_t* sbox = sStore + (store_group & 1) * (BM * 64 * 2);
-        if (tma_out && (c & 1) == 0) {
-          if (issuer) tma_store_wait_read1();
-          epi_bar_sync();
-        }
-        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + c * 32);
-        tmem_ld_32x32b_x32(taddr, r);
-        tmem_wait_ld();
-        const int colbase = tn * BN + c * 32;
-        if (row_ok && colbase < p.N) {
-#pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            const int col = colbase + g * 8;
-            if (col >= p.N) break;
-            float v[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[g * 8 + j]) * p.alpha;
-            if (p.bias) {
-              const uint4 bv = *reinterpret_cast<const uint4*>(p.bias + col);
-              const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                float2 f = unpack_bf16x2(bw[j]);
-                v[2 * j] += f.x;
-                v[2 * j + 1] += f.y;
-              }
-            }
-            if (p.act == 1) {
-#pragma unroll
-              for (int j = 0; j < 8; ++j) v[j] = gelu_erf(v[j]);
-            }
-            if (p.residual) {
-              const uint4 rv = *reinterpret_cast<const uint4*>(p.residual + grow * p.ldr + col);
-              const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                float2 f = unpack_bf16x2(rw[j]);
-                v[2 * j] += f.x;
-                v[2 * j + 1] += f.y;
-              }
-            }
-            if (p.out_f32) {
-              float* dst = reinterpret_cast<float*>(p.C) + grow * p.ldc + col;
-              if (p.accumulate) {
-                const float4 o0 = *reinterpret_cast<const float4*>(dst);
-                const float4 o1 = *reinterpret_cast<const float4*>(dst + 4);
-                v[0] += o0.x; v[1] += o0.y; v[2] += o0.z; v[3] += o0.w;
-                v[4] += o1.x; v[5] += o1.y; v[6] += o1.z; v[7] += o1.w;
-              }
-              *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
-              *reinterpret_cast<float4*>(dst + 4) = make_float4(v[4], v[5], v[6], v[7]);
-            } else {
-              __nv_bfloat16* dst;
-              if (p.rs_rows) {
-                const int owner = (int)(grow / p.rs_rows);
-                dst = reinterpret_cast<__nv_bfloat16*>(p.rs_base[owner]) +
-                      ((long)p.rs_self * p.rs_rows + (grow - (long)owner * p.rs_rows)) * p.ldc + col;
-              } else {
-                dst = reinterpret_cast<__nv_bfloat16*>(p.C) + grow * p.ldc + col;
-              }
-              if (p.accumulate) {
-                const uint4 ov = *reinterpret_cast<const uint4*>(dst);
-                const uint32_t ow[4] = {ov.x, ov.y, ov.z, ov.w};
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  float2 f = unpack_bf16x2(ow[j]);
-                  v[2 * j] += f.x;
-                  v[2 * j + 1] += f.y;
-                }
-              }
-              uint4 o;
-              o.x = pack_bf16x2(v[0], v[1]);
-              o.y = pack_bf16x2(v[2], v[3]);
-              o.z = pack_bf16x2(v[4], v[5]);
-              o.w = pack_bf16x2(v[6], v[7]);
-              if (tma_out) *reinterpret_cast<uint4*>(sbox + store_box_offset(row_in_tile, (c & 1) * 32 + g * 8)) = o;
-              else *reinterpret_cast<uint4*>(dst) = o;
-            }
-          }
-        }
-        if (tma_out && (c & 1) == 1) {
-          fence_proxy_async_smem();
-          epi_bar_sync();
-          if (issuer) {
-            const int x = tn * BN + (c >> 1) * 64;
-            if (x < p.N && row0 < p.M) {
-              if (p.rs_rows) {
-                const int owner = row0 / p.rs_rows;
-                tma_store_2d(&tmC.m[owner], sbox, x, row0 - owner * p.rs_rows);
-              } else {
-                tma_store_2d(&tmC.m[0], sbox, x, row0);
-              }
-            }
-            tma_store_commit();
-          }
-          ++store_group;
-        }
-      }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty[acc]), 0));
+      epilogue_block<BN>(p, tmC, tmem_base + (uint32_t)(acc * BN), tm * BMT + (int)rank * BM, tn * BN, q, half, lane,
+                         slab, map_to_cta(smem_u32(&tempty[acc]), 0));
       acc ^= 1;
       if (acc == 0) acc_ph ^= 1;
     }
-    if (tma_out && issuer) {
+    if (lane == 0) {
       tma_store_wait_all();
       asm volatile("fence.proxy.async;" ::: "memory");
     }
@@ -741,6 +716,12 @@ gemm_bf16_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_con
   __syncthreads();
   cluster_sync_all();          // nobody leaves (or frees tensor memory) while the peer may still touch it
   if (warp == 1) tmem_dealloc_pair(tmem_base, C_::TMEM_COLS);
+  if (p.clk && blockIdx.x == 0 && threadIdx.x == 0) {
+    unsigned long long t1;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+    p.clk[0] = (unsigned long long)(clock64() - clk_c0);
+    p.clk[1] = t1 - clk_t0;
+  }
   if (p.rs_rows && threadIdx.x == 0) {
     if (atomicAdd(p.rs_counter, 1) == (int)gridDim.x - 1) {
       *p.rs_counter = 0;
@@ -765,6 +746,7 @@ bool ensure_encode() {
   return true;
 }
 
+int g_l2promo = 3;   // CUtensorMapL2promotion of operand maps: 0 none, 1 64 B, 2 128 B, 3 256 B
 uint32_t g_mn_lbo = 8192, g_mn_sbo = 1024, g_mn_kstep = 2048;
 
 template <int BN, int MT>
@@ -799,8 +781,11 @@ int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const OutMaps& tc,
   return (int)cudaGetLastError();
 }
 
-int g_force_mt = 0;
-int g_use_pair = 0;   // 0 = choose, 1 / 2 = force the number of 128-row accumulators per tile
+int g_force_mt = 0;   // 0 = choose, 1 / 2 = force the number of 128-row accumulators per tile, 3 = 2-CTA kernel
+int g_use_pair = 0;
+int g_group_m = 0;
+unsigned long long* g_clk = nullptr;
+int g_dbg = 0;
 
 }  // namespace
 
@@ -814,13 +799,22 @@ extern "C" int mmt_make_tmap_2d(CUtensorMap* out, const void* ptr, uint64_t inne
   cuuint32_t box[2] = {box_inner, box_outer};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = g_encode(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, (CUtensorMapL2promotion)g_l2promo,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return (int)r;
 }
 
 // Tuning knob: 0 = choose per call, 1 = 128-row tiles, 2 = 256-row tiles in one CTA, 3 = 2-CTA kernel.
 extern "C" void mmt_gemm_force_mt(int mt) { g_force_mt = mt; }
+// Raster band height in m-tiles (0 = choose, -1 = one band: m-fastest over the whole matrix).
+extern "C" void mmt_gemm_group_m(int g) { g_group_m = g; }
+// Measurement aid: device pointer to two 64-bit words that CTA 0 of every following GEMM fills with the SM
+// cycles and the nanoseconds it spent in the kernel (nullptr = off).  cycles / ns = SM clock in GHz under load.
+extern "C" void mmt_gemm_set_clock_probe(unsigned long long* p) { g_clk = p; }
+// Tuning knob: L2 promotion size of the tensor maps (0 none, 1 64 B, 2 128 B, 3 256 B).
+extern "C" void mmt_gemm_set_l2promo(int v) { g_l2promo = v; }
+// Measurement only (results are wrong): see GemmParams::dbg.
+extern "C" void mmt_gemm_set_dbg(int d) { g_dbg = d; }
 // Default kernel for M >= 256 and 256-wide tiles: 1 = the 2-CTA kernel, 0 = the 1-CTA kernels.
 extern "C" void mmt_gemm_use_pair(int on) { g_use_pair = on; }
 
@@ -868,13 +862,18 @@ extern "C" int mmt_gemm_bf16(const void* A, const void* B, void* C, const void* 
     // it leaves a partial last wave; narrower tiles only for narrow outputs.
     bn = N > 192 ? 256 : (N > 128 ? 192 : (N > 64 ? 128 : 64));
   }
-  // tile height: 256 rows (two accumulators sharing each B tile) when it does not cost a wave
+  // Tile height.  256-row tiles (two accumulators sharing each B tile) move a third less data per flop, which under
+  // the board's power limit is what sets the clock, but their two accumulators fill tensor memory, so the
+  // epilogue is not hidden behind the next tile.  Cost model fitted to sustained measurements on B200, in units of
+  // one 128 x 256 x 64 step: a 128-row tile costs 0.56 per k-block, a 256-row tile 1.0 per k-block plus 3.9.
   int mt = 1;
   if (bn == 256) {
     const int tn = (N + 255) / 256;
+    const long kb = (K + BK - 1) / BK;
     const long w1 = ((long)((M + 127) / 128) * tn + sms - 1) / sms;          // waves of 128-row tiles
     const long w2 = ((long)((M + 255) / 256) * tn + sms - 1) / sms;          // waves of 256-row tiles
-    if (M >= 256 && 2 * w2 <= w1 && w1 <= 3) mt = 2;   // measured: pays only when it removes a partial wave of a short grid
+    const double c1 = (double)w1 * 0.5615 * (double)kb, c2 = (double)w2 * ((double)kb + 3.9);
+    if (M >= 256 && c2 < c1) mt = 2;
     if (g_use_pair && M >= 256) mt = 3;                  // 2-CTA kernel: 256 x 256 tile per CTA pair
     if (g_force_mt) mt = g_force_mt;
     if (M < 256) mt = 1;
@@ -900,6 +899,12 @@ extern "C" int mmt_gemm_bf16(const void* A, const void* B, void* C, const void* 
   p.a_mn = a_mn; p.b_mn = b_mn;
   p.mn_lbo = g_mn_lbo; p.mn_sbo = g_mn_sbo; p.mn_kstep = g_mn_kstep;
   p.ew = mmt_error_word();
+  p.clk = g_clk;
+  p.dbg = g_dbg;
+  p.tiles_n = (N + bn - 1) / bn;
+  // raster bands of 2048 rows: a wave of CTAs then covers a roughly square block of C, so the A and B tiles it
+  // needs are shared by many CTAs while they are in L2
+  p.group_m = g_group_m > 0 ? g_group_m : (g_group_m < 0 ? 0 : 2048 / (mt == 1 ? BM : 2 * BM));
   p.ag_flags = nullptr;
   p.ag_epoch = p.ag_rows = p.ag_self = 0;
   p.rs_rows = p.rs_self = p.rs_ranks = p.rs_epoch = 0;
@@ -925,13 +930,13 @@ extern "C" int mmt_gemm_bf16(const void* A, const void* B, void* C, const void* 
         for (int i = 0; i < p.rs_ranks; ++i) {
           const __nv_bfloat16* base = reinterpret_cast<const __nv_bfloat16*>(p.rs_base[i]) +
                                       (long)p.rs_self * p.rs_rows * ldc;
-          r = mmt_make_tmap_2d(&tc.m[i], base, (uint64_t)N, (uint64_t)p.rs_rows, (uint64_t)ldc, 64, BM);
+          r = mmt_make_tmap_2d(&tc.m[i], base, (uint64_t)N, (uint64_t)p.rs_rows, (uint64_t)ldc, 64, 32);
           if (r) return 3000 + r;
         }
       }
     } else {
       p.tma_store = 1;
-      r = mmt_make_tmap_2d(&tc.m[0], C, (uint64_t)N, (uint64_t)M, (uint64_t)ldc, 64, BM);
+      r = mmt_make_tmap_2d(&tc.m[0], C, (uint64_t)N, (uint64_t)M, (uint64_t)ldc, 64, 32);
       if (r) return 3000 + r;
     }
   }
