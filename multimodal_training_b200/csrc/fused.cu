@@ -170,13 +170,20 @@ __global__ void __launch_bounds__(256) rs_reduce_kernel(const bf16* __restrict__
 // ----------------------------------------------------------------------------
 __global__ void route_rows_kernel(const bf16* __restrict__ src, const int* __restrict__ dest_rank,
                                   const long* __restrict__ dest_row, PeerSet ps, int* counter, int epoch, long rows,
-                                  int cols, long src_ld, long dst_ld) {
+                                  int cols, long src_ld, long dst_ld, long dst_rows, MmtErrorWord* ew) {
   const long r = blockIdx.x * (long)(blockDim.x >> 5) + (threadIdx.x >> 5);
   if (r < rows) {
     const int lane = threadIdx.x & 31;
-    bf16* dst = reinterpret_cast<bf16*>(ps.base[dest_rank[r]]) + dest_row[r] * dst_ld;
-    for (int c = lane * 8; c < cols; c += 256)
-      *reinterpret_cast<uint4*>(dst + c) = *reinterpret_cast<const uint4*>(src + r * src_ld + c);
+    const int dr = dest_rank[r];
+    const long drow = dest_row[r];
+    if (dr < 0 || dr >= ps.n || drow < 0 || drow >= dst_rows) {
+      // a destination outside the region would be a wild store into a peer's memory: skip it and say so
+      if (lane == 0) mmt_report(ew, MMT_ERR_BOUNDS, 920, (int)r);
+    } else {
+      bf16* dst = reinterpret_cast<bf16*>(ps.base[dr]) + drow * dst_ld;
+      for (int c = lane * 8; c < cols; c += 256)
+        *reinterpret_cast<uint4*>(dst + c) = *reinterpret_cast<const uint4*>(src + r * src_ld + c);
+    }
   }
   publish_when_last(counter, ps, epoch);
 }
@@ -350,12 +357,14 @@ int mmt_rs_reduce(const void* staging, const int* flags, int epoch, int n_src, i
   return (int)cudaGetLastError();
 }
 
+// dest_rank: int32 index into `peers`; dest_row: int64 row of the destination region, which has dst_rows rows.
 int mmt_route_rows(const void* src, const int* dest_rank, const long* dest_row, const MmtPeerSet* peers, int* counter,
-                   int epoch, long rows, int cols, long src_ld, long dst_ld, void* stream) {
+                   int epoch, long rows, int cols, long src_ld, long dst_ld, long dst_rows, void* stream) {
   if (cols % 8 || src_ld % 8 || dst_ld % 8) return -2;
   const long blocks = rows > 0 ? (rows + 7) / 8 : 1;
   route_rows_kernel<<<(unsigned)blocks, 256, 0, ST(stream)>>>(reinterpret_cast<const bf16*>(src), dest_rank, dest_row,
-                                                             to_ps(peers), counter, epoch, rows, cols, src_ld, dst_ld);
+                                                             to_ps(peers), counter, epoch, rows, cols, src_ld, dst_ld, dst_rows,
+                                                             mmt_error_word());
   return (int)cudaGetLastError();
 }
 

@@ -53,7 +53,7 @@ _P, _I, _L, _Fl = ctypes.c_void_p, ctypes.c_int, ctypes.c_long, ctypes.c_float
 nv.declare("mmt_gemm_set_comm", None, [ctypes.POINTER(GemmCommC)])
 nv.declare("mmt_rmsnorm_push", _I, [_P, _P, _P, ctypes.POINTER(PeerSetC), _P, _I, _L, _L, _I, _Fl, _P])
 nv.declare("mmt_rs_reduce", _I, [_P, _P, _I, _I, _I, _P, _P, _L, _I, _P])
-nv.declare("mmt_route_rows", _I, [_P, _P, _P, ctypes.POINTER(PeerSetC), _P, _I, _L, _I, _L, _L, _P])
+nv.declare("mmt_route_rows", _I, [_P, _P, _P, ctypes.POINTER(PeerSetC), _P, _I, _L, _I, _L, _L, _L, _P])
 nv.declare("mmt_wait_flags", _I, [_P, _I, _I, _I, _P])
 nv.declare("mmt_publish", _I, [ctypes.POINTER(PeerSetC), _I, _P])
 nv.declare("mmt_zero1_adamw", _I, [ctypes.POINTER(ZeroPeersC), _P, _I, _I, _P, _I, _P, _P, _P, _L, _L, _L, _Fl, _Fl,
@@ -177,13 +177,15 @@ class FusedComm:
 
     def route(self, src, dest_rank, dest_row, region: str, region_rows: int, cols: int):
         """Store src rows to (world rank, row) destinations of ``region`` and wait for everybody's rows."""
+        if dest_rank.dtype != torch.int32 or dest_row.dtype != torch.int64:
+            raise TypeError("route: dest_rank must be int32 and dest_row int64")
         off, local = self._region(region, (region_rows, cols))
         slot = self.ctx.slot(region)
         epoch = self.ctx.next_epoch(slot)
         ps = self.ctx.peerset(off, self.world_ranks, slot, self.mesh.rank)
         nv.call("mmt_route_rows", src.data_ptr(), dest_rank.data_ptr(), dest_row.data_ptr(), ctypes.byref(ps),
                 self.ctx.counter_addr(slot), epoch, src.shape[0], cols, src.stride(0) if src.shape[0] else cols, cols,
-                nv.stream())
+                region_rows, nv.stream())
         nv.call("mmt_wait_flags", self.ctx.local_flags(slot), self.mesh.world, -1, epoch, nv.stream())
         return local
 

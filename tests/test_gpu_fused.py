@@ -116,12 +116,23 @@ def test_route_rows_and_wait():
         dr_d, drow_d = dr.to(DEV), drow.to(DEV)      # keep the device copies alive across the launch
         keep.append((dr_d, drow_d))
         nv.call("mmt_route_rows", src[r].data_ptr(), dr_d.data_ptr(), drow_d.data_ptr(), ctypes.byref(ps),
-                counters[r].data_ptr(), 1, n, H, H, H, nv.stream())
+                counters[r].data_ptr(), 1, n, H, H, H, 200, nv.stream())
     torch.cuda.synchronize()
     for r in range(world):
         nv.call("mmt_wait_flags", flags[r].data_ptr(), world, -1, 1, nv.stream())
         assert torch.equal(region[r], expect[r])
     assert nv.get_error()[0] == 0
+    # a destination row outside the region is skipped and reported, never stored
+    ps = _peerset(fused, region, flags, 0)
+    bad_rank = torch.zeros(8, device=DEV, dtype=torch.int32)
+    bad_row = torch.full((8,), 10 ** 9, device=DEV, dtype=torch.int64)
+    nv.call("mmt_route_rows", src[0].data_ptr(), bad_rank.data_ptr(), bad_row.data_ptr(), ctypes.byref(ps),
+            counters[0].data_ptr(), 2, 8, H, H, H, 200, nv.stream())
+    torch.cuda.synchronize()
+    code, where = nv.get_error()[:2]
+    assert (code, where) == (3, 920)
+    nv.lib().mmt_clear_error()
+    assert torch.equal(region[0], expect[0])
 
 
 def test_zero1_adamw_matches_reduce_then_adamw():
