@@ -92,8 +92,13 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_co
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kv0 = blockIdx.x * BKV;
-  const int kv_head = blockIdx.y;
-  const int group = p.n_q / p.n_kv;
+  // grid.y = kv heads, each CTA looping over the q heads of its group; or, with a partial-sum workspace,
+  // grid.y = q heads (group times more CTAs for short sequences), each CTA writing its own fp32 partial
+  const bool split = p.ws_dk != nullptr;
+  const int full_group = p.n_q / p.n_kv;
+  const int kv_head = split ? (int)blockIdx.y / full_group : (int)blockIdx.y;
+  const int head0 = split ? (int)blockIdx.y : kv_head * full_group;
+  const int group = split ? 1 : full_group;
   const int kv_last = min(kv0 + BKV, p.T) - 1;
   const int q_lo = p.causal ? kv0 : p.seq_lo[kv0];
   const int q_hi = p.seq_hi[kv_last];
@@ -131,7 +136,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_co
       tma_load_2d(sV + CHUNK, &tm_qkv, kv_full, xv + 64, kv0);
       for (int it = 0; it < n_iter; ++it) {
         const int g = it / n_qt, i = it % n_qt;
-        const int head = kv_head * group + g;
+        const int head = head0 + g;
         const int r0 = q_lo + i * BQ;
         if (!mbar_wait(mma2_done, (it & 1) ^ 1, p.ew, 700)) break;
         mbar_expect_tx(qdo_full, 4 * CHUNK);
@@ -178,7 +183,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_co
     bool ok = true;
     for (int it = 0; it < n_iter; ++it) {
       const int g = it / n_qt, i = it % n_qt;
-      const int head = kv_head * group + g;
+      const int head = head0 + g;
       const int qrow = q_lo + i * BQ + row;
       const bool row_ok = qrow < q_hi;
       int lo = 0, hi = 0;
@@ -232,7 +237,15 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_co
 #pragma unroll
           for (int i = 0; i < 16; ++i) rk[i] = rv[i] = 0u;
         }
-        if (kvrow < p.T) {
+        if (kvrow < p.T && split) {
+          float* wk = p.ws_dk + ((long)head0 * p.T + kvrow) * DIM + c * 16;
+          float* wv = p.ws_dv + ((long)head0 * p.T + kvrow) * DIM + c * 16;
+#pragma unroll
+          for (int i = 0; i < 16; i += 4) {
+            *reinterpret_cast<uint4*>(wk + i) = make_uint4(rk[i], rk[i + 1], rk[i + 2], rk[i + 3]);
+            *reinterpret_cast<uint4*>(wv + i) = make_uint4(rv[i], rv[i + 1], rv[i + 2], rv[i + 3]);
+          }
+        } else if (kvrow < p.T) {
 #pragma unroll
           for (int h2 = 0; h2 < 2; ++h2) {
             uint4 a, b;
@@ -254,6 +267,31 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_co
   tc_fence_before();
   __syncthreads();
   if (warp == 5) tmem_dealloc(tmem_base, 512);
+}
+
+// dK / dV of a GQA group = sum of its q heads' fp32 partials, in head order (deterministic), rounded once.
+__global__ void attn_group_reduce_kernel(const float* __restrict__ ws_dk, const float* __restrict__ ws_dv,
+                                         __nv_bfloat16* __restrict__ dqkv, int T, int n_q, int n_kv, int dim, long ld) {
+  const int group = n_q / n_kv;
+  const int per_row = n_kv * dim / 4;                 // float4 items per token and tensor
+  const long idx = blockIdx.x * (long)blockDim.x + threadIdx.x;
+  if (idx >= (long)T * per_row * 2) return;
+  const int which = (int)(idx / ((long)T * per_row));  // 0 = dK, 1 = dV
+  const long rem = idx - (long)which * T * per_row;
+  const int t = (int)(rem / per_row);
+  const int e = (int)(rem % per_row) * 4;
+  const int kvh = e / dim, c = e % dim;
+  const float* ws = which ? ws_dv : ws_dk;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int g = 0; g < group; ++g) {
+    const float4 v = *reinterpret_cast<const float4*>(ws + ((long)(kvh * group + g) * T + t) * dim + c);
+    acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+  }
+  __nv_bfloat16* dst = dqkv + (long)t * ld + (long)(n_q + which * n_kv + kvh) * dim + c;
+  uint2 o;
+  o.x = pack_bf16x2(acc.x, acc.y);
+  o.y = pack_bf16x2(acc.z, acc.w);
+  *reinterpret_cast<uint2*>(dst) = o;
 }
 
 // ----------------------------------------------------------------------------------------------
@@ -457,17 +495,24 @@ int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tdo, const AttnParams& 
     attr = true;
   }
   const int tiles = (p.T + BQ - 1) / BQ;
-  attn_bwd_dkdv_kernel<DIM><<<dim3(tiles, p.n_kv), kThreads, kBwdSmem, st>>>(tq, tdo, p);
+  attn_bwd_dkdv_kernel<DIM><<<dim3(tiles, p.ws_dk ? p.n_q : p.n_kv), kThreads, kBwdSmem, st>>>(tq, tdo, p);
+  if (p.ws_dk) {
+    const long items = (long)p.T * (p.n_kv * DIM / 4) * 2;
+    attn_group_reduce_kernel<<<(unsigned)((items + 255) / 256), 256, 0, st>>>(p.ws_dk, p.ws_dv, p.dqkv, p.T, p.n_q,
+                                                                             p.n_kv, DIM, p.ld);
+  }
   attn_bwd_dq_kernel<DIM><<<dim3(tiles, p.n_q), kThreads, kBwdSmem, st>>>(tq, tdo, p);
   return (int)cudaGetLastError();
 }
 
 }  // namespace
 
-// dqkv [T, ld] receives dq | dk | dv in the layout of qkv.  delta is fp32 scratch [n_q, T].
+// dqkv [T, ld] receives dq | dk | dv in the layout of qkv.  delta is fp32 scratch [n_q, T].  ws is optional fp32
+// scratch of 2 * n_q * T * dim floats: with it (and n_q > n_kv) dK/dV run one CTA per q head and are summed over
+// each GQA group afterwards, which fills the GPU when there are few KV tiles.
 extern "C" int mmt_attn_bwd(const void* qkv, const void* out, const void* dout, const float* lse, float* delta,
                             void* dqkv, const int* seq_lo, const int* seq_hi, long T, int n_q, int n_kv, int dim,
-                            long ld, int causal, float scale, void* stream) {
+                            long ld, int causal, float scale, float* ws, void* stream) {
   if (T <= 0) return 0;
   if (mmt_ensure_context(qkv)) return -7;
   if ((dim != 80 && dim != 128) || n_q % n_kv || (ld & 7)) return -2;
@@ -498,5 +543,8 @@ extern "C" int mmt_attn_bwd(const void* qkv, const void* out, const void* dout, 
   p.dout = reinterpret_cast<const __nv_bfloat16*>(dout);
   p.delta = delta;
   p.dqkv = reinterpret_cast<__nv_bfloat16*>(dqkv);
+  const bool split = ws != nullptr && n_q > n_kv;
+  p.ws_dk = split ? ws : nullptr;
+  p.ws_dv = split ? ws + (long)n_q * T * dim : nullptr;
   return dim == 80 ? launch_bwd<80>(tq, tdo, p, st) : launch_bwd<128>(tq, tdo, p, st);
 }

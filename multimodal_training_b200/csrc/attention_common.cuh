@@ -31,6 +31,8 @@ struct AttnParams {
   const __nv_bfloat16* dout;   // [T, n_q*dim]
   const float* delta;          // [n_q, T]  rowsum(out * dout)
   __nv_bfloat16* dqkv;         // [T, ld]
+  float* ws_dk;                // optional [n_q, T, dim] fp32 per-q-head partial dK (GQA: one CTA per q head)
+  float* ws_dv;
 };
 
 // byte offset of element (row, col) inside a [128 x 64] SW128 box with 128-byte rows

@@ -121,9 +121,14 @@ class _Sm100AttentionFn(torch.autograd.Function):
         dout = dout if dout.is_contiguous() else dout.contiguous()
         dqkv = torch.empty_like(qkv)
         delta = torch.empty(n_q, T, device=qkv.device, dtype=torch.float32)
+        # GQA with few KV tiles: one dK/dV CTA per q head needs an fp32 partial-sum workspace
+        tiles = (T + 127) // 128
+        ws = None
+        if n_q > n_kv and tiles * n_kv < 2 * _sm_count():
+            ws = torch.empty(2 * n_q * T * dim, device=qkv.device, dtype=torch.float32)
         nv.call("mmt_attn_bwd", qkv.data_ptr(), out.data_ptr(), dout.data_ptr(), lse.data_ptr(), delta.data_ptr(),
                 dqkv.data_ptr(), lo.data_ptr(), hi.data_ptr(), T, n_q, n_kv, dim, qkv.stride(0), int(causal), scale,
-                nv.stream())
+                nv.ptr(ws), nv.stream())
         return dqkv, None, None, None, None, None, None
 
 
@@ -138,4 +143,8 @@ def flash_attention(qkv: torch.Tensor, n_q: int, n_kv: int, dim: int, info: SeqI
 nv.declare("mmt_attn_fwd", nv.c_int, [nv._P, nv._P, nv._P, nv._P, nv._P, nv.c_long, nv.c_int, nv.c_int, nv.c_int,
                                       nv.c_long, nv.c_int, nv.c_float, nv._P])
 nv.declare("mmt_attn_bwd", nv.c_int, [nv._P, nv._P, nv._P, nv._P, nv._P, nv._P, nv._P, nv._P, nv.c_long, nv.c_int,
-                                      nv.c_int, nv.c_int, nv.c_long, nv.c_int, nv.c_float, nv._P])
+                                      nv.c_int, nv.c_int, nv.c_long, nv.c_int, nv.c_float, nv._P, nv._P])
+
+
+def _sm_count() -> int:
+    return torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
