@@ -39,6 +39,10 @@ REFERENCE_UNAVAILABLE = (
     "the image or the wheelhouse")
 
 
+MODEL_NAMES = {"qwen2_5_vl_3b": "Qwen2.5-VL-3B", "qwen2_5_vl_7b": "Qwen2.5-VL-7B", "qwen2_5_vl_32b": "Qwen2.5-VL-32B",
+               "qwen2_5_vl_72b": "Qwen2.5-VL-72B"}
+
+
 def _clock_sampler(path: str):
     q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
          "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
@@ -87,6 +91,8 @@ def main() -> int:
     ap.add_argument("--image-size", type=int, default=896)
     ap.add_argument("--text-tokens", type=int, default=1024)
     ap.add_argument("--per-gpu-batch", type=int, default=1)
+    ap.add_argument("--global-batch", type=int, default=0, help="overrides --per-gpu-batch x N (other configs)")
+    ap.add_argument("--tp", type=int, default=0, help="text tensor-parallel size (default min(N, 4))")
     ap.add_argument("--no-fused-comm", action="store_true")
     args = ap.parse_args()
 
@@ -117,9 +123,11 @@ def main() -> int:
     from multimodal_training_b200.ops import native as nv
 
     N = args.gpus
-    tp = min(N, 4)
+    tp = args.tp or min(N, 4)
     sp = N
-    global_batch = N * args.per_gpu_batch
+    global_batch = args.global_batch or N * args.per_gpu_batch
+    if global_batch % (N // tp):
+        raise SystemExit(f"global batch {global_batch} is not divisible by the {N // tp} text data-parallel replicas")
     ov = [
         f"vision.model_name={args.model}", f"text.model_name={args.model}",
         "vision.parallelism=sequence", "text.parallelism=tensor", f"text.tensor_parallel_size={tp}",
@@ -162,8 +170,10 @@ def main() -> int:
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     last = None
+    h0 = time.perf_counter()
     for s in range(args.steps):
         last = engine.train_step(step0 + s)
+    host_enqueue_ms = (time.perf_counter() - h0) * 1e3 / args.steps
     e1.record()
     barrier()
     dev_ms = e0.elapsed_time(e1)
@@ -174,8 +184,15 @@ def main() -> int:
     step0 += args.steps
     barrier()
     t0 = time.perf_counter()
+    # every step: inputs go host -> device from pinned memory inside train_step, the loss goes device -> host into
+    # pinned memory; the host reads the loss of step s-1 after it has launched step s
+    pending = None
     for s in range(args.steps):
-        losses.append(float(engine.train_step(step0 + s).item()))
+        handle = engine.train_step_async(step0 + s)
+        if pending is not None:
+            losses.append(pending.value())
+        pending = handle
+    losses.append(pending.value())
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
     barrier()
@@ -205,7 +222,8 @@ def main() -> int:
         e2e_value = patches / (e2e_ms / args.steps / 1e3)
         par = f"sp{sp}" + (f"+tp{tp}" if tp > 1 else "") + (f"xdp{N // tp}" if N // tp > 1 else "")
         out = {
-            "metric": "Qwen2.5-VL-7B train tokens/s (vision patches x global batch / step time, max over ranks)",
+            "metric": f"{MODEL_NAMES.get(args.model, args.model)} train tokens/s (vision patches x global batch / step "
+                      "time, max over ranks)",
             "value": value, "unit": "tokens/s", "n_gpus": N, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic (N(0,1) pixels, uniform-random token ids, random-init weights)",
@@ -225,7 +243,9 @@ def main() -> int:
             "clocks": _parse_clocks(clock_path, N),
             "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": e2e_ms / args.steps,
                     "h2d_bytes_per_step": float(h2d[0]), "d2h_bytes_per_step": 4.0 * N,
-                    "timer": "host wall clock between barriers, max over ranks"},
+                    "timer": "host wall clock between barriers, max over ranks",
+                    "loss_read": "copied to pinned host memory every step, read by the host one step later"},
+            "host_enqueue_ms_per_step": host_enqueue_ms,
             "gpu_launches": int(launches),
         }
         print(json.dumps(out))

@@ -71,6 +71,7 @@ DEFAULTS: dict[str, Any] = {
         "backend": None,           # torch.distributed backend: default nccl on GPU, gloo on CPU
         "runtime": "auto",         # actor runtime: auto | ray | builtin
         "fused_comm": True,        # peer-memory fused collectives when a symmetric heap is available
+        "symm_heap_mb": 8192,      # size of each GPU's symmetric heap (exchange buffers of the fused collectives)
     },
     "data": {
         "datasets": [],

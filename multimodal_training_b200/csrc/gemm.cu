@@ -70,7 +70,8 @@ struct GemmParams {
 };
 
 // tile index -> (tile_m, tile_n); with an all-gather consumer the m tiles are rotated so that the CTA wave
-// starts on this rank's own rows while the peers' rows are still in flight.
+// starts on this rank's own rows while the peers' rows are still in flight; with a reduce-scatter producer they
+// are rotated so that the ranks' stores are spread over the owners.
 MMT_DEVICE void tile_coords(const GemmParams& p, int tile, int tiles_m, int bmt, int& tm, int& tn) {
   // Grouped raster: tiles are walked in bands of `group_m` m-tiles, n-fastest inside a band... i.e. a wave of
   // CTAs covers a roughly square block of the output, so every A and B tile it needs is shared by many CTAs
@@ -83,6 +84,9 @@ MMT_DEVICE void tile_coords(const GemmParams& p, int tile, int tiles_m, int bmt,
   tm = first + local % rows;
   tn = local / rows;
   if (p.ag_flags) tm = (tm + (int)(((long)p.ag_self * p.ag_rows) / bmt)) % tiles_m;
+  // reduce-scatter producer: rank r starts on the rows owned by rank r + 1, so at any moment the ranks store
+  // into different owners instead of all converging on rank 0's NVLink ingress
+  else if (p.rs_rows) tm = (tm + (int)(((long)((p.rs_self + 1) % p.rs_ranks) * p.rs_rows) / bmt)) % tiles_m;
 }
 
 // MT = number of 128-row accumulators per CTA tile.  MT == 1: 128 x BN tile, the accumulator is double

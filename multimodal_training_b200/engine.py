@@ -18,6 +18,20 @@ from .trainers.trainer import process_state
 from .trainers.vision import VisionTrainer
 
 
+class LossHandle:
+    """Loss of one step on its way to the host (see ``HybridEngine.train_step_async``)."""
+
+    __slots__ = ("host", "event")
+
+    def __init__(self, host: torch.Tensor, event):
+        self.host, self.event = host, event
+
+    def value(self) -> float:
+        if self.event is not None:
+            self.event.synchronize()
+        return float(self.host[0])
+
+
 class HybridEngine:
     def __init__(self, vision_config: dict, text_config: dict, rank: int | None = None):
         import os
@@ -72,6 +86,27 @@ class HybridEngine:
             tr.global_step += 1
         self.step_index = step + 1
         return t_out["loss"]
+
+    def train_step_async(self, step: int | None = None) -> "LossHandle":
+        """``train_step`` plus a non-blocking copy of the loss into pinned host memory.
+
+        The host does not wait for the GPU: the returned handle's ``value()`` waits for that step's copy only, so
+        a training loop that reads the loss of step s-1 after launching step s logs every loss without ever
+        draining the launch queue.  At most ``len(ring)`` handles may be outstanding.
+        """
+        loss = self.train_step(step)
+        if not hasattr(self, "_loss_ring"):
+            pin = loss.is_cuda
+            self._loss_ring = [torch.zeros(1, dtype=torch.float32, pin_memory=pin) for _ in range(8)]
+            self._loss_i = 0
+        host = self._loss_ring[self._loss_i % len(self._loss_ring)]
+        self._loss_i += 1
+        host.copy_(loss.detach().float().reshape(1), non_blocking=True)
+        event = None
+        if loss.is_cuda:
+            event = torch.cuda.Event()
+            event.record()
+        return LossHandle(host, event)
 
     def mean_loss(self, loss: torch.Tensor) -> float:
         """Mean over text replicas (every TP rank of a replica holds the same loss)."""

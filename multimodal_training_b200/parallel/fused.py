@@ -344,7 +344,7 @@ def try_create(mesh, config):
                 return None, None
         if mesh.world > MAX_PEERS:
             return None, None
-        heap_mb = int(config.get("symm_heap_mb", 2048))
+        heap_mb = int(config.get("symm_heap_mb", 8192))
         fc = FusedComm(mesh, dev, heap_mb << 20, checkpointed=bool(config.get("activation_checkpointing", True)))
         return fc.ctx, fc
     except Exception as e:  # the NCCL path still works; say why the fused one does not

@@ -85,7 +85,8 @@ class SymmetricHeap:
             return off
         off = (self._off + align - 1) // align * align
         if off + nbytes > self.nbytes:
-            raise MemoryError(f"symmetric heap exhausted: {off + nbytes} > {self.nbytes} bytes (region {name})")
+            raise MemoryError(f"symmetric heap exhausted: {off + nbytes} > {self.nbytes} bytes (region {name}); "
+                              "raise training.symm_heap_mb")
         self._off = off + nbytes
         self._regions[name] = (off, nbytes)
         return off
