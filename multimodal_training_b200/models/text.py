@@ -9,10 +9,14 @@ from the reference/HF key layout (q_proj/k_proj/v_proj, gate_proj/up_proj).
 """
 from __future__ import annotations
 
+import math
+
 import torch
 import torch.nn as nn
 
 from ..config.model_configs import TextConfig
+from ..ops import attention as attn_mod
+from ..ops import blocks
 from ..ops import functional as F
 from ..ops.attention import SeqInfo
 from ..parallel import comm
@@ -119,6 +123,18 @@ class TextDecoder(nn.Module):
     def forward(self, x_shard: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, seq: SeqInfo) -> torch.Tensor:
         """[T/tp, H] token shard -> final hidden token shard (before the last norm)."""
         x = x_shard
+        # without tensor parallelism a layer has no communication inside and runs as one hand-written autograd
+        # node (ops/blocks.py); tensor-parallel layers, the CPU path and un-checkpointed runs use the per-op graph
+        one_node = (self.tp.size == 1 and self.ckpt and torch.is_grad_enabled() and blocks.usable(x)
+                    and attn_mod.BACKEND == "sm100")
+        if one_node:
+            d = self.cfg.head_dim
+            spec = blocks.BlockSpec(n_q=self.n_q, n_kv=self.n_kv, head_dim=d, rope_heads=self.n_q + self.n_kv,
+                                    causal=True, eps=self.cfg.rms_norm_eps, scale=1.0 / math.sqrt(d))
+            for L in self.layers:
+                x = blocks.local_block(x, spec, cos, sin, seq, (L.ln1_w, L.qkv_w, L.qkv_b, L.o_w, None, L.ln2_w,
+                                                                L.gate_up_w, None, L.down_w, None))
+            return x
         for L in self.layers:
             x = checkpoint(lambda t, L=L: self._layer(t, L, cos, sin, seq), (x,), enabled=self.ckpt)
         return x

@@ -20,10 +20,14 @@ What differs by design:
 """
 from __future__ import annotations
 
+import math
+
 import torch
 import torch.nn as nn
 
 from ..config.model_configs import VisionConfig
+from ..ops import attention as attn_mod
+from ..ops import blocks
 from ..ops import functional as F
 from ..ops.attention import SeqInfo
 from ..parallel import comm
@@ -134,8 +138,19 @@ class VisionEncoder(nn.Module):
         win_seq = plan.win_seq
         full_seq = plan.full_seq if self.sp.size > 1 else plan.local_image_seq
         x = F.linear(local_patches, self.patch_embed_w)
+        # blocks without communication inside run as one hand-written autograd node each (ops/blocks.py); the
+        # Ulysses layers of a sequence-parallel run, the CPU path and un-checkpointed runs use the per-op graph
+        one_node = self.ckpt and torch.is_grad_enabled() and blocks.usable(x) and attn_mod.BACKEND == "sm100"
+        spec = blocks.BlockSpec(n_q=cfg.num_heads, n_kv=cfg.num_heads, head_dim=cfg.head_dim,
+                                rope_heads=2 * cfg.num_heads, causal=False, eps=cfg.rms_norm_eps,
+                                scale=1.0 / math.sqrt(cfg.head_dim))
         for i, B in enumerate(self.blocks):
             is_full = i in cfg.fullatt_block_indexes
+            if one_node and (not is_full or self.sp.size == 1):
+                x = blocks.local_block(x, spec, cos, sin, full_seq if is_full else win_seq,
+                                       (B.norm1_w, B.qkv_w, B.qkv_b, B.proj_w, B.proj_b, B.norm2_w, B.gate_up_w,
+                                        B.gate_up_b, B.down_w, B.down_b))
+                continue
             x = checkpoint(lambda t, B=B, f=is_full: self._block(t, B, cos, sin, plan, win_seq, full_seq, f), (x,),
                            enabled=self.ckpt)
         h = F.rmsnorm(x, self.ln_q_w, cfg.rms_norm_eps)

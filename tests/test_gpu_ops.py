@@ -205,3 +205,64 @@ def test_native_library_is_loaded():
     F, nv = _F()
     assert isinstance(nv.lib(), ctypes.CDLL)
     assert nv.lib().mmt_version().decode().startswith("mmt_b200")
+
+
+@pytest.mark.parametrize("kind", ["vision", "text"])
+def test_local_block_matches_per_op_graph(kind):
+    """The one-node transformer block (hand-written backward) against the same block built from the per-op
+    autograd functions: same kernels, so outputs and every gradient agree to rounding."""
+    import math
+    F, nv = _F()
+    from multimodal_training_b200.ops import blocks
+    from multimodal_training_b200.ops.attention import SeqInfo
+    torch.manual_seed(11)
+    if kind == "vision":
+        n_q, n_kv, d, C, inter, causal, cu = 4, 4, 80, 320, 512, False, [0, 64, 128, 192, 300]
+        has_bias = (True, True, True, True)
+    else:
+        n_q, n_kv, d, C, inter, causal, cu = 4, 2, 128, 512, 768, True, [0, 200, 456]
+        has_bias = (True, False, False, False)
+    T = cu[-1]
+    W = (n_q + 2 * n_kv) * d
+
+    def P(*shape, scale=0.05):
+        return (torch.randn(*shape, device=DEV, dtype=torch.bfloat16) * scale).requires_grad_()
+
+    def make():
+        torch.manual_seed(12)
+        return dict(ln1=P(C, scale=1.0), qkv_w=P(W, C), qkv_b=P(W) if has_bias[0] else None, o_w=P(C, n_q * d),
+                    o_b=P(C) if has_bias[1] else None, ln2=P(C, scale=1.0), gu_w=P(2 * inter, C),
+                    gu_b=P(2 * inter) if has_bias[2] else None, dn_w=P(C, inter), dn_b=P(C) if has_bias[3] else None)
+
+    x0 = torch.randn(T, C, device=DEV, dtype=torch.bfloat16)
+    dy = torch.randn(T, C, device=DEV, dtype=torch.bfloat16)
+    cos = torch.rand(T, d, device=DEV, dtype=torch.float32)
+    sin = torch.rand(T, d, device=DEV, dtype=torch.float32)
+    seq = SeqInfo.from_list(cu, DEV)
+    rope_heads = n_q + n_kv
+
+    def per_op(x, p):
+        h = F.rmsnorm(x, p["ln1"], 1e-6)
+        qkv = F.rope(F.linear(h, p["qkv_w"], p["qkv_b"]), cos, sin, rope_heads, d)
+        a = F.attention(qkv, n_q, n_kv, d, seq, causal=causal)
+        x1 = F.linear(a, p["o_w"], p["o_b"], x)
+        h2 = F.rmsnorm(x1, p["ln2"], 1e-6)
+        m = F.swiglu(F.linear(h2, p["gu_w"], p["gu_b"]))
+        return F.linear(m, p["dn_w"], p["dn_b"], x1)
+
+    pa, pb = make(), make()
+    xa = x0.clone().requires_grad_()
+    ya = per_op(xa, pa)
+    ya.backward(dy)
+    xb = x0.clone().requires_grad_()
+    spec = blocks.BlockSpec(n_q=n_q, n_kv=n_kv, head_dim=d, rope_heads=rope_heads, causal=causal, eps=1e-6,
+                            scale=1.0 / math.sqrt(d))
+    yb = blocks.local_block(xb, spec, cos, sin, seq, (pb["ln1"], pb["qkv_w"], pb["qkv_b"], pb["o_w"], pb["o_b"],
+                                                      pb["ln2"], pb["gu_w"], pb["gu_b"], pb["dn_w"], pb["dn_b"]))
+    yb.backward(dy)
+    assert nv.get_error()[0] == 0
+    assert rel_err(yb, ya.float()) < 1e-3
+    assert rel_err(xb.grad, xa.grad.float()) < 1e-2
+    for k in pa:
+        if pa[k] is not None:
+            assert rel_err(pb[k].grad, pa[k].grad.float()) < 1e-2, k
