@@ -310,7 +310,9 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tm, const AttnParams p, con
   int q0[2], head[2], kv_lo[2], n_tiles[2], xq[2], xk[2], xv[2];
 #pragma unroll
   for (int w = 0; w < 2; ++w) {
-    const int item = blockIdx.x * 2 + w;
+    // causal: the last query tiles see the most KV tiles, so they are started first (longest work first)
+    const int cta = p.causal ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;
+    const int item = cta * 2 + w;
     n_tiles[w] = 0;
     q0[w] = head[w] = kv_lo[w] = xq[w] = xk[w] = xv[w] = 0;
     if (item < n_items) {
