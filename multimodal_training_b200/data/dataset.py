@@ -118,6 +118,31 @@ class LazySupervisedDataset(Dataset):
         return item
 
 
+def default_processor(model_name, model_cfg=None):
+    """The model's own HF processor when its files are on this machine, else the in-tree image processor and
+    chat template (``data/processor.py``) around the HF tokenizer if that is available, else around the byte
+    tokenizer (synthetic and test runs)."""
+    import logging
+    from .processor import ByteTokenizer, Qwen2_5_VLImageProcessor, Qwen2_5_VLProcessor
+    try:
+        from transformers import AutoProcessor
+        return AutoProcessor.from_pretrained(model_name, local_files_only=True)
+    except Exception as e:  # no files / no network: say so once and continue with the in-tree one
+        logging.getLogger("mmt_b200").warning("HF processor for %s unavailable (%s): using the in-tree processor",
+                                              model_name, type(e).__name__)
+    tok = None
+    try:
+        from transformers import AutoTokenizer
+        tok = AutoTokenizer.from_pretrained(model_name, local_files_only=True)
+    except Exception:
+        tok = ByteTokenizer()
+    v = getattr(model_cfg, "vision", None)
+    ip = Qwen2_5_VLImageProcessor(patch_size=getattr(v, "patch_size", 14),
+                                  temporal_patch_size=getattr(v, "temporal_patch_size", 2),
+                                  merge_size=getattr(v, "spatial_merge_size", 2))
+    return Qwen2_5_VLProcessor(ip, tok)
+
+
 def build_dataloader(processor, data_config: DataConfig, batch_size: int, rank: int = 0, world_size: int = 1,
                      generator=None, worker_init_fn=None, drop_last: bool = True, modality: str = "all",
                      seed: int = 42, **dataset_kw) -> DataLoader:
@@ -145,8 +170,7 @@ class DatasetSource:
     def __init__(self, config: dict, model_cfg, mesh, processor=None):
         self.cfg = DataConfig.from_flat(config)
         if processor is None:
-            from transformers import AutoProcessor
-            processor = AutoProcessor.from_pretrained(config.get("model_name"), local_files_only=True)
+            processor = default_processor(config.get("model_name"), model_cfg)
         self.dataset = LazySupervisedDataset(processor, self.cfg, modality="all", seed=int(config.get("seed", 42)),
                                              spatial_merge_size=model_cfg.vision.spatial_merge_size,
                                              image_token_id=model_cfg.image_token_id,
