@@ -68,6 +68,7 @@ DEFAULTS: dict[str, Any] = {
         "checkpoint_dir": "/tmp/checkpoints",
         "log_interval": 1,
         "profile_time": False,
+        "trace": False,            # NVTX ranges + device-timed phases (utils/tracing.py)
         "backend": None,           # torch.distributed backend: default nccl on GPU, gloo on CPU
         "runtime": "auto",         # actor runtime: auto | ray | builtin
         "fused_comm": True,        # peer-memory fused collectives when a symmetric heap is available

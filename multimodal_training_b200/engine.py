@@ -16,6 +16,7 @@ import torch.distributed as dist
 from .trainers.text import TextTrainer
 from .trainers.trainer import process_state
 from .trainers.vision import VisionTrainer
+from .utils import tracing
 
 
 class LossHandle:
@@ -47,6 +48,11 @@ class HybridEngine:
         self.max_norm = float(text_config.get("max_grad_norm", 1.0))
         self.step_index = 0
         self.last_grad_norm = None
+        # device-timed phases (CUDA events, no host syncs) when training.trace is on
+        self.timer = None
+        if bool(text_config.get("trace", False)) or tracing.enabled():
+            tracing.enable(True)
+            self.timer = tracing.PhaseTimer()
 
     @classmethod
     def from_config(cls, cfg: dict) -> "HybridEngine":
@@ -71,19 +77,27 @@ class HybridEngine:
     def train_step(self, step: int | None = None) -> torch.Tensor:
         """One optimisation step on the global batch of ``step``; returns this rank's loss (device scalar)."""
         step = self.step_index if step is None else step
+        ph = self.timer.phase if self.timer is not None else (lambda name: tracing.trace_range(name))
         self.vision.zero_grad()
         self.text.zero_grad()
-        v_out = self.vision.forward_step(step)
-        t_out = self.text.forward_step(v_out, step)
-        g = self.text.backward_step()
+        with ph("vision.forward"):
+            v_out = self.vision.forward_step(step)
+        with ph("text.forward"):
+            t_out = self.text.forward_step(v_out, step)
+        with ph("text.backward"):
+            g = self.text.backward_step()
         if g["grad"] is not None:
-            self.vision.backward_step(g)
-        scale = self._global_grad_scale() if self.clip else None
-        for tr in (self.text, self.vision):
-            shard = getattr(tr, "_reduced_shard", None)
-            tr._reduced_shard = None
-            tr.optimizer.step(lr=tr.current_lr(), grad_scale=scale, shard=shard)
-            tr.global_step += 1
+            with ph("vision.backward"):
+                self.vision.backward_step(g)
+        with ph("optimizer"):
+            scale = self._global_grad_scale() if self.clip else None
+            for tr in (self.text, self.vision):
+                shard = getattr(tr, "_reduced_shard", None)
+                tr._reduced_shard = None
+                tr.optimizer.step(lr=tr.current_lr(), grad_scale=scale, shard=shard)
+                tr.global_step += 1
+        if self.timer is not None:
+            self.timer.end_step()
         self.step_index = step + 1
         return t_out["loss"]
 

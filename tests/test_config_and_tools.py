@@ -140,3 +140,23 @@ def test_vision_token_calculator_and_sweep_generator(tmp_path, capsys):
     assert cfg["data"]["force_fixed_size"] and cfg["data"]["synthetic"]["image_size"] == 448
     big = load_config(tmp_path / "sweep" / "configs" / "32b_64k_tokens_sequence_bs2.yaml")
     assert big["deepspeed"]["reduce_bucket_size"] == 100000000 and big["training"]["parallel_size"] == 8
+
+
+def test_phase_timer_and_chrome_trace(tmp_path):
+    import json
+    import time
+    from multimodal_training_b200.utils import tracing
+    t = tracing.PhaseTimer(use_cuda=False)
+    for _ in range(2):
+        with t.phase("a"):
+            time.sleep(0.002)
+        with t.phase("b"):
+            pass
+        t.end_step()
+    s = t.summary()
+    assert set(s) == {"a", "b"} and s["a"] >= 1.0 and s["b"] < s["a"]
+    path = t.chrome_trace(str(tmp_path / "trace.json"), rank=3)
+    ev = json.load(open(path))["traceEvents"]
+    assert len(ev) == 4 and ev[0]["pid"] == 3 and ev[0]["args"]["step"] == 0 and ev[-1]["args"]["step"] == 1
+    with tracing.trace_range("noop"):        # off by default: must be a plain no-op
+        pass
