@@ -87,6 +87,7 @@ def main(argv=None) -> int:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--no-flush", action="store_true")
     ap.add_argument("--fwd-version", type=int, default=0, help="attention forward: 2 = ping-pong kernel, 1 = first one")
+    ap.add_argument("--bwd-version", type=int, default=0, help="attention backward: 2 = pipelined kernels, 1 = first ones")
     ap.add_argument("--pair", type=int, default=-1, help="GEMM: 1 = 2-CTA kernel, 0 = 1-CTA kernels, -1 = default")
     a = ap.parse_args(argv)
     dev = "cuda"
@@ -94,6 +95,8 @@ def main(argv=None) -> int:
     flush = not a.no_flush
     if a.fwd_version:
         nv.lib().mmt_attn_set_fwd_version(a.fwd_version)
+    if a.bwd_version:
+        nv.lib().mmt_attn_set_bwd_version(a.bwd_version)
     if a.kernel == "gemm":
         if a.pair >= 0:
             nv.lib().mmt_gemm_use_pair(a.pair)
