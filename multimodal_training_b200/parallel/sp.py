@@ -161,9 +161,33 @@ class Geometry:
         return np.concatenate(parts) if parts else np.zeros(0, np.int64)
 
 
+# Geometry and plans depend only on the image grids and the split, not on the pixels; batches of a fixed
+# resolution repeat them every step, so the most recent ones are kept (with the device tensors that
+# ``models.vision.prepare_plan`` attaches to a plan).
+_GEOM_CACHE: dict = {}
+_PLAN_CACHE: dict = {}
+_CACHE_LIMIT = 16
+
+
+def _cache_put(cache: dict, key, value):
+    if len(cache) >= _CACHE_LIMIT:
+        cache.pop(next(iter(cache)))
+    cache[key] = value
+    return value
+
+
 def compute_geometry(grid_thw, *, sp: int, spatial_merge_size: int = 2, window_size: int = 112,
                      patch_size: int = 14, window_aligned: bool = True) -> Geometry:
     grid_thw = [tuple(int(x) for x in g) for g in grid_thw]
+    key = (tuple(grid_thw), sp, spatial_merge_size, window_size, patch_size, window_aligned)
+    hit = _GEOM_CACHE.get(key)
+    if hit is not None:
+        return hit
+    return _cache_put(_GEOM_CACHE, key, _compute_geometry(grid_thw, sp, spatial_merge_size, window_size, patch_size,
+                                                          window_aligned))
+
+
+def _compute_geometry(grid_thw, sp, spatial_merge_size, window_size, patch_size, window_aligned) -> Geometry:
     unit = spatial_merge_size ** 2
     widx, cu_win = window_index(grid_thw, spatial_merge_size, window_size, patch_size)
     n_patches = sum(t * h * w for t, h, w in grid_thw)
@@ -195,6 +219,16 @@ def build_vision_plan(grid_thw, *, sp: int, rank: int, spatial_merge_size: int =
     if geom is None:
         geom = compute_geometry(grid_thw, sp=sp, spatial_merge_size=spatial_merge_size, window_size=window_size,
                                 patch_size=patch_size, window_aligned=window_aligned)
+    key = (id(geom), sp, rank, head_dim)
+    hit = _PLAN_CACHE.get(key)
+    if hit is not None and hit[0] is geom:
+        return hit[1]
+    plan = _build_vision_plan(geom, sp, rank, head_dim)
+    _cache_put(_PLAN_CACHE, key, (geom, plan))
+    return plan
+
+
+def _build_vision_plan(geom: Geometry, sp: int, rank: int, head_dim: int) -> VisionPlan:
     grid_thw, unit, widx, cu_arr = geom.grid_thw, geom.unit, geom.widx, geom.cu_arr
     img_start, patch_in_window_order, pos, slices = geom.img_start, geom.patch_in_window_order, geom.pos, geom.slices
     n_patches = geom.n_patches
