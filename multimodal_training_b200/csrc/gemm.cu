@@ -23,6 +23,7 @@
 // (python/models/qwen2_5_vl/modeling_qwen2_5_vl.py:198-200,334-338,1143-1145,1226-1229).
 #include <cudaTypedefs.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include "common.cuh"
@@ -53,6 +54,14 @@ struct GemmParams {
   int group_m, tiles_n;           // raster: m-tiles per band (0 = all), number of n-tiles
   uint32_t mn_lbo, mn_sbo, mn_kstep;  // descriptor constants of MN-major tiles
   MmtErrorWord* ew;
+  // --- stream-K for the last partial wave: the final `sk_tiles` tiles are cut along K into gridDim.x equal runs of
+  //     k-blocks, one per CTA; a CTA that does not reach the end of a tile leaves its fp32 partial in `sk_ws`
+  //     (slot = CTA index) and raises sk_flags[CTA] to sk_epoch; the CTA that reaches the end adds the partials of
+  //     the CTAs before it, in CTA order, and runs the epilogue.  sk_tiles == 0: off.
+  int sk_tiles;
+  float* sk_ws;
+  int* sk_flags;
+  int sk_epoch;
   int dbg;                        // measurement only: bit 0 = operands are loaded once (ring filled, then reused), bit 1 = no
                                   // per-stage commit, bit 2 = no TMA stores, bit 3 = no epilogue work at all
   unsigned long long* clk;        // optional: CTA 0 writes {SM cycles, nanoseconds} it spent in the kernel
@@ -87,6 +96,68 @@ MMT_DEVICE void tile_coords(const GemmParams& p, int tile, int tiles_m, int bmt,
   // reduce-scatter producer: rank r starts on the rows owned by rank r + 1, so at any moment the ranks store
   // into different owners instead of all converging on rank 0's NVLink ingress
   else if (p.rs_rows) tm = (tm + (int)(((long)((p.rs_self + 1) % p.rs_ranks) * p.rs_rows) / bmt)) % tiles_m;
+}
+
+// One unit of work of a CTA: k-blocks [k0, k1) of tile `tile`.
+//   kind 0: a whole tile;  kind 1: a run that stops before the tile's last k-block (partial sums go to the
+//   workspace);  kind 2: a run that ends the tile after other CTAs did its first k-blocks (their partial sums
+//   are added before the epilogue; `first_contrib` .. cta - 1 are those CTAs).
+struct WorkItem {
+  int tile, k0, k1, kind, first_contrib;
+};
+
+// i-th work item of CTA `cta`: the stream-K runs first (partial sums before finishing runs, so that they are ready
+// when their tile ends), then this CTA's whole tiles.
+MMT_DEVICE bool work_item(const GemmParams& p, int i, int cta, int grid, int KB, int ntiles, WorkItem& w) {
+  const int i0 = i;
+  const int full = ntiles - p.sk_tiles;
+  int n_sk = 0;
+  if (p.sk_tiles > 0) {
+    const long units = (long)p.sk_tiles * KB;
+    const long u0 = units * cta / grid, u1 = units * (cta + 1) / grid;
+    if (u1 > u0) {
+      const int ta = (int)(u0 / KB);
+      const long end_a = min(u1, (long)(ta + 1) * KB);
+      n_sk = u1 > end_a ? 2 : 1;
+      // a run that crosses into the next tile is worked in two items; the head of the NEXT tile (a partial sum, which
+      // depends on nobody) goes first and the tail of the current tile (which may have to wait for the CTAs before
+      // this one) second: partial sums are then produced by all CTAs at once instead of one CTA after the other
+      if (n_sk == 2) i = 1 - i;
+      if (i == 0) {
+        w.tile = full + ta;
+        w.k0 = (int)(u0 - (long)ta * KB);
+        w.k1 = (int)(end_a - (long)ta * KB);
+        w.first_contrib = cta;
+        if (w.k1 < KB) {
+          w.kind = 1;
+        } else if (w.k0 == 0) {
+          w.kind = 0;
+        } else {
+          w.kind = 2;
+          int c = cta;                       // CTAs before this one whose run ends inside this tile
+          while (c > 0 && units * c / grid > (long)ta * KB) --c;
+          w.first_contrib = c;
+        }
+        return true;
+      }
+      if (i == 1 && n_sk == 2) {
+        w.tile = full + ta + 1;
+        w.k0 = 0;
+        w.k1 = (int)(u1 - (long)(ta + 1) * KB);
+        w.kind = 1;
+        w.first_contrib = cta;
+        return true;
+      }
+    }
+  }
+  const int t = cta + (i0 - n_sk) * grid;
+  if (t >= full) return false;
+  w.tile = t;
+  w.k0 = 0;
+  w.k1 = KB;
+  w.kind = 0;
+  w.first_contrib = cta;
+  return true;
 }
 
 // MT = number of 128-row accumulators per CTA tile.  MT == 1: 128 x BN tile, the accumulator is double
@@ -181,9 +252,12 @@ MMT_DEVICE void tmem_dealloc_pair(uint32_t taddr, uint32_t cols) {
 // fp32 outputs, C += and ragged reduce-scatter rows use direct 16-byte global stores instead of the slab.
 // ------------------------------------------------------------------------------------
 
+// sk_part / sk_n / sk_stride: stream-K partial sums of this accumulator left by sk_n earlier CTAs (fp32, [128][BN],
+// one slot of sk_stride floats per CTA), added in CTA order before the epilogue arithmetic.
 template <int BN>
 MMT_DEVICE void epilogue_block(const GemmParams& p, const OutMaps& tmC, uint32_t tmem_acc, int row0, int col_tile0,
-                               int q, int half, int lane, uint8_t* slab, uint32_t release_bar) {
+                               int q, int half, int lane, uint8_t* slab, uint32_t release_bar,
+                               const float* sk_part = nullptr, int sk_n = 0, long sk_stride = 0) {
   constexpr int kGroups = BN / 64;
   const bool tma_out = !p.out_f32 && p.tma_store;
   const int srow0 = row0 + q * 32;                 // first row of this warp's slab
@@ -207,6 +281,23 @@ MMT_DEVICE void epilogue_block(const GemmParams& p, const OutMaps& tmC, uint32_t
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(release_bar);
+    }
+    for (int c = 0; c < sk_n; ++c) {
+      // slot layout: [64-column group][16-byte chunk][row], so that a warp reads 512 contiguous bytes per request
+      const float4* src = reinterpret_cast<const float4*>(sk_part + (long)c * sk_stride) + (long)g * 16 * 128 +
+                          (q * 32 + lane);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float4 a = src[i * 128], b = src[(8 + i) * 128];
+        r0[4 * i] = __float_as_uint(__uint_as_float(r0[4 * i]) + a.x);
+        r0[4 * i + 1] = __float_as_uint(__uint_as_float(r0[4 * i + 1]) + a.y);
+        r0[4 * i + 2] = __float_as_uint(__uint_as_float(r0[4 * i + 2]) + a.z);
+        r0[4 * i + 3] = __float_as_uint(__uint_as_float(r0[4 * i + 3]) + a.w);
+        r1[4 * i] = __float_as_uint(__uint_as_float(r1[4 * i]) + b.x);
+        r1[4 * i + 1] = __float_as_uint(__uint_as_float(r1[4 * i + 1]) + b.y);
+        r1[4 * i + 2] = __float_as_uint(__uint_as_float(r1[4 * i + 2]) + b.z);
+        r1[4 * i + 3] = __float_as_uint(__uint_as_float(r1[4 * i + 3]) + b.w);
+      }
     }
     const int colg = col_tile0 + g * 64;
     if (p.dbg & 8) continue;                        // measurement only: drain the accumulator, store nothing
@@ -306,6 +397,41 @@ MMT_DEVICE void epilogue_block(const GemmParams& p, const OutMaps& tmC, uint32_t
   }
 }
 
+// Stream-K run that stops before the end of its tile: the accumulator goes to this CTA's workspace slot as fp32.
+template <int BN>
+MMT_DEVICE void epilogue_partial(uint32_t tmem_acc, float* dst, int q, int half, int lane, uint32_t release_bar) {
+  constexpr int kGroups = BN / 64;
+  const uint32_t taddr0 = tmem_acc + ((uint32_t)(q * 32) << 16);
+  int last_g = -1;
+  for (int g = half; g < kGroups; g += 2) last_g = g;
+  if (last_g < 0) {
+    __syncwarp();
+    if (lane == 0) mbar_arrive_cluster(release_bar);
+    return;
+  }
+#pragma unroll 1
+  for (int g = half; g < kGroups; g += 2) {
+    uint32_t r0[32], r1[32];
+    tmem_ld_32x32b_x32(taddr0 + (uint32_t)(g * 64), r0);
+    tmem_ld_32x32b_x32(taddr0 + (uint32_t)(g * 64 + 32), r1);
+    tmem_wait_ld();
+    if (g == last_g) {
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(release_bar);
+    }
+    // [64-column group][16-byte chunk][row]: every store request of a warp covers 512 contiguous bytes
+    uint4* out = reinterpret_cast<uint4*>(dst) + (long)g * 16 * 128 + (q * 32 + lane);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      out[i * 128] = make_uint4(r0[4 * i], r0[4 * i + 1], r0[4 * i + 2], r0[4 * i + 3]);
+      out[(8 + i) * 128] = make_uint4(r1[4 * i], r1[4 * i + 1], r1[4 * i + 2], r1[4 * i + 3]);
+    }
+  }
+}
+
+MMT_DEVICE void epi_bar_sync() { asm volatile("bar.sync 2, 256;" ::: "memory"); }
+
 template <int BN, int MT>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -366,9 +492,10 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       bool ok = true;
       uint32_t ag_seen = p.ag_flags ? (1u << p.ag_self) : 0u;
       int kcount = 0;
-      for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+      WorkItem w;
+      for (int wi = 0; ok && work_item(p, wi, blockIdx.x, gridDim.x, KB, ntiles, w); ++wi) {
         int tm, tn;
-        tile_coords(p, tile, tiles_m, BMT, tm, tn);
+        tile_coords(p, w.tile, tiles_m, BMT, tm, tn);
         if (p.ag_flags) {
           const int r0 = tm * BMT, r1 = min(r0 + BMT, p.M) - 1;
           for (int src = r0 / p.ag_rows; src <= r1 / p.ag_rows && ok; ++src) {
@@ -379,7 +506,7 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           if (!ok) break;
           asm volatile("fence.proxy.async;" ::: "memory");
         }
-        for (int kb = 0; kb < KB; ++kb) {
+        for (int kb = w.k0; kb < w.k1; ++kb) {
           if ((p.dbg & 1) && kcount++ >= kStages) continue;
           if (!mbar_wait(&empty[s], ph ^ 1, p.ew, 100)) { ok = false; break; }
           uint8_t* sA = smem + (size_t)s * C_::STAGE_BYTES;
@@ -419,13 +546,14 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       // every ~128 cycles.  Whether the NEXT ring slot is full is looked up (non-blocking) in the shadow of the
       // current slot's instructions, so the common case never waits for a barrier round trip.
       bool ready = false;
-      for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+      WorkItem w;
+      for (int wi = 0; ok && work_item(p, wi, blockIdx.x, gridDim.x, KB, ntiles, w); ++wi) {
         // the accumulator (MT == 1) or both halves (MT == 2) of an earlier tile must have been drained
         if (!mbar_wait(&tempty[MT == 2 ? 0 : acc], acc_ph ^ 1, p.ew, 200)) { ok = false; break; }
         if (MT == 2 && !mbar_wait(&tempty[1], acc_ph ^ 1, p.ew, 202)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d0 = tmem_base + (uint32_t)((MT == 2 ? 0 : acc) * BN);
-        for (int kb = 0; kb < KB; ++kb) {
+        for (int kb = 0; kb < w.k1 - w.k0; ++kb) {      // kb counts from the start of this run: a fresh accumulator
           const bool skip = (p.dbg & 1) && kcount++ >= kStages;
           if (!ready && !skip && !mbar_wait(&full[s], ph, p.ew, 201)) { ok = false; break; }
           const uint32_t so = (uint32_t)s * (C_::STAGE_BYTES >> 4);
@@ -468,9 +596,19 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     int acc = 0;
     uint32_t acc_ph = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+    WorkItem w;
+    constexpr long kSlot = (long)BMT * BN;      // floats per stream-K workspace slot
+    for (int wi = 0; ok && work_item(p, wi, blockIdx.x, gridDim.x, KB, ntiles, w); ++wi) {
       int tm, tn;
-      tile_coords(p, tile, tiles_m, BMT, tm, tn);
+      tile_coords(p, w.tile, tiles_m, BMT, tm, tn);
+      const int n_contrib = (w.kind == 2 && !(p.dbg & 32)) ? (int)blockIdx.x - w.first_contrib : 0;
+      if (w.kind == 2 && !(p.dbg & 16)) {
+        // the CTAs that did the first k-blocks of this tile have left their partial sums
+        for (int c = w.first_contrib; c < (int)blockIdx.x && ok; ++c)
+          ok = flag_wait_ge(&p.sk_flags[c], p.sk_epoch, MMT_WAIT_NS, p.ew, 310);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+      }
 #pragma unroll 1
       for (int h = 0; h < MT; ++h) {
         const int slot = MT == 2 ? h : acc;
@@ -478,8 +616,25 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
-        epilogue_block<BN>(p, tmC, tmem_base + (uint32_t)(slot * BN), tm * BMT + h * BM, tn * BN, q, half, lane, slab,
-                           smem_u32(&tempty[slot]));
+        if (w.kind == 1 && (p.dbg & 64)) {       // measurement only: drop the partial sums
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(smem_u32(&tempty[slot]));
+        } else if (w.kind == 1) {
+          epilogue_partial<BN>(tmem_base + (uint32_t)(slot * BN), p.sk_ws + (long)blockIdx.x * kSlot + (long)h * BM * BN,
+                               q, half, lane, smem_u32(&tempty[slot]));
+        } else {
+          epilogue_block<BN>(p, tmC, tmem_base + (uint32_t)(slot * BN), tm * BMT + h * BM, tn * BN, q, half, lane, slab,
+                             smem_u32(&tempty[slot]), p.sk_ws + (long)w.first_contrib * kSlot + (long)h * BM * BN,
+                             n_contrib, kSlot);
+        }
+      }
+      if (!ok) break;
+      if (w.kind == 1) {
+        // every epilogue warp has stored its part: publish "the partial sums of CTA blockIdx.x are complete"
+        __threadfence();
+        epi_bar_sync();
+        if (warp == 2 && lane == 0) flag_store_release_sys(&p.sk_flags[blockIdx.x], p.sk_epoch);
       }
       if (MT == 1) {
         acc ^= 1;
@@ -765,7 +920,7 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const OutMaps& tc, cons
     attr_set = true;
   }
   const int tiles = ((p.M + C_::BMT - 1) / C_::BMT) * ((p.N + BN - 1) / BN);
-  const int grid = tiles < sms ? tiles : sms;
+  const int grid = (tiles < sms && p.sk_tiles == 0) ? tiles : sms;
   gemm_bf16_tcgen05<BN, MT><<<grid, kThreads, C_::SMEM, st>>>(ta, tb, tc, p);
   return (int)cudaGetLastError();
 }
@@ -783,6 +938,52 @@ int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const OutMaps& tc,
   const int pairs = tiles < sms / 2 ? tiles : sms / 2;
   gemm_bf16_tcgen05_pair<<<2 * pairs, kThreads, PairCfg::SMEM, st>>>(ta, tb, tc, p);
   return (int)cudaGetLastError();
+}
+
+// stream-K workspace of this process's device: one fp32 slot per CTA and one flag word per CTA
+float* g_sk_ws = nullptr;
+int* g_sk_flags = nullptr;
+int g_sk_epoch = 0;
+// Stream-K is OFF unless asked for (MMT_GEMM_STREAM_K=1 or mmt_gemm_set_stream_k(1)): on isolated GEMMs with a
+// partial last wave it saves 5-17 % (e.g. 2048 x 3584 x 18944: 247 -> 204 us with 128-row tiles), but inside a
+// training step at the board's power cap its extra partial-sum traffic costs as much as the idle SMs it fills
+// (7B step on one B200: 204.5 ms without, 205.9 ms with).
+int g_sk_mode = -1;           // 1 = on, 0 = off, -1 = not yet read from the environment
+double g_mt2_const = -1.0;    // fixed cost of a 256-row tile in the tile-shape model (MMT_GEMM_MT2_CONST overrides)
+
+void read_env_once() {
+  if (g_sk_mode < 0) {
+    const char* e = getenv("MMT_GEMM_STREAM_K");
+    g_sk_mode = (e && e[0] == '1') ? 1 : 0;
+  }
+  if (g_mt2_const < 0.0) {
+    const char* e = getenv("MMT_GEMM_MT2_CONST");
+    g_mt2_const = e ? atof(e) : 3.9;
+  }
+}
+cudaEvent_t g_sk_event = nullptr;
+cudaStream_t g_sk_stream = nullptr;
+constexpr int kSkMaxCtas = 160;
+
+bool sk_ready() {
+  if (g_sk_ws) return true;
+  if (cudaMalloc(&g_sk_ws, (size_t)kSkMaxCtas * 256 * 256 * sizeof(float)) != cudaSuccess) return false;
+  if (cudaMalloc(&g_sk_flags, kSkMaxCtas * sizeof(int)) != cudaSuccess) return false;
+  cudaMemset(g_sk_flags, 0, kSkMaxCtas * sizeof(int));
+  cudaEventCreateWithFlags(&g_sk_event, cudaEventDisableTiming);
+  return true;
+}
+
+// Number of trailing tiles to cut along K (0 = none): worth it when the last wave is clearly partial and every CTA
+// still gets a few k-blocks of it.
+int sk_tiles_for(int tiles, long kb, int sms, int mt) {
+  read_env_once();
+  if (!g_sk_mode || sms > kSkMaxCtas || kb < 4) return 0;
+  const int rem = tiles % sms;
+  if (rem == 0 || rem > (sms * 17) / 20) return 0;
+  // each CTA needs a run long enough to pay for its partial-sum traffic (128 KB per 128-row accumulator)
+  if ((long)rem * kb < (mt == 2 ? 48L : 24L) * sms) return 0;
+  return rem;
 }
 
 int g_force_mt = 0;   // 0 = choose, 1 / 2 = force the number of 128-row accumulators per tile, 3 = 2-CTA kernel
@@ -874,9 +1075,18 @@ extern "C" int mmt_gemm_bf16(const void* A, const void* B, void* C, const void* 
   if (bn == 256) {
     const int tn = (N + 255) / 256;
     const long kb = (K + BK - 1) / BK;
-    const long w1 = ((long)((M + 127) / 128) * tn + sms - 1) / sms;          // waves of 128-row tiles
-    const long w2 = ((long)((M + 255) / 256) * tn + sms - 1) / sms;          // waves of 256-row tiles
-    const double c1 = (double)w1 * 0.5615 * (double)kb, c2 = (double)w2 * ((double)kb + 3.9);
+    // waves of 128-row / 256-row tiles; a partial last wave that stream-K spreads over all CTAs counts as a fraction
+    const bool plain = g_comm == nullptr;
+    read_env_once();
+    auto waves = [&](long tiles, int m) {
+      const long full = tiles / sms, rem = tiles % sms;
+      if (rem == 0) return (double)full;
+      if (plain && sk_tiles_for((int)tiles, kb, sms, m) > 0)
+        return (double)full + (double)rem / sms + (m == 2 ? 16.0 : 8.0) / (double)kb;
+      return (double)full + 1.0;
+    };
+    const double w1 = waves((long)((M + 127) / 128) * tn, 1), w2 = waves((long)((M + 255) / 256) * tn, 2);
+    const double c1 = w1 * 0.5615 * (double)kb, c2 = w2 * ((double)kb + g_mt2_const);
     if (M >= 256 && c2 < c1) mt = 2;
     if (g_use_pair && M >= 256) mt = 3;                  // 2-CTA kernel: 256 x 256 tile per CTA pair
     if (g_force_mt) mt = g_force_mt;
@@ -923,6 +1133,23 @@ extern "C" int mmt_gemm_bf16(const void* A, const void* B, void* C, const void* 
     if (p.ag_flags && (p.ag_rows <= 0 || a_mn)) return -5;
     if (p.rs_rows && (out_f32 || p.rs_ranks > 8 || p.rs_ranks < 1)) return -6;
   }
+  // stream-K for a partial last wave (plain GEMMs on the 1-CTA kernels only)
+  p.sk_tiles = 0;
+  p.sk_ws = nullptr;
+  p.sk_flags = nullptr;
+  p.sk_epoch = 0;
+  bool sk_on = false;
+  if (!p.ag_flags && !p.rs_rows && mt != 3 && !(p.dbg & 1)) {
+    const int tiles = ((M + bmt - 1) / bmt) * ((N + bn - 1) / bn);
+    const int skt = sk_tiles_for(tiles, (K + BK - 1) / BK, sms, mt);
+    if (skt > 0 && sk_ready()) {
+      p.sk_tiles = skt;
+      p.sk_ws = g_sk_ws;
+      p.sk_flags = g_sk_flags;
+      p.sk_epoch = ++g_sk_epoch;
+      sk_on = true;
+    }
+  }
   // output tensor maps for the TMA-store epilogue
   OutMaps tc;
   memset(&tc, 0, sizeof(tc));
@@ -945,13 +1172,25 @@ extern "C" int mmt_gemm_bf16(const void* A, const void* B, void* C, const void* 
     }
   }
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  // the stream-K workspace is shared: a launch on another stream than the previous user waits for that one
+  if (sk_on && g_sk_stream != st && g_sk_epoch > 1) cudaStreamWaitEvent(st, g_sk_event, 0);
+  int rc;
   switch (bn) {
     case 256:
-      if (mt == 3) return launch_pair(ta, tb, tc, p, sms, st);
-      return mt == 2 ? launch<256, 2>(ta, tb, tc, p, sms, st) : launch<256, 1>(ta, tb, tc, p, sms, st);
-    case 192: return launch<192, 1>(ta, tb, tc, p, sms, st);
-    case 128: return launch<128, 1>(ta, tb, tc, p, sms, st);
-    case 64:  return launch<64, 1>(ta, tb, tc, p, sms, st);
+      if (mt == 3) rc = launch_pair(ta, tb, tc, p, sms, st);
+      else rc = mt == 2 ? launch<256, 2>(ta, tb, tc, p, sms, st) : launch<256, 1>(ta, tb, tc, p, sms, st);
+      break;
+    case 192: rc = launch<192, 1>(ta, tb, tc, p, sms, st); break;
+    case 128: rc = launch<128, 1>(ta, tb, tc, p, sms, st); break;
+    case 64:  rc = launch<64, 1>(ta, tb, tc, p, sms, st); break;
     default:  return -4;
   }
+  if (sk_on) {
+    cudaEventRecord(g_sk_event, st);
+    g_sk_stream = st;
+  }
+  return rc;
 }
+
+// Tuning knob: 1 = stream-K for partial last waves, 0 = whole tiles only (default).
+extern "C" void mmt_gemm_set_stream_k(int on) { g_sk_mode = on; }

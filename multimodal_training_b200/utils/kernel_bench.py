@@ -88,6 +88,7 @@ def main(argv=None) -> int:
     ap.add_argument("--no-flush", action="store_true")
     ap.add_argument("--fwd-version", type=int, default=0, help="attention forward: 2 = ping-pong kernel, 1 = first one")
     ap.add_argument("--bwd-version", type=int, default=0, help="attention backward: 2 = pipelined kernels, 1 = first ones")
+    ap.add_argument("--stream-k", type=int, default=-1, help="GEMM: 1 = stream-K for partial last waves, 0 = off (default)")
     ap.add_argument("--pair", type=int, default=-1, help="GEMM: 1 = 2-CTA kernel, 0 = 1-CTA kernels, -1 = default")
     a = ap.parse_args(argv)
     dev = "cuda"
@@ -100,6 +101,8 @@ def main(argv=None) -> int:
     if a.kernel == "gemm":
         if a.pair >= 0:
             nv.lib().mmt_gemm_use_pair(a.pair)
+        if a.stream_k >= 0:
+            nv.lib().mmt_gemm_set_stream_k(a.stream_k)
         a_mn, b_mn = a.layout == "mn_mn", a.layout != "kk"
         A = torch.randn((a.k, a.m) if a_mn else (a.m, a.k), device=dev, dtype=torch.bfloat16)
         B = torch.randn((a.k, a.n) if b_mn else (a.n, a.k), device=dev, dtype=torch.bfloat16)

@@ -266,3 +266,33 @@ def test_local_block_matches_per_op_graph(kind):
     for k in pa:
         if pa[k] is not None:
             assert rel_err(pb[k].grad, pa[k].grad.float()) < 1e-2, k
+
+
+@pytest.mark.parametrize("M,N,K", [(2048, 3584, 3584), (2048, 3584, 9472), (4096, 1280, 3424), (1000, 1176, 4096),
+                                   (300, 520, 2048)])
+@pytest.mark.parametrize("mt", [1, 2])
+def test_gemm_stream_k_matches_whole_tiles(M, N, K, mt):
+    """Tiles of a partial last wave are cut along K across all CTAs (fp32 partial sums, fixed order): same result
+    as whole tiles up to fp32 summation order, on both tile heights, with bias and residual in the epilogue."""
+    F, nv = _F()
+    L = nv.lib()
+    torch.manual_seed(3)
+    a = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    b = torch.randn(N, K, device=DEV, dtype=torch.bfloat16) * 0.05
+    bias = torch.randn(N, device=DEV, dtype=torch.bfloat16)
+    res = torch.randn(M, N, device=DEV, dtype=torch.bfloat16)
+    ref = a.float() @ b.float().t() + bias.float() + res.float()
+    L.mmt_gemm_force_mt(mt)
+    try:
+        L.mmt_gemm_set_stream_k(0)
+        whole = F.gemm(a, b, bias=bias, residual=res)
+        L.mmt_gemm_set_stream_k(1)
+        cut1 = F.gemm(a, b, bias=bias, residual=res)
+        cut2 = F.gemm(a, b, bias=bias, residual=res)
+    finally:
+        L.mmt_gemm_force_mt(0)
+        L.mmt_gemm_set_stream_k(0)
+    assert nv.get_error()[0] == 0, nv.get_error()
+    assert rel_err(cut1, ref) < 1e-2 and rel_err(whole, ref) < 1e-2
+    assert rel_err(cut1, whole.float()) < 1e-2      # one bf16 ulp of the largest outputs
+    assert torch.equal(cut1, cut2)          # fixed summation order: bit-reproducible
