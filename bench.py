@@ -94,6 +94,7 @@ def main() -> int:
     ap.add_argument("--global-batch", type=int, default=0, help="overrides --per-gpu-batch x N (other configs)")
     ap.add_argument("--tp", type=int, default=0, help="text tensor-parallel size (default min(N, 4))")
     ap.add_argument("--no-fused-comm", action="store_true")
+    ap.add_argument("--symm-heap-mb", type=int, default=0, help="size of the symmetric heap (default: the config's)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -139,6 +140,8 @@ def main() -> int:
         f"+data.synthetic.global_batch={global_batch}", "+data.synthetic.repeat=2",
         f"training.fused_comm={'false' if args.no_fused_comm else 'true'}",
     ]
+    if args.symm_heap_mb:
+        ov.append(f"training.symm_heap_mb={args.symm_heap_mb}")
     if args.impl == "lib":
         ov += ["+training.library_attention=true", "training.fused_comm=false"]
     cfg = load_config(None, ov)
