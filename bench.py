@@ -34,7 +34,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 REFERENCE_UNAVAILABLE = (
-    "pip install of /root/reference fails offline (no setup.py/pyproject.toml) and its public API "
+    "pip install of the reference tree fails offline (no setup.py/pyproject.toml) and its public API "
     "(python -m python.train_ray) imports ray, deepspeed (a git fork), hydra and omegaconf, none of which is in "
     "the image or the wheelhouse")
 

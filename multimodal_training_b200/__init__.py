@@ -1,4 +1,5 @@
-"""B200-native disaggregated hybrid-parallel VLM trainer (see README.md and DESIGN.md)."""
+"""B200-native disaggregated hybrid-parallel VLM trainer: vision encoder sequence-parallel, text decoder
+tensor-parallel, both on the same GPUs, hot ops as hand-written sm_100a kernels (see README.md)."""
 __version__ = "0.1.0"
 
 from .config.loader import load_config, trainer_configs  # noqa: F401

@@ -6,7 +6,7 @@ with a bump allocator that every rank calls in the same order, so a region has t
 all ranks and a peer's copy is ``peer_base + offset``.  Flags are int32 words inside the heap that
 count epochs upward and are never reset.
 
-SURVEY-style mapping: this replaces the reference's per-tensor IPC handle + event transfer
+Counterpart in the reference: this replaces the reference's per-tensor IPC handle + event transfer
 (python/ray/tensor_transfer.py:35-96) and is the substrate of ``parallel/fused.py``.
 """
 from __future__ import annotations
