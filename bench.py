@@ -177,6 +177,7 @@ def main() -> int:
     for s in range(args.steps):
         last = engine.train_step(step0 + s)
     host_enqueue_ms = (time.perf_counter() - h0) * 1e3 / args.steps
+    engine.join_streams()          # the timed region ends after the last optimizer update, whichever stream ran it
     e1.record()
     barrier()
     dev_ms = e0.elapsed_time(e1)
@@ -196,6 +197,7 @@ def main() -> int:
             losses.append(pending.value())
         pending = handle
     losses.append(pending.value())
+    engine.join_streams()
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
     barrier()

@@ -72,6 +72,7 @@ DEFAULTS: dict[str, Any] = {
         "backend": None,           # torch.distributed backend: default nccl on GPU, gloo on CPU
         "runtime": "auto",         # actor runtime: auto | ray | builtin
         "fused_comm": True,        # peer-memory fused collectives when a symmetric heap is available
+        "overlap_optimizer": False,  # single-GPU engine: text AdamW on a side stream behind the next vision forward
         "symm_heap_mb": 8192,      # size of each GPU's symmetric heap (exchange buffers of the fused collectives)
     },
     "data": {
