@@ -94,6 +94,8 @@ def main() -> int:
     ap.add_argument("--global-batch", type=int, default=0, help="overrides --per-gpu-batch x N (other configs)")
     ap.add_argument("--tp", type=int, default=0, help="text tensor-parallel size (default min(N, 4))")
     ap.add_argument("--no-fused-comm", action="store_true")
+    ap.add_argument("--activation-checkpointing", default="auto", choices=["auto", "on", "off"],
+                    help="auto (default): keep activations when they fit in HBM, recompute them otherwise")
     ap.add_argument("--symm-heap-mb", type=int, default=0, help="size of the symmetric heap (default: the config's)")
     args = ap.parse_args()
 
@@ -140,6 +142,8 @@ def main() -> int:
         f"+data.synthetic.global_batch={global_batch}", "+data.synthetic.repeat=2",
         f"training.fused_comm={'false' if args.no_fused_comm else 'true'}",
     ]
+    ckpt = {"auto": "auto", "on": "true", "off": "false"}[args.activation_checkpointing]
+    ov += [f"vision.activation_checkpointing={ckpt}", f"text.activation_checkpointing={ckpt}"]
     if args.symm_heap_mb:
         ov.append(f"training.symm_heap_mb={args.symm_heap_mb}")
     if args.impl == "lib":
@@ -158,7 +162,7 @@ def main() -> int:
         engine.vision.step_context(s)
     losses = []
     for s in range(args.warmup):
-        losses.append(float(engine.train_step(s)))
+        losses.append(engine.train_step_async(s).value())
     nv.raise_on_device_error()
 
     clock_path = os.path.join("/tmp", f"bench_clocks_{os.getpid()}.csv")
@@ -207,10 +211,32 @@ def main() -> int:
         fh.close()
     nv.raise_on_device_error()
 
-    t = torch.tensor([dev_ms, e2e_s * 1e3], device="cuda", dtype=torch.float64)
+    # ---- the same steps with activation recomputation forced on (the reference's setting), for comparison
+    policy = {"vision": bool(engine.vision.model.ckpt_now), "text": bool(engine.text.model.ckpt_now)}
+    ckpt_on_ms = None
+    if args.activation_checkpointing == "auto" and not all(policy.values()):
+        saved = (engine.vision.model.ckpt, engine.text.model.ckpt)
+        engine.vision.model.ckpt = engine.text.model.ckpt = True
+        step0 += args.steps
+        for s in range(2):
+            engine.train_step(step0 + s)
+        barrier()
+        c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        c0.record()
+        for s in range(args.steps):
+            engine.train_step(step0 + 2 + s)
+        engine.join_streams()
+        c1.record()
+        barrier()
+        ckpt_on_ms = c0.elapsed_time(c1) / args.steps
+        engine.vision.model.ckpt, engine.text.model.ckpt = saved
+        nv.raise_on_device_error()
+
+    t = torch.tensor([dev_ms, e2e_s * 1e3, ckpt_on_ms or 0.0], device="cuda", dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     dev_ms, e2e_ms = float(t[0]), float(t[1])
+    ckpt_on_ms = float(t[2]) if ckpt_on_ms is not None else None
     h2d = torch.tensor([float(engine.vision.h2d_bytes + engine.text.h2d_bytes)], device="cuda", dtype=torch.float64)
     if world > 1:
         dist.all_reduce(h2d, op=dist.ReduceOp.SUM)
@@ -237,7 +263,14 @@ def main() -> int:
                 "model": args.model, "global_batch": global_batch, "seq_len": args.text_tokens + patches // global_batch // 4,
                 "image": f"{args.image_size}x{args.image_size}", "vision_patches_per_sample": patches // global_batch,
                 "text_tokens_per_sample": args.text_tokens, "parallelism": par,
-                "optimizer": "AdamW fp32 master+moments, ZeRO-1", "activation_checkpointing": True,
+                "optimizer": "AdamW fp32 master+moments, ZeRO-1",
+                "activation_checkpointing": {
+                    "setting": args.activation_checkpointing,
+                    "recompute_in_this_run": policy,
+                    "note": "auto keeps the activations of a half of the model when they fit into half of the free "
+                            "HBM and recomputes them otherwise; the reference always recomputes (80 GB GPUs)",
+                    "ms_per_step_with_recompute_forced_on": ckpt_on_ms,
+                    "value_with_recompute_forced_on": (patches / (ckpt_on_ms / 1e3)) if ckpt_on_ms else None},
                 "llm_tokens_per_s": llm_tokens / (ms_per_step / 1e3),
                 "l2": "working set per step (weights, gradients, optimizer state: >100 GB) far exceeds the 126 MB L2; "
                       "no explicit flush",

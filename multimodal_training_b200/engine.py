@@ -48,6 +48,10 @@ class HybridEngine:
         self.max_norm = float(text_config.get("max_grad_norm", 1.0))
         self.step_index = 0
         self.last_grad_norm = None
+        # pinned host slots for train_step_async (allocated here: the first pinned allocation of a process is slow)
+        pin = torch.cuda.is_available()
+        self._loss_ring = [torch.zeros(1, dtype=torch.float32, pin_memory=pin) for _ in range(8)]
+        self._loss_i = 0
         # single-GPU runs hold the whole optimizer state on one device (37 ms of AdamW per 7B step);
         # training.overlap_optimizer puts the text update on a side stream behind the next vision forward.  Off by
         # default: measured on a B200 it changes nothing (206.6 ms with, 204-209 ms without), because the update's
@@ -144,10 +148,6 @@ class HybridEngine:
         draining the launch queue.  At most ``len(ring)`` handles may be outstanding.
         """
         loss = self.train_step(step)
-        if not hasattr(self, "_loss_ring"):
-            pin = loss.is_cuda
-            self._loss_ring = [torch.zeros(1, dtype=torch.float32, pin_memory=pin) for _ in range(8)]
-            self._loss_i = 0
         host = self._loss_ring[self._loss_i % len(self._loss_ring)]
         self._loss_i += 1
         host.copy_(loss.detach().float().reshape(1), non_blocking=True)

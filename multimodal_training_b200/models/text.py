@@ -22,6 +22,7 @@ from ..ops.attention import SeqInfo
 from ..parallel import comm
 from ..parallel.tp import TPContext, column_parallel_linear, row_parallel_linear, vocab_range
 from ..utils.checkpointing import checkpoint
+from ..utils.checkpointing import decide as decide_ckpt
 
 
 def mrope_cos_sin(position_ids: torch.Tensor, head_dim: int, theta: float, mrope_section: list[int]):
@@ -120,12 +121,26 @@ class TextDecoder(nn.Module):
         m = F.swiglu(gu)
         return row_parallel_linear(m, L.down_w, x, self.tp, role="down")
 
+    def activation_bytes(self, shard_tokens: int) -> int:
+        """Bytes of activations that all layers of this rank keep for backward when nothing is recomputed (bf16);
+        ``shard_tokens`` rows per rank, ``shard_tokens * tp`` gathered rows inside a layer."""
+        cfg, tpn = self.cfg, self.tp.size
+        T = int(shard_tokens) * tpn
+        d = cfg.head_dim
+        per_layer = int(shard_tokens) * 4 * cfg.hidden_size \
+            + T * ((self.n_q + 2 * self.n_kv) * d + self.n_q * d + 3 * cfg.intermediate_size // tpn + 2 * cfg.hidden_size)
+        return per_layer * 2 * len(self.layers)
+
     def forward(self, x_shard: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, seq: SeqInfo) -> torch.Tensor:
         """[T/tp, H] token shard -> final hidden token shard (before the last norm)."""
         x = x_shard
         # without tensor parallelism a layer has no communication inside and runs as one hand-written autograd
         # node (ops/blocks.py); tensor-parallel layers, the CPU path and un-checkpointed runs use the per-op graph
-        one_node = (self.tp.size == 1 and self.ckpt and torch.is_grad_enabled() and blocks.usable(x)
+        ckpt = decide_ckpt(self.ckpt, self.activation_bytes(x.shape[0]), x.device) if torch.is_grad_enabled() else False
+        self.ckpt_now = ckpt
+        if self.tp.fused is not None:
+            self.tp.fused.set_checkpointed("text", ckpt)
+        one_node = (self.tp.size == 1 and torch.is_grad_enabled() and blocks.usable(x)
                     and attn_mod.BACKEND == "sm100")
         if one_node:
             d = self.cfg.head_dim
@@ -133,10 +148,10 @@ class TextDecoder(nn.Module):
                                     causal=True, eps=self.cfg.rms_norm_eps, scale=1.0 / math.sqrt(d))
             for L in self.layers:
                 x = blocks.local_block(x, spec, cos, sin, seq, (L.ln1_w, L.qkv_w, L.qkv_b, L.o_w, None, L.ln2_w,
-                                                                L.gate_up_w, None, L.down_w, None))
+                                                                L.gate_up_w, None, L.down_w, None), recompute=ckpt)
             return x
         for L in self.layers:
-            x = checkpoint(lambda t, L=L: self._layer(t, L, cos, sin, seq), (x,), enabled=self.ckpt)
+            x = checkpoint(lambda t, L=L: self._layer(t, L, cos, sin, seq), (x,), enabled=ckpt)
         return x
 
     def loss(self, x_shard: torch.Tensor, shifted_labels: torch.Tensor, chunk_rows: int = 4096) -> torch.Tensor:

@@ -33,6 +33,7 @@ from ..ops.attention import SeqInfo
 from ..parallel import comm
 from ..parallel.sp import VisionPlan
 from ..utils.checkpointing import checkpoint
+from ..utils.checkpointing import decide as decide_ckpt
 
 
 class SPContext:
@@ -128,6 +129,12 @@ class VisionEncoder(nn.Module):
         m = F.swiglu(F.linear(h, B.gate_up_w, B.gate_up_b))
         return F.linear(m, B.down_w, B.down_b, x)
 
+    def activation_bytes(self, tokens: int) -> int:
+        """Bytes of activations that all blocks keep for backward when nothing is recomputed (bf16)."""
+        cfg = self.cfg
+        per_token = 4 * cfg.hidden_size + 3 * cfg.hidden_size + 3 * cfg.padded_intermediate_size
+        return int(tokens) * per_token * 2 * len(self.blocks)
+
     # ------------------------------------------------------------------ forward
     def forward(self, local_patches: torch.Tensor, plan: VisionPlan) -> torch.Tensor:
         """[T_loc, patch_dim] patches of this rank in local window order -> merged tokens [T_loc/4, out_hidden]."""
@@ -139,8 +146,13 @@ class VisionEncoder(nn.Module):
         full_seq = plan.full_seq if self.sp.size > 1 else plan.local_image_seq
         x = F.linear(local_patches, self.patch_embed_w)
         # blocks without communication inside run as one hand-written autograd node each (ops/blocks.py); the
-        # Ulysses layers of a sequence-parallel run, the CPU path and un-checkpointed runs use the per-op graph
-        one_node = self.ckpt and torch.is_grad_enabled() and blocks.usable(x) and attn_mod.BACKEND == "sm100"
+        # Ulysses layers of a sequence-parallel run and the CPU path use the per-op graph.  Whether activations
+        # are recomputed in backward is decided per step (True / False / "auto": keep them when they fit)
+        ckpt = decide_ckpt(self.ckpt, self.activation_bytes(x.shape[0]), x.device) if torch.is_grad_enabled() else False
+        self.ckpt_now = ckpt
+        if self.sp.fused is not None:
+            self.sp.fused.fc.set_checkpointed("vision", ckpt)
+        one_node = torch.is_grad_enabled() and blocks.usable(x) and attn_mod.BACKEND == "sm100"
         spec = blocks.BlockSpec(n_q=cfg.num_heads, n_kv=cfg.num_heads, head_dim=cfg.head_dim,
                                 rope_heads=2 * cfg.num_heads, causal=False, eps=cfg.rms_norm_eps,
                                 scale=1.0 / math.sqrt(cfg.head_dim))
@@ -149,10 +161,10 @@ class VisionEncoder(nn.Module):
             if one_node and (not is_full or self.sp.size == 1):
                 x = blocks.local_block(x, spec, cos, sin, full_seq if is_full else win_seq,
                                        (B.norm1_w, B.qkv_w, B.qkv_b, B.proj_w, B.proj_b, B.norm2_w, B.gate_up_w,
-                                        B.gate_up_b, B.down_w, B.down_b))
+                                        B.gate_up_b, B.down_w, B.down_b), recompute=ckpt)
                 continue
             x = checkpoint(lambda t, B=B, f=is_full: self._block(t, B, cos, sin, plan, win_seq, full_seq, f), (x,),
-                           enabled=self.ckpt)
+                           enabled=ckpt)
         h = F.rmsnorm(x, self.ln_q_w, cfg.rms_norm_eps)
         h = h.view(-1, cfg.hidden_size * cfg.merge_unit)
         h = F.gelu(F.linear(h, self.merger_fc1_w, self.merger_fc1_b))

@@ -12,8 +12,9 @@ checkpoint, such a block costs about forty graph nodes and two passes through th
 and on a B200 the HOST then needs as long to enqueue a training step as the GPU needs to run it.  This module
 issues the same kernels directly:
 
-* forward keeps nothing but the block input (activation checkpointing is built in);
-* backward recomputes the intermediates and walks the chain by hand, writing weight gradients straight into
+* forward keeps the block input only (activation checkpointing) or, when memory allows, also the GEMM and
+  attention results;
+* backward recomputes what was not kept and walks the chain by hand, writing weight gradients straight into
   the parameters' ``main_grad`` views of the flat gradient buffer.
 
 The arithmetic, kernel by kernel, is identical to the per-op path, which stays in use on the CPU, for blocks
@@ -141,10 +142,17 @@ def _forward_chain(x, s: BlockSpec, cos, sin, seq, P, keep: bool):
 
 class _LocalBlockFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, spec, cos, sin, seq, *params):
+    def forward(ctx, x, spec, cos, sin, seq, recompute, *params):
         x = x if x.is_contiguous() else x.contiguous()
-        y, _ = _forward_chain(x, spec, cos, sin, seq, params, keep=False)
-        ctx.save_for_backward(x, cos, sin, *[p for p in params if p is not None])
+        y, kept = _forward_chain(x, spec, cos, sin, seq, params, keep=not recompute)
+        extra = ()
+        if not recompute:
+            # keep what is expensive to rebuild (GEMM and attention results); the three element-wise intermediates
+            # (both normalised inputs and the SwiGLU output) are recomputed from them in backward
+            h1, rstd1, qkv, a, lse, x1, h2, rstd2, gu, m = kept
+            extra = (qkv, a, lse, x1, gu)
+        ctx.n_extra = len(extra)
+        ctx.save_for_backward(x, cos, sin, *extra, *[p for p in params if p is not None])
         ctx.has = [p is not None for p in params]
         ctx.spec, ctx.seq = spec, seq
         return y
@@ -153,12 +161,19 @@ class _LocalBlockFn(torch.autograd.Function):
     def backward(ctx, dy):
         saved = ctx.saved_tensors
         x, cos, sin = saved[0], saved[1], saved[2]
-        it = iter(saved[3:])
+        extra = saved[3:3 + ctx.n_extra]
+        it = iter(saved[3 + ctx.n_extra:])
         P = tuple(next(it) if h else None for h in ctx.has)
         s, seq = ctx.spec, ctx.seq
         ln1_w, qkv_w, qkv_b, proj_w, proj_b, ln2_w, gu_w, gu_b, down_w, down_b = P
         dy = dy if dy.is_contiguous() else dy.contiguous()
-        _, (h1, rstd1, qkv, a, lse, x1, h2, rstd2, gu, m) = _forward_chain(x, s, cos, sin, seq, P, keep=True)
+        if ctx.n_extra:
+            qkv, a, lse, x1, gu = extra
+            h1, rstd1 = _rmsnorm_fwd(x, ln1_w, s.eps)
+            h2, rstd2 = _rmsnorm_fwd(x1, ln2_w, s.eps)
+            m = _swiglu_fwd(gu)
+        else:
+            _, (h1, rstd1, qkv, a, lse, x1, h2, rstd2, gu, m) = _forward_chain(x, s, cos, sin, seq, P, keep=True)
         # MLP half
         dm = _linear_bwd(dy, m, down_w, down_b)
         dgu = _swiglu_bwd(dm, gu)
@@ -172,13 +187,15 @@ class _LocalBlockFn(torch.autograd.Function):
         dh1 = _linear_bwd(dqkv, h1, qkv_w, qkv_b)
         dx = _rmsnorm_bwd(dh1, x, ln1_w, rstd1)
         nv.call("mmt_add", dx.data_ptr(), dx1.data_ptr(), dx.data_ptr(), dx.numel(), nv.stream())
-        return (dx, None, None, None, None) + (None,) * len(ctx.has)
+        return (dx, None, None, None, None, None) + (None,) * len(ctx.has)
 
 
-def local_block(x: torch.Tensor, spec: BlockSpec, cos: torch.Tensor, sin: torch.Tensor, seq: SeqInfo, params: tuple):
+def local_block(x: torch.Tensor, spec: BlockSpec, cos: torch.Tensor, sin: torch.Tensor, seq: SeqInfo, params: tuple,
+                recompute: bool = True):
     """``params`` = (ln1_w, qkv_w, qkv_b, proj_w, proj_b, ln2_w, gate_up_w, gate_up_b, down_w, down_b); biases may
-    be None.  x is [T, C] bf16 on the GPU; the result has the same shape."""
-    return _LocalBlockFn.apply(x, spec, cos, sin, seq, *params)
+    be None.  x is [T, C] bf16 on the GPU; the result has the same shape.  ``recompute``: keep only the block input
+    and rebuild everything in backward (activation checkpointing), or keep the GEMM / attention results."""
+    return _LocalBlockFn.apply(x, spec, cos, sin, seq, bool(recompute), *params)
 
 
 def usable(x: torch.Tensor) -> bool:

@@ -108,10 +108,20 @@ class FusedComm:
         self.mesh = mesh
         self.device = device
         self.ctx = HeapContext(mesh.world_group, heap_bytes, device)
-        self.checkpointed = checkpointed
+        # results that live in reusable heap regions may be handed out as views only while BOTH halves recompute
+        # their activations in backward; otherwise they are cloned (see set_checkpointed)
+        self._ckpt = {"vision": bool(checkpointed), "text": bool(checkpointed)}
         base = mesh.tdp_rank * mesh.tp
         self.tp_ranks = [base + i for i in range(mesh.tp)]      # world (= heap) ranks of my TP group
         self.world_ranks = list(range(mesh.world))
+
+    @property
+    def checkpointed(self) -> bool:
+        return all(self._ckpt.values())
+
+    def set_checkpointed(self, half: str, on: bool) -> None:
+        """Per-step decision of one half of the model ("vision" / "text") on activation recomputation."""
+        self._ckpt[half] = bool(on)
 
     # ------------------------------------------------------------------ tensor parallel
     def _region(self, name: str, shape, dtype=torch.bfloat16) -> tuple[int, torch.Tensor]:
@@ -345,7 +355,7 @@ def try_create(mesh, config):
         if mesh.world > MAX_PEERS:
             return None, None
         heap_mb = int(config.get("symm_heap_mb", 8192))
-        fc = FusedComm(mesh, dev, heap_mb << 20, checkpointed=bool(config.get("activation_checkpointing", True)))
+        fc = FusedComm(mesh, dev, heap_mb << 20, checkpointed=config.get("activation_checkpointing", True) is True)
         return fc.ctx, fc
     except Exception as e:  # the NCCL path still works; say why the fused one does not
         log.warning("fused collectives unavailable: %s", e)

@@ -30,7 +30,7 @@ class TextTrainer(Trainer):
             attn_mod.set_backend("lib")
         tp = TPContext(mesh.tp_group, mesh.tp, mesh.tp_rank, fused=self.state.fused)
         self.model = TextDecoder(cfg.text, tp, dtype=dt, device=dev, seed=self.seed,
-                                 activation_checkpointing=bool(self.config.get("activation_checkpointing", True)))
+                                 activation_checkpointing=self.config.get("activation_checkpointing", True))
         pre = self.config.get("pretrained_checkpoint_dir")
         if pre:
             self._load_pretrained(pre)

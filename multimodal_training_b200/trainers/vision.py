@@ -34,7 +34,7 @@ class VisionTrainer(Trainer):
             ulysses = UlyssesFused(self.state.fused)
         sp = SPContext(mesh.sp_group, mesh.sp, mesh.sp_rank, fused=ulysses)
         self.model = VisionEncoder(cfg.vision, sp, dtype=dt, device=dev, seed=self.seed,
-                                   activation_checkpointing=bool(self.config.get("activation_checkpointing", True)))
+                                   activation_checkpointing=self.config.get("activation_checkpointing", True))
         pre = self.config.get("pretrained_checkpoint_dir")
         if pre:
             self._load_pretrained(pre)

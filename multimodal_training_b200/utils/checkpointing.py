@@ -44,3 +44,23 @@ def checkpoint(fn, tensors: tuple, extra: tuple = (), enabled: bool = True):
     if not enabled or not torch.is_grad_enabled():
         return fn(*tensors, *extra)
     return _Checkpoint.apply(fn, len(tensors), *tensors, *extra)
+
+
+def decide(mode, need_bytes: int, device=None, headroom: float = 0.5) -> bool:
+    """Should a stack of blocks recompute its activations in backward?
+
+    ``mode`` is the config value: True / False, or ``"auto"``: keep the activations (no recomputation, about a
+    quarter less work per step) when ``need_bytes`` of them fit into ``headroom`` of the memory that is free right
+    now on ``device``, recompute otherwise.  The reference always checkpoints (it was sized for 80 GB GPUs,
+    python/ray/trainer.py:257-267); on a 180 GB B200 the 7B model's activations at the benchmark's sequence
+    lengths fit many times over.
+    """
+    if isinstance(mode, str):
+        if mode.lower() != "auto":
+            return mode.lower() not in ("false", "0", "off", "no")
+        if device is None or torch.device(device).type != "cuda":
+            return False
+        free, _ = torch.cuda.mem_get_info(device)
+        free += torch.cuda.memory_reserved(device) - torch.cuda.memory_allocated(device)
+        return need_bytes > headroom * free
+    return bool(mode)

@@ -160,3 +160,10 @@ def test_phase_timer_and_chrome_trace(tmp_path):
     assert len(ev) == 4 and ev[0]["pid"] == 3 and ev[0]["args"]["step"] == 0 and ev[-1]["args"]["step"] == 1
     with tracing.trace_range("noop"):        # off by default: must be a plain no-op
         pass
+
+
+def test_checkpoint_policy_decision():
+    from multimodal_training_b200.utils.checkpointing import decide
+    assert decide(True, 0) is True and decide(False, 10 ** 15) is False
+    assert decide("false", 1) is False and decide("true", 1) is True
+    assert decide("auto", 10 ** 15, "cpu") is False          # no device memory to protect on the CPU path
