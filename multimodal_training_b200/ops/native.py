@@ -81,8 +81,22 @@ def declare(name: str, restype, argtypes) -> None:
         fn.argtypes = argtypes
 
 
+_DEVICE_INDEX = None
+
+
 def stream() -> int:
-    return torch.cuda.current_stream().cuda_stream
+    """Raw handle of the current CUDA stream of this process's device.
+
+    ``torch.cuda.current_stream().cuda_stream`` builds a Stream object and resolves the device on every call
+    (about 3 us, once per kernel launch); the private raw getter costs well under 0.1 us.  A process drives one
+    GPU, so the device index is read once."""
+    global _DEVICE_INDEX
+    if _DEVICE_INDEX is None:
+        _DEVICE_INDEX = torch.cuda.current_device()
+    try:
+        return torch._C._cuda_getCurrentRawStream(_DEVICE_INDEX)
+    except AttributeError:      # a torch build without the raw getter
+        return torch.cuda.current_stream().cuda_stream
 
 
 def ptr(t: torch.Tensor | None) -> int | None:
@@ -98,11 +112,17 @@ def check(code: int, what: str) -> None:
 _LAUNCHES = {"mmt_rmsnorm_bwd": 2, "mmt_colsum": 2, "mmt_attn_bwd": 3}
 
 
+_FN: dict = {}
+
+
 def call(name: str, *args) -> None:
     """Invoke an int-returning entry point and raise on a non-zero code."""
     global launch_count
     launch_count += _LAUNCHES.get(name, 1)
-    code = getattr(lib(), name)(*args)
+    fn = _FN.get(name)
+    if fn is None:
+        fn = _FN[name] = getattr(lib(), name)
+    code = fn(*args)
     if code != 0:
         raise RuntimeError(f"{name} failed with code {code}")
 
