@@ -194,7 +194,11 @@ def test_adamw_and_sumsq():
         F.adamw_step(pcb, gc, wc, mc, vc, n_decay=n // 2, lr=1e-2, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.1,
                      step=step, grad_scale=torch.tensor([0.5]))
     assert rel_err(master.cpu(), wc) < 1e-5
-    assert torch.equal(p.cpu(), wc.to(torch.bfloat16))
+    # the kernel's fp32 arithmetic (fast division / square root) may differ from the CPU's in the last bits, which can
+    # flip the bf16 rounding of a few parameters by one unit in the last place, never more
+    got, want = p.cpu().float(), wc.to(torch.bfloat16).float()
+    assert (got != want).float().mean().item() < 1e-3
+    assert ((got - want).abs() <= want.abs() * 2.0 ** -7 + 1e-30).all()
     out = torch.zeros(1, device=DEV)
     F.sum_squares(g, out)
     assert abs(out.item() - g.float().pow(2).sum().item()) < 1e-3 * out.item()
