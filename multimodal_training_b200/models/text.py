@@ -136,7 +136,8 @@ class TextDecoder(nn.Module):
         x = x_shard
         # without tensor parallelism a layer has no communication inside and runs as one hand-written autograd
         # node (ops/blocks.py); tensor-parallel layers, the CPU path and un-checkpointed runs use the per-op graph
-        ckpt = decide_ckpt(self.ckpt, self.activation_bytes(x.shape[0]), x.device) if torch.is_grad_enabled() else False
+        ckpt = decide_ckpt(self.ckpt, self.activation_bytes(x.shape[0]), x.device, group=self.tp.group,
+                           key=("text", id(self))) if torch.is_grad_enabled() else False
         self.ckpt_now = ckpt
         if self.tp.fused is not None:
             self.tp.fused.set_checkpointed("text", ckpt)

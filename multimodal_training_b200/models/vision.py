@@ -148,7 +148,8 @@ class VisionEncoder(nn.Module):
         # blocks without communication inside run as one hand-written autograd node each (ops/blocks.py); the
         # Ulysses layers of a sequence-parallel run and the CPU path use the per-op graph.  Whether activations
         # are recomputed in backward is decided per step (True / False / "auto": keep them when they fit)
-        ckpt = decide_ckpt(self.ckpt, self.activation_bytes(x.shape[0]), x.device) if torch.is_grad_enabled() else False
+        ckpt = decide_ckpt(self.ckpt, self.activation_bytes(x.shape[0]), x.device, group=self.sp.group,
+                           key=("vision", id(self))) if torch.is_grad_enabled() else False
         self.ckpt_now = ckpt
         if self.sp.fused is not None:
             self.sp.fused.fc.set_checkpointed("vision", ckpt)

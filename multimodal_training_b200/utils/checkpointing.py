@@ -9,6 +9,7 @@ are written by the ops themselves (``main_grad``) or accumulate into ``.grad`` a
 from __future__ import annotations
 
 import torch
+import torch.distributed
 
 
 class _Checkpoint(torch.autograd.Function):
@@ -46,7 +47,10 @@ def checkpoint(fn, tensors: tuple, extra: tuple = (), enabled: bool = True):
     return _Checkpoint.apply(fn, len(tensors), *tensors, *extra)
 
 
-def decide(mode, need_bytes: int, device=None, headroom: float = 0.5) -> bool:
+_DECISIONS: dict = {}
+
+
+def decide(mode, need_bytes: int, device=None, headroom: float = 0.5, group=None, key=None) -> bool:
     """Should a stack of blocks recompute its activations in backward?
 
     ``mode`` is the config value: True / False, or ``"auto"``: keep the activations (no recomputation, about a
@@ -60,7 +64,21 @@ def decide(mode, need_bytes: int, device=None, headroom: float = 0.5) -> bool:
             return mode.lower() not in ("false", "0", "off", "no")
         if device is None or torch.device(device).type != "cuda":
             return False
+        # Ranks that exchange activations inside the blocks (sequence / tensor parallel peers) must all take the
+        # same branch, or the ones that recompute would wait for exchanges the others never start.  The decision is
+        # therefore the OR over ``group`` and is taken once per (key, size): later steps with the same shapes reuse it
+        # without a collective or a host synchronisation.
+        ck = (key, int(need_bytes))
+        hit = _DECISIONS.get(ck)
+        if hit is not None:
+            return hit
         free, _ = torch.cuda.mem_get_info(device)
         free += torch.cuda.memory_reserved(device) - torch.cuda.memory_allocated(device)
-        return need_bytes > headroom * free
+        recompute = need_bytes > headroom * free
+        if group is not None and torch.distributed.is_initialized() and torch.distributed.get_world_size(group) > 1:
+            flag = torch.tensor([1 if recompute else 0], device=device, dtype=torch.int32)
+            torch.distributed.all_reduce(flag, op=torch.distributed.ReduceOp.MAX, group=group)
+            recompute = bool(flag.item())
+        _DECISIONS[ck] = recompute
+        return recompute
     return bool(mode)
