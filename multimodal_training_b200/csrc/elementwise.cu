@@ -122,7 +122,8 @@ __global__ void __launch_bounds__(kNormThreads) rmsnorm_bwd_kernel(const bf16* _
                                                                   const bf16* __restrict__ w,
                                                                   const float* __restrict__ rstd_in,
                                                                   bf16* __restrict__ dx, float* __restrict__ dw_partial,
-                                                                  int rows, int cols) {
+                                                                  int rows, int cols,
+                                                                  const bf16* __restrict__ extra = nullptr) {
   __shared__ float red[32];
   const int nvec = cols >> 3;
   float dwacc[kNormVec][8];
@@ -162,6 +163,12 @@ __global__ void __launch_bounds__(kNormThreads) rmsnorm_bwd_kernel(const bf16* _
         float o[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) o[j] = rstd * (g[i][j] - xv[i][j] * coef);
+        if (extra) {      // gradient that reaches the same tensor through the residual connection
+          float ev[8];
+          load8(extra + row * cols + c * 8, ev);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] += ev[j];
+        }
         store8(dx + row * cols + c * 8, o);
       }
     }
@@ -539,6 +546,19 @@ int mmt_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* r
   const int parts = mmt_rmsnorm_bwd_parts(rows);
   rmsnorm_bwd_kernel<<<parts, kNormThreads, 0, ST(stream)>>>(CBF(dy), CBF(x), CBF(w), rstd, BF(dx), scratch, (int)rows,
                                                             cols);
+  reduce_partials_kernel<<<(cols + 255) / 256, 256, 0, ST(stream)>>>(scratch, BF(dw), parts, cols, accumulate_dw);
+  return (int)cudaGetLastError();
+}
+
+// As mmt_rmsnorm_bwd, with dx = (gradient through the norm) + extra: the pre-norm residual block's
+// "gradient of the norm input plus gradient of the skip path" in one pass instead of a separate add.
+int mmt_rmsnorm_bwd_add(const void* dy, const void* x, const void* w, const float* rstd, const void* extra, void* dx,
+                        void* dw, float* scratch, long rows, int cols, int accumulate_dw, void* stream) {
+  if (cols % 8 || cols > 8 * kNormThreads * kNormVec) return -2;
+  if (rows == 0) return 0;
+  const int parts = mmt_rmsnorm_bwd_parts(rows);
+  rmsnorm_bwd_kernel<<<parts, kNormThreads, 0, ST(stream)>>>(CBF(dy), CBF(x), CBF(w), rstd, BF(dx), scratch, (int)rows,
+                                                            cols, CBF(extra));
   reduce_partials_kernel<<<(cols + 255) / 256, 256, 0, ST(stream)>>>(scratch, BF(dw), parts, cols, accumulate_dw);
   return (int)cudaGetLastError();
 }

@@ -50,15 +50,17 @@ def _rmsnorm_fwd(x: torch.Tensor, w: torch.Tensor, eps: float):
     return y, rstd
 
 
-def _rmsnorm_bwd(dy: torch.Tensor, x: torch.Tensor, w: torch.Tensor, rstd: torch.Tensor) -> torch.Tensor:
+def _rmsnorm_bwd(dy: torch.Tensor, x: torch.Tensor, w: torch.Tensor, rstd: torch.Tensor,
+                 extra: torch.Tensor) -> torch.Tensor:
+    """Gradient of the norm's input plus ``extra`` (the gradient arriving through the residual connection)."""
     rows, cols = x.shape
     dx = torch.empty_like(x)
     parts = nv.lib().mmt_rmsnorm_bwd_parts(rows)
     scratch = F._scratch_f32(parts * cols, x.device, "rmsnorm")
 
     def run(out, acc):
-        nv.call("mmt_rmsnorm_bwd", dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr(), dx.data_ptr(),
-                out.data_ptr(), scratch.data_ptr(), rows, cols, int(acc), nv.stream())
+        nv.call("mmt_rmsnorm_bwd_add", dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr(), extra.data_ptr(),
+                dx.data_ptr(), out.data_ptr(), scratch.data_ptr(), rows, cols, int(acc), nv.stream())
 
     _grad_into(w, run)
     return dx
@@ -178,15 +180,13 @@ class _LocalBlockFn(torch.autograd.Function):
         dm = _linear_bwd(dy, m, down_w, down_b)
         dgu = _swiglu_bwd(dm, gu)
         dh2 = _linear_bwd(dgu, h2, gu_w, gu_b)
-        dx1 = _rmsnorm_bwd(dh2, x1, ln2_w, rstd2)
-        nv.call("mmt_add", dx1.data_ptr(), dy.data_ptr(), dx1.data_ptr(), dx1.numel(), nv.stream())
+        dx1 = _rmsnorm_bwd(dh2, x1, ln2_w, rstd2, dy)
         # attention half
         da = _linear_bwd(dx1, a, proj_w, proj_b)
         dqkv = _attn_bwd(qkv, a, da, lse, s, seq)
         _rope_(dqkv, cos, sin, s.rope_heads, s.head_dim, True)
         dh1 = _linear_bwd(dqkv, h1, qkv_w, qkv_b)
-        dx = _rmsnorm_bwd(dh1, x, ln1_w, rstd1)
-        nv.call("mmt_add", dx.data_ptr(), dx1.data_ptr(), dx.data_ptr(), dx.numel(), nv.stream())
+        dx = _rmsnorm_bwd(dh1, x, ln1_w, rstd1, dx1)
         return (dx, None, None, None, None, None) + (None,) * len(ctx.has)
 
 

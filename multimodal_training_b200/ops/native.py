@@ -30,6 +30,7 @@ _SIGS = {
     "mmt_rmsnorm_fwd": (c_int, [_P, _P, _P, _P, c_long, c_int, c_float, _P]),
     "mmt_rmsnorm_bwd_parts": (c_int, [c_long]),
     "mmt_rmsnorm_bwd": (c_int, [_P, _P, _P, _P, _P, _P, _P, c_long, c_int, c_int, _P]),
+    "mmt_rmsnorm_bwd_add": (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, c_long, c_int, c_int, _P]),
     "mmt_rope": (c_int, [_P, _P, _P, c_long, c_int, c_int, c_long, c_int, _P]),
     "mmt_swiglu_fwd": (c_int, [_P, _P, c_long, c_int, _P]),
     "mmt_swiglu_bwd": (c_int, [_P, _P, _P, c_long, c_int, _P]),
@@ -109,7 +110,7 @@ def check(code: int, what: str) -> None:
 
 
 # entry points that launch more than one kernel per call
-_LAUNCHES = {"mmt_rmsnorm_bwd": 2, "mmt_colsum": 2, "mmt_attn_bwd": 3}
+_LAUNCHES = {"mmt_rmsnorm_bwd": 2, "mmt_rmsnorm_bwd_add": 2, "mmt_colsum": 2, "mmt_attn_bwd": 3}
 
 
 _FN: dict = {}
