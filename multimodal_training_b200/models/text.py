@@ -139,6 +139,8 @@ class TextDecoder(nn.Module):
         ckpt = decide_ckpt(self.ckpt, self.activation_bytes(x.shape[0]), x.device, group=self.tp.group,
                            key=("text", id(self))) if torch.is_grad_enabled() else False
         self.ckpt_now = ckpt
+        keep_ew = (not ckpt) and x.is_cuda and not decide_ckpt("auto", self.activation_bytes(x.shape[0]) * 3, x.device,
+                                                              group=self.tp.group, key=("text-ew", id(self)))
         if self.tp.fused is not None:
             self.tp.fused.set_checkpointed("text", ckpt)
         one_node = (self.tp.size == 1 and torch.is_grad_enabled() and blocks.usable(x)
@@ -149,7 +151,8 @@ class TextDecoder(nn.Module):
                                     causal=True, eps=self.cfg.rms_norm_eps, scale=1.0 / math.sqrt(d))
             for L in self.layers:
                 x = blocks.local_block(x, spec, cos, sin, seq, (L.ln1_w, L.qkv_w, L.qkv_b, L.o_w, None, L.ln2_w,
-                                                                L.gate_up_w, None, L.down_w, None), recompute=ckpt)
+                                                                L.gate_up_w, None, L.down_w, None), recompute=ckpt,
+                                       keep_elementwise=keep_ew)
             return x
         for L in self.layers:
             x = checkpoint(lambda t, L=L: self._layer(t, L, cos, sin, seq), (x,), enabled=ckpt)

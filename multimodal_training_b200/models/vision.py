@@ -151,6 +151,9 @@ class VisionEncoder(nn.Module):
         ckpt = decide_ckpt(self.ckpt, self.activation_bytes(x.shape[0]), x.device, group=self.sp.group,
                            key=("vision", id(self))) if torch.is_grad_enabled() else False
         self.ckpt_now = ckpt
+        # with memory to spare the element-wise intermediates are kept as well (1.5x the bytes, a quarter of the budget)
+        keep_ew = (not ckpt) and x.is_cuda and not decide_ckpt("auto", self.activation_bytes(x.shape[0]) * 3, x.device,
+                                                              group=self.sp.group, key=("vision-ew", id(self)))
         if self.sp.fused is not None:
             self.sp.fused.fc.set_checkpointed("vision", ckpt)
         one_node = torch.is_grad_enabled() and blocks.usable(x) and attn_mod.BACKEND == "sm100"
@@ -162,7 +165,7 @@ class VisionEncoder(nn.Module):
             if one_node and (not is_full or self.sp.size == 1):
                 x = blocks.local_block(x, spec, cos, sin, full_seq if is_full else win_seq,
                                        (B.norm1_w, B.qkv_w, B.qkv_b, B.proj_w, B.proj_b, B.norm2_w, B.gate_up_w,
-                                        B.gate_up_b, B.down_w, B.down_b), recompute=ckpt)
+                                        B.gate_up_b, B.down_w, B.down_b), recompute=ckpt, keep_elementwise=keep_ew)
                 continue
             x = checkpoint(lambda t, B=B, f=is_full: self._block(t, B, cos, sin, plan, win_seq, full_seq, f), (x,),
                            enabled=ckpt)

@@ -145,14 +145,14 @@ def _forward_chain(x, s: BlockSpec, cos, sin, seq, P, keep: bool):
 class _LocalBlockFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, spec, cos, sin, seq, recompute, *params):
+        # recompute: 2 = keep only the block input, 1 = also keep what is expensive to rebuild (GEMM and attention
+        # results; the element-wise intermediates are recomputed from them), 0 = keep every intermediate
         x = x if x.is_contiguous() else x.contiguous()
-        y, kept = _forward_chain(x, spec, cos, sin, seq, params, keep=not recompute)
+        y, kept = _forward_chain(x, spec, cos, sin, seq, params, keep=recompute < 2)
         extra = ()
-        if not recompute:
-            # keep what is expensive to rebuild (GEMM and attention results); the three element-wise intermediates
-            # (both normalised inputs and the SwiGLU output) are recomputed from them in backward
+        if recompute < 2:
             h1, rstd1, qkv, a, lse, x1, h2, rstd2, gu, m = kept
-            extra = (qkv, a, lse, x1, gu)
+            extra = (qkv, a, lse, x1, gu) if recompute == 1 else (qkv, a, lse, x1, gu, h1, rstd1, h2, rstd2, m)
         ctx.n_extra = len(extra)
         ctx.save_for_backward(x, cos, sin, *extra, *[p for p in params if p is not None])
         ctx.has = [p is not None for p in params]
@@ -169,7 +169,9 @@ class _LocalBlockFn(torch.autograd.Function):
         s, seq = ctx.spec, ctx.seq
         ln1_w, qkv_w, qkv_b, proj_w, proj_b, ln2_w, gu_w, gu_b, down_w, down_b = P
         dy = dy if dy.is_contiguous() else dy.contiguous()
-        if ctx.n_extra:
+        if ctx.n_extra == 10:
+            qkv, a, lse, x1, gu, h1, rstd1, h2, rstd2, m = extra
+        elif ctx.n_extra:
             qkv, a, lse, x1, gu = extra
             h1, rstd1 = _rmsnorm_fwd(x, ln1_w, s.eps)
             h2, rstd2 = _rmsnorm_fwd(x1, ln2_w, s.eps)
@@ -191,11 +193,13 @@ class _LocalBlockFn(torch.autograd.Function):
 
 
 def local_block(x: torch.Tensor, spec: BlockSpec, cos: torch.Tensor, sin: torch.Tensor, seq: SeqInfo, params: tuple,
-                recompute: bool = True):
+                recompute: bool = True, keep_elementwise: bool = False):
     """``params`` = (ln1_w, qkv_w, qkv_b, proj_w, proj_b, ln2_w, gate_up_w, gate_up_b, down_w, down_b); biases may
     be None.  x is [T, C] bf16 on the GPU; the result has the same shape.  ``recompute``: keep only the block input
-    and rebuild everything in backward (activation checkpointing), or keep the GEMM / attention results."""
-    return _LocalBlockFn.apply(x, spec, cos, sin, seq, bool(recompute), *params)
+    and rebuild everything in backward (activation checkpointing); else keep the GEMM / attention results and, with
+    ``keep_elementwise``, the normalised inputs and the SwiGLU output as well."""
+    level = 2 if recompute else (0 if keep_elementwise else 1)
+    return _LocalBlockFn.apply(x, spec, cos, sin, seq, level, *params)
 
 
 def usable(x: torch.Tensor) -> bool:

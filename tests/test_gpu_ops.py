@@ -211,7 +211,7 @@ def test_native_library_is_loaded():
     assert nv.lib().mmt_version().decode().startswith("mmt_b200")
 
 
-@pytest.mark.parametrize("recompute", [True, False])
+@pytest.mark.parametrize("recompute", [True, False, "keep_all"])
 @pytest.mark.parametrize("kind", ["vision", "text"])
 def test_local_block_matches_per_op_graph(kind, recompute):
     """The one-node transformer block (hand-written backward) against the same block built from the per-op
@@ -264,7 +264,7 @@ def test_local_block_matches_per_op_graph(kind, recompute):
                             scale=1.0 / math.sqrt(d))
     yb = blocks.local_block(xb, spec, cos, sin, seq, (pb["ln1"], pb["qkv_w"], pb["qkv_b"], pb["o_w"], pb["o_b"],
                                                       pb["ln2"], pb["gu_w"], pb["gu_b"], pb["dn_w"], pb["dn_b"]),
-                           recompute=recompute)
+                           recompute=recompute is True, keep_elementwise=recompute == "keep_all")
     yb.backward(dy)
     assert nv.get_error()[0] == 0
     assert rel_err(yb, ya.float()) < 1e-3
