@@ -161,8 +161,6 @@ def validate(cfg: dict) -> dict:
               "gradient_accumulation_steps"):
         if not isinstance(tr[k], int) or tr[k] < 1:
             raise ConfigError(f"training.{k} must be a positive integer")
-    if tr["gradient_accumulation_steps"] != 1:
-        raise ConfigError("training.gradient_accumulation_steps > 1 is not supported by the step loop")
     if float(tr["learning_rate"]) <= 0:
         raise ConfigError("training.learning_rate must be positive")
     return cfg

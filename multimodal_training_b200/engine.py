@@ -47,6 +47,7 @@ class HybridEngine:
         self.clip = bool(text_config.get("clip_grad_norm", False))
         self.max_norm = float(text_config.get("max_grad_norm", 1.0))
         self.step_index = 0
+        self.accum = self.text.accumulation_steps
         self.last_grad_norm = None
         # pinned host slots for train_step_async (allocated here: the first pinned allocation of a process is slow)
         pin = torch.cuda.is_available()
@@ -88,24 +89,33 @@ class HybridEngine:
         return torch.clamp(self.max_norm / (norm + 1e-6), max=1.0)
 
     def train_step(self, step: int | None = None) -> torch.Tensor:
-        """One optimisation step on the global batch of ``step``; returns this rank's loss (device scalar)."""
+        """One optimisation step (``gradient_accumulation_steps`` micro-batches of one global batch each); returns
+        this rank's loss averaged over the micro-batches (device scalar)."""
         step = self.step_index if step is None else step
         ph = self.timer.phase if self.timer is not None else (lambda name: tracing.trace_range(name))
         self.vision.zero_grad()
         self.text.zero_grad()
-        with ph("vision.forward"):
-            v_out = self.vision.forward_step(step)
-        if self._text_opt_event is not None:
-            # the text optimizer of the previous step ran on its own stream, behind this step's vision forward
-            torch.cuda.current_stream().wait_event(self._text_opt_event)
-            self._text_opt_event = None
-        with ph("text.forward"):
-            t_out = self.text.forward_step(v_out, step)
-        with ph("text.backward"):
-            g = self.text.backward_step()
-        if g["grad"] is not None:
-            with ph("vision.backward"):
-                self.vision.backward_step(g)
+        # gradient accumulation: micro-batches run back to back into the same flat gradient (the weight-gradient
+        # kernels overwrite on the first write of a step and accumulate afterwards); one optimizer step follows
+        loss = None
+        for micro in range(self.accum):
+            idx = self.text.data_index(step, micro)
+            with ph("vision.forward"):
+                v_out = self.vision.forward_step(idx)
+            if self._text_opt_event is not None:
+                # the text optimizer of the previous step ran on its own stream, behind this step's vision forward
+                torch.cuda.current_stream().wait_event(self._text_opt_event)
+                self._text_opt_event = None
+            with ph("text.forward"):
+                t_out = self.text.forward_step(v_out, idx)
+            with ph("text.backward"):
+                g = self.text.backward_step()
+            if g["grad"] is not None:
+                with ph("vision.backward"):
+                    self.vision.backward_step(g)
+            loss = t_out["loss"] if loss is None else loss + t_out["loss"]
+        if self.accum > 1:
+            loss = loss / self.accum
         with ph("optimizer"):
             scale = self._global_grad_scale() if self.clip else None
             for tr in (self.text, self.vision):
@@ -125,7 +135,7 @@ class HybridEngine:
         if self.timer is not None:
             self.timer.end_step()
         self.step_index = step + 1
-        return t_out["loss"]
+        return loss
 
     def join_streams(self) -> None:
         """Make the current stream wait for work this engine put on its side stream (no host synchronisation)."""

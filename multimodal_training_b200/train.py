@@ -91,6 +91,7 @@ def _run(cfg, vision_group, text_group, num_actors, parallel_size, dp_size) -> d
 
     num_epochs, num_iterations = int(tr["num_epochs"]), int(tr["num_iterations"])
     warmup_steps = int(tr.get("warmup_steps", 0))
+    accum = max(1, int(tr.get("gradient_accumulation_steps", 1)))
     log_interval = max(1, int(tr.get("log_interval", 1)))
     clip = bool(tr.get("clip_grad_norm", False))
     profile_time = bool(tr.get("profile_time", False))
@@ -115,14 +116,20 @@ def _run(cfg, vision_group, text_group, num_actors, parallel_size, dp_size) -> d
             t0 = time.perf_counter()
             vision_group.execute_all("zero_grad")
             text_group.execute_all("zero_grad")
-            vision_refs = vision_group.execute_all_async("forward_step", global_step)
-            text_refs = text_group.execute_all_async("forward_step", vision_refs, [global_step] * num_actors)
-            text_out = get(text_refs)
-            step_losses = [float(o["loss"]) for o in text_out]
-            loss = sum(step_losses) / len(step_losses)
-            text_bwd_refs = text_group.execute_all_async("backward_step")
-            vision_bwd_refs = vision_group.execute_all_async("backward_step", text_bwd_refs)
-            text_bwd, vision_bwd = get(text_bwd_refs), get(vision_bwd_refs)
+            loss = 0.0
+            for micro in range(accum):
+                if micro:
+                    vision_group.free(vision_refs + vision_bwd_refs)
+                    text_group.free(text_refs + text_bwd_refs)
+                idx = global_step * accum + micro
+                vision_refs = vision_group.execute_all_async("forward_step", idx)
+                text_refs = text_group.execute_all_async("forward_step", vision_refs, [idx] * num_actors)
+                text_out = get(text_refs)
+                step_losses = [float(o["loss"]) for o in text_out]
+                loss += sum(step_losses) / len(step_losses) / accum
+                text_bwd_refs = text_group.execute_all_async("backward_step")
+                vision_bwd_refs = vision_group.execute_all_async("backward_step", text_bwd_refs)
+                text_bwd, vision_bwd = get(text_bwd_refs), get(vision_bwd_refs)
             global_norm = None
             if clip:
                 vn = vision_group.execute_all("compute_grad_norm_contribution")

@@ -189,8 +189,18 @@ class Trainer(RayActor):
         if self.optimizer is not None:
             self.optimizer.zero_grad(set_to_none)
 
+    @property
+    def accumulation_steps(self) -> int:
+        return max(1, int(self.config.get("gradient_accumulation_steps", 1)))
+
+    def data_index(self, step: int, micro: int = 0) -> int:
+        """Index of the global batch that micro-step ``micro`` of optimizer step ``step`` consumes."""
+        return step * self.accumulation_steps + micro
+
     def _build_optimizer(self, named_params, group, grad_divisor: float, partial_grad_group=None):
         c = self.config
+        # micro-batches of one optimizer step accumulate in the flat gradient; their mean is what AdamW sees
+        grad_divisor = grad_divisor * self.accumulation_steps
         self.optimizer = ZeroAdamW(named_params, group=group, lr=float(c.get("learning_rate", 1e-4)),
                                    betas=(float(c.get("adam_beta1", 0.9)), float(c.get("adam_beta2", 0.999))),
                                    eps=float(c.get("adam_eps", 1e-8)), weight_decay=float(c.get("weight_decay", 0.0)),

@@ -128,3 +128,32 @@ def test_sp2_with_text_data_parallel_matches_single_process(single, tmp_path):
 def test_sp4_tp2_dp2_matches_single_process(single, tmp_path):
     multi = run_ranks(_worker, 4, tmp_path, 4, 2, 3)
     _compare(single, multi, tp=2)
+
+
+def _accum_worker(rank, world, global_batch, accum, steps):
+    from multimodal_training_b200.config.loader import load_config
+    from multimodal_training_b200.engine import HybridEngine
+
+    ov = [o for o in OV if "global_batch" not in o] + [
+        f"+data.synthetic.global_batch={global_batch}", f"training.batch_size={global_batch}",
+        f"training.gradient_accumulation_steps={accum}", "vision.parallelism=none", "text.parallelism=none",
+        "training.parallel_size=1", "training.clip_grad_norm=true", "training.max_grad_norm=0.5"]
+    eng = HybridEngine.from_config(load_config(None, ov))
+    losses = [float(eng.train_step(s)) for s in range(steps)]
+    return {"losses": losses, "norm": float(eng.last_grad_norm),
+            "vision": eng.vision.optimizer.flat_param.clone(), "text": eng.text.optimizer.flat_param.clone()}
+
+
+@pytest.mark.integration
+def test_gradient_accumulation_equals_the_larger_batch(tmp_path):
+    """Two micro-batches of one sample per optimizer step train exactly like one batch of the same two samples
+    (every synthetic sample has the same number of supervised tokens, so the mean of means is the mean)."""
+    (tmp_path / "a").mkdir()
+    (tmp_path / "b").mkdir()
+    big = run_ranks(_accum_worker, 1, tmp_path / "a", 2, 1, 3)[0]
+    acc = run_ranks(_accum_worker, 1, tmp_path / "b", 1, 2, 3)[0]
+    for a, b in zip(big["losses"], acc["losses"]):
+        assert abs(a - b) < 5e-5 * abs(a), (big["losses"], acc["losses"])
+    assert abs(big["norm"] - acc["norm"]) < 1e-4 * big["norm"]
+    for k in ("vision", "text"):
+        assert torch.allclose(big[k], acc[k], rtol=0, atol=2e-6), k
