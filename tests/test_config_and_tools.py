@@ -27,7 +27,7 @@ def test_sample_yaml_loads_through_the_hydra_style_cli():
 
 
 @pytest.mark.parametrize("ov", ["vision.parallelism=ring", "text.dtype=int8", "training.batch_size=0",
-                                "training.gradient_accumulation_steps=4", "vision.model_type=llava",
+                                "training.gradient_accumulation_steps=0", "vision.model_type=llava",
                                 "nosuch.key=1", "justakey"])
 def test_invalid_configs_are_rejected(ov):
     with pytest.raises(ConfigError):
