@@ -27,6 +27,9 @@ log = logging.getLogger("mmt_b200.merge")
 DIM0_PATTERNS = ("embed_tokens", "lm_head", "q_proj", "k_proj", "v_proj", "gate_proj", "up_proj", ".q.", ".k.", ".v.",
                  "qkv", "mlp.0", "fc1")
 DIM1_PATTERNS = ("o_proj", "down_proj", "attn.proj", "mlp.2", "fc2")
+ALWAYS_DIM0 = ("embed_tokens", "lm_head", "q_proj", "k_proj", "v_proj", "gate_proj", "up_proj", ".q.", ".k.", ".v.",
+               "attn.qkv")
+ALWAYS_DIM1 = ("o_proj", "down_proj", "attn.proj")
 
 
 def merge_tensor(key: str, shards: list[torch.Tensor]) -> torch.Tensor:
@@ -34,6 +37,12 @@ def merge_tensor(key: str, shards: list[torch.Tensor]) -> torch.Tensor:
     first = shards[0]
     if len(shards) == 1:
         return first
+    # layers that are always split by a tensor-parallel run are concatenated even when their shards happen to be
+    # bit-equal (biases that are still zero)
+    if any(p in key for p in ALWAYS_DIM0):
+        return torch.cat(shards, dim=0)
+    if any(p in key for p in ALWAYS_DIM1) and not key.endswith(".bias"):
+        return torch.cat(shards, dim=1)
     if all(s.shape == first.shape and torch.equal(s, first) for s in shards[1:]):
         return first                                        # replicated
     if first.dim() == 1:
@@ -53,6 +62,15 @@ def merge_tensor(key: str, shards: list[torch.Tensor]) -> torch.Tensor:
 def merge_state_dicts(rank_state_dicts: list[dict]) -> dict:
     keys = list(rank_state_dicts[0].keys())
     out = {}
+
+    def local(t):
+        return t.to_local() if hasattr(t, "to_local") else t
+
+    # data-parallel replicas (no tensor parallelism in that half): every file holds the same full tensors
+    first = rank_state_dicts[0]
+    if all(all(local(sd[k]).shape == local(first[k]).shape and torch.equal(local(sd[k]), local(first[k]))
+               for k in keys) for sd in rank_state_dicts[1:]):
+        return {k: local(first[k]) for k in keys}
     for k in keys:
         shards = []
         for sd in rank_state_dicts:
@@ -93,9 +111,11 @@ def refuse_vision_qkv(sd: dict) -> dict:
 
 
 def merge_checkpoint(checkpoint_dir: str, output_dir: str, model_name: str, parallel_size: int,
-                     text_parallel_size: int | None = None, keep_split_qkv: bool = False) -> str:
+                     text_parallel_size: int | None = None, keep_split_qkv: bool = False,
+                     vision_tensor_parallel: bool = False) -> str:
+    # sequence-parallel vision ranks hold identical weights (rank 0 is read); tensor-parallel ones hold shards
     vision = load_and_merge_sharded_weights(os.path.join(checkpoint_dir, "vision"), parallel_size, "vision",
-                                            replicated=True)
+                                            replicated=not vision_tensor_parallel)
     text = load_and_merge_sharded_weights(os.path.join(checkpoint_dir, "text"), text_parallel_size or parallel_size,
                                           "text")
     if not keep_split_qkv:
@@ -128,10 +148,12 @@ def main(argv=None) -> int:
     ap.add_argument("--parallel-size", type=int, default=1)
     ap.add_argument("--text-parallel-size", type=int, default=None)
     ap.add_argument("--keep-split-qkv", action="store_true")
+    ap.add_argument("--vision-tensor-parallel", action="store_true",
+                    help="the run used vision.parallelism=tensor: merge the vision shards of --parallel-size ranks")
     a = ap.parse_args(argv)
     logging.basicConfig(level=logging.INFO)
     merge_checkpoint(a.checkpoint_dir, a.output_dir, a.model_name, a.parallel_size, a.text_parallel_size,
-                     a.keep_split_qkv)
+                     a.keep_split_qkv, a.vision_tensor_parallel)
     return 0
 
 

@@ -81,7 +81,9 @@ class HybridEngine:
         self.vision._reduced_shard, self.text._reduced_shard = vs, ts
         va, vb = vo.grad_norm_sq_local(vs)
         ta, tb = to.grad_norm_sq_local(ts)
-        total = va + vb + ta + tb / max(self.mesh.tp, 1)
+        # parts that are replicated inside a tensor-parallel group are counted once
+        vtp = self.mesh.sp if getattr(self.vision, "tensor_parallel", False) else 1
+        total = va + vb / vtp + ta + tb / max(self.mesh.tp, 1)
         if self.mesh.world > 1:
             dist.all_reduce(total, group=self.mesh.world_group)
         norm = total.sqrt()

@@ -17,6 +17,12 @@ What differs by design:
   straight to their text rows (``parallel/handoff.py``).
 * q|k|v and gate|up are fused projections; the MLP width is zero-padded to a multiple of 8 so that
   activation rows are 16-byte aligned for TMA.  State dicts convert to the reference/HF layout.
+
+``vision.parallelism: tensor`` (the reference's DTensor plan for the encoder, python/ray/vision.py:200-219,687-702)
+is the second mode: every rank of the group sees all tokens of its replica's images, holds ``heads / tp`` attention
+heads and ``1 / tp`` of the MLP width (column-parallel q|k|v and gate|up, row-parallel proj and down) and the block
+outputs are all-reduced; norms, biases of the row-parallel layers, patch embedding and merger are replicated.
+Sequence parallelism is the faster layout (28 of 32 layers without communication); this mode exists for parity.
 """
 from __future__ import annotations
 
@@ -32,6 +38,7 @@ from ..ops import functional as F
 from ..ops.attention import SeqInfo
 from ..parallel import comm
 from ..parallel.sp import VisionPlan
+from ..parallel.tp import TPContext, copy_to_tp, reduce_from_tp
 from ..utils.checkpointing import checkpoint
 from ..utils.checkpointing import decide as decide_ckpt
 
@@ -45,14 +52,23 @@ class SPContext:
 
 class VisionEncoder(nn.Module):
     def __init__(self, cfg: VisionConfig, sp: SPContext | None = None, dtype=torch.float32, device="cpu",
-                 seed: int = 0, activation_checkpointing: bool = True):
+                 seed: int = 0, activation_checkpointing: bool = True, tp: TPContext | None = None):
         super().__init__()
         self.cfg = cfg
         self.sp = sp or SPContext()
+        self.tp = tp or TPContext.single()
         self.ckpt = activation_checkpointing
+        tpn, tpr = self.tp.size, self.tp.rank
         C, I, Ip = cfg.hidden_size, cfg.intermediate_size, cfg.padded_intermediate_size
         if cfg.num_heads % self.sp.size:
             raise ValueError(f"num_heads {cfg.num_heads} is not divisible by sequence_parallel_size {self.sp.size}")
+        if tpn > 1:
+            if self.sp.size > 1:
+                raise ValueError("the vision encoder is either sequence parallel or tensor parallel, not both")
+            if cfg.num_heads % tpn:
+                raise ValueError(f"num_heads {cfg.num_heads} is not divisible by tensor_parallel_size {tpn}")
+            Ip = (I + 8 * tpn - 1) // (8 * tpn) * (8 * tpn)      # every rank's slice of the MLP width 16-byte aligned
+        self.Ip, self.Il, self.Cl = Ip, Ip // tpn, C // tpn
         std = cfg.initializer_range
         gen = torch.Generator(device=device)
 
@@ -73,6 +89,20 @@ class VisionEncoder(nn.Module):
                 return t
             return torch.cat([t, t.new_zeros(t.shape[0], n - t.shape[1])], dim=1)
 
+        def head_rows(t):                 # [3C, ...] -> this rank's heads of q, of k and of v
+            if tpn == 1:
+                return t
+            Cl = C // tpn
+            return torch.cat([t[j * C + tpr * Cl:j * C + (tpr + 1) * Cl] for j in range(3)], 0)
+
+        def my_rows(t):
+            n = t.shape[0] // tpn
+            return t[tpr * n:(tpr + 1) * n]
+
+        def my_cols(t):
+            n = t.shape[1] // tpn
+            return t[:, tpr * n:(tpr + 1) * n]
+
         z = lambda n: torch.zeros(n, device=device)  # noqa: E731
         o = lambda n: torch.ones(n, device=device)   # noqa: E731
         idx = 0
@@ -82,17 +112,25 @@ class VisionEncoder(nn.Module):
         for _ in range(cfg.depth):
             B = nn.Module()
             B.norm1_w, B.norm2_w = P(o(C)), P(o(C))
-            B.qkv_w, B.qkv_b = P(full((3 * C, C), idx)), P(z(3 * C))
-            B.proj_w, B.proj_b = P(full((C, C), idx + 1)), P(z(C))
-            B.gate_up_w = P(torch.cat([pad_rows(full((I, C), idx + 2), Ip), pad_rows(full((I, C), idx + 3), Ip)], 0))
-            B.gate_up_b = P(z(2 * Ip))
-            B.down_w, B.down_b = P(pad_cols(full((C, I), idx + 4), Ip)), P(z(C))
+            B.qkv_w, B.qkv_b = P(head_rows(full((3 * C, C), idx))), P(z(3 * C // tpn))
+            B.proj_w, B.proj_b = P(my_cols(full((C, C), idx + 1))), P(z(C))
+            B.gate_up_w = P(torch.cat([my_rows(pad_rows(full((I, C), idx + 2), Ip)),
+                                       my_rows(pad_rows(full((I, C), idx + 3), Ip))], 0))
+            B.gate_up_b = P(z(2 * Ip // tpn))
+            B.down_w, B.down_b = P(my_cols(pad_cols(full((C, I), idx + 4), Ip))), P(z(C))
             idx += 5
             self.blocks.append(B)
         M = C * cfg.merge_unit
         self.ln_q_w = P(o(C))
         self.merger_fc1_w, self.merger_fc1_b = P(full((M, M), idx)), P(z(M))
         self.merger_fc2_w, self.merger_fc2_b = P(full((cfg.out_hidden_size, M), idx + 1)), P(z(cfg.out_hidden_size))
+        if tpn > 1:
+            # identical on every tensor-parallel rank (same inputs, all-reduced gradients): counted once in the norm
+            sharded = {id(p) for B in self.blocks for p in (B.qkv_w, B.qkv_b, B.proj_w, B.gate_up_w, B.gate_up_b,
+                                                            B.down_w)}
+            for p in self.parameters():
+                if id(p) not in sharded:
+                    p.tensor_replicated = True
 
     # ------------------------------------------------------------------ attention variants
     def _full_attention(self, qkv: torch.Tensor, plan: VisionPlan, full_seq: SeqInfo) -> torch.Tensor:
@@ -129,6 +167,19 @@ class VisionEncoder(nn.Module):
         m = F.swiglu(F.linear(h, B.gate_up_w, B.gate_up_b))
         return F.linear(m, B.down_w, B.down_b, x)
 
+    def _block_tp(self, x, B, cos, sin, seq):
+        """Tensor-parallel block on replicated activations: local heads / local MLP columns, two all-reduces."""
+        cfg, tp = self.cfg, self.tp
+        nh, d = cfg.num_heads // tp.size, cfg.head_dim
+        h = copy_to_tp(F.rmsnorm(x, B.norm1_w, cfg.rms_norm_eps), tp)
+        qkv = F.linear(h, B.qkv_w, B.qkv_b)
+        qkv = F.rope(qkv, cos, sin, 2 * nh, d)
+        a = F.attention(qkv, nh, nh, d, seq, causal=False)
+        x = x + reduce_from_tp(F.linear(a, B.proj_w), tp) + B.proj_b
+        h = copy_to_tp(F.rmsnorm(x, B.norm2_w, cfg.rms_norm_eps), tp)
+        m = F.swiglu(F.linear(h, B.gate_up_w, B.gate_up_b))
+        return x + reduce_from_tp(F.linear(m, B.down_w), tp) + B.down_b
+
     def activation_bytes(self, tokens: int) -> int:
         """Bytes of activations that all blocks keep for backward when nothing is recomputed (bf16)."""
         cfg = self.cfg
@@ -148,20 +199,26 @@ class VisionEncoder(nn.Module):
         # blocks without communication inside run as one hand-written autograd node each (ops/blocks.py); the
         # Ulysses layers of a sequence-parallel run and the CPU path use the per-op graph.  Whether activations
         # are recomputed in backward is decided per step (True / False / "auto": keep them when they fit)
-        ckpt = decide_ckpt(self.ckpt, self.activation_bytes(x.shape[0]), x.device, group=self.sp.group,
+        peers = self.tp.group if self.tp.size > 1 else self.sp.group
+        ckpt = decide_ckpt(self.ckpt, self.activation_bytes(x.shape[0]), x.device, group=peers,
                            key=("vision", id(self))) if torch.is_grad_enabled() else False
         self.ckpt_now = ckpt
         # with memory to spare the element-wise intermediates are kept as well (1.5x the bytes, a quarter of the budget)
         keep_ew = (not ckpt) and x.is_cuda and not decide_ckpt("auto", self.activation_bytes(x.shape[0]) * 3, x.device,
-                                                              group=self.sp.group, key=("vision-ew", id(self)))
+                                                              group=peers, key=("vision-ew", id(self)))
         if self.sp.fused is not None:
             self.sp.fused.fc.set_checkpointed("vision", ckpt)
-        one_node = torch.is_grad_enabled() and blocks.usable(x) and attn_mod.BACKEND == "sm100"
+        one_node = (torch.is_grad_enabled() and blocks.usable(x) and attn_mod.BACKEND == "sm100"
+                    and self.tp.size == 1)
         spec = blocks.BlockSpec(n_q=cfg.num_heads, n_kv=cfg.num_heads, head_dim=cfg.head_dim,
                                 rope_heads=2 * cfg.num_heads, causal=False, eps=cfg.rms_norm_eps,
                                 scale=1.0 / math.sqrt(cfg.head_dim))
         for i, B in enumerate(self.blocks):
             is_full = i in cfg.fullatt_block_indexes
+            if self.tp.size > 1:
+                x = checkpoint(lambda t, B=B, f=is_full: self._block_tp(t, B, cos, sin, full_seq if f else win_seq),
+                               (x,), enabled=ckpt)
+                continue
             if one_node and (not is_full or self.sp.size == 1):
                 x = blocks.local_block(x, spec, cos, sin, full_seq if is_full else win_seq,
                                        (B.norm1_w, B.qkv_w, B.qkv_b, B.proj_w, B.proj_b, B.norm2_w, B.gate_up_w,
@@ -180,20 +237,24 @@ class VisionEncoder(nn.Module):
         ``merger.{ln_q,mlp.0,mlp.2}``, ``patch_embed.proj.weight`` [C,3,2,14,14].  ``fused_qkv`` emits HF's
         ``attn.qkv`` instead of the reference's split q/k/v (python/ray/vision.py:322-345)."""
         cfg = self.cfg
-        C, I, Ip = cfg.hidden_size, cfg.intermediate_size, cfg.padded_intermediate_size
+        # a tensor-parallel rank emits its shards under the same keys (rows of q/k/v/gate/up, columns of proj/down;
+        # the zero padding of the MLP width is cut off, so the shards concatenate to the reference's shapes)
+        C, Cl, Il = cfg.hidden_size, self.Cl, self.Il
+        I = min(max(cfg.intermediate_size - self.tp.rank * Il, 0), Il)        # valid MLP columns of this rank
+        Ip = Il
         out = {"patch_embed.proj.weight": self.patch_embed_w.detach().view(
             C, cfg.in_channels, cfg.temporal_patch_size, cfg.patch_size, cfg.patch_size)}
         for i, B in enumerate(self.blocks):
             p = f"blocks.{i}."
             out[p + "norm1.weight"] = B.norm1_w.detach()
             out[p + "norm2.weight"] = B.norm2_w.detach()
-            if fused_qkv:
+            if fused_qkv and self.tp.size == 1:
                 out[p + "attn.qkv.weight"] = B.qkv_w.detach()
                 out[p + "attn.qkv.bias"] = B.qkv_b.detach()
             else:
                 for j, n in enumerate("qkv"):
-                    out[p + f"attn.{n}.weight"] = B.qkv_w.detach()[j * C:(j + 1) * C]
-                    out[p + f"attn.{n}.bias"] = B.qkv_b.detach()[j * C:(j + 1) * C]
+                    out[p + f"attn.{n}.weight"] = B.qkv_w.detach()[j * Cl:(j + 1) * Cl]
+                    out[p + f"attn.{n}.bias"] = B.qkv_b.detach()[j * Cl:(j + 1) * Cl]
             out[p + "attn.proj.weight"] = B.proj_w.detach()
             out[p + "attn.proj.bias"] = B.proj_b.detach()
             out[p + "mlp.gate_proj.weight"] = B.gate_up_w.detach()[:I]
@@ -210,10 +271,29 @@ class VisionEncoder(nn.Module):
         return {k: v.clone() for k, v in out.items()}
 
     @torch.no_grad()
-    def load_reference_state_dict(self, sd: dict[str, torch.Tensor]) -> list[str]:
-        """Accepts split q/k/v (reference) or fused ``attn.qkv`` (HF); prefixes ``visual.`` / ``model.visual.``."""
+    def load_reference_state_dict(self, sd: dict[str, torch.Tensor], sharded: bool = False) -> list[str]:
+        """Accepts split q/k/v (reference) or fused ``attn.qkv`` (HF); prefixes ``visual.`` / ``model.visual.``.
+        A tensor-parallel rank takes its slices of full tensors, or with ``sharded`` its own shards as written by
+        ``reference_state_dict``."""
         cfg = self.cfg
-        C, I, Ip = cfg.hidden_size, cfg.intermediate_size, cfg.padded_intermediate_size
+        C, Cl, Il = cfg.hidden_size, self.Cl, self.Il
+        tpn, tpr = self.tp.size, self.tp.rank
+        I = min(max(cfg.intermediate_size - tpr * Il, 0), Il)
+        Ip = Il
+        take = tpn > 1 and not sharded
+
+        def rows(t, width=None):          # this rank's rows of a full column-parallel tensor
+            if not take:
+                return t
+            n = width or t.shape[0] // tpn
+            return t[tpr * n:tpr * n + n]
+
+        def cols(t, width=None):
+            if not take:
+                return t
+            n = width or t.shape[1] // tpn
+            return t[:, tpr * n:tpr * n + n]
+
         clean = {}
         for k, v in sd.items():
             for pre in ("model.visual.", "visual."):
@@ -233,21 +313,22 @@ class VisionEncoder(nn.Module):
             B.norm1_w.copy_(get(p + "norm1.weight"))
             B.norm2_w.copy_(get(p + "norm2.weight"))
             if p + "attn.qkv.weight" in clean:
-                B.qkv_w.copy_(get(p + "attn.qkv.weight"))
-                B.qkv_b.copy_(get(p + "attn.qkv.bias"))
+                w, b = get(p + "attn.qkv.weight"), get(p + "attn.qkv.bias")
+                B.qkv_w.copy_(torch.cat([rows(w[j * C:(j + 1) * C]) for j in range(3)], 0) if take else w)
+                B.qkv_b.copy_(torch.cat([rows(b[j * C:(j + 1) * C]) for j in range(3)], 0) if take else b)
             else:
-                B.qkv_w.copy_(torch.cat([get(p + f"attn.{n}.weight") for n in "qkv"], 0))
-                B.qkv_b.copy_(torch.cat([get(p + f"attn.{n}.bias") for n in "qkv"], 0))
-            B.proj_w.copy_(get(p + "attn.proj.weight"))
+                B.qkv_w.copy_(torch.cat([rows(get(p + f"attn.{n}.weight")) for n in "qkv"], 0))
+                B.qkv_b.copy_(torch.cat([rows(get(p + f"attn.{n}.bias")) for n in "qkv"], 0))
+            B.proj_w.copy_(cols(get(p + "attn.proj.weight")))
             B.proj_b.copy_(get(p + "attn.proj.bias"))
             B.gate_up_w.zero_()
             B.gate_up_b.zero_()
             B.down_w.zero_()
-            B.gate_up_w[:I].copy_(get(p + "mlp.gate_proj.weight"))
-            B.gate_up_w[Ip:Ip + I].copy_(get(p + "mlp.up_proj.weight"))
-            B.gate_up_b[:I].copy_(get(p + "mlp.gate_proj.bias"))
-            B.gate_up_b[Ip:Ip + I].copy_(get(p + "mlp.up_proj.bias"))
-            B.down_w[:, :I].copy_(get(p + "mlp.down_proj.weight"))
+            B.gate_up_w[:I].copy_(rows(get(p + "mlp.gate_proj.weight"), Il))
+            B.gate_up_w[Ip:Ip + I].copy_(rows(get(p + "mlp.up_proj.weight"), Il))
+            B.gate_up_b[:I].copy_(rows(get(p + "mlp.gate_proj.bias"), Il))
+            B.gate_up_b[Ip:Ip + I].copy_(rows(get(p + "mlp.up_proj.bias"), Il))
+            B.down_w[:, :I].copy_(cols(get(p + "mlp.down_proj.weight"), Il))
             B.down_b.copy_(get(p + "mlp.down_proj.bias"))
         self.ln_q_w.copy_(get("merger.ln_q.weight"))
         self.merger_fc1_w.copy_(get("merger.mlp.0.weight"))

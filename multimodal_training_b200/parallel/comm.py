@@ -89,6 +89,20 @@ def reduce_scatter(x: torch.Tensor, group) -> torch.Tensor:
     return _ReduceScatter.apply(x, group)
 
 
+def all_gather_ragged(x: torch.Tensor, rows: list[int], group) -> list[torch.Tensor]:
+    """Every rank's ``[rows[p], ...]`` tensor on every rank (no autograd); shorter ones travel padded."""
+    n = group_size(group)
+    if n == 1:
+        return [x]
+    width = max(rows)
+    mine = x.contiguous()
+    if mine.shape[0] < width:
+        mine = torch.cat([mine, mine.new_zeros((width - mine.shape[0],) + tuple(mine.shape[1:]))], 0)
+    parts = [torch.empty_like(mine) for _ in range(n)]
+    dist.all_gather(parts, mine, group=group)
+    return [p[:r] for p, r in zip(parts, rows)]
+
+
 # ---------------------------------------------------------------------------
 # all-reduce variants
 # ---------------------------------------------------------------------------

@@ -1,4 +1,5 @@
-"""Tensor parallelism with sequence-parallel activations for the text decoder.
+"""Tensor parallelism: sequence-parallel activations for the text decoder, replicated activations for the vision
+encoder's optional tensor-parallel mode (``copy_to_tp`` / ``reduce_from_tp``).
 
 Activations between layers are sharded along the token axis (T/tp rows per rank).  A
 column-parallel linear all-gathers its input rows and multiplies by its slice of the output
@@ -53,6 +54,16 @@ def row_parallel_linear(x: torch.Tensor, w: torch.Tensor, residual_shard: torch.
         return ctx.fused.linear_rs(x, w, residual_shard, role=role)
     y = comm.reduce_scatter(F.linear(x, w), ctx.group)
     return y if residual_shard is None else y + residual_shard
+
+
+def copy_to_tp(x: torch.Tensor, ctx: TPContext) -> torch.Tensor:
+    """Input of a column-parallel linear on replicated activations: identity, gradient summed over the group."""
+    return x if ctx.size == 1 else comm.copy_to_group(x, ctx.group)
+
+
+def reduce_from_tp(x: torch.Tensor, ctx: TPContext) -> torch.Tensor:
+    """Output of a row-parallel linear on replicated activations: summed over the group, gradient passes through."""
+    return x if ctx.size == 1 else comm.all_reduce_sum_autograd(x, ctx.group)
 
 
 def shard_rows(full: torch.Tensor, size: int, rank: int) -> torch.Tensor:

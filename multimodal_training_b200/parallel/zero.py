@@ -11,9 +11,11 @@ Replaces DeepSpeed ZeRO-1 around an external ``torch.optim.Adam`` in the referen
 decoupled weight decay (AdamW), fp32 master weights and moments, gradients summed over ranks that
 split tokens (sequence parallel) and averaged over data-parallel replicas.
 
-Layout of the flat buffer: [decayed params | non-decayed params | non-decayed params whose
-gradient is a partial sum over the tensor-parallel group], each parameter padded to 128 elements,
-the total padded so that all shards are equal and 1024-aligned.
+Layout of the flat buffer: [decayed | decayed, replicated over the tensor-parallel group |
+non-decayed, replicated (among them the sequence-parallel ones whose gradient is a partial sum over
+that group) | non-decayed], each parameter padded to 128 elements, the total padded so that all
+shards are equal and 1024-aligned.  The replicated range is contiguous: the gradient norm counts it
+once per tensor-parallel group.
 """
 from __future__ import annotations
 
@@ -53,22 +55,32 @@ class ZeroAdamW:
         self.fused = fused
         self.step_count = 0
 
-        decay = [(n, p) for n, p in uniq if not no_decay_fn(n)]
-        partial = [(n, p) for n, p in uniq if no_decay_fn(n) and getattr(p, "sequence_parallel", False)]
-        nodecay = [(n, p) for n, p in uniq if no_decay_fn(n) and not getattr(p, "sequence_parallel", False)]
+        def replicated(p):
+            return getattr(p, "sequence_parallel", False) or getattr(p, "tensor_replicated", False)
+
+        for n, p in uniq:
+            if getattr(p, "sequence_parallel", False) and not no_decay_fn(n):
+                raise ValueError(f"{n}: a parameter with partial-sum gradients must be in the non-decayed set")
+        decay = [(n, p) for n, p in uniq if not no_decay_fn(n) and not replicated(p)]
+        decay_rep = [(n, p) for n, p in uniq if not no_decay_fn(n) and replicated(p)]
+        nodecay_rep = [(n, p) for n, p in uniq if no_decay_fn(n) and replicated(p)]
+        nodecay = [(n, p) for n, p in uniq if no_decay_fn(n) and not replicated(p)]
         self.names, self.params, offsets = [], [], []
         off = 0
-        for seg in (decay, nodecay, partial):
+        marks = {}
+        for tag, seg in (("decay", decay), ("decay_rep", decay_rep), ("nodecay_rep", nodecay_rep),
+                         ("nodecay", nodecay)):
+            marks[tag] = off
             for n, p in seg:
                 self.names.append(n)
                 self.params.append(p)
                 offsets.append(off)
                 off += (p.numel() + ALIGN - 1) // ALIGN * ALIGN
-            if seg is decay:
-                self.n_decay = off
-            if seg is nodecay:
-                self.partial_start = off
-        self.partial_end = off
+        self.n_decay = marks["nodecay_rep"]            # [0, n_decay) gets weight decay
+        # [rep_start, rep_end): identical on every rank of the tensor-parallel group (counted once in the norm);
+        # its non-decayed part [partial_start, partial_end) is what ``partial_grad_group`` all-reduces
+        self.rep_start, self.rep_end = marks["decay_rep"], marks["nodecay"]
+        self.partial_start, self.partial_end = marks["nodecay_rep"], marks["nodecay"]
         quantum = self.gsize * 1024
         self.total = (off + quantum - 1) // quantum * quantum if off else quantum
         self.shard = self.total // self.gsize
@@ -149,7 +161,7 @@ class ZeroAdamW:
         """(sum of squares of TP-sharded parameters' gradients, same for TP-replicated ones) in this shard,
         after ``reduce_gradients`` and including the ``grad_divisor`` scaling."""
         lo, hi = self.shard_lo, self.shard_lo + self.shard
-        ps, pe = max(self.partial_start, lo), min(self.partial_end, hi)
+        ps, pe = max(self.rep_start, lo), min(self.rep_end, hi)
         total = torch.zeros(1, dtype=torch.float32, device=self.device)
         F.sum_squares(shard, total)
         rep = torch.zeros(1, dtype=torch.float32, device=self.device)

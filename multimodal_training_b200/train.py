@@ -52,7 +52,8 @@ def aggregate_grad_norms(vision_norms: list[dict], text_norms: list[dict], dp_si
     """
     total = 0.0
     for n in vision_norms:
-        total += float(n.get("sharded", 0.0)) + float(n.get("replicated", 0.0))
+        vtp = max(1, int(n.get("tp_size", 1))) if n.get("type") == "tensor" else 1
+        total += float(n.get("sharded", 0.0)) + float(n.get("replicated", 0.0)) / vtp
     tp = max(1, int(text_norms[0].get("tp_size", parallel_size))) if text_norms else 1
     for n in text_norms:
         total += float(n.get("sharded", 0.0)) + float(n.get("replicated", 0.0)) / tp

@@ -91,9 +91,9 @@ def build_step_context(step: int, samples: list, cfg: VLConfig, mesh: Mesh, *, p
                        n_text)
 
 
-def local_pixels(ctx: StepContext, out: torch.Tensor | None = None) -> torch.Tensor:
+def local_pixels(ctx: StepContext, out: torch.Tensor | None = None, plan: VisionPlan | None = None) -> torch.Tensor:
     """Host gather of this rank's patches (local window order) from the samples' pixel arrays."""
-    plan = ctx.vision_plan
+    plan = plan or ctx.vision_plan
     pix = [ctx.samples[i].pixel_values for i in ctx.vision_samples]
     allpix = pix[0] if len(pix) == 1 else torch.cat(pix, dim=0)
     if out is not None:

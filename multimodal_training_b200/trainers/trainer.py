@@ -230,7 +230,14 @@ class Trainer(RayActor):
         a, b = opt.grad_norm_sq_local(shard)
         self._last_norm_parts = (a, b)
         return {"type": self.norm_type, "sharded": float(a.item()), "replicated": float(b.item()),
-                "zero_size": opt.gsize, "zero_rank": opt.grank, "tp_size": self._ensure_mesh().tp}
+                "zero_size": opt.gsize, "zero_rank": opt.grank, "tp_size": self._norm_tp_size()}
+
+    def _norm_tp_size(self) -> int:
+        """Size of the group inside which this trainer's replicated parameters repeat."""
+        mesh = self._ensure_mesh()
+        if self.kind == "vision":
+            return mesh.sp if getattr(self, "tensor_parallel", False) else 1
+        return mesh.tp
 
     def optimizer_step(self, global_grad_norm: float | None = None) -> float:
         """Clip (if configured and a global norm is given) -> fused AdamW on the owned shard -> parameter all-gather."""

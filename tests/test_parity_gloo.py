@@ -157,3 +157,88 @@ def test_gradient_accumulation_equals_the_larger_batch(tmp_path):
     assert abs(big["norm"] - acc["norm"]) < 1e-4 * big["norm"]
     for k in ("vision", "text"):
         assert torch.allclose(big[k], acc[k], rtol=0, atol=2e-6), k
+
+
+def _vision_tp_worker(rank, world, steps, tp=None):
+    """Vision tensor parallel over all ranks (replicated activations, all-reduce), text tensor parallel."""
+    import torch.distributed as dist
+    from multimodal_training_b200.config.loader import load_config
+    from multimodal_training_b200.engine import HybridEngine
+
+    tp = tp or world
+    ov = OV + ["vision.parallelism=tensor", "text.parallelism=tensor", f"text.tensor_parallel_size={tp}",
+               f"training.parallel_size={tp}", f"training.dp_size={world // tp}",
+               f"training.batch_size={2 // (world // tp)}"]
+    eng = HybridEngine.from_config(load_config(None, ov))
+    assert eng.vision.tensor_parallel and eng.vision.model.tp.size == tp
+    eng.vision.zero_grad()
+    eng.text.zero_grad()
+    vo = eng.vision.forward_step(0)
+    to = eng.text.forward_step(vo, 0)
+    g = eng.text.backward_step()
+    eng.vision.backward_step(g)
+    eng.vision.optimizer._finish_grads()
+    vgrads = _grads_reference_layout(eng.vision.model)
+    loss0 = eng.mean_loss(to["loss"])
+    losses = [eng.mean_loss(eng.train_step(s)) for s in range(steps)]
+    # clipping path: the norm counts replicated parameters once
+    eng.clip, eng.max_norm = True, 1e9
+    eng.train_step(steps)
+    return {"loss0": loss0, "losses": losses, "vgrads": vgrads, "norm": float(eng.last_grad_norm),
+            "weights": eng.vision.model.reference_state_dict(), "rank": rank, "tp_rank": eng.mesh.sp_rank}
+
+
+def _single_norm_worker(rank, world, steps):
+    from multimodal_training_b200.config.loader import load_config
+    from multimodal_training_b200.engine import HybridEngine
+    ov = OV + ["vision.parallelism=none", "text.parallelism=none", "training.parallel_size=1",
+               "training.batch_size=2"]
+    eng = HybridEngine.from_config(load_config(None, ov))
+    for s in range(steps):
+        eng.train_step(s)
+    eng.clip, eng.max_norm = True, 1e9
+    eng.train_step(steps)
+    return {"norm": float(eng.last_grad_norm), "weights": eng.vision.model.reference_state_dict()}
+
+
+@pytest.mark.integration
+def test_vision_tensor_parallel_matches_single_process(single, tmp_path):
+    from multimodal_training_b200.cli.merge_checkpoint import merge_state_dicts
+    (tmp_path / "tp").mkdir()
+    (tmp_path / "one").mkdir()
+    multi = sorted(run_ranks(_vision_tp_worker, 2, tmp_path / "tp", 3), key=lambda r: r["rank"])
+    assert abs(single["loss0"] - multi[0]["loss0"]) < 2e-5 * abs(single["loss0"])
+    for a, b in zip(single["losses"], multi[0]["losses"]):
+        assert abs(a - b) < 5e-5 * abs(a), (single["losses"], multi[0]["losses"])
+    merged = merge_state_dicts([r["vgrads"] for r in multi])
+    for k, ref in single["vgrads"].items():
+        got = merged[k]
+        assert got.shape == ref.shape, (k, got.shape, ref.shape)
+        err = (got - ref).abs().max().item() / (ref.abs().max().item() + 1e-12)
+        assert err < 2e-4, ("vision", k, err)
+    one = run_ranks(_single_norm_worker, 1, tmp_path / "one", 3)[0]
+    assert abs(one["norm"] - multi[0]["norm"]) < 1e-4 * one["norm"], (one["norm"], multi[0]["norm"])
+    weights = merge_state_dicts([r["weights"] for r in multi])
+    for k, ref in one["weights"].items():
+        assert weights[k].shape == ref.shape, k
+        # Adam's early updates are +-lr whatever the gradient's size, so elements whose gradient is rounding noise
+        # may move differently; everything else must agree closely
+        diff = (weights[k] - ref).abs()
+        assert diff.max().item() <= 4 * 2e-4 + 1e-6, (k, diff.max().item())
+        assert (diff > 1e-5).float().mean().item() < 0.02, (k, (diff > 1e-5).float().mean().item())
+
+
+@pytest.mark.integration
+def test_vision_tensor_parallel_with_data_parallel(single, tmp_path):
+    """Vision and text tensor parallel of size 2, two data-parallel replicas with one sample each."""
+    multi = run_ranks(_vision_tp_worker, 4, tmp_path, 3, 2)
+    for a, b in zip(single["losses"], multi[0]["losses"]):
+        assert abs(a - b) < 5e-5 * abs(a), (single["losses"], multi[0]["losses"])
+    for r in multi[1:]:
+        assert abs(r["norm"] - multi[0]["norm"]) < 1e-5 * multi[0]["norm"]
+    # replicas hold the same weights after the steps
+    for a in multi:
+        for b in multi:
+            if a["tp_rank"] == b["tp_rank"]:
+                for k in a["weights"]:
+                    assert torch.equal(a["weights"][k], b["weights"][k]), k

@@ -57,3 +57,31 @@ def test_greedy_generate_and_merged_checkpoint_round_trip():
     dst.load_merged_state_dict(state)
     with torch.no_grad():
         assert torch.allclose(dst.model(ids, pix, [(1, 16, 16)]), src.model(ids, pix, [(1, 16, 16)]), atol=1e-5)
+
+
+def test_vision_tensor_parallel_shards_round_trip():
+    """Shards written by tensor-parallel vision ranks merge to the single-process state dict (MLP padding cut off),
+    and a tensor-parallel rank loads its slices from full weights or its own shard."""
+    from multimodal_training_b200.cli.merge_checkpoint import merge_state_dicts
+    from multimodal_training_b200.config.model_configs import get_model_config
+    from multimodal_training_b200.models.vision import VisionEncoder
+    from multimodal_training_b200.parallel.tp import TPContext
+
+    cfg = get_model_config("tiny").vision
+    full = VisionEncoder(cfg, seed=3).reference_state_dict()
+    ranks = [VisionEncoder(cfg, seed=3, tp=TPContext(None, 2, r)) for r in range(2)]
+    merged = merge_state_dicts([m.reference_state_dict() for m in ranks])
+    assert merged.keys() == full.keys()
+    for k, v in full.items():
+        assert torch.equal(merged[k], v), k
+    other = VisionEncoder(cfg, seed=9).reference_state_dict()
+    for r, m in enumerate(ranks):
+        m.load_reference_state_dict(other)                                   # slices of full tensors
+        shard = m.reference_state_dict()
+        fresh = VisionEncoder(cfg, seed=1, tp=TPContext(None, 2, r))
+        fresh.load_reference_state_dict(shard, sharded=True)                 # its own shard
+        for (ka, a), (kb, b) in zip(m.state_dict().items(), fresh.state_dict().items()):
+            assert ka == kb and torch.equal(a, b), ka
+    merged = merge_state_dicts([m.reference_state_dict() for m in ranks])
+    for k, v in other.items():
+        assert torch.equal(merged[k], v), k
