@@ -1,6 +1,7 @@
 """Worker of tests/test_gpu_multi.py (run under torch.distributed.run, one rank per GPU):
-trains the small bf16 model for a few steps with the fused peer-memory collectives and again with the
-NCCL collectives from the same initial weights, and prints both loss series as JSON on rank 0."""
+trains the small bf16 model for a few steps with the fused peer-memory collectives, again with the NCCL
+collectives, and once more with a tensor-parallel vision encoder, each from the same initial weights, and prints
+the loss series as JSON on rank 0."""
 import json
 import os
 import sys
@@ -11,7 +12,7 @@ import torch  # noqa: E402
 import torch.distributed as dist  # noqa: E402
 
 
-def run(fused: bool, steps: int):
+def run(fused: bool, steps: int, vision: str = "sequence"):
     from multimodal_training_b200.config.loader import load_config
     from multimodal_training_b200.engine import HybridEngine
     from multimodal_training_b200.ops import native as nv
@@ -19,7 +20,7 @@ def run(fused: bool, steps: int):
 
     world = dist.get_world_size()
     cfg = load_config(None, [
-        "vision.model_name=smoke", "text.model_name=smoke", "vision.parallelism=sequence", "text.parallelism=tensor",
+        "vision.model_name=smoke", "text.model_name=smoke", f"vision.parallelism={vision}", "text.parallelism=tensor",
         f"training.parallel_size={world}", f"text.tensor_parallel_size={min(world, 2)}", "training.batch_size=2",
         "training.learning_rate=1e-3", "training.warmup_ratio=0", "training.warmup_steps=0",
         "training.lr_scheduler_type=constant", "+data.synthetic.image_size=448", "+data.synthetic.text_tokens=256",
@@ -38,8 +39,9 @@ def main():
     dist.init_process_group("nccl", device_id=torch.device("cuda", int(os.environ["LOCAL_RANK"])))
     fused = run(True, 4)
     lib = run(False, 4)
+    vtp = run(False, 4, vision="tensor")          # tensor-parallel vision encoder (all-reduce per block)
     if dist.get_rank() == 0:
-        print("RESULT " + json.dumps({"fused": fused, "lib": lib}))
+        print("RESULT " + json.dumps({"fused": fused, "lib": lib, "vision_tp": vtp}))
     dist.barrier()
     dist.destroy_process_group()
 

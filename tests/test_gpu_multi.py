@@ -1,4 +1,5 @@
-"""Multi-GPU checks (skipped on a single-GPU box): the fused peer-memory collectives train like the NCCL path."""
+"""Multi-GPU checks (skipped on a single-GPU box): the fused peer-memory collectives train like the NCCL path, and so
+does the tensor-parallel layout of the vision encoder."""
 import json
 import os
 import subprocess
@@ -22,4 +23,6 @@ def test_fused_collectives_match_nccl_on_two_gpus():
     res = json.loads(line[len("RESULT "):])
     assert res["fused"][-1] < res["fused"][0]
     for a, b in zip(res["fused"], res["lib"]):
+        assert abs(a - b) < 3e-2 * abs(b), res
+    for a, b in zip(res["vision_tp"], res["lib"]):
         assert abs(a - b) < 3e-2 * abs(b), res
