@@ -113,68 +113,110 @@ __global__ void __launch_bounds__(kNormThreads) rmsnorm_fwd_kernel(const bf16* _
   }
 }
 
-// dx = rstd * (g - x * rstd^2 * mean(g * x)),  g = dy * w.
-// Each CTA walks rows blockIdx.x, +gridDim.x, ... and keeps its share of
-// dw = sum_rows(dy * x * rstd) in registers; the per-CTA partial sums go to
-// `dw_partial` [gridDim.x, cols] (fp32 scratch) for the second-stage reduction.
-__global__ void __launch_bounds__(kNormThreads) rmsnorm_bwd_kernel(const bf16* __restrict__ dy,
-                                                                  const bf16* __restrict__ x,
-                                                                  const bf16* __restrict__ w,
-                                                                  const float* __restrict__ rstd_in,
-                                                                  bf16* __restrict__ dx, float* __restrict__ dw_partial,
-                                                                  int rows, int cols,
-                                                                  const bf16* __restrict__ extra = nullptr) {
-  __shared__ float red[32];
-  const int nvec = cols >> 3;
-  float dwacc[kNormVec][8];
-  float wv[kNormVec][8];
+MMT_DEVICE void unpack8(const uint4& u, float (&v)[8]) {
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
-  for (int i = 0; i < kNormVec; ++i) {
+  for (int j = 0; j < 4; ++j) {
+    const float2 f = unpack_bf16x2(w[j]);
+    v[2 * j] = f.x;
+    v[2 * j + 1] = f.y;
+  }
+}
+
+// dx = rstd * (g - x * rstd^2 * mean(g * x)) (+ extra),  g = dy * w.
+// A thread owns VEC fixed 8-column vectors, so its share of dw = sum_rows(dy * x * rstd) stays in registers; the
+// per-CTA partial sums go to `dw_partial` [gridDim.x, cols] (fp32 scratch) for the second-stage reduction.
+// A CTA takes R rows per iteration: all their loads are issued before the one block reduction of the R row
+// dots (one __syncthreads per iteration, the exchange buffer alternates), which keeps enough bytes in flight per SM
+// to run at memory speed; the rows are held as raw bf16 so that R x VEC vectors fit in registers.
+template <int VEC, int R>
+__global__ void __launch_bounds__(kNormThreads, VEC <= 2 ? 2 : 1) rmsnorm_bwd_kernel(const bf16* __restrict__ dy,
+                                                                     const bf16* __restrict__ x,
+                                                                     const bf16* __restrict__ w,
+                                                                     const float* __restrict__ rstd_in,
+                                                                     bf16* __restrict__ dx,
+                                                                     float* __restrict__ dw_partial, int rows, int cols,
+                                                                     const bf16* __restrict__ extra) {
+  constexpr int kWarps = kNormThreads / 32;
+  __shared__ float red[2][R][kWarps];
+  const int nvec = cols >> 3;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float dwacc[VEC][8];
+  float wv[VEC][8];
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) {
     const int c = threadIdx.x + i * kNormThreads;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) dwacc[i][j] = 0.f;
+    for (int j = 0; j < 8; ++j) dwacc[i][j] = 0.f, wv[i][j] = 0.f;
     if (c < nvec) load8(w + c * 8, wv[i]);
   }
-  for (long row = blockIdx.x; row < rows; row += gridDim.x) {
-    const float rstd = rstd_in[row];
-    float xv[kNormVec][8], g[kNormVec][8];
-    float dot = 0.f;
+  int buf = 0;
+  for (long row0 = (long)blockIdx.x * R; row0 < rows; row0 += (long)gridDim.x * R, buf ^= 1) {
+    uint4 xr[R][VEC], dr[R][VEC], er[R][VEC];
+    float rs[R], dot[R];
 #pragma unroll
-    for (int i = 0; i < kNormVec; ++i) {
-      const int c = threadIdx.x + i * kNormThreads;
-      if (c < nvec) {
-        float d[8];
-        load8(x + row * cols + c * 8, xv[i]);
-        load8(dy + row * cols + c * 8, d);
+    for (int r = 0; r < R; ++r) {
+      const long row = row0 + r;
+      const bool ok = row < rows;
+      rs[r] = ok ? rstd_in[row] : 0.f;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          g[i][j] = d[j] * wv[i][j];
-          dot += g[i][j] * xv[i][j];
-          dwacc[i][j] += d[j] * xv[i][j] * rstd;
+      for (int i = 0; i < VEC; ++i) {
+        const int c = threadIdx.x + i * kNormThreads;
+        xr[r][i] = dr[r][i] = er[r][i] = make_uint4(0u, 0u, 0u, 0u);
+        if (ok && c < nvec) {
+          xr[r][i] = *reinterpret_cast<const uint4*>(x + row * cols + c * 8);
+          dr[r][i] = *reinterpret_cast<const uint4*>(dy + row * cols + c * 8);
+          if (extra) er[r][i] = *reinterpret_cast<const uint4*>(extra + row * cols + c * 8);
         }
       }
     }
-    dot = block_sum<kNormThreads>(dot, red);
-    const float coef = dot * rstd * rstd / (float)cols;
 #pragma unroll
-    for (int i = 0; i < kNormVec; ++i) {
-      const int c = threadIdx.x + i * kNormThreads;
-      if (c < nvec) {
-        float o[8];
+    for (int r = 0; r < R; ++r) {
+      float acc = 0.f;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) o[j] = rstd * (g[i][j] - xv[i][j] * coef);
-        if (extra) {      // gradient that reaches the same tensor through the residual connection
-          float ev[8];
-          load8(extra + row * cols + c * 8, ev);
+      for (int i = 0; i < VEC; ++i) {
+        float xv[8], d[8];
+        unpack8(xr[r][i], xv);
+        unpack8(dr[r][i], d);
 #pragma unroll
-          for (int j = 0; j < 8; ++j) o[j] += ev[j];
+        for (int j = 0; j < 8; ++j) {
+          acc += d[j] * wv[i][j] * xv[j];
+          dwacc[i][j] += d[j] * xv[j] * rs[r];
         }
-        store8(dx + row * cols + c * 8, o);
+      }
+      acc = warp_sum(acc);
+      if (lane == 0) red[buf][r][warp] = acc;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      float t = 0.f;
+#pragma unroll
+      for (int k = 0; k < kWarps; ++k) t += red[buf][r][k];
+      dot[r] = t;
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const long row = row0 + r;
+      if (row >= rows) continue;
+      const float coef = dot[r] * rs[r] * rs[r] / (float)cols;
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) {
+        const int c = threadIdx.x + i * kNormThreads;
+        if (c < nvec) {
+          float xv[8], d[8], e[8], o[8];
+          unpack8(xr[r][i], xv);
+          unpack8(dr[r][i], d);
+          unpack8(er[r][i], e);      // zeros without `extra`
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] = rs[r] * (d[j] * wv[i][j] - xv[j] * coef) + e[j];
+          store8(dx + row * cols + c * 8, o);
+        }
       }
     }
   }
 #pragma unroll
-  for (int i = 0; i < kNormVec; ++i) {
+  for (int i = 0; i < VEC; ++i) {
     const int c = threadIdx.x + i * kNormThreads;
     if (c < nvec) {
       float* dst = dw_partial + (long)blockIdx.x * cols + c * 8;
@@ -184,15 +226,26 @@ __global__ void __launch_bounds__(kNormThreads) rmsnorm_bwd_kernel(const bf16* _
   }
 }
 
-// out[c] (+)= sum_p partial[p, c]; out is bf16.
-__global__ void reduce_partials_kernel(const float* __restrict__ partial, bf16* __restrict__ out, int parts, int cols,
-                                       int accumulate) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= cols) return;
+// out[c] (+)= sum_p partial[p, c]; out is bf16.  Block (32 columns, 8 part lanes): the parts are summed by eight
+// lanes with independent loads and combined in a fixed order, so the result does not depend on scheduling.
+__global__ void __launch_bounds__(256) reduce_partials_kernel(const float* __restrict__ partial, bf16* __restrict__ out,
+                                                              int parts, int cols, int accumulate) {
+  __shared__ float red[8][33];
+  const int c = blockIdx.x * 32 + threadIdx.x;
   float s = 0.f;
-  for (int p = 0; p < parts; ++p) s += partial[(long)p * cols + c];
-  if (accumulate) s += __bfloat162float(out[c]);
-  out[c] = __float2bfloat16(s);
+  if (c < cols) {
+#pragma unroll 4
+    for (int p = threadIdx.y; p < parts; p += 8) s += partial[(long)p * cols + c];
+  }
+  red[threadIdx.y][threadIdx.x] = s;
+  __syncthreads();
+  if (threadIdx.y == 0 && c < cols) {
+    float t = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) t += red[k][threadIdx.x];
+    if (accumulate) t += __bfloat162float(out[c]);
+    out[c] = __float2bfloat16(t);
+  }
 }
 
 // ----------------------------------------------------------------------------
@@ -538,15 +591,40 @@ int mmt_rmsnorm_bwd_parts(long rows) {
   return (int)(rows < cap ? (rows > 0 ? rows : 1) : cap);
 }
 
+static void launch_reduce_partials(const float* scratch, void* out, int parts, int cols, int accumulate,
+                                   void* stream) {
+  reduce_partials_kernel<<<(cols + 31) / 32, dim3(32, 8), 0, ST(stream)>>>(scratch, BF(out), parts, cols, accumulate);
+}
+
+// Launches the backward kernel on at most `max_parts` CTAs; returns the number of partial rows it wrote.
+static int launch_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, const void* extra,
+                              void* dx, float* scratch, long rows, int cols, int max_parts, void* stream) {
+  const int vec = (cols / 8 + kNormThreads - 1) / kNormThreads;
+  const int r = vec == 1 ? 4 : 2;
+  long grid = (rows + r - 1) / r;
+  if (grid > max_parts) grid = max_parts;
+  if (grid < 1) grid = 1;
+#define MMT_NORM_BWD(V, RR)                                                                                        \
+  rmsnorm_bwd_kernel<V, RR><<<(unsigned)grid, kNormThreads, 0, ST(stream)>>>(CBF(dy), CBF(x), CBF(w), rstd, BF(dx), \
+                                                                             scratch, (int)rows, cols, CBF(extra))
+  switch (vec) {
+    case 1: MMT_NORM_BWD(1, 4); break;
+    case 2: MMT_NORM_BWD(2, 2); break;
+    case 3: MMT_NORM_BWD(3, 2); break;
+    default: MMT_NORM_BWD(4, 2); break;
+  }
+#undef MMT_NORM_BWD
+  return (int)grid;
+}
+
 // dx and dw (bf16; accumulate_dw adds to the existing dw).  scratch: fp32 [parts, cols].
 int mmt_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx, void* dw,
                     float* scratch, long rows, int cols, int accumulate_dw, void* stream) {
   if (cols % 8 || cols > 8 * kNormThreads * kNormVec) return -2;
   if (rows == 0) return 0;
-  const int parts = mmt_rmsnorm_bwd_parts(rows);
-  rmsnorm_bwd_kernel<<<parts, kNormThreads, 0, ST(stream)>>>(CBF(dy), CBF(x), CBF(w), rstd, BF(dx), scratch, (int)rows,
-                                                            cols);
-  reduce_partials_kernel<<<(cols + 255) / 256, 256, 0, ST(stream)>>>(scratch, BF(dw), parts, cols, accumulate_dw);
+  const int parts = launch_rmsnorm_bwd(dy, x, w, rstd, nullptr, dx, scratch, rows, cols, mmt_rmsnorm_bwd_parts(rows),
+                                       stream);
+  launch_reduce_partials(scratch, dw, parts, cols, accumulate_dw, stream);
   return (int)cudaGetLastError();
 }
 
@@ -556,10 +634,9 @@ int mmt_rmsnorm_bwd_add(const void* dy, const void* x, const void* w, const floa
                         void* dw, float* scratch, long rows, int cols, int accumulate_dw, void* stream) {
   if (cols % 8 || cols > 8 * kNormThreads * kNormVec) return -2;
   if (rows == 0) return 0;
-  const int parts = mmt_rmsnorm_bwd_parts(rows);
-  rmsnorm_bwd_kernel<<<parts, kNormThreads, 0, ST(stream)>>>(CBF(dy), CBF(x), CBF(w), rstd, BF(dx), scratch, (int)rows,
-                                                            cols, CBF(extra));
-  reduce_partials_kernel<<<(cols + 255) / 256, 256, 0, ST(stream)>>>(scratch, BF(dw), parts, cols, accumulate_dw);
+  const int parts = launch_rmsnorm_bwd(dy, x, w, rstd, extra, dx, scratch, rows, cols, mmt_rmsnorm_bwd_parts(rows),
+                                       stream);
+  launch_reduce_partials(scratch, dw, parts, cols, accumulate_dw, stream);
   return (int)cudaGetLastError();
 }
 
@@ -635,7 +712,7 @@ int mmt_colsum(const void* x, void* out, float* scratch, long rows, int cols, lo
   const int parts = mmt_colsum_parts(rows);
   dim3 grid((cols + 255) / 256, parts), block(32, 8);
   colsum_partial_kernel<<<grid, block, 0, ST(stream)>>>(CBF(x), scratch, rows, cols, ld);
-  reduce_partials_kernel<<<(cols + 255) / 256, 256, 0, ST(stream)>>>(scratch, BF(out), parts, cols, accumulate);
+  launch_reduce_partials(scratch, out, parts, cols, accumulate, stream);
   return (int)cudaGetLastError();
 }
 
@@ -724,8 +801,7 @@ extern "C" int mmt_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void
   int parts = mmt_rmsnorm_bwd_parts(rows);
   const int cap = MMT_NOALLOC_SCRATCH_FLOATS / cols;
   if (parts > cap) parts = cap;
-  rmsnorm_bwd_kernel<<<parts, kNormThreads, 0, ST(stream)>>>(CBF(dy), CBF(x), CBF(w), rstd, BF(dx), scratch,
-                                                            (int)rows, cols);
-  reduce_partials_kernel<<<(cols + 255) / 256, 256, 0, ST(stream)>>>(scratch, BF(dw), parts, cols, accumulate_dw);
+  parts = launch_rmsnorm_bwd(dy, x, w, rstd, nullptr, dx, scratch, rows, cols, parts, stream);
+  launch_reduce_partials(scratch, dw, parts, cols, accumulate_dw, stream);
   return (int)cudaGetLastError();
 }

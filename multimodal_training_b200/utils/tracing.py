@@ -34,13 +34,16 @@ def enabled() -> bool:
 
 @contextlib.contextmanager
 def trace_range(name: str):
-    """NVTX range around a block of launches (no-op unless tracing is on and CUDA is in use)."""
+    """NVTX range around a block of launches (no-op unless tracing is on and CUDA is in use).
+
+    A start/end range, not push/pop: push/pop ranges belong to the calling thread, and the kernels of a backward
+    pass are launched by autograd's worker thread, so a profiler filtering on a push/pop range would miss them."""
     if _ENABLED and torch.cuda.is_available():
-        torch.cuda.nvtx.range_push(name)
+        handle = torch.cuda.nvtx.range_start(name)
         try:
             yield
         finally:
-            torch.cuda.nvtx.range_pop()
+            torch.cuda.nvtx.range_end(handle)
     else:
         yield
 

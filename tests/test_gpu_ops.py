@@ -78,7 +78,7 @@ def test_linear_autograd_matches_reference():
     assert rel_err(r.grad, rf.grad) < 1e-6
 
 
-@pytest.mark.parametrize("rows,cols", [(1000, 1280), (333, 3584), (64, 5120), (17, 256)])
+@pytest.mark.parametrize("rows,cols", [(1001, 1280), (333, 3584), (65, 5120), (37, 8192), (17, 256)])
 def test_rmsnorm(rows, cols):
     F, nv = _F()
     torch.manual_seed(3)
