@@ -123,6 +123,51 @@ MMT_DEVICE void unpack8(const uint4& u, float (&v)[8]) {
   }
 }
 
+// Forward for rows of up to 4096 columns: one warp per row (the row stays in registers as raw bf16, the sum of
+// squares needs shuffles only), eight rows per CTA, no block-wide barrier.
+template <int VPL>
+__global__ void __launch_bounds__(kNormThreads) rmsnorm_fwd_warp_kernel(const bf16* __restrict__ x,
+                                                                       const bf16* __restrict__ w,
+                                                                       bf16* __restrict__ y,
+                                                                       float* __restrict__ rstd_out, long rows,
+                                                                       int cols, float eps) {
+  const int lane = threadIdx.x & 31;
+  const long row = (long)blockIdx.x * (kNormThreads / 32) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int nvec = cols >> 3;
+  const bf16* xr = x + row * cols;
+  uint4 raw[VPL];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    const int c = lane + i * 32;
+    raw[i] = make_uint4(0u, 0u, 0u, 0u);
+    if (c < nvec) raw[i] = *reinterpret_cast<const uint4*>(xr + c * 8);
+  }
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    float v[8];
+    unpack8(raw[i], v);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) ss += v[j] * v[j];
+  }
+  ss = warp_sum(ss);
+  const float rstd = rsqrtf(ss / (float)cols + eps);
+  if (lane == 0 && rstd_out) rstd_out[row] = rstd;
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    const int c = lane + i * 32;
+    if (c < nvec) {
+      float v[8], wv[8], o[8];
+      unpack8(raw[i], v);
+      load8(w + c * 8, wv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = v[j] * rstd * wv[j];
+      store8(y + row * cols + c * 8, o);
+    }
+  }
+}
+
 // dx = rstd * (g - x * rstd^2 * mean(g * x)) (+ extra),  g = dy * w.
 // A thread owns VEC fixed 8-column vectors, so its share of dw = sum_rows(dy * x * rstd) stays in registers; the
 // per-CTA partial sums go to `dw_partial` [gridDim.x, cols] (fp32 scratch) for the second-stage reduction.
@@ -287,6 +332,50 @@ __global__ void rope_kernel(bf16* __restrict__ x, const float* __restrict__ cos_
     }
     *reinterpret_cast<uint32_t*>(base + c) = pack_bf16x2(o_lo0, o_lo1);
     *reinterpret_cast<uint32_t*>(base + c + half) = pack_bf16x2(o_hi0, o_hi1);
+  }
+}
+
+// Same rotation with 16-byte accesses: a thread takes eight adjacent columns of the low half of a head and the
+// matching eight of the high half (needs dim / 2 to be a multiple of 8).
+__global__ void __launch_bounds__(256, 4) rope_vec8_kernel(bf16* __restrict__ x, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                 long tokens, int heads, int dim, long row_stride, float sign) {
+  const int half = dim >> 1;
+  const int vecs = half >> 3;
+  const long total = tokens * heads * vecs;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    const int vv = (int)(i % vecs);
+    const long th = i / vecs;
+    const int h = (int)(th % heads);
+    const long t = th / heads;
+    const int c = vv * 8;
+    bf16* base = x + t * row_stride + (long)h * dim;
+    float lo[8], hi[8], o_lo[8], o_hi[8];
+    load8(base + c, lo);
+    load8(base + c + half, hi);
+    const float* cr = cos_t + t * dim;
+    const float* sr = sin_t + t * dim;
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      const float4 c_lo = *reinterpret_cast<const float4*>(cr + c + 4 * q);
+      const float4 c_hi = *reinterpret_cast<const float4*>(cr + c + half + 4 * q);
+      const float4 s_lo = *reinterpret_cast<const float4*>(sr + c + 4 * q);
+      const float4 s_hi = *reinterpret_cast<const float4*>(sr + c + half + 4 * q);
+      const float cl[4] = {c_lo.x, c_lo.y, c_lo.z, c_lo.w}, ch[4] = {c_hi.x, c_hi.y, c_hi.z, c_hi.w};
+      const float sl[4] = {s_lo.x, s_lo.y, s_lo.z, s_lo.w}, sh[4] = {s_hi.x, s_hi.y, s_hi.z, s_hi.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int k = 4 * q + j;
+        if (sign > 0.f) {
+          o_lo[k] = lo[k] * cl[j] - hi[k] * sl[j];
+          o_hi[k] = hi[k] * ch[j] + lo[k] * sh[j];
+        } else {
+          o_lo[k] = lo[k] * cl[j] + hi[k] * sh[j];
+          o_hi[k] = hi[k] * ch[j] - lo[k] * sl[j];
+        }
+      }
+    }
+    store8(base + c, o_lo);
+    store8(base + c + half, o_hi);
   }
 }
 
@@ -581,7 +670,15 @@ extern "C" {
 int mmt_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, long rows, int cols, float eps, void* stream) {
   if (cols % 8 || cols > 8 * kNormThreads * kNormVec) return -2;
   if (rows == 0) return 0;
-  rmsnorm_fwd_kernel<<<(unsigned)rows, kNormThreads, 0, ST(stream)>>>(CBF(x), CBF(w), BF(y), rstd, cols, eps);
+  const int vpl = (cols / 8 + 31) / 32;
+  const unsigned grid8 = (unsigned)((rows + kNormThreads / 32 - 1) / (kNormThreads / 32));
+  if (vpl <= 8) {
+    rmsnorm_fwd_warp_kernel<8><<<grid8, kNormThreads, 0, ST(stream)>>>(CBF(x), CBF(w), BF(y), rstd, rows, cols, eps);
+  } else if (vpl <= 16) {
+    rmsnorm_fwd_warp_kernel<16><<<grid8, kNormThreads, 0, ST(stream)>>>(CBF(x), CBF(w), BF(y), rstd, rows, cols, eps);
+  } else {
+    rmsnorm_fwd_kernel<<<(unsigned)rows, kNormThreads, 0, ST(stream)>>>(CBF(x), CBF(w), BF(y), rstd, cols, eps);
+  }
   return (int)cudaGetLastError();
 }
 
@@ -645,6 +742,14 @@ int mmt_rope(void* x, const float* cos_t, const float* sin_t, long tokens, int h
   if (dim % 4) return -2;
   const long work = tokens * heads * (dim / 4);
   if (work == 0) return 0;
+  const bool aligned = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(cos_t) |
+                         reinterpret_cast<uintptr_t>(sin_t)) & 15) == 0;
+  if (dim % 16 == 0 && row_stride % 8 == 0 && aligned) {
+    const long work8 = tokens * heads * (dim / 16);
+    rope_vec8_kernel<<<grid_for(work8, 256, mmt_sm_count() * 8), 256, 0, ST(stream)>>>(
+        BF(x), cos_t, sin_t, tokens, heads, dim, row_stride, backward ? -1.f : 1.f);
+    return (int)cudaGetLastError();
+  }
   rope_kernel<<<grid_for(work, 256, mmt_sm_count() * 8), 256, 0, ST(stream)>>>(BF(x), cos_t, sin_t, tokens, heads, dim,
                                                                               row_stride, backward ? -1.f : 1.f);
   return (int)cudaGetLastError();
