@@ -284,6 +284,9 @@ def main() -> int:
                     "timer": "host wall clock between barriers, max over ranks",
                     "loss_read": "copied to pinned host memory every step, read by the host one step later"},
             "host_enqueue_ms_per_step": host_enqueue_ms,
+            "host_enqueue_note": "wall time of the loop that enqueues the timed steps; once the host is about a "
+                                 "thousand launches ahead it waits for launch-queue slots, so this approaches the "
+                                 "device time from below even when the host is not the limit",
             "gpu_launches": int(launches),
         }
         print(json.dumps(out))
