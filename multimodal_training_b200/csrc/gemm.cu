@@ -676,7 +676,7 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 // leader CTA issues tcgen05.mma.cta_group::2 with M = 256, and each CTA's tensor memory receives its
 // 128 x 256 half of the accumulator.  Compared with the 1-CTA kernel every B byte is read from
 // shared memory once per 256 rows instead of once per 128, which is what lifts the shared-memory
-// bandwidth bound of 128 x 256 tiles.  No multicast anywhere: every CTA loads exactly what it keeps.
+// bandwidth bound of 128 x 256 tiles.  Every CTA loads exactly what it keeps (plain TMA loads only).
 //
 // Barriers: full[s] lives in the leader and counts the bytes of BOTH CTAs' TMA loads (the follower's
 // loads signal the leader's barrier); empty[s] and tfull[a] exist in both CTAs and the leader's
