@@ -69,7 +69,8 @@ def report(name: str, seconds: float, flops: float = 0.0, bytes_: float = 0.0, *
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["gemm", "attention", "attention_bwd", "rmsnorm", "swiglu", "adamw", "ce"])
+    ap.add_argument("kernel", choices=["gemm", "attention", "attention_bwd", "rmsnorm", "rmsnorm_bwd", "rope", "swiglu",
+                                      "adamw", "ce"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8192)
     ap.add_argument("--k", type=int, default=8192)
@@ -143,6 +144,23 @@ def main(argv=None) -> int:
         with torch.no_grad():
             t = timed(lambda: F.rmsnorm(x, w), a.iters, a.warmup, flush)
         report("rmsnorm_fwd", t, bytes_=4.0 * a.rows * a.cols, shape=[a.rows, a.cols])
+    elif a.kernel == "rmsnorm_bwd":
+        from ..ops import blocks
+        x = torch.randn(a.rows, a.cols, device=dev, dtype=torch.bfloat16)
+        dy, extra = torch.randn_like(x), torch.randn_like(x)
+        w = torch.ones(a.cols, device=dev, dtype=torch.bfloat16)
+        _, rstd = blocks._rmsnorm_fwd(x, w, 1e-6)
+        t = timed(lambda: blocks._rmsnorm_bwd(dy, x, w, rstd, extra), a.iters, a.warmup, flush)
+        report("rmsnorm_bwd(+residual gradient, dw)", t, bytes_=8.0 * a.rows * a.cols, shape=[a.rows, a.cols])
+    elif a.kernel == "rope":
+        width = a.heads * a.dim
+        x = torch.randn(a.rows, width, device=dev, dtype=torch.bfloat16)
+        ang = torch.rand(a.rows, a.dim // 2, device=dev) * 6.28
+        ang = torch.cat([ang, ang], -1)
+        cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+        from ..ops import blocks
+        t = timed(lambda: blocks._rope_(x, cos, sin, a.heads, a.dim, False), a.iters, a.warmup, flush)
+        report("rope (in place)", t, bytes_=4.0 * a.rows * width + 8.0 * a.rows * a.dim, shape=[a.rows, a.heads, a.dim])
     elif a.kernel == "swiglu":
         gu = torch.randn(a.rows, 2 * a.cols, device=dev, dtype=torch.bfloat16)
         with torch.no_grad():
