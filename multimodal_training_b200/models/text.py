@@ -139,7 +139,7 @@ class TextDecoder(nn.Module):
         ckpt = decide_ckpt(self.ckpt, self.activation_bytes(x.shape[0]), x.device, group=self.tp.group,
                            key=("text", id(self))) if torch.is_grad_enabled() else False
         self.ckpt_now = ckpt
-        keep_ew = (not ckpt) and x.is_cuda and not decide_ckpt("auto", self.activation_bytes(x.shape[0]) * 3, x.device,
+        keep_ew = (not ckpt) and x.is_cuda and not decide_ckpt("auto", self.activation_bytes(x.shape[0]) * 2, x.device,
                                                               group=self.tp.group, key=("text-ew", id(self)))
         if self.tp.fused is not None:
             self.tp.fused.set_checkpointed("text", ckpt)

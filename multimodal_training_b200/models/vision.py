@@ -203,8 +203,8 @@ class VisionEncoder(nn.Module):
         ckpt = decide_ckpt(self.ckpt, self.activation_bytes(x.shape[0]), x.device, group=peers,
                            key=("vision", id(self))) if torch.is_grad_enabled() else False
         self.ckpt_now = ckpt
-        # with memory to spare the element-wise intermediates are kept as well (1.5x the bytes, a quarter of the budget)
-        keep_ew = (not ckpt) and x.is_cuda and not decide_ckpt("auto", self.activation_bytes(x.shape[0]) * 3, x.device,
+        # with memory to spare (twice the estimate still fits the budget) the element-wise intermediates are kept too
+        keep_ew = (not ckpt) and x.is_cuda and not decide_ckpt("auto", self.activation_bytes(x.shape[0]) * 2, x.device,
                                                               group=peers, key=("vision-ew", id(self)))
         if self.sp.fused is not None:
             self.sp.fused.fc.set_checkpointed("vision", ckpt)
