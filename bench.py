@@ -7,7 +7,8 @@
 Configuration (weak scaling: one sample per GPU, global batch = N): every sample is one 896x896
 image (N(0,1) pixels, 4096 patches -> 1024 merged vision tokens) spliced into 1024 uniform-random
 text tokens; random-init weights of the 7B architecture; bf16 compute; full AdamW (fp32 master
-weights and moments) with ZeRO-1; activation checkpointing.  Parallel layout: vision
+weights and moments) with ZeRO-1; activation checkpointing ``auto`` (activations are kept when they fit
+in HBM; the same steps are also timed with recomputation forced on and reported in ``config``).  Parallel layout: vision
 sequence-parallel over all N GPUs, text tensor-parallel over min(N, 4) GPUs with sequence-parallel
 activations, data-parallel above that (N=8: SP=8 + TP=4 x DP=2).
 
