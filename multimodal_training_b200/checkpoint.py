@@ -36,14 +36,21 @@ def find_latest_checkpoint(checkpoint_dir: str) -> int | None:
 
 
 def save_epoch_checkpoint(checkpoint_dir: str, epoch: int, vision_group, text_group, config: dict) -> str:
+    return _save(checkpoint_dir, epoch, f"epoch_{epoch}", vision_group, text_group, config, {})
+
+
+def _save(checkpoint_dir: str, tag, name: str, vision_group, text_group, config: dict, extra_meta: dict) -> str:
+    """Fan ``save_checkpoint(checkpoint_dir, tag)`` out to every actor, then write ``{name}/metadata.json`` (last,
+    so a directory without it is an interrupted save and is ignored by the finders)."""
     from .runtime.actor_group import get
 
-    v_refs = vision_group.execute_all_async("save_checkpoint", checkpoint_dir, epoch)
-    t_refs = text_group.execute_all_async("save_checkpoint", checkpoint_dir, epoch)
+    v_refs = vision_group.execute_all_async("save_checkpoint", checkpoint_dir, tag)
+    t_refs = text_group.execute_all_async("save_checkpoint", checkpoint_dir, tag)
     v_paths, t_paths = get(v_refs), get(t_refs)
-    epoch_dir = os.path.join(checkpoint_dir, f"epoch_{epoch}")
+    epoch_dir = os.path.join(checkpoint_dir, name)
     os.makedirs(epoch_dir, exist_ok=True)
     tr = config.get("training", {})
+    epoch = extra_meta.get("epoch", tag)
     meta = {
         "epoch": epoch,
         "timestamp": time.strftime("%Y-%m-%dT%H:%M:%S"),
@@ -57,12 +64,56 @@ def save_epoch_checkpoint(checkpoint_dir: str, epoch: int, vision_group, text_gr
             "dp_size": tr.get("dp_size", 1),
         },
     }
+    meta.update(extra_meta)
     tmp = os.path.join(epoch_dir, "metadata.json.tmp")
     with open(tmp, "w") as f:
         json.dump(meta, f, indent=2)
     os.replace(tmp, os.path.join(epoch_dir, "metadata.json"))
-    log.info("Saved checkpoint for epoch %d to %s", epoch, epoch_dir)
+    log.info("Saved checkpoint %s to %s", name, epoch_dir)
     return epoch_dir
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# Step-granular checkpoints (``training.save_every_steps``): ``{checkpoint_dir}/step_{S}/`` with the layout of an
+# epoch checkpoint; S is the number of optimizer steps done.  The reference only saves at epoch ends
+# (python/train_ray.py:441-443); a run that dies inside a long epoch loses the whole epoch there.
+# ---------------------------------------------------------------------------------------------------------------
+def save_step_checkpoint(checkpoint_dir: str, global_step: int, epoch: int, iteration: int, vision_group, text_group,
+                         config: dict, keep: int = 2) -> str:
+    """``global_step`` optimizer steps are done; ``iteration`` is the next iteration of ``epoch`` to run."""
+    name = f"step_{global_step}"
+    out = _save(checkpoint_dir, name, name, vision_group, text_group, config,
+                {"epoch": epoch, "next_iteration": iteration, "global_step": global_step})
+    if keep > 0:
+        import shutil
+        steps = sorted(_step_dirs(checkpoint_dir))
+        for old in steps[:-keep]:
+            shutil.rmtree(os.path.join(checkpoint_dir, f"step_{old}"), ignore_errors=True)
+    return out
+
+
+def _step_dirs(checkpoint_dir: str) -> list[int]:
+    if not os.path.isdir(checkpoint_dir):
+        return []
+    out = []
+    for name in os.listdir(checkpoint_dir):
+        m = re.fullmatch(r"step_(\d+)", name)
+        if m and os.path.isfile(os.path.join(checkpoint_dir, name, "metadata.json")):
+            out.append(int(m.group(1)))
+    return out
+
+
+def find_latest_step_checkpoint(checkpoint_dir: str) -> dict | None:
+    """Metadata of the newest complete ``step_S`` checkpoint, or None."""
+    steps = _step_dirs(checkpoint_dir)
+    if not steps:
+        return None
+    with open(os.path.join(checkpoint_dir, f"step_{max(steps)}", "metadata.json")) as f:
+        return json.load(f)
+
+
+def load_step_checkpoint(checkpoint_dir: str, global_step: int, vision_group, text_group) -> bool:
+    return load_epoch_checkpoint(checkpoint_dir, f"step_{global_step}", vision_group, text_group)
 
 
 def load_epoch_checkpoint(checkpoint_dir: str, epoch: int, vision_group, text_group) -> bool:
@@ -73,5 +124,5 @@ def load_epoch_checkpoint(checkpoint_dir: str, epoch: int, vision_group, text_gr
     t = get(text_group.execute_all_async("load_checkpoint", checkpoint_dir, epoch))
     ok = all(v) and all(t)
     if not ok:
-        log.warning("checkpoint epoch_%d could not be loaded on every actor (vision %s, text %s)", epoch, v, t)
+        log.warning("checkpoint %s could not be loaded on every actor (vision %s, text %s)", epoch, v, t)
     return ok

@@ -65,6 +65,9 @@ DEFAULTS: dict[str, Any] = {
         "clip_grad_norm": False,
         "max_grad_norm": 1.0,
         "no_checkpoint": True,
+        "save_every_steps": 0,          # also save step_{S}/ every this many optimizer steps (0 = epoch ends only)
+        "keep_step_checkpoints": 2,
+        "max_steps": 0,                 # stop after this many optimizer steps (0 = all epochs)
         "checkpoint_dir": "/tmp/checkpoints",
         "log_interval": 1,
         "profile_time": False,

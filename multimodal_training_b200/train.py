@@ -18,7 +18,8 @@ import os
 import sys
 import time
 
-from .checkpoint import find_latest_checkpoint, load_epoch_checkpoint, save_epoch_checkpoint
+from .checkpoint import (find_latest_checkpoint, find_latest_step_checkpoint, load_epoch_checkpoint,
+                         load_step_checkpoint, save_epoch_checkpoint, save_step_checkpoint)
 from .config.loader import parse_cli, trainer_configs
 from .runtime.actor_group import ActorGroup, get
 from .runtime.logger import setup_logging
@@ -99,20 +100,39 @@ def _run(cfg, vision_group, text_group, num_actors, parallel_size, dp_size) -> d
     checkpoint_dir = tr.get("checkpoint_dir", "/tmp/checkpoints")
     use_ckpt = not bool(tr.get("no_checkpoint", True))
 
-    start_epoch = 0
+    save_every = int(tr.get("save_every_steps", 0) or 0)
+    keep_steps = int(tr.get("keep_step_checkpoints", 2))
+    max_steps = int(tr.get("max_steps", 0) or 0)          # stop after this many optimizer steps (0 = run to the end)
+
+    start_epoch, start_iteration = 0, 0
     if use_ckpt:
         latest = find_latest_checkpoint(checkpoint_dir)
-        if latest is not None:
+        step_meta = find_latest_step_checkpoint(checkpoint_dir)
+        epoch_steps = -1 if latest is None else (latest + 1) * num_iterations
+        if step_meta is not None and int(step_meta["global_step"]) > epoch_steps:
+            # a step checkpoint inside an unfinished epoch is newer than the last finished epoch
+            done = int(step_meta["global_step"])
+            if load_step_checkpoint(checkpoint_dir, done, vision_group, text_group):
+                start_epoch, start_iteration = done // num_iterations, done % num_iterations
+                log.info("Resumed from step %d (epoch %d, iteration %d)", done, start_epoch, start_iteration)
+            else:
+                log.warning("Failed to load checkpoint of step %d; starting from scratch", done)
+        elif latest is not None:
             if load_epoch_checkpoint(checkpoint_dir, latest, vision_group, text_group):
                 start_epoch = latest + 1
                 log.info("Resumed from epoch %d", latest)
             else:
                 log.warning("Failed to load checkpoint of epoch %d; starting from scratch", latest)
 
-    global_step = start_epoch * num_iterations
+    global_step = start_epoch * num_iterations + start_iteration
+    if global_step:
+        # the learning-rate schedule continues where the saved run stopped
+        vision_group.execute_all("set_global_step", global_step)
+        text_group.execute_all("set_global_step", global_step)
     measured, measured_time, losses = 0, 0.0, []
+    stop = False
     for epoch in range(start_epoch, num_epochs):
-        for iteration in range(num_iterations):
+        for iteration in range(start_iteration if epoch == start_epoch else 0, num_iterations):
             is_warmup = global_step < warmup_steps
             t0 = time.perf_counter()
             vision_group.execute_all("zero_grad")
@@ -162,8 +182,18 @@ def _run(cfg, vision_group, text_group, num_actors, parallel_size, dp_size) -> d
             vision_group.free(vision_refs + vision_bwd_refs)
             text_group.free(text_refs + text_bwd_refs)
             global_step += 1
-        if use_ckpt:
+            last_of_epoch = iteration + 1 == num_iterations
+            if use_ckpt and save_every and global_step % save_every == 0 and not last_of_epoch:
+                save_step_checkpoint(checkpoint_dir, global_step, epoch, iteration + 1, vision_group, text_group, cfg,
+                                     keep=keep_steps)
+            if max_steps and global_step >= max_steps:
+                stop = True
+                break
+        if use_ckpt and global_step == (epoch + 1) * num_iterations:       # the epoch ran to its end
             save_epoch_checkpoint(checkpoint_dir, epoch, vision_group, text_group, cfg)
+        if stop:
+            log.info("Stopping after %d steps (training.max_steps)", global_step)
+            break
     avg_t = measured_time / measured if measured else float("nan")
     log.info("Training completed! %d epochs, %d total steps, %d measured steps (avg %.3fs/step)", num_epochs,
              global_step, measured, avg_t)

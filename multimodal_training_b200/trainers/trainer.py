@@ -281,10 +281,20 @@ class Trainer(RayActor):
         return (time.perf_counter() - t0) * 1e3
 
     # ------------------------------------------------------------------ checkpoints (reference layout)
-    def _ckpt_path(self, checkpoint_dir: str, epoch: int) -> str:
-        return os.path.join(checkpoint_dir, f"epoch_{epoch}", self.kind, f"rank_{self.rank}.pt")
+    @staticmethod
+    def _ckpt_name(epoch) -> str:
+        """``epoch`` is an epoch number or the name of a checkpoint directory (``step_120``)."""
+        return epoch if isinstance(epoch, str) else f"epoch_{epoch}"
 
-    def save_checkpoint(self, checkpoint_dir: str, epoch: int) -> str:
+    def _ckpt_path(self, checkpoint_dir: str, epoch) -> str:
+        return os.path.join(checkpoint_dir, self._ckpt_name(epoch), self.kind, f"rank_{self.rank}.pt")
+
+    def set_global_step(self, step: int) -> int:
+        """Position of the learning-rate schedule after a resume (optimizer steps already done)."""
+        self.global_step = int(step)
+        return self.global_step
+
+    def save_checkpoint(self, checkpoint_dir: str, epoch) -> str:
         path = self._ckpt_path(checkpoint_dir, epoch)
         os.makedirs(os.path.dirname(path), exist_ok=True)
         payload = {"model": {k: v.cpu() for k, v in self.model.reference_state_dict().items()}}
@@ -292,7 +302,7 @@ class Trainer(RayActor):
         torch.save(payload, tmp)
         os.replace(tmp, path)
         if self.config.get("save_optimizer", False) and self.optimizer is not None:
-            opath = os.path.join(checkpoint_dir, f"epoch_{epoch}", self.kind + "_optim", f"rank_{self.rank}.pt")
+            opath = os.path.join(checkpoint_dir, self._ckpt_name(epoch), self.kind + "_optim", f"rank_{self.rank}.pt")
             os.makedirs(os.path.dirname(opath), exist_ok=True)
             extra = {"optimizer": self.optimizer.state_dict(), "global_step": self.global_step,
                      "rng": torch.get_rng_state()}
@@ -300,7 +310,7 @@ class Trainer(RayActor):
             os.replace(opath + ".tmp", opath)
         return path
 
-    def load_checkpoint(self, checkpoint_dir: str, epoch: int) -> bool:
+    def load_checkpoint(self, checkpoint_dir: str, epoch) -> bool:
         path = self._ckpt_path(checkpoint_dir, epoch)
         if not os.path.exists(path):
             log.warning("checkpoint %s not found", path)
@@ -310,7 +320,8 @@ class Trainer(RayActor):
             self._load_model_state(payload["model"], sharded=True)
             if self.optimizer is not None:
                 self.optimizer.refresh_master_from_params()
-                opath = os.path.join(checkpoint_dir, f"epoch_{epoch}", self.kind + "_optim", f"rank_{self.rank}.pt")
+                opath = os.path.join(checkpoint_dir, self._ckpt_name(epoch), self.kind + "_optim",
+                                     f"rank_{self.rank}.pt")
                 if os.path.exists(opath):
                     extra = torch.load(opath, map_location="cpu", weights_only=False)
                     self.optimizer.load_state_dict(extra["optimizer"])

@@ -156,3 +156,32 @@ def test_driver_trains_checkpoints_and_resumes(tmp_path, caplog):
     assert find_latest_checkpoint(str(ck)) == 1
     log = open("/tmp/ray_train.log").read() if os.path.exists("/tmp/ray_train.log") else ""
     assert "Training completed!" in log and "avg" in log
+
+
+def test_step_checkpoints_resume_inside_an_epoch(tmp_path):
+    """A run that stops inside an epoch continues from its last ``step_S`` checkpoint (weights, optimizer shards, step
+    counter, data position) and then produces the losses of a run that was never interrupted."""
+    from multimodal_training_b200 import train
+    from multimodal_training_b200.checkpoint import find_latest_checkpoint, find_latest_step_checkpoint
+    common = {"training.num_iterations": 5, "+data.synthetic.repeat": 0, "+training.save_optimizer": "true",
+              "training.lr_scheduler_type": "cosine", "training.warmup_steps": 0}
+    whole = train.main(_cfg(tmp_path / "a", **common))
+    assert whole["steps"] == 5
+    part = dict(common, **{"training.save_every_steps": 2, "training.max_steps": 3})
+    first = train.main(_cfg(tmp_path / "b", **part))
+    ck = tmp_path / "b" / "ckpt"
+    assert first["steps"] == 3 and find_latest_checkpoint(str(ck)) is None
+    meta = find_latest_step_checkpoint(str(ck))
+    assert meta["global_step"] == 2 and meta["epoch"] == 0 and meta["next_iteration"] == 2
+    assert (ck / "step_2" / "text_optim" / "rank_0.pt").exists()
+    rest = train.main(_cfg(tmp_path / "b", **dict(common, **{"training.save_every_steps": 2})))
+    assert rest["steps"] == 5 and len(rest["losses"]) == 3          # steps 2, 3 and 4 ran again / for the first time
+    for a, b in zip(first["losses"], whole["losses"][:3]):
+        assert abs(a - b) < 1e-6 * abs(b)
+    for a, b in zip(rest["losses"], whole["losses"][2:]):
+        assert abs(a - b) < 1e-5 * abs(b), (rest["losses"], whole["losses"])
+    # the finished epoch supersedes the step checkpoints; only the newest two of those are kept
+    assert find_latest_checkpoint(str(ck)) == 0
+    assert sorted(p.name for p in ck.iterdir() if p.name.startswith("step_")) == ["step_2", "step_4"]
+    again = train.main(_cfg(tmp_path / "b", **dict(common, **{"training.save_every_steps": 2})))
+    assert again["steps"] == 5 and again["losses"] == []            # nothing left to do
