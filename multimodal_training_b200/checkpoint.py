@@ -47,10 +47,16 @@ def _save(checkpoint_dir: str, tag, name: str, vision_group, text_group, config:
     v_refs = vision_group.execute_all_async("save_checkpoint", checkpoint_dir, tag)
     t_refs = text_group.execute_all_async("save_checkpoint", checkpoint_dir, tag)
     v_paths, t_paths = get(v_refs), get(t_refs)
+    return write_metadata(checkpoint_dir, name, v_paths, t_paths, config, dict({"epoch": tag}, **extra_meta))
+
+
+def write_metadata(checkpoint_dir: str, name: str, v_paths: list, t_paths: list, config: dict,
+                   extra_meta: dict) -> str:
+    """``{name}/metadata.json`` for shards that are already on disk (atomic: temporary name, then rename)."""
     epoch_dir = os.path.join(checkpoint_dir, name)
     os.makedirs(epoch_dir, exist_ok=True)
     tr = config.get("training", {})
-    epoch = extra_meta.get("epoch", tag)
+    epoch = extra_meta.get("epoch")
     meta = {
         "epoch": epoch,
         "timestamp": time.strftime("%Y-%m-%dT%H:%M:%S"),
@@ -126,3 +132,17 @@ def load_epoch_checkpoint(checkpoint_dir: str, epoch: int, vision_group, text_gr
     if not ok:
         log.warning("checkpoint %s could not be loaded on every actor (vision %s, text %s)", epoch, v, t)
     return ok
+
+
+def plan_resume(checkpoint_dir: str, num_iterations: int) -> tuple | None:
+    """What to load to continue a run: ``(tag, start_epoch, start_iteration)`` or None for a fresh start.
+    A step checkpoint inside an unfinished epoch wins over the last finished epoch when it is newer."""
+    latest = find_latest_checkpoint(checkpoint_dir)
+    step_meta = find_latest_step_checkpoint(checkpoint_dir)
+    epoch_steps = -1 if latest is None else (latest + 1) * num_iterations
+    if step_meta is not None and int(step_meta["global_step"]) > epoch_steps:
+        done = int(step_meta["global_step"])
+        return f"step_{done}", done // num_iterations, done % num_iterations
+    if latest is not None:
+        return latest, latest + 1, 0
+    return None

@@ -169,6 +169,42 @@ class HybridEngine:
             event.record()
         return LossHandle(host, event)
 
+    # ------------------------------------------------------------------ checkpoints (same layout as the actor driver)
+    def save_checkpoint(self, checkpoint_dir: str, tag, config: dict | None = None, extra_meta: dict | None = None):
+        """Every rank writes its vision and text shard under ``epoch_N`` (``tag`` an int) or the directory named
+        ``tag``; rank 0 then writes ``metadata.json``, which marks the checkpoint complete."""
+        from .checkpoint import write_metadata
+        self.synchronize()
+        self.vision.save_checkpoint(checkpoint_dir, tag)
+        self.text.save_checkpoint(checkpoint_dir, tag)
+        if self.mesh.world > 1:
+            dist.barrier(group=self.mesh.world_group)
+        name = self.text._ckpt_name(tag)
+        if self.mesh.rank == 0:
+            import os
+            paths = {k: [os.path.join(checkpoint_dir, name, k, f"rank_{r}.pt") for r in range(self.mesh.world)]
+                     for k in ("vision", "text")}
+            write_metadata(checkpoint_dir, name, paths["vision"], paths["text"], config or {},
+                           dict({"epoch": tag}, **(extra_meta or {})))
+        if self.mesh.world > 1:
+            dist.barrier(group=self.mesh.world_group)
+        return name
+
+    def load_checkpoint(self, checkpoint_dir: str, tag) -> bool:
+        """True only if every rank loaded both of its shards."""
+        ok = self.vision.load_checkpoint(checkpoint_dir, tag) and self.text.load_checkpoint(checkpoint_dir, tag)
+        if self.mesh.world > 1:
+            dev = next(self.text.model.parameters()).device
+            flag = torch.tensor([1 if ok else 0], device=dev, dtype=torch.int32)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.mesh.world_group)
+            ok = bool(flag.item())
+        return ok
+
+    def set_global_step(self, step: int) -> None:
+        self.vision.set_global_step(step)
+        self.text.set_global_step(step)
+        self.step_index = int(step)
+
     def mean_loss(self, loss: torch.Tensor) -> float:
         """Mean over text replicas (every TP rank of a replica holds the same loss)."""
         t = loss.detach().float().clone().reshape(1)

@@ -18,8 +18,7 @@ import os
 import sys
 import time
 
-from .checkpoint import (find_latest_checkpoint, find_latest_step_checkpoint, load_epoch_checkpoint,
-                         load_step_checkpoint, save_epoch_checkpoint, save_step_checkpoint)
+from .checkpoint import load_epoch_checkpoint, plan_resume, save_epoch_checkpoint, save_step_checkpoint
 from .config.loader import parse_cli, trainer_configs
 from .runtime.actor_group import ActorGroup, get
 from .runtime.logger import setup_logging
@@ -105,24 +104,15 @@ def _run(cfg, vision_group, text_group, num_actors, parallel_size, dp_size) -> d
     max_steps = int(tr.get("max_steps", 0) or 0)          # stop after this many optimizer steps (0 = run to the end)
 
     start_epoch, start_iteration = 0, 0
-    if use_ckpt:
-        latest = find_latest_checkpoint(checkpoint_dir)
-        step_meta = find_latest_step_checkpoint(checkpoint_dir)
-        epoch_steps = -1 if latest is None else (latest + 1) * num_iterations
-        if step_meta is not None and int(step_meta["global_step"]) > epoch_steps:
-            # a step checkpoint inside an unfinished epoch is newer than the last finished epoch
-            done = int(step_meta["global_step"])
-            if load_step_checkpoint(checkpoint_dir, done, vision_group, text_group):
-                start_epoch, start_iteration = done // num_iterations, done % num_iterations
-                log.info("Resumed from step %d (epoch %d, iteration %d)", done, start_epoch, start_iteration)
-            else:
-                log.warning("Failed to load checkpoint of step %d; starting from scratch", done)
-        elif latest is not None:
-            if load_epoch_checkpoint(checkpoint_dir, latest, vision_group, text_group):
-                start_epoch = latest + 1
-                log.info("Resumed from epoch %d", latest)
-            else:
-                log.warning("Failed to load checkpoint of epoch %d; starting from scratch", latest)
+    plan = plan_resume(checkpoint_dir, num_iterations) if use_ckpt else None
+    if plan is not None:
+        tag, e, i = plan
+        if load_epoch_checkpoint(checkpoint_dir, tag, vision_group, text_group):
+            start_epoch, start_iteration = e, i
+            log.info("Resumed from %s (next: epoch %d, iteration %d)", tag if isinstance(tag, str) else f"epoch {tag}",
+                     e, i)
+        else:
+            log.warning("Failed to load checkpoint %s; starting from scratch", tag)
 
     global_step = start_epoch * num_iterations + start_iteration
     if global_step:

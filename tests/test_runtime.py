@@ -185,3 +185,38 @@ def test_step_checkpoints_resume_inside_an_epoch(tmp_path):
     assert sorted(p.name for p in ck.iterdir() if p.name.startswith("step_")) == ["step_2", "step_4"]
     again = train.main(_cfg(tmp_path / "b", **dict(common, **{"training.save_every_steps": 2})))
     assert again["steps"] == 5 and again["losses"] == []            # nothing left to do
+
+
+def _spmd_worker(rank, world, ckpt_root, over):
+    from multimodal_training_b200 import train_spmd
+    import pathlib
+    return train_spmd.main(_cfg(pathlib.Path(ckpt_root), **over))
+
+
+def test_spmd_driver_matches_the_actor_driver_and_resumes(tmp_path):
+    """The torchrun-style driver trains like the actor driver on the same configuration (same losses), writes the
+    same checkpoint layout, and each can resume from the other's checkpoint."""
+    from dist_utils import run_ranks
+    from multimodal_training_b200 import train
+    from multimodal_training_b200.checkpoint import find_latest_checkpoint
+    actor = train.main(_cfg(tmp_path / "actor"))
+    for d in ("r1", "r2"):
+        (tmp_path / d).mkdir()
+    spmd = run_ranks(_spmd_worker, 2, tmp_path / "r1", str(tmp_path / "spmd"), {})
+    assert spmd[0]["steps"] == 3 and spmd[0]["losses"] == spmd[1]["losses"]
+    for a, b in zip(spmd[0]["losses"], actor["losses"]):
+        assert abs(a - b) < 1e-6 * abs(b), (spmd[0]["losses"], actor["losses"])
+    ck = tmp_path / "spmd" / "ckpt"
+    assert find_latest_checkpoint(str(ck)) == 0
+    for half in ("vision", "text"):
+        for r in range(2):
+            assert (ck / "epoch_0" / half / f"rank_{r}.pt").exists()
+    # second epoch: the SPMD driver continues from its own checkpoint, the actor driver from the SPMD one
+    more = run_ranks(_spmd_worker, 2, tmp_path / "r2", str(tmp_path / "spmd"), {"training.num_epochs": 2})
+    assert more[0]["steps"] == 6 and len(more[0]["losses"]) == 3
+    import shutil
+    shutil.rmtree(ck / "epoch_1")
+    cross = train.main(_cfg(tmp_path / "spmd", **{"training.num_epochs": 2}))
+    assert cross["steps"] == 6
+    for a, b in zip(more[0]["losses"], cross["losses"]):
+        assert abs(a - b) < 1e-6 * abs(b)
