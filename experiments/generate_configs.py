@@ -63,7 +63,7 @@ while read -r name; do
   log="logs/${name}.log"
   mkdir -p logs
   echo "=== $name"
-  if (cd "$REPO" && python -m multimodal_training_b200.train --config-path "$PWD/configs" --config-name "$name") > "$log" 2>&1; then
+  if (cd "$REPO" && __LAUNCH__ --config-path "$PWD/configs" --config-name "$name") > "$log" 2>&1; then
     line=$(grep -E "Training completed!.*avg [0-9.]+s/step" "$log" | tail -1)
     avg=$(echo "$line" | sed -E 's/.*avg ([0-9.]+)s\\/step.*/\\1/')
     echo "$name OK Average iteration time: ${avg}s" | tee -a results.txt
@@ -80,6 +80,10 @@ def main(argv=None) -> int:
     ap.add_argument("--mscoco-data-path", default="/path/to/mscoco2017")
     ap.add_argument("--laion-data-path", default="/path/to/laion_pop")
     ap.add_argument("--synthetic", action="store_true", help="random data, no dataset files needed")
+    ap.add_argument("--launcher", default="actors", choices=["actors", "torchrun"],
+                    help="actors: the driver spawns one host process per GPU itself; torchrun: one rank per GPU "
+                         "launched by torch.distributed.run (multimodal_training_b200.train_spmd)")
+    ap.add_argument("--gpus", type=int, default=8, help="ranks per run for --launcher torchrun")
     a = ap.parse_args(argv)
     out = Path(a.output_dir)
     (out / "configs").mkdir(parents=True, exist_ok=True)
@@ -100,7 +104,12 @@ def main(argv=None) -> int:
                     names.append(name)
     (out / "manifest.txt").write_text("\n".join(names) + "\n")
     runner = out / "run_sweep.sh"
-    runner.write_text(RUNNER)
+    if a.launcher == "torchrun":
+        launch = (f"python -m torch.distributed.run --nnodes=1 --nproc-per-node {a.gpus} --master-addr 127.0.0.1 "
+                  "-m multimodal_training_b200.train_spmd")
+    else:
+        launch = "python -m multimodal_training_b200.train"
+    runner.write_text(RUNNER.replace("__LAUNCH__", launch))
     os.chmod(runner, 0o755)
     print(f"wrote {len(names)} configs to {out}")
     return 0

@@ -140,6 +140,11 @@ def test_vision_token_calculator_and_sweep_generator(tmp_path, capsys):
     assert cfg["data"]["force_fixed_size"] and cfg["data"]["synthetic"]["image_size"] == 448
     big = load_config(tmp_path / "sweep" / "configs" / "32b_64k_tokens_sequence_bs2.yaml")
     assert big["deepspeed"]["reduce_bucket_size"] == 100000000 and big["training"]["parallel_size"] == 8
+    runner = (tmp_path / "sweep" / "run_sweep.sh").read_text()
+    assert "python -m multimodal_training_b200.train --config-path" in runner and "__LAUNCH__" not in runner
+    assert gen.main(["--output-dir", str(tmp_path / "sweep2"), "--synthetic", "--launcher", "torchrun"]) == 0
+    runner = (tmp_path / "sweep2" / "run_sweep.sh").read_text()
+    assert "--nproc-per-node 8" in runner and "-m multimodal_training_b200.train_spmd --config-path" in runner
 
 
 def test_phase_timer_and_chrome_trace(tmp_path):
