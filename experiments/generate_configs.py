@@ -83,7 +83,6 @@ def main(argv=None) -> int:
     ap.add_argument("--launcher", default="actors", choices=["actors", "torchrun"],
                     help="actors: the driver spawns one host process per GPU itself; torchrun: one rank per GPU "
                          "launched by torch.distributed.run (multimodal_training_b200.train_spmd)")
-    ap.add_argument("--gpus", type=int, default=8, help="ranks per run for --launcher torchrun")
     a = ap.parse_args(argv)
     out = Path(a.output_dir)
     (out / "configs").mkdir(parents=True, exist_ok=True)
@@ -105,7 +104,10 @@ def main(argv=None) -> int:
     (out / "manifest.txt").write_text("\n".join(names) + "\n")
     runner = out / "run_sweep.sh"
     if a.launcher == "torchrun":
-        launch = (f"python -m torch.distributed.run --nnodes=1 --nproc-per-node {a.gpus} --master-addr 127.0.0.1 "
+        # one rank per GPU of the config's own layout (parallel_size x dp_size)
+        launch = ("python -m torch.distributed.run --nnodes=1 --nproc-per-node \"$(python -c \"import yaml; "
+                  "t = yaml.safe_load(open('$PWD/configs/$name.yaml'))['training']; "
+                  "print(t['parallel_size'] * t.get('dp_size', 1))\")\" --master-addr 127.0.0.1 "
                   "-m multimodal_training_b200.train_spmd")
     else:
         launch = "python -m multimodal_training_b200.train"

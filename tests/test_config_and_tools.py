@@ -144,7 +144,16 @@ def test_vision_token_calculator_and_sweep_generator(tmp_path, capsys):
     assert "python -m multimodal_training_b200.train --config-path" in runner and "__LAUNCH__" not in runner
     assert gen.main(["--output-dir", str(tmp_path / "sweep2"), "--synthetic", "--launcher", "torchrun"]) == 0
     runner = (tmp_path / "sweep2" / "run_sweep.sh").read_text()
-    assert "--nproc-per-node 8" in runner and "-m multimodal_training_b200.train_spmd --config-path" in runner
+    assert "--nproc-per-node" in runner and "-m multimodal_training_b200.train_spmd --config-path" in runner
+    # the rank count comes from the config itself: check the embedded one-liner on a generated file
+    import subprocess
+    import sys
+    name = "7b_1k_tokens_sequence_bs1"
+    code = ("import yaml; t = yaml.safe_load(open('%s'))['training']; print(t['parallel_size'] * t.get('dp_size', 1))"
+            % (tmp_path / "sweep2" / "configs" / (name + ".yaml")))
+    assert "import yaml; t = yaml.safe_load(open('$PWD/configs/$name.yaml'))['training']" in runner
+    assert subprocess.run([sys.executable, "-c", code], capture_output=True, text=True).stdout.strip() == "4"
+    assert subprocess.run(["bash", "-n", str(tmp_path / "sweep2" / "run_sweep.sh")]).returncode == 0
 
 
 def test_phase_timer_and_chrome_trace(tmp_path):
