@@ -56,14 +56,15 @@ RUNNER = """#!/usr/bin/env bash
 # Runs every config of manifest.txt; one line per config in results.txt.
 set -u
 cd "$(dirname "$0")"
-REPO="$(cd ../.. && pwd)"
+HERE="$PWD"
+REPO="${MMT_REPO:-__REPO__}"      # where the package lives (override with MMT_REPO)
 : > results.txt
 while read -r name; do
   [ -z "$name" ] && continue
   log="logs/${name}.log"
   mkdir -p logs
   echo "=== $name"
-  if (cd "$REPO" && __LAUNCH__ --config-path "$PWD/configs" --config-name "$name") > "$log" 2>&1; then
+  if (cd "$REPO" && __LAUNCH__ --config-path "$HERE/configs" --config-name "$name") > "$log" 2>&1; then
     line=$(grep -E "Training completed!.*avg [0-9.]+s/step" "$log" | tail -1)
     avg=$(echo "$line" | sed -E 's/.*avg ([0-9.]+)s\\/step.*/\\1/')
     echo "$name OK Average iteration time: ${avg}s" | tee -a results.txt
@@ -106,12 +107,13 @@ def main(argv=None) -> int:
     if a.launcher == "torchrun":
         # one rank per GPU of the config's own layout (parallel_size x dp_size)
         launch = ("python -m torch.distributed.run --nnodes=1 --nproc-per-node \"$(python -c \"import yaml; "
-                  "t = yaml.safe_load(open('$PWD/configs/$name.yaml'))['training']; "
+                  "t = yaml.safe_load(open('$HERE/configs/$name.yaml'))['training']; "
                   "print(t['parallel_size'] * t.get('dp_size', 1))\")\" --master-addr 127.0.0.1 "
                   "-m multimodal_training_b200.train_spmd")
     else:
         launch = "python -m multimodal_training_b200.train"
-    runner.write_text(RUNNER.replace("__LAUNCH__", launch))
+    repo = str(Path(__file__).resolve().parent.parent)
+    runner.write_text(RUNNER.replace("__LAUNCH__", launch).replace("__REPO__", repo))
     os.chmod(runner, 0o755)
     print(f"wrote {len(names)} configs to {out}")
     return 0

@@ -142,6 +142,7 @@ def test_vision_token_calculator_and_sweep_generator(tmp_path, capsys):
     assert big["deepspeed"]["reduce_bucket_size"] == 100000000 and big["training"]["parallel_size"] == 8
     runner = (tmp_path / "sweep" / "run_sweep.sh").read_text()
     assert "python -m multimodal_training_b200.train --config-path" in runner and "__LAUNCH__" not in runner
+    assert 'HERE="$PWD"' in runner and '--config-path "$HERE/configs"' in runner   # $PWD changes with the cd to the repo
     assert gen.main(["--output-dir", str(tmp_path / "sweep2"), "--synthetic", "--launcher", "torchrun"]) == 0
     runner = (tmp_path / "sweep2" / "run_sweep.sh").read_text()
     assert "--nproc-per-node" in runner and "-m multimodal_training_b200.train_spmd --config-path" in runner
@@ -151,7 +152,7 @@ def test_vision_token_calculator_and_sweep_generator(tmp_path, capsys):
     name = "7b_1k_tokens_sequence_bs1"
     code = ("import yaml; t = yaml.safe_load(open('%s'))['training']; print(t['parallel_size'] * t.get('dp_size', 1))"
             % (tmp_path / "sweep2" / "configs" / (name + ".yaml")))
-    assert "import yaml; t = yaml.safe_load(open('$PWD/configs/$name.yaml'))['training']" in runner
+    assert "import yaml; t = yaml.safe_load(open('$HERE/configs/$name.yaml'))['training']" in runner
     assert subprocess.run([sys.executable, "-c", code], capture_output=True, text=True).stdout.strip() == "4"
     assert subprocess.run(["bash", "-n", str(tmp_path / "sweep2" / "run_sweep.sh")]).returncode == 0
 
