@@ -135,7 +135,7 @@ def default_processor(model_name, model_cfg=None):
         from transformers import AutoTokenizer
         tok = AutoTokenizer.from_pretrained(model_name, local_files_only=True)
     except Exception:
-        tok = ByteTokenizer()
+        tok = ByteTokenizer.for_config(model_cfg)
     v = getattr(model_cfg, "vision", None)
     ip = Qwen2_5_VLImageProcessor(patch_size=getattr(v, "patch_size", 14),
                                   temporal_patch_size=getattr(v, "temporal_patch_size", 2),

@@ -73,6 +73,27 @@ def mask_labels(input_ids: torch.Tensor, assistant_id: int = ASSISTANT_TOKEN_ID,
     return torch.tensor(labels, dtype=torch.long).reshape(input_ids.shape)
 
 
+def chat_token_ids(processor) -> tuple[int, int]:
+    """(id of the ``assistant`` role token, id of ``<|im_end|>``) of the processor's tokenizer; Qwen's ids when the
+    tokenizer cannot say."""
+    tok = getattr(processor, "tokenizer", None)
+    assistant, im_end = ASSISTANT_TOKEN_ID, IM_END_TOKEN_ID
+    if tok is None:
+        return assistant, im_end
+    if hasattr(tok, "assistant_token_id"):                       # in-tree byte tokenizer
+        return int(tok.assistant_token_id), int(tok.special.get("<|im_end|>", im_end))
+    try:                                                          # Hugging Face tokenizer
+        ids = tok.encode("assistant", add_special_tokens=False)
+        if len(ids) == 1:
+            assistant = int(ids[0])
+        e = tok.convert_tokens_to_ids("<|im_end|>")
+        if isinstance(e, int) and e >= 0:
+            im_end = e
+    except Exception:
+        pass
+    return assistant, im_end
+
+
 def preprocess_qwen_visual(sources: list[dict], processor, *, data_path: str = "", max_pixels: int | None = None,
                            min_pixels: int | None = None, force_fixed_size: bool = False) -> dict:
     """One sample -> ``{"input_ids" [1,S], "labels" [1,S], "pixel_values", "image_grid_thw"}``."""
@@ -102,7 +123,8 @@ def preprocess_qwen_visual(sources: list[dict], processor, *, data_path: str = "
     if not isinstance(input_ids, torch.Tensor):
         input_ids = torch.tensor(input_ids)
     input_ids = input_ids.reshape(1, -1)
-    out = {"input_ids": input_ids, "labels": mask_labels(input_ids)}
+    assistant_id, im_end_id = chat_token_ids(processor)
+    out = {"input_ids": input_ids, "labels": mask_labels(input_ids, assistant_id, im_end_id)}
     for k in ("pixel_values", "image_grid_thw"):
         if k in enc and enc[k] is not None:
             out[k] = enc[k] if isinstance(enc[k], torch.Tensor) else torch.tensor(enc[k])

@@ -56,7 +56,7 @@ def _to_chw_float(image) -> torch.Tensor:
     arr = np.asarray(image)
     if arr.ndim == 2:
         arr = np.stack([arr] * 3, axis=-1)
-    t = torch.from_numpy(np.ascontiguousarray(arr[..., :3])).permute(2, 0, 1).float()
+    t = torch.from_numpy(np.array(arr[..., :3])).permute(2, 0, 1).float()        # a writable copy
     return t / 255.0 if arr.dtype == np.uint8 or t.max() > 1.5 else t
 
 
@@ -111,6 +111,27 @@ class ByteTokenizer:
         self.inv = {v: k for k, v in self.special.items()}
         self.pad_token_id = self.special.get("<|endoftext|>", 0)
         self.eos_token_id = self.special.get(IM_END, 0)
+
+    @classmethod
+    def for_config(cls, model_cfg) -> "ByteTokenizer":
+        """Special tokens at the ids of ``model_cfg``.  Configurations with Qwen's vocabulary keep Qwen's ids; small
+        test configurations get the chat-control tokens right above the byte range."""
+        vocab = getattr(getattr(model_cfg, "text", None), "vocab_size", 0)
+        if model_cfg is None or vocab > max(cls.SPECIAL.values()):
+            return cls()
+        special = {IMAGE_PAD: model_cfg.image_token_id, VISION_START: model_cfg.vision_start_token_id,
+                   VISION_END: model_cfg.vision_end_token_id, "<|video_pad|>": model_cfg.video_token_id,
+                   IM_START: 256, IM_END: 257, "<|endoftext|>": 259}
+        if len(set(special.values())) != len(special) or max(special.values()) >= vocab:
+            raise ValueError(f"special token ids {special} do not fit a vocabulary of {vocab}")
+        tok = cls(special)
+        tok.ROLE_IDS = {"assistant": 258}
+        tok.pad_token_id = getattr(model_cfg, "pad_token_id", 0) or 0
+        return tok
+
+    @property
+    def assistant_token_id(self) -> int:
+        return self.ROLE_IDS["assistant"]
 
     def encode(self, text: str) -> list[int]:
         ids: list[int] = []
