@@ -264,3 +264,39 @@ def test_driver_trains_on_image_files(tmp_path):
     res = train.main(load_config(None, ov))
     assert res["steps"] == 3 and all(v == v and v < 20 for v in res["losses"])
     assert res["losses"][-1] < res["losses"][0]          # 4 samples, batch 2: the third step sees step one's data again
+
+
+def test_pretrained_split_train_merge_chain_keeps_the_weights(tmp_path):
+    """A full HF-layout checkpoint is split, loaded by sequence-parallel vision and tensor-parallel text trainers
+    (``pretrained_checkpoint_dir``), saved as per-rank shards after steps with a vanishing learning rate, merged, and
+    loaded into the single-process model: its logits equal the original model's."""
+    from multimodal_training_b200 import train
+    from multimodal_training_b200.cli import merge_checkpoint, split_checkpoint
+    from multimodal_training_b200.models.vlm import Qwen2_5_VLForConditionalGeneration
+    src = Qwen2_5_VLForConditionalGeneration("tiny", seed=5)
+    full = {"model.visual." + k: v for k, v in src.model.visual.reference_state_dict(fused_qkv=True).items()}
+    for k, v in src.model.language_model.reference_state_dict().items():
+        full[k if k.startswith("lm_head") else "model.language_model." + k] = v
+    torch.save(full, tmp_path / "hf_full.pt")
+    split_dir = split_checkpoint.split_checkpoint(str(tmp_path / "hf_full.pt"), str(tmp_path / "split"))
+    cfg = _cfg(tmp_path, **{"training.learning_rate": 1e-30, "training.num_iterations": 2,
+                            "training.weight_decay": 0.0, "+vision.pretrained_checkpoint_dir": split_dir,
+                            "+text.pretrained_checkpoint_dir": split_dir})
+    res = train.main(cfg)
+    assert res["steps"] == 2
+    out = merge_checkpoint.merge_checkpoint(str(tmp_path / "ckpt" / "epoch_0"), str(tmp_path / "merged"), "tiny", 2)
+    merged = torch.load(os.path.join(out, "pytorch_model.bin"))
+    for k, v in full.items():
+        key = k[len("model."):] if k.startswith("model.") else k
+        assert key in merged, key
+        assert merged[key].shape == v.shape, key
+        assert torch.allclose(merged[key], v, rtol=0, atol=1e-20), key     # two AdamW steps of size 1e-30
+    dst = Qwen2_5_VLForConditionalGeneration("tiny", seed=99)
+    dst.load_merged_state_dict(merged)
+    cfgm = src.config
+    ids = torch.randint(10, 900, (1, 80))
+    ids[0, 5] = cfgm.vision_start_token_id
+    ids[0, 6:70] = cfgm.image_token_id
+    pix = torch.randn(256, cfgm.vision.patch_dim)
+    with torch.no_grad():
+        assert torch.allclose(dst.model(ids, pix, [(1, 16, 16)]), src.model(ids, pix, [(1, 16, 16)]), atol=1e-5)
