@@ -112,9 +112,8 @@ class HybridEngine:
                 t_out = self.text.forward_step(v_out, idx)
             with ph("text.backward"):
                 g = self.text.backward_step()
-            if g["grad"] is not None:
-                with ph("vision.backward"):
-                    self.vision.backward_step(g)
+            with ph("vision.backward"):
+                self.vision.backward_step(g)          # a no-op for a batch without images
             loss = t_out["loss"] if loss is None else loss + t_out["loss"]
         if self.accum > 1:
             loss = loss / self.accum

@@ -94,7 +94,7 @@ def build_step_context(step: int, samples: list, cfg: VLConfig, mesh: Mesh, *, p
 def local_pixels(ctx: StepContext, out: torch.Tensor | None = None, plan: VisionPlan | None = None) -> torch.Tensor:
     """Host gather of this rank's patches (local window order) from the samples' pixel arrays."""
     plan = plan or ctx.vision_plan
-    pix = [ctx.samples[i].pixel_values for i in ctx.vision_samples]
+    pix = [ctx.samples[i].pixel_values for i in ctx.vision_samples if ctx.samples[i].pixel_values is not None]
     allpix = pix[0] if len(pix) == 1 else torch.cat(pix, dim=0)
     if out is not None:
         return torch.index_select(allpix, 0, plan.local_patch_index, out=out)

@@ -116,6 +116,12 @@ class VisionTrainer(Trainer):
         ctx = self.step_context(iteration)
         dev = self._get_device()
         plan, rows = ctx.vision_plan, None
+        if plan is None:
+            # no image in this replica's share of the batch: nothing to encode, nothing to hand over
+            self._pending.append(None)
+            return {"vision_embeddings": None, "sample_index": [ctx.samples[i].sample_index
+                                                                for i in ctx.vision_samples],
+                    "iteration": iteration}
         if self.tensor_parallel:
             plan, rows = self._tensor_parallel_views(ctx)
         if dev.type == "cuda":
@@ -146,6 +152,8 @@ class VisionTrainer(Trainer):
         if isinstance(grad, dict):
             grad = grad["grad"]
         merged = self._pending.pop(0)
+        if merged is None or grad is None:
+            return {}
         if grad.dim() == merged.dim() + 1:
             grad = grad.squeeze(0)
         merged.backward(gradient=grad.to(merged.dtype))

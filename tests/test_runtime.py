@@ -266,7 +266,8 @@ def test_driver_trains_on_image_files(tmp_path):
     assert res["losses"][-1] < res["losses"][0]          # 4 samples, batch 2: the third step sees step one's data again
 
 
-def test_pretrained_split_train_merge_chain_keeps_the_weights(tmp_path):
+@pytest.mark.parametrize("vision_mode", ["sequence", "tensor"])
+def test_pretrained_split_train_merge_chain_keeps_the_weights(tmp_path, vision_mode):
     """A full HF-layout checkpoint is split, loaded by sequence-parallel vision and tensor-parallel text trainers
     (``pretrained_checkpoint_dir``), saved as per-rank shards after steps with a vanishing learning rate, merged, and
     loaded into the single-process model: its logits equal the original model's."""
@@ -281,10 +282,11 @@ def test_pretrained_split_train_merge_chain_keeps_the_weights(tmp_path):
     split_dir = split_checkpoint.split_checkpoint(str(tmp_path / "hf_full.pt"), str(tmp_path / "split"))
     cfg = _cfg(tmp_path, **{"training.learning_rate": 1e-30, "training.num_iterations": 2,
                             "training.weight_decay": 0.0, "+vision.pretrained_checkpoint_dir": split_dir,
-                            "+text.pretrained_checkpoint_dir": split_dir})
+                            "+text.pretrained_checkpoint_dir": split_dir, "vision.parallelism": vision_mode})
     res = train.main(cfg)
     assert res["steps"] == 2
-    out = merge_checkpoint.merge_checkpoint(str(tmp_path / "ckpt" / "epoch_0"), str(tmp_path / "merged"), "tiny", 2)
+    out = merge_checkpoint.merge_checkpoint(str(tmp_path / "ckpt" / "epoch_0"), str(tmp_path / "merged"), "tiny", 2,
+                                            vision_tensor_parallel=vision_mode == "tensor")
     merged = torch.load(os.path.join(out, "pytorch_model.bin"))
     for k, v in full.items():
         key = k[len("model."):] if k.startswith("model.") else k
@@ -300,3 +302,45 @@ def test_pretrained_split_train_merge_chain_keeps_the_weights(tmp_path):
     pix = torch.randn(256, cfgm.vision.patch_dim)
     with torch.no_grad():
         assert torch.allclose(dst.model(ids, pix, [(1, 16, 16)]), src.model(ids, pix, [(1, 16, 16)]), atol=1e-5)
+
+
+def _file_cfg(tmp_path, ann_name, **over):
+    from multimodal_training_b200.config.loader import load_config
+    ov = ["vision.model_name=tiny", "text.model_name=tiny", "vision.dtype=float32", "text.dtype=float32",
+          "vision.parallelism=sequence", "text.parallelism=tensor", "training.parallel_size=2",
+          "training.batch_size=2", "training.num_iterations=4", "training.num_epochs=1", "training.warmup_steps=0",
+          "training.learning_rate=1e-3", "training.warmup_ratio=0", "training.lr_scheduler_type=constant",
+          "training.clip_grad_norm=true", "+training.device=cpu", "training.backend=gloo", "training.runtime=builtin",
+          "data.datasets=[toy]", f"+data.data_registry.toy.annotation_path={tmp_path / ann_name}",
+          f"+data.data_registry.toy.data_path={tmp_path}", "data.num_workers=0", "data.pin_memory=false",
+          "data.force_fixed_size=false", "data.min_pixels=3136", "data.max_pixels=200704"]
+    return load_config(None, ov + [f"{k}={v}" for k, v in over.items()])
+
+
+def test_driver_handles_ragged_multi_image_and_text_only_samples(tmp_path):
+    """Images of different sizes and aspect ratios (no fixed-size resize), a sample with two images and a sample
+    without any share batches; a data set without a single image trains the decoder alone."""
+    import json
+    import numpy as np
+    from PIL import Image
+    from multimodal_training_b200 import train
+    rng = np.random.default_rng(1)
+    ann = []
+    for i, (h, w) in enumerate([(200, 260), (336, 224), (280, 420), (140, 500), (448, 448), (230, 230)]):
+        Image.fromarray(rng.integers(0, 255, (h, w, 3), dtype=np.uint8)).save(tmp_path / f"im{i}.png")
+        ann.append({"image": f"im{i}.png", "conversations": [{"from": "human", "value": "<image>\nDescribe."},
+                                                             {"from": "gpt", "value": f"Image {i}, {h} by {w}."}]})
+    ann.append({"image": ["im0.png", "im4.png"], "conversations": [{"from": "human", "value": "<image><image>\nSame?"},
+                                                                   {"from": "gpt", "value": "No."}]})
+    ann.append({"conversations": [{"from": "human", "value": "Hello?"}, {"from": "gpt", "value": "Hi."}]})
+    (tmp_path / "ann.json").write_text(json.dumps(ann))
+    res = train.main(_file_cfg(tmp_path, "ann.json"))               # 4 steps x 2 samples: every sample once
+    assert res["steps"] == 4 and all(v == v and v < 20 for v in res["losses"])
+    # text tensor parallel off, two data-parallel text replicas with one sample each (with and without images)
+    res = train.main(_file_cfg(tmp_path, "ann.json", **{"text.parallelism": "none", "training.batch_size": 1}))
+    assert res["steps"] == 4 and all(v == v and v < 20 for v in res["losses"])
+    text_only = [{"conversations": [{"from": "human", "value": f"Hello {i}?"}, {"from": "gpt", "value": f"Hi {i}."}]}
+                 for i in range(4)]
+    (tmp_path / "text.json").write_text(json.dumps(text_only))
+    res = train.main(_file_cfg(tmp_path, "text.json", **{"training.num_iterations": 2}))
+    assert res["steps"] == 2 and res["losses"][1] < res["losses"][0]
