@@ -195,6 +195,10 @@ class Qwen2_5_VLProcessor:
                         body.append(f"{VISION_START}{IMAGE_PAD}{VISION_END}")
                     elif item.get("type") == "text":
                         body.append(item["text"])
+                    elif item.get("type") == "video":
+                        # the training pipeline is image-only, like the reference's (its M-RoPE ids cover images:
+                        # python/data/rope_utils.py); dropping the clip silently would train on a wrong prompt
+                        raise NotImplementedError("video content is not supported by the in-tree processor")
             parts.append(f"{IM_START}{msg['role']}\n{''.join(body)}{IM_END}\n")
         if add_generation_prompt:
             parts.append(f"{IM_START}assistant\n")

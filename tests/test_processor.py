@@ -62,3 +62,11 @@ def test_llava_sample_through_chat_template_masks_everything_but_the_answer():
     assert tok.decode(kept).startswith("\nA test.") or tok.decode(kept).startswith("A test.")
     assert int((labels[0] != -100).sum()) < ids.shape[1] // 2
     assert enc["pixel_values"].shape[0] == int(enc["image_grid_thw"].prod())
+
+
+def test_video_content_is_refused_not_dropped():
+    import pytest
+    from multimodal_training_b200.data.processor import Qwen2_5_VLProcessor
+    with pytest.raises(NotImplementedError):
+        Qwen2_5_VLProcessor().apply_chat_template([{"role": "user", "content": [{"type": "video", "video": "clip.mp4"},
+                                                                                {"type": "text", "text": "What happens?"}]}])
