@@ -165,7 +165,15 @@ def build_dataloader(processor, data_config: DataConfig, batch_size: int, rank: 
 
 
 class DatasetSource:
-    """Global batches from annotation files for the trainers: step -> list of :class:`Sample` (all replicas)."""
+    """Global batches from annotation files for the trainers: step -> list of :class:`Sample` (all replicas).
+
+    The batch of a step is a pure function of the step index, so the batches of the next steps are prepared ahead
+    on ``data.num_workers`` threads (image decoding, resizing and patch extraction release the GIL for most of
+    their time) while the GPU runs the current step; ``num_workers: 0`` prepares every batch when it is asked for.
+    The reference gets the same overlap from ``DataLoader`` worker processes (python/ray/trainer.py:92-104).
+    """
+
+    PREFETCH_STEPS = 2
 
     def __init__(self, config: dict, model_cfg, mesh, processor=None):
         self.cfg = DataConfig.from_flat(config)
@@ -177,16 +185,30 @@ class DatasetSource:
                                              vision_start_token_id=model_cfg.vision_start_token_id)
         self.global_batch = int(config["batch_size"]) * max(mesh.tdp, 1)
         self.dtype = torch.bfloat16 if torch.cuda.is_available() else torch.float32
+        self._pool = None
+        self._futures: dict[tuple[int, int], object] = {}
+        workers = int(self.cfg.num_workers or 0)
+        if workers > 0:
+            from concurrent.futures import ThreadPoolExecutor
+            self._pool = ThreadPoolExecutor(max_workers=workers, thread_name_prefix="mmt-data")
+
+    def _sample(self, step: int, j: int) -> Sample:
+        idx = (step * self.global_batch + j) % len(self.dataset)
+        it = self.dataset[idx]
+        px = it.get("pixel_values")
+        grid = it.get("image_grid_thw")
+        return Sample(it["input_ids"].reshape(-1), it["labels"].reshape(-1),
+                      None if px is None else px.to(self.dtype),
+                      [] if grid is None else [tuple(int(x) for x in g) for g in grid.tolist()], idx)
 
     def global_batch_at(self, step: int) -> list[Sample]:
-        out = []
-        n = len(self.dataset)
-        for j in range(self.global_batch):
-            idx = (step * self.global_batch + j) % n
-            it = self.dataset[idx]
-            px = it.get("pixel_values")
-            grid = it.get("image_grid_thw")
-            out.append(Sample(it["input_ids"].reshape(-1), it["labels"].reshape(-1),
-                              None if px is None else px.to(self.dtype),
-                              [] if grid is None else [tuple(int(x) for x in g) for g in grid.tolist()], idx))
+        if self._pool is None:
+            return [self._sample(step, j) for j in range(self.global_batch)]
+        for s in range(step, step + 1 + self.PREFETCH_STEPS):
+            for j in range(self.global_batch):
+                if (s, j) not in self._futures:
+                    self._futures[(s, j)] = self._pool.submit(self._sample, s, j)
+        out = [self._futures.pop((step, j)).result() for j in range(self.global_batch)]
+        for key in [k for k in self._futures if k[0] < step]:          # steps that were skipped (resume, evaluation)
+            self._futures.pop(key).cancel()
         return out

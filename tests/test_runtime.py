@@ -336,6 +336,9 @@ def test_driver_handles_ragged_multi_image_and_text_only_samples(tmp_path):
     (tmp_path / "ann.json").write_text(json.dumps(ann))
     res = train.main(_file_cfg(tmp_path, "ann.json"))               # 4 steps x 2 samples: every sample once
     assert res["steps"] == 4 and all(v == v and v < 20 for v in res["losses"])
+    # batches prepared ahead on worker threads are the same batches
+    ahead = train.main(_file_cfg(tmp_path, "ann.json", **{"data.num_workers": 2}))
+    assert ahead["losses"] == res["losses"]
     # text tensor parallel off, two data-parallel text replicas with one sample each (with and without images)
     res = train.main(_file_cfg(tmp_path, "ann.json", **{"text.parallelism": "none", "training.batch_size": 1}))
     assert res["steps"] == 4 and all(v == v and v < 20 for v in res["losses"])
