@@ -334,11 +334,21 @@ def test_driver_handles_ragged_multi_image_and_text_only_samples(tmp_path):
                                                                    {"from": "gpt", "value": "No."}]})
     ann.append({"conversations": [{"from": "human", "value": "Hello?"}, {"from": "gpt", "value": "Hi."}]})
     (tmp_path / "ann.json").write_text(json.dumps(ann))
-    res = train.main(_file_cfg(tmp_path, "ann.json"))               # 4 steps x 2 samples: every sample once
-    assert res["steps"] == 4 and all(v == v and v < 20 for v in res["losses"])
     # batches prepared ahead on worker threads are the same batches
-    ahead = train.main(_file_cfg(tmp_path, "ann.json", **{"data.num_workers": 2}))
-    assert ahead["losses"] == res["losses"]
+    from multimodal_training_b200.config.loader import trainer_configs
+    from multimodal_training_b200.config.model_configs import get_model_config
+    from multimodal_training_b200.data.dataset import DatasetSource
+    from multimodal_training_b200.parallel.mesh import Mesh
+    sources = [DatasetSource(trainer_configs(_file_cfg(tmp_path, "ann.json", **{"data.num_workers": w}))[1],
+                             get_model_config("tiny"), Mesh()) for w in (0, 2)]
+    for step in (0, 1, 3):                                           # step 2 is skipped on purpose
+        for a, b in zip(sources[0].global_batch_at(step), sources[1].global_batch_at(step)):
+            assert torch.equal(a.input_ids, b.input_ids) and torch.equal(a.labels, b.labels)
+            assert a.grid_thw == b.grid_thw and a.sample_index == b.sample_index
+            assert (a.pixel_values is None) == (b.pixel_values is None)
+            assert a.pixel_values is None or torch.equal(a.pixel_values, b.pixel_values)
+    res = train.main(_file_cfg(tmp_path, "ann.json", **{"data.num_workers": 2}))   # 4 steps x 2: every sample once
+    assert res["steps"] == 4 and all(v == v and v < 20 for v in res["losses"])
     # text tensor parallel off, two data-parallel text replicas with one sample each (with and without images)
     res = train.main(_file_cfg(tmp_path, "ann.json", **{"text.parallelism": "none", "training.batch_size": 1}))
     assert res["steps"] == 4 and all(v == v and v < 20 for v in res["losses"])
