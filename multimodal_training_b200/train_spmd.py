@@ -126,6 +126,14 @@ def main(cfg: dict) -> dict:
         if stop:
             break
     engine.synchronize()
+    if engine.timer is not None:
+        # training.trace: device time per phase, and a chrome://tracing file per rank when a path is given
+        phases = engine.timer.summary()
+        if rank == 0:
+            log.info("Device time per phase (mean ms per step): %s",
+                     ", ".join(f"{k} {v:.2f}" for k, v in phases.items()))
+        if tr.get("trace_file"):
+            engine.timer.chrome_trace(f"{tr['trace_file']}.rank{rank}.json", rank=rank)
     avg_t = measured_time / measured if measured else float("nan")
     if rank == 0:
         log.info("Training completed! %d epochs, %d total steps, %d measured steps (avg %.3fs/step)", num_epochs,
