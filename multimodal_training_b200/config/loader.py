@@ -72,6 +72,7 @@ DEFAULTS: dict[str, Any] = {
         "log_interval": 1,
         "profile_time": False,
         "trace": False,            # NVTX ranges + device-timed phases (utils/tracing.py)
+        "dist_timeout_s": None,    # torch.distributed timeout of the torchrun-style driver (None = library default)
         "trace_file": None,        # with trace: prefix of the per-rank chrome://tracing files (train_spmd)
         "backend": None,           # torch.distributed backend: default nccl on GPU, gloo on CPU
         "runtime": "auto",         # actor runtime: auto | ray | builtin

@@ -29,7 +29,9 @@ log = logging.getLogger("mmt_b200")
 def main(cfg: dict) -> dict:
     setup_logging(force=True)
     tr = cfg["training"]
-    init_distributed_comm(tr.get("backend"))
+    # a rank that dies between steps makes the others' next collective fail after this long instead of waiting for
+    # the library's default (ten minutes for NCCL)
+    init_distributed_comm(tr.get("backend"), tr.get("dist_timeout_s"))
     world = dist.get_world_size() if dist.is_initialized() else 1
     rank = dist.get_rank() if dist.is_initialized() else 0
     expected = int(tr["parallel_size"]) * int(tr.get("dp_size", 1))

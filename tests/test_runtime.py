@@ -357,3 +357,47 @@ def test_driver_handles_ragged_multi_image_and_text_only_samples(tmp_path):
     (tmp_path / "text.json").write_text(json.dumps(text_only))
     res = train.main(_file_cfg(tmp_path, "text.json", **{"training.num_iterations": 2}))
     assert res["steps"] == 2 and res["losses"][1] < res["losses"][0]
+
+
+def _lossy_spmd_worker(rank, world, root):
+    """Rank 1 leaves after the first step (between steps, nothing of its own in flight); rank 0 must get an error
+    from its next collective instead of waiting forever."""
+    import pathlib
+    import torch.distributed as dist
+    from multimodal_training_b200.engine import HybridEngine
+    eng = HybridEngine.from_config(_cfg(pathlib.Path(root)))
+    first = float(eng.train_step(0))
+    dist.barrier()
+    if rank == 1:
+        os._exit(0)
+    import json
+    t0 = time.time()
+    try:
+        eng.train_step(1)
+        out = {"first": first, "error": None, "waited": time.time() - t0}
+    except Exception as e:      # gloo reports the closed connection
+        out = {"first": first, "error": type(e).__name__, "waited": time.time() - t0}
+    with open(os.path.join(root, "survivor.json"), "w") as f:       # the harness's own final barrier fails too
+        json.dump(out, f)
+    return out
+
+
+def test_a_rank_that_leaves_between_steps_fails_the_others_next_collective(tmp_path):
+    import torch.multiprocessing as mp
+    from dist_utils import _entry, free_port
+    port = free_port()
+    (tmp_path / "c").mkdir()
+    ctx = mp.get_context("spawn")
+    procs = [ctx.Process(target=_entry, args=(r, 2, port, _lossy_spmd_worker, (str(tmp_path / "c"),), str(tmp_path)))
+             for r in range(2)]
+    for p in procs:
+        p.start()
+    procs[0].join(180)
+    alive = procs[0].is_alive()
+    for p in procs:
+        if p.is_alive():
+            p.terminate()
+    assert not alive, "rank 0 is still waiting for the rank that left"
+    import json
+    res = json.load(open(tmp_path / "c" / "survivor.json"))
+    assert res["error"] is not None and res["waited"] < 120 and res["first"] == res["first"], res
