@@ -123,6 +123,15 @@ def _registry() -> dict[str, VLConfig]:
                  num_key_value_heads=2, mrope_section=[8, 12, 12], tie_word_embeddings=False),
             image_token_id=1000, video_token_id=1001, vision_start_token_id=1002, vision_end_token_id=1003,
             pad_token_id=0),
+        # the tiny model with the input embedding reused as the output projection (as in the 3B model)
+        "tiny_tied": _vl(
+            "tiny_tied",
+            dict(depth=4, hidden_size=128, num_heads=4, intermediate_size=512, out_hidden_size=256, patch_size=14,
+                 spatial_merge_size=2, window_size=112, fullatt_block_indexes=[3]),
+            dict(vocab_size=1024, hidden_size=256, intermediate_size=688, num_hidden_layers=4, num_attention_heads=4,
+                 num_key_value_heads=2, mrope_section=[8, 12, 12], tie_word_embeddings=True),
+            image_token_id=1000, video_token_id=1001, vision_start_token_id=1002, vision_end_token_id=1003,
+            pad_token_id=0),
         # a bf16-friendly small model for single-GPU smoke runs (head_dim 80 vision / 128 text like the real ones)
         "smoke": _vl(
             "smoke",

@@ -30,12 +30,12 @@ def _grads_reference_layout(model):
             p.data = d
 
 
-def _worker(rank, world, sp, tp, steps):
+def _worker(rank, world, sp, tp, steps, model="tiny"):
     import torch.distributed as dist
     from multimodal_training_b200.config.loader import load_config
     from multimodal_training_b200.engine import HybridEngine
 
-    ov = OV + ["vision.parallelism=" + ("sequence" if sp > 1 else "none"),
+    ov = [o.replace("model_name=tiny", f"model_name={model}") for o in OV] + ["vision.parallelism=" + ("sequence" if sp > 1 else "none"),
                "text.parallelism=" + ("tensor" if tp > 1 else "none"), f"text.tensor_parallel_size={tp}",
                f"training.parallel_size={world}", f"training.batch_size={2 // (world // tp)}"]
     cfg = load_config(None, ov)
@@ -242,3 +242,15 @@ def test_vision_tensor_parallel_with_data_parallel(single, tmp_path):
             if a["tp_rank"] == b["tp_rank"]:
                 for k in a["weights"]:
                     assert torch.equal(a["weights"][k], b["weights"][k]), k
+
+
+@pytest.mark.integration
+def test_tied_embeddings_sp2_tp2_matches_single_process(tmp_path):
+    """The input embedding doubles as the output projection (3B model): its gradient is the sum of both uses, on
+    vocabulary shards as in one process."""
+    (tmp_path / "one").mkdir()
+    (tmp_path / "two").mkdir()
+    one = run_ranks(_worker, 1, tmp_path / "one", 1, 1, 3, "tiny_tied")[0]
+    assert "lm_head.weight" not in one["tgrads"]
+    multi = run_ranks(_worker, 2, tmp_path / "two", 2, 2, 3, "tiny_tied")
+    _compare(one, multi, tp=2)
