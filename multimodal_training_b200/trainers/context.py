@@ -99,3 +99,41 @@ def local_pixels(ctx: StepContext, out: torch.Tensor | None = None, plan: Vision
     if out is not None:
         return torch.index_select(allpix, 0, plan.local_patch_index, out=out)
     return allpix.index_select(0, plan.local_patch_index)
+
+
+class StagingRing:
+    """Host buffers for host->device copies that are enqueued, not awaited.
+
+    The host runs ahead of the GPU (the loss is read a step late), so a single pinned buffer would be overwritten
+    with the next step's pixels before the copy of this step has executed.  The ring hands out ``slots`` buffers in
+    turn; a buffer is reused only after the event recorded behind its last copy has completed, which normally
+    happened long ago.  On CPU (``pin=False``) the buffers are plain tensors and nothing is waited for.
+    """
+
+    def __init__(self, slots: int = 3, pin: bool = True):
+        self.slots = [[None, None] for _ in range(slots)]      # [buffer, event of the last copy out of it]
+        self.pin = pin
+        self._next = 0
+        self._current = None
+
+    def acquire(self, rows: int, cols: int, dtype) -> torch.Tensor:
+        slot = self.slots[self._next % len(self.slots)]
+        self._next += 1
+        buf, event = slot
+        if event is not None:
+            event.synchronize()
+            slot[1] = None
+        if buf is None or buf.shape[0] < rows or buf.shape[1] != cols or buf.dtype != dtype:
+            buf = torch.empty(rows, cols, dtype=dtype)
+            if self.pin:
+                buf = buf.pin_memory()
+            slot[0] = buf
+        self._current = slot
+        return buf[:rows]
+
+    def copied(self) -> None:
+        """Call right after enqueueing the copy out of the buffer that ``acquire`` returned last."""
+        if self.pin and self._current is not None:
+            event = torch.cuda.Event()
+            event.record()
+            self._current[1] = event

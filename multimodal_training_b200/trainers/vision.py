@@ -22,7 +22,7 @@ from ..ops import attention as attn_mod
 from ..parallel import comm
 from ..parallel.sp import build_vision_plan
 from ..parallel.tp import TPContext
-from .context import local_pixels
+from .context import StagingRing, local_pixels
 from .trainer import Trainer
 
 
@@ -78,7 +78,7 @@ class VisionTrainer(Trainer):
             zero_group = mesh.vision_zero_group if mesh.world > 1 else None
         self._build_optimizer(self.model.named_parameters(), zero_group, grad_divisor=float(mesh.tdp))
         self._pending = []
-        self._staging = None
+        self._staging = StagingRing(pin=dev.type == "cuda")
         return True
 
     def _load_pretrained(self, directory: str) -> None:
@@ -126,10 +126,9 @@ class VisionTrainer(Trainer):
             plan, rows = self._tensor_parallel_views(ctx)
         if dev.type == "cuda":
             n, d = plan.local_patch_index.numel(), self._model_cfg().vision.patch_dim
-            if self._staging is None or self._staging.shape[0] < n:
-                self._staging = torch.empty(n, d, dtype=torch.bfloat16).pin_memory()
-            host = local_pixels(ctx, out=self._staging[:n], plan=plan)
+            host = local_pixels(ctx, out=self._staging.acquire(n, d, torch.bfloat16), plan=plan)
             pixels = host.to(dev, non_blocking=True)
+            self._staging.copied()
             self.h2d_bytes = host.numel() * host.element_size()
         else:
             pixels = local_pixels(ctx, plan=plan).to(self._dtype())

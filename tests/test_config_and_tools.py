@@ -182,3 +182,28 @@ def test_checkpoint_policy_decision():
     assert decide(True, 0) is True and decide(False, 10 ** 15) is False
     assert decide("false", 1) is False and decide("true", 1) is True
     assert decide("auto", 10 ** 15, "cpu") is False          # no device memory to protect on the CPU path
+
+
+def test_staging_ring_reuses_a_buffer_only_after_its_copy_finished():
+    from multimodal_training_b200.trainers.context import StagingRing
+    ring = StagingRing(slots=3, pin=False)
+    a = ring.acquire(4, 8, torch.float32)
+    b = ring.acquire(4, 8, torch.float32)
+    c = ring.acquire(6, 8, torch.float32)
+    assert a.shape == (4, 8) and c.shape == (6, 8)
+    assert len({a.data_ptr(), b.data_ptr(), c.data_ptr()}) == 3        # three steps in flight never share memory
+
+    class Event:
+        waited = 0
+
+        def synchronize(self):
+            Event.waited += 1
+
+    ring.slots[0][1] = Event()               # as recorded behind the copy out of the first buffer
+    again = ring.acquire(3, 8, torch.float32)
+    assert again.data_ptr() == a.data_ptr() and again.shape == (3, 8) and Event.waited == 1
+    assert ring.slots[0][1] is None
+    bigger = ring.acquire(16, 8, torch.float32)                           # second slot grows
+    assert bigger.shape == (16, 8) and bigger.data_ptr() != b.data_ptr()
+    ring.copied()                                                         # no events without pinned memory
+    assert ring.slots[1][1] is None
