@@ -21,7 +21,7 @@ from ..ops import functional as F
 from ..ops.attention import SeqInfo
 from ..parallel import comm
 from ..parallel.tp import TPContext, column_parallel_linear, row_parallel_linear, vocab_range
-from ..utils.checkpointing import checkpoint
+from ..utils.checkpointing import bucket_tokens, checkpoint
 from ..utils.checkpointing import decide as decide_ckpt
 
 
@@ -136,11 +136,12 @@ class TextDecoder(nn.Module):
         x = x_shard
         # without tensor parallelism a layer has no communication inside and runs as one hand-written autograd
         # node (ops/blocks.py); tensor-parallel layers, the CPU path and un-checkpointed runs use the per-op graph
-        ckpt = decide_ckpt(self.ckpt, self.activation_bytes(x.shape[0]), x.device, group=self.tp.group,
+        need = self.activation_bytes(bucket_tokens(x.shape[0]))       # token shards are equal on all TP ranks
+        ckpt = decide_ckpt(self.ckpt, need, x.device, group=self.tp.group,
                            key=("text", id(self))) if torch.is_grad_enabled() else False
         self.ckpt_now = ckpt
-        keep_ew = (not ckpt) and x.is_cuda and not decide_ckpt("auto", self.activation_bytes(x.shape[0]) * 2, x.device,
-                                                              group=self.tp.group, key=("text-ew", id(self)))
+        keep_ew = (not ckpt) and x.is_cuda and not decide_ckpt("auto", need * 2, x.device, group=self.tp.group,
+                                                              key=("text-ew", id(self)))
         if self.tp.fused is not None:
             self.tp.fused.set_checkpointed("text", ckpt)
         one_node = (self.tp.size == 1 and torch.is_grad_enabled() and blocks.usable(x)

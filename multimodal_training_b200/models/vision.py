@@ -39,7 +39,7 @@ from ..ops.attention import SeqInfo
 from ..parallel import comm
 from ..parallel.sp import VisionPlan
 from ..parallel.tp import TPContext, copy_to_tp, reduce_from_tp
-from ..utils.checkpointing import checkpoint
+from ..utils.checkpointing import bucket_tokens, checkpoint
 from ..utils.checkpointing import decide as decide_ckpt
 
 
@@ -200,12 +200,14 @@ class VisionEncoder(nn.Module):
         # Ulysses layers of a sequence-parallel run and the CPU path use the per-op graph.  Whether activations
         # are recomputed in backward is decided per step (True / False / "auto": keep them when they fit)
         peers = self.tp.group if self.tp.size > 1 else self.sp.group
-        ckpt = decide_ckpt(self.ckpt, self.activation_bytes(x.shape[0]), x.device, group=peers,
+        # the size every peer agrees on: the largest rank's token count (ragged cuts differ per rank), bucketed
+        need = self.activation_bytes(bucket_tokens(max(plan.rank_tokens)))
+        ckpt = decide_ckpt(self.ckpt, need, x.device, group=peers,
                            key=("vision", id(self))) if torch.is_grad_enabled() else False
         self.ckpt_now = ckpt
         # with memory to spare (twice the estimate still fits the budget) the element-wise intermediates are kept too
-        keep_ew = (not ckpt) and x.is_cuda and not decide_ckpt("auto", self.activation_bytes(x.shape[0]) * 2, x.device,
-                                                              group=peers, key=("vision-ew", id(self)))
+        keep_ew = (not ckpt) and x.is_cuda and not decide_ckpt("auto", need * 2, x.device, group=peers,
+                                                              key=("vision-ew", id(self)))
         if self.sp.fused is not None:
             self.sp.fused.fc.set_checkpointed("vision", ckpt)
         one_node = (torch.is_grad_enabled() and blocks.usable(x) and attn_mod.BACKEND == "sm100"

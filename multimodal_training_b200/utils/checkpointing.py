@@ -50,6 +50,20 @@ def checkpoint(fn, tensors: tuple, extra: tuple = (), enabled: bool = True):
 _DECISIONS: dict = {}
 
 
+def bucket_tokens(n: int) -> int:
+    """Token count rounded up to a quarter of an octave (1024, 1280, 1536, 1792, 2048, 2560, ...).
+
+    ``decide`` caches one decision per size; with images of varying sizes nearly every batch has a new token count,
+    and every new size costs a collective and a host synchronisation.  Buckets bound the number of sizes (and make
+    the estimate an upper bound)."""
+    n = max(int(n), 1)
+    if n <= 1024:
+        return 1024
+    top = 1 << (n - 1).bit_length()
+    step = top // 8
+    return -(-n // step) * step
+
+
 def decide(mode, need_bytes: int, device=None, headroom: float = 0.5, group=None, key=None) -> bool:
     """Should a stack of blocks recompute its activations in backward?
 
@@ -67,7 +81,9 @@ def decide(mode, need_bytes: int, device=None, headroom: float = 0.5, group=None
         # Ranks that exchange activations inside the blocks (sequence / tensor parallel peers) must all take the
         # same branch, or the ones that recompute would wait for exchanges the others never start.  The decision is
         # therefore the OR over ``group`` and is taken once per (key, size): later steps with the same shapes reuse it
-        # without a collective or a host synchronisation.
+        # without a collective or a host synchronisation.  Callers must pass a ``need_bytes`` that is the SAME on
+        # every rank of ``group`` (derived from the largest rank's token count, not from the local one): the cache
+        # decides who enters the collective, so peers with different sizes would enter it in different steps.
         ck = (key, int(need_bytes))
         hit = _DECISIONS.get(ck)
         if hit is not None:

@@ -207,3 +207,11 @@ def test_staging_ring_reuses_a_buffer_only_after_its_copy_finished():
     assert bigger.shape == (16, 8) and bigger.data_ptr() != b.data_ptr()
     ring.copied()                                                         # no events without pinned memory
     assert ring.slots[1][1] is None
+
+
+def test_token_buckets_bound_the_number_of_checkpointing_decisions():
+    from multimodal_training_b200.utils.checkpointing import bucket_tokens
+    assert [bucket_tokens(n) for n in (1, 1024, 1025, 1040, 2048, 2049, 4096, 36864)] == \
+        [1024, 1024, 1280, 1280, 2048, 2560, 4096, 40960]
+    sizes = {bucket_tokens(n) for n in range(1000, 70000, 7)}
+    assert len(sizes) <= 4 * 7 + 1 and all(bucket_tokens(n) >= n for n in range(1, 70000, 97))
