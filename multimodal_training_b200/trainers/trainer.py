@@ -148,10 +148,25 @@ class Trainer(RayActor):
             sp = int(self.config.get("mesh_sp", self.config.get("sequence_parallel_size", 1)) or 1)
             tp = int(self.config.get("mesh_tp", self.config.get("tensor_parallel_size", 1)) or 1)
             st.mesh = build_mesh(min(sp, world), min(tp, world))
-            if self._get_device().type == "cuda" and st.mesh.world > 1 and self.config.get("fused_comm", True):
+            if self._get_device().type == "cuda" and st.mesh.world > 1 and self._want_fused_comm():
                 from ..parallel import fused as fused_mod
                 st.heap, st.fused = fused_mod.try_create(st.mesh, self.config)
         return st.mesh
+
+    def _want_fused_comm(self) -> bool:
+        """``training.fused_comm``: true / false, or auto = on when every step has the same shapes (synthetic data).
+        The regions of the symmetric heap are reserved at first use with the sizes of that step; batches of a data
+        set vary in length, and a later, longer batch would not fit its regions."""
+        v = self.config.get("fused_comm", "auto")
+        if isinstance(v, str):
+            if v.lower() != "auto":
+                return v.lower() in ("true", "1", "on", "yes")
+            on = bool(self.config.get("synthetic"))
+            if not on:
+                log.info("fused_comm auto: off for data-set batches of varying length (NCCL collectives are used); "
+                         "set training.fused_comm=true for fixed-shape data")
+            return on
+        return bool(v)
 
     def _ensure_source(self):
         st = self.state

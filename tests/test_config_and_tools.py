@@ -215,3 +215,14 @@ def test_token_buckets_bound_the_number_of_checkpointing_decisions():
         [1024, 1024, 1280, 1280, 2048, 2560, 4096, 40960]
     sizes = {bucket_tokens(n) for n in range(1000, 70000, 7)}
     assert len(sizes) <= 4 * 7 + 1 and all(bucket_tokens(n) >= n for n in range(1, 70000, 97))
+
+
+def test_fused_comm_auto_is_on_for_fixed_shapes_only():
+    from multimodal_training_b200.trainers.trainer import Trainer
+    want = lambda cfg: Trainer(cfg)._want_fused_comm()  # noqa: E731
+    assert want({"synthetic": {"image_size": 448}}) and not want({})
+    assert want({"fused_comm": "auto", "synthetic": {"image_size": 448}}) and not want({"fused_comm": "auto"})
+    assert want({"fused_comm": True}) and want({"fused_comm": "true"})
+    assert not want({"fused_comm": False, "synthetic": {"image_size": 448}}) and not want({"fused_comm": "false"})
+    v, _ = trainer_configs(load_config(None, []))
+    assert v["fused_comm"] == "auto"
