@@ -96,11 +96,13 @@ def load_and_merge_sharded_weights(checkpoint_dir: str, num_ranks: int, componen
 
 
 def refuse_vision_qkv(sd: dict) -> dict:
-    """``blocks.N.attn.{q,k,v}.{weight,bias}`` -> ``blocks.N.attn.qkv.{weight,bias}`` (HF layout)."""
+    """``blocks.N.attn.{q,k,v}_proj.{weight,bias}`` (the reference's names, modeling_qwen2_5_vl.py:334-338; the
+    shorter ``attn.{q,k,v}`` of earlier checkpoints of this package is accepted too) ->
+    ``blocks.N.attn.qkv.{weight,bias}`` (HF layout)."""
     out = {}
     groups: dict[tuple[str, str], dict[str, torch.Tensor]] = {}
     for k, v in sd.items():
-        m = re.fullmatch(r"(.*\.attn)\.([qkv])\.(weight|bias)", k)
+        m = re.fullmatch(r"(.*\.attn)\.([qkv])(?:_proj)?\.(weight|bias)", k)
         if m:
             groups.setdefault((m.group(1), m.group(3)), {})[m.group(2)] = v
         else:

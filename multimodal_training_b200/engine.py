@@ -62,6 +62,10 @@ class HybridEngine:
         if (torch.cuda.is_available() and self.mesh.world == 1
                 and bool(text_config.get("overlap_optimizer", False))):
             self._opt_stream = torch.cuda.Stream()
+        # bench.py sets this to time the optimizer phase (gradient reduction, AdamW, parameter all-gather) of every
+        # step with a pair of CUDA events, so that a step time without the optimizer can be reported
+        self.record_optimizer_time = False
+        self._opt_events: list = []
         # device-timed phases (CUDA events, no host syncs) when training.trace is on
         self.timer = None
         if bool(text_config.get("trace", False)) or tracing.enabled():
@@ -117,6 +121,10 @@ class HybridEngine:
             loss = t_out["loss"] if loss is None else loss + t_out["loss"]
         if self.accum > 1:
             loss = loss / self.accum
+        opt_ev = None
+        if self.record_optimizer_time and torch.cuda.is_available():
+            opt_ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+            opt_ev[0].record()
         with ph("optimizer"):
             scale = self._global_grad_scale() if self.clip else None
             for tr in (self.text, self.vision):
@@ -133,10 +141,24 @@ class HybridEngine:
                 else:
                     tr.optimizer.step(lr=tr.current_lr(), grad_scale=scale, shard=shard)
                 tr.global_step += 1
+        if opt_ev is not None:
+            self.join_streams()
+            opt_ev[1].record()
+            self._opt_events.append(opt_ev)
         if self.timer is not None:
             self.timer.end_step()
         self.step_index = step + 1
         return loss
+
+    def optimizer_ms(self) -> float:
+        """Device time of the optimizer phases recorded since the last call (synchronises; see
+        ``record_optimizer_time``)."""
+        if not self._opt_events:
+            return 0.0
+        self._opt_events[-1][1].synchronize()
+        total = sum(a.elapsed_time(b) for a, b in self._opt_events)
+        self._opt_events = []
+        return total
 
     def join_streams(self) -> None:
         """Make the current stream wait for work this engine put on its side stream (no host synchronisation)."""

@@ -235,9 +235,10 @@ class VisionEncoder(nn.Module):
 
     # ------------------------------------------------------------------ state dict in the reference/HF key layout
     def reference_state_dict(self, fused_qkv: bool = False) -> dict[str, torch.Tensor]:
-        """Keys of the reference's vision model: ``blocks.N.attn.{q,k,v,proj}``, ``mlp.{gate,up,down}_proj``,
-        ``merger.{ln_q,mlp.0,mlp.2}``, ``patch_embed.proj.weight`` [C,3,2,14,14].  ``fused_qkv`` emits HF's
-        ``attn.qkv`` instead of the reference's split q/k/v (python/ray/vision.py:322-345)."""
+        """Keys of the reference's vision model: ``blocks.N.attn.{q_proj,k_proj,v_proj,proj}``
+        (modeling_qwen2_5_vl.py:334-338), ``mlp.{gate,up,down}_proj``, ``merger.{ln_q,mlp.0,mlp.2}``,
+        ``patch_embed.proj.weight`` [C,3,2,14,14].  ``fused_qkv`` emits HF's ``attn.qkv`` instead of the
+        reference's split projections (python/ray/vision.py:322-345)."""
         cfg = self.cfg
         # a tensor-parallel rank emits its shards under the same keys (rows of q/k/v/gate/up, columns of proj/down;
         # the zero padding of the MLP width is cut off, so the shards concatenate to the reference's shapes)
@@ -255,8 +256,8 @@ class VisionEncoder(nn.Module):
                 out[p + "attn.qkv.bias"] = B.qkv_b.detach()
             else:
                 for j, n in enumerate("qkv"):
-                    out[p + f"attn.{n}.weight"] = B.qkv_w.detach()[j * Cl:(j + 1) * Cl]
-                    out[p + f"attn.{n}.bias"] = B.qkv_b.detach()[j * Cl:(j + 1) * Cl]
+                    out[p + f"attn.{n}_proj.weight"] = B.qkv_w.detach()[j * Cl:(j + 1) * Cl]
+                    out[p + f"attn.{n}_proj.bias"] = B.qkv_b.detach()[j * Cl:(j + 1) * Cl]
             out[p + "attn.proj.weight"] = B.proj_w.detach()
             out[p + "attn.proj.bias"] = B.proj_b.detach()
             out[p + "mlp.gate_proj.weight"] = B.gate_up_w.detach()[:I]
@@ -274,7 +275,8 @@ class VisionEncoder(nn.Module):
 
     @torch.no_grad()
     def load_reference_state_dict(self, sd: dict[str, torch.Tensor], sharded: bool = False) -> list[str]:
-        """Accepts split q/k/v (reference) or fused ``attn.qkv`` (HF); prefixes ``visual.`` / ``model.visual.``.
+        """Accepts the reference's split ``attn.{q,k,v}_proj`` (also the shorter ``attn.{q,k,v}`` that earlier
+        checkpoints of this package used) or HF's fused ``attn.qkv``; prefixes ``visual.`` / ``model.visual.``.
         A tensor-parallel rank takes its slices of full tensors, or with ``sharded`` its own shards as written by
         ``reference_state_dict``."""
         cfg = self.cfg
@@ -319,8 +321,9 @@ class VisionEncoder(nn.Module):
                 B.qkv_w.copy_(torch.cat([rows(w[j * C:(j + 1) * C]) for j in range(3)], 0) if take else w)
                 B.qkv_b.copy_(torch.cat([rows(b[j * C:(j + 1) * C]) for j in range(3)], 0) if take else b)
             else:
-                B.qkv_w.copy_(torch.cat([rows(get(p + f"attn.{n}.weight")) for n in "qkv"], 0))
-                B.qkv_b.copy_(torch.cat([rows(get(p + f"attn.{n}.bias")) for n in "qkv"], 0))
+                suf = "_proj" if p + "attn.q_proj.weight" in clean else ""
+                B.qkv_w.copy_(torch.cat([rows(get(p + f"attn.{n}{suf}.weight")) for n in "qkv"], 0))
+                B.qkv_b.copy_(torch.cat([rows(get(p + f"attn.{n}{suf}.bias")) for n in "qkv"], 0))
             B.proj_w.copy_(cols(get(p + "attn.proj.weight")))
             B.proj_b.copy_(get(p + "attn.proj.bias"))
             B.gate_up_w.zero_()

@@ -1,0 +1,69 @@
+"""How much of a training step the GPU spends idle between kernels (is the host the limit?).
+
+A step is a few thousand kernel launches.  If the host cannot enqueue them as fast as the device retires them,
+the device timeline shows gaps between consecutive kernels; if the launch queue stays ahead, it does not.  This
+module records the device timeline of a few steps with ``torch.profiler`` (CUPTI activity records: start and end
+of every kernel and copy on every stream of this process's GPU), merges the intervals of all streams and reports
+the busy time, the idle time and the largest gaps.
+
+The recording itself makes every launch a little more expensive on the host, so the idle share it reports is an
+UPPER bound; step times are never taken from a profiled run.
+"""
+from __future__ import annotations
+
+import torch
+
+
+def merge_intervals(intervals: list[tuple[float, float]]) -> list[tuple[float, float]]:
+    """Union of possibly overlapping [start, end) intervals, sorted."""
+    out: list[list[float]] = []
+    for s, e in sorted(intervals):
+        if out and s <= out[-1][1]:
+            if e > out[-1][1]:
+                out[-1][1] = e
+        else:
+            out.append([s, e])
+    return [(a, b) for a, b in out]
+
+
+def summarize(intervals: list[tuple[float, float]], steps: int, gap_floor_us: float = 2.0) -> dict:
+    """``intervals`` in microseconds -> per-step busy / idle milliseconds and gap statistics."""
+    merged = merge_intervals(intervals)
+    if not merged:
+        return {"kernels": 0}
+    span = merged[-1][1] - merged[0][0]
+    busy = sum(b - a for a, b in merged)
+    gaps = [merged[i + 1][0] - merged[i][1] for i in range(len(merged) - 1)]
+    big = sorted((g for g in gaps if g > gap_floor_us), reverse=True)
+    return {"kernels": len(intervals), "steps": steps,
+            "span_ms_per_step": span / 1e3 / steps, "busy_ms_per_step": busy / 1e3 / steps,
+            "idle_ms_per_step": (span - busy) / 1e3 / steps, "idle_share": (span - busy) / span if span else 0.0,
+            "gaps_over_floor_per_step": len(big) / steps, "gap_floor_us": gap_floor_us,
+            "largest_gaps_us": [round(g, 1) for g in big[:5]]}
+
+
+def measure(step_fn, steps: int = 2, ready=None) -> dict:
+    """Run ``step_fn()`` ``steps`` times under a CUDA activity trace and summarise the device timeline.
+
+    ``ready`` is called once the trace is recording and before the first step: in a multi-rank run pass a barrier,
+    so that the ranks that are not traced do not start (and wait in bounded device-side waits) while this rank is
+    still bringing the tracer up."""
+    from torch.autograd import DeviceType
+    from torch.profiler import ProfilerActivity, profile
+
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        if ready is not None:
+            ready()
+        for _ in range(steps):
+            step_fn()
+        torch.cuda.synchronize()
+    iv = []
+    for e in prof.events():
+        if e.device_type == DeviceType.CUDA:
+            r = e.time_range
+            iv.append((float(r.start), float(r.end)))
+    out = summarize(iv, steps)
+    out["note"] = ("device timeline of this rank recorded with CUPTI activity tracing in a phase of its own after all "
+                   "timed regions; tracing slows the host's launches, so the idle share is an upper bound")
+    return out

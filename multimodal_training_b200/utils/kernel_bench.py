@@ -4,6 +4,7 @@
     python -m multimodal_training_b200.utils.kernel_bench attention --tokens 16384 --heads 7 --kv-heads 1 --dim 128 --causal
     python -m multimodal_training_b200.utils.kernel_bench rmsnorm --rows 65536 --cols 3584
     python -m multimodal_training_b200.utils.kernel_bench adamw --elems 268435456
+    python -m multimodal_training_b200.utils.kernel_bench gemm_shapes      # the training step's GEMMs beside cuBLAS
 
 Timing: CUDA events on the launching stream, >= 3 warm-up launches, an L2 flush (a 256 MiB write)
 between timed launches, median of the timed launches.  Fractions are relative to the measured peaks in
@@ -67,9 +68,113 @@ def report(name: str, seconds: float, flops: float = 0.0, bytes_: float = 0.0, *
     return out
 
 
+# GEMMs of one Qwen2.5-VL-7B training step on one GPU (896 px image + 1024 text tokens): (tokens, out features,
+# in features) of every linear layer; each runs as forward, input-gradient and weight-gradient GEMM
+STEP_SHAPES = [("text qkv", 2048, 4608, 3584), ("text o_proj", 2048, 3584, 3584), ("text gate|up", 2048, 37888, 3584),
+               ("text down", 2048, 3584, 18944), ("lm_head", 2048, 152064, 3584), ("vision qkv", 4096, 3840, 1280),
+               ("vision proj", 4096, 1280, 1280), ("vision gate|up", 4096, 6848, 1280),
+               ("vision down", 4096, 1280, 3424)]
+
+
+class _ClockLog:
+    """SM clock samples (nvidia-smi, 100 ms) with host timestamps, to attribute a median clock to a timed loop."""
+
+    def __init__(self):
+        import subprocess
+        import tempfile
+        self.path = tempfile.mktemp(suffix=".csv")
+        self.f = open(self.path, "w")
+        try:
+            self.p = subprocess.Popen(["nvidia-smi", "-i", str(torch.cuda.current_device()),
+                                       "--query-gpu=timestamp,clocks.sm", "--format=csv,noheader,nounits", "-lms", "100"],
+                                      stdout=self.f, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.p = None
+
+    def close(self):
+        if self.p is not None:
+            self.p.terminate()
+            self.p.wait()
+        self.f.close()
+        import datetime
+        self.samples = []
+        for line in open(self.path):
+            try:
+                ts, mhz = line.rsplit(",", 1)
+                t = datetime.datetime.strptime(ts.strip(), "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                self.samples.append((t, float(mhz)))
+            except ValueError:
+                continue
+
+    def median(self, t0: float, t1: float):
+        v = sorted(m for t, m in self.samples if t0 + 0.15 <= t <= t1)
+        return v[len(v) // 2] if v else None
+
+
+def sustained(fn, seconds: float) -> tuple[float, float, float]:
+    """Back-to-back launches for about ``seconds``: (seconds per launch, host t0, host t1)."""
+    import time
+    fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    fn()
+    e1.record()
+    torch.cuda.synchronize()
+    n = max(3, int(seconds / max(e0.elapsed_time(e1) * 1e-3, 1e-6)))
+    t0 = time.time()
+    e0.record()
+    for _ in range(n):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e-3 / n, t0, time.time()
+
+
+def gemm_shapes(a) -> int:
+    """Every GEMM shape of the 7B step in its three operand layouts: this library's kernel beside cuBLAS
+    (``torch.matmul``), burst (L2 flushed, median) and sustained (back to back under the power cap), with the median
+    SM clock sampled during each sustained loop."""
+    dev = "cuda"
+    log = _ClockLog()
+    rows = []
+    for name, T, O, I in STEP_SHAPES:
+        x = torch.randn(T, I, device=dev, dtype=torch.bfloat16)
+        w = torch.randn(O, I, device=dev, dtype=torch.bfloat16) * 0.02
+        dy = torch.randn(T, O, device=dev, dtype=torch.bfloat16)
+        y, dx, dw = torch.empty_like(dy), torch.empty_like(x), torch.empty_like(w)
+        cases = [("fwd", lambda: F.gemm(x, w, out=y), lambda: torch.matmul(x, w.t(), out=y)),
+                 ("dgrad", lambda: F.gemm(dy, w, b_mn=True, out=dx), lambda: torch.matmul(dy, w, out=dx)),
+                 ("wgrad", lambda: F.gemm(dy, x, a_mn=True, b_mn=True, out=dw), lambda: torch.matmul(dy.t(), x, out=dw))]
+        for layout, mine, cublas in cases:
+            fl = 2.0 * T * O * I
+            r = {"gemm": name, "layout": layout, "tokens": T, "out": O, "in": I}
+            r["burst_tflops"] = fl / timed(mine, a.iters, a.warmup, True) / 1e12
+            r["cublas_burst_tflops"] = fl / timed(cublas, a.iters, a.warmup, True) / 1e12
+            ts, t0, t1 = sustained(mine, a.sustain)
+            tc, c0, c1 = sustained(cublas, a.sustain)
+            r["sustained_tflops"], r["cublas_sustained_tflops"] = fl / ts / 1e12, fl / tc / 1e12
+            r["_t"] = (t0, t1, c0, c1)
+            rows.append(r)
+    log.close()
+    tot = {"mine": 0.0, "cublas": 0.0}
+    for r in rows:
+        t0, t1, c0, c1 = r.pop("_t")
+        r["sm_mhz"], r["cublas_sm_mhz"] = log.median(t0, t1), log.median(c0, c1)
+        r["burst_vs_cublas"] = r["burst_tflops"] / r["cublas_burst_tflops"]
+        r["sustained_vs_cublas"] = r["sustained_tflops"] / r["cublas_sustained_tflops"]
+        fl = 2.0 * r["tokens"] * r["out"] * r["in"] * (28 if r["gemm"].startswith("text") else 32 if r["gemm"].startswith("vision") else 1)
+        tot["mine"] += fl / r["sustained_tflops"]
+        tot["cublas"] += fl / r["cublas_sustained_tflops"]
+        print(json.dumps(r))
+    print(json.dumps({"step_weighted_sustained_vs_cublas": tot["cublas"] / tot["mine"],
+                      "note": "time of all GEMMs of one step (layer counts applied) with cuBLAS / with this kernel"}))
+    return 0
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["gemm", "attention", "attention_bwd", "rmsnorm", "rmsnorm_bwd", "rope", "swiglu",
+    ap.add_argument("kernel", choices=["gemm_shapes", "gemm", "attention", "attention_bwd", "rmsnorm", "rmsnorm_bwd", "rope", "swiglu",
                                       "adamw", "ce"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8192)
@@ -91,6 +196,7 @@ def main(argv=None) -> int:
     ap.add_argument("--bwd-version", type=int, default=0, help="attention backward: 2 = pipelined kernels, 1 = first ones")
     ap.add_argument("--stream-k", type=int, default=-1, help="GEMM: 1 = stream-K for partial last waves, 0 = off (default)")
     ap.add_argument("--pair", type=int, default=-1, help="GEMM: 1 = 2-CTA kernel, 0 = 1-CTA kernels, -1 = default")
+    ap.add_argument("--sustain", type=float, default=0.5, help="gemm_shapes: seconds of back-to-back launches per case")
     a = ap.parse_args(argv)
     dev = "cuda"
     nv.lib()
@@ -99,6 +205,15 @@ def main(argv=None) -> int:
         nv.lib().mmt_attn_set_fwd_version(a.fwd_version)
     if a.bwd_version:
         nv.lib().mmt_attn_set_bwd_version(a.bwd_version)
+    if a.kernel == "gemm_shapes":
+        if a.pair >= 0:
+            nv.lib().mmt_gemm_use_pair(a.pair)
+        rc = gemm_shapes(a)
+        code = nv.get_error()
+        if code[0]:
+            print(json.dumps({"device_error": code}))
+            return 1
+        return rc
     if a.kernel == "gemm":
         if a.pair >= 0:
             nv.lib().mmt_gemm_use_pair(a.pair)

@@ -91,12 +91,15 @@ def _shard(sd, tp, r):
     return out
 
 
-def test_split_train_merge_round_trip(tmp_path):
+@pytest.mark.parametrize("names", ["{n}_proj", "{n}"])
+def test_split_train_merge_round_trip(tmp_path, names):
+    """Vision keys as the reference's module tree names them (attn.q_proj, modeling_qwen2_5_vl.py:334-338) and
+    as earlier checkpoints of this package did (attn.q)."""
     text = _fake_text_sd()
     vision = {"patch_embed.proj.weight": torch.randn(4, 3, 2, 2, 2), "merger.ln_q.weight": torch.ones(4)}
     for n in "qkv":
-        vision[f"blocks.0.attn.{n}.weight"] = torch.randn(4, 4)
-        vision[f"blocks.0.attn.{n}.bias"] = torch.randn(4)
+        vision[f"blocks.0.attn.{names.format(n=n)}.weight"] = torch.randn(4, 4)
+        vision[f"blocks.0.attn.{names.format(n=n)}.bias"] = torch.randn(4)
     full = {**{"model.visual." + k: v for k, v in vision.items()},
             **{"model.language_model." + k: v for k, v in text.items() if not k.startswith("lm_head")},
             "lm_head.weight": text["lm_head.weight"]}
@@ -119,9 +122,9 @@ def test_split_train_merge_round_trip(tmp_path):
     for k, v in text.items():
         key = k if k.startswith("lm_head") else "language_model." + k
         assert torch.equal(merged[key], v), k
-    qkv = torch.cat([vision[f"blocks.0.attn.{n}.weight"] for n in "qkv"])
+    qkv = torch.cat([vision[f"blocks.0.attn.{names.format(n=n)}.weight"] for n in "qkv"])
     assert torch.equal(merged["visual.blocks.0.attn.qkv.weight"], qkv)      # re-fused for stock HF
-    assert "visual.blocks.0.attn.q.weight" not in merged
+    assert not any(".attn.q" in k and ".attn.qkv" not in k for k in merged)
     assert json.load(open(os.path.join(out, "merge_metadata.json")))["vision_qkv"] == "fused"
 
 
