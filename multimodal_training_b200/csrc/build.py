@@ -27,6 +27,10 @@ NVCC_FLAGS = [
 ]
 
 
+# extra -D switches for measurement builds (e.g. MMT_NVCC_DEFINES="-DMMT_GEMM_TRACE"); part of the build stamp
+NVCC_FLAGS += [f for f in os.environ.get("MMT_NVCC_DEFINES", "").split() if f.startswith("-D")]
+
+
 def sources() -> list[Path]:
     return sorted(CSRC.glob("*.cu"))
 

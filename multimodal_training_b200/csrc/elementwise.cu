@@ -718,6 +718,7 @@ static int launch_rmsnorm_bwd(const void* dy, const void* x, const void* w, cons
 int mmt_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx, void* dw,
                     float* scratch, long rows, int cols, int accumulate_dw, void* stream) {
   if (cols % 8 || cols > 8 * kNormThreads * kNormVec) return -2;
+  if (rows < 0 || rows > 0x7fffffffL) return -5;      // the kernel indexes rows with 32-bit integers
   if (rows == 0) return 0;
   const int parts = launch_rmsnorm_bwd(dy, x, w, rstd, nullptr, dx, scratch, rows, cols, mmt_rmsnorm_bwd_parts(rows),
                                        stream);
@@ -730,6 +731,7 @@ int mmt_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* r
 int mmt_rmsnorm_bwd_add(const void* dy, const void* x, const void* w, const float* rstd, const void* extra, void* dx,
                         void* dw, float* scratch, long rows, int cols, int accumulate_dw, void* stream) {
   if (cols % 8 || cols > 8 * kNormThreads * kNormVec) return -2;
+  if (rows < 0 || rows > 0x7fffffffL) return -5;      // the kernel indexes rows with 32-bit integers
   if (rows == 0) return 0;
   const int parts = launch_rmsnorm_bwd(dy, x, w, rstd, extra, dx, scratch, rows, cols, mmt_rmsnorm_bwd_parts(rows),
                                        stream);

@@ -65,6 +65,16 @@ MMT_DEVICE void publish_when_last(int* counter, const PeerSet& ps, int epoch) {
   }
 }
 
+// A CTA that gives up (its bounded wait ran out) still counts itself out, so that the counter is back at zero for
+// the next launch; it publishes nothing: the peers' own waits run out and the host reads the error word.
+MMT_DEVICE void retire_without_publishing(int* counter) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned total = gridDim.x * gridDim.y;
+    if (atomicAdd(counter, 1) == (int)total - 1) *counter = 0;
+  }
+}
+
 // One CTA waits for n local flag words (skipping `self`); all threads learn the outcome.
 MMT_DEVICE bool wait_all_flags(const int* flags, int n, int self, int epoch, MmtErrorWord* ew, int where) {
   __shared__ int ok_s;
@@ -213,7 +223,10 @@ __global__ void __launch_bounds__(256) zero1_adamw_kernel(ZeroPeers zp, const in
                                                          float lr, float b1, float b2, float eps, float wd, float bc1,
                                                          float bc2, const float* __restrict__ gscale_ptr,
                                                          float* __restrict__ normsq_out, MmtErrorWord* ew) {
-  if (!wait_all_flags(grad_flags, zp.n, self, grad_epoch, ew, 920)) return;
+  if (!wait_all_flags(grad_flags, zp.n, self, grad_epoch, ew, 920)) {
+    retire_without_publishing(counter);
+    return;
+  }
   const float gs = gscale_ptr ? *gscale_ptr : 1.f;
   const long n8 = n >> 3;
   float nsq = 0.f;

@@ -50,7 +50,7 @@ struct GemmParams {
   int out_f32;                    // C is float
   float alpha;
   int a_mn, b_mn;                 // operand majors
-  int tma_store;                  // bf16 output leaves through shared memory + TMA stores
+  int tma_store;                  // bf16 output leaves through the epilogue warps' shared-memory slabs
   int group_m, tiles_n;           // raster: m-tiles per band (0 = all), number of n-tiles
   uint32_t mn_lbo, mn_sbo, mn_kstep;  // descriptor constants of MN-major tiles
   MmtErrorWord* ew;
@@ -179,11 +179,11 @@ struct Cfg {
   static_assert(MT == 1 || 2 * BN <= 512, "two accumulators must fit tensor memory");
 };
 
-// Output tensor maps: index 0 for a plain GEMM; one per owner rank for a reduce-scatter producer.
+
+// Output tensor maps ([32 x 64] boxes): index 0 for a plain GEMM; one per owner rank for a reduce-scatter producer.
 struct OutMaps {
   CUtensorMap m[8];
 };
-
 
 // byte offset of (row, col) in a [rows x 64] bf16 box (1024-byte aligned) with 128-byte rows and the 128B swizzle
 MMT_DEVICE uint32_t store_box_offset(int row, int col) {
@@ -254,8 +254,21 @@ MMT_DEVICE void tmem_dealloc_pair(uint32_t taddr, uint32_t cols) {
 
 // sk_part / sk_n / sk_stride: stream-K partial sums of this accumulator left by sk_n earlier CTAs (fp32, [128][BN],
 // one slot of sk_stride floats per CTA), added in CTA order before the epilogue arithmetic.
+#ifdef MMT_GEMM_TRACE
+// measurement build: warp 2 of CTA 0 appends SM cycle stamps to p.clk[2..] (see the epilogue loop)
+#define MMT_TRACE_STAMP(id)                                                                         \
+  do {                                                                                              \
+    if (p.clk && blockIdx.x == 0 && (threadIdx.x >> 5) == 2 && (threadIdx.x & 31) == 0) {            \
+      const unsigned long long n_ = p.clk[2];                                                       \
+      if (n_ < 500) { p.clk[3 + 2 * n_] = (id); p.clk[4 + 2 * n_] = (unsigned long long)clock64(); p.clk[2] = n_ + 1; } \
+    }                                                                                               \
+  } while (0)
+#else
+#define MMT_TRACE_STAMP(id) do { } while (0)
+#endif
+
 template <int BN>
-MMT_DEVICE void epilogue_block(const GemmParams& p, const OutMaps& tmC, uint32_t tmem_acc, int row0, int col_tile0,
+MMT_DEVICE void epilogue_block(const GemmParams& p, uint32_t tmem_acc, int row0, int col_tile0,
                                int q, int half, int lane, uint8_t* slab, uint32_t release_bar,
                                const float* sk_part = nullptr, int sk_n = 0, long sk_stride = 0) {
   constexpr int kGroups = BN / 64;
@@ -277,11 +290,13 @@ MMT_DEVICE void epilogue_block(const GemmParams& p, const OutMaps& tmC, uint32_t
     tmem_ld_32x32b_x32(taddr0 + (uint32_t)(g * 64), r0);
     tmem_ld_32x32b_x32(taddr0 + (uint32_t)(g * 64 + 32), r1);
     tmem_wait_ld();
+    MMT_TRACE_STAMP(10 + g);
     if (g == last_g) {
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(release_bar);
     }
+    MMT_TRACE_STAMP(20 + g);
     for (int c = 0; c < sk_n; ++c) {
       // slot layout: [64-column group][16-byte chunk][row], so that a warp reads 512 contiguous bytes per request
       const float4* src = reinterpret_cast<const float4*>(sk_part + (long)c * sk_stride) + (long)g * 16 * 128 +
@@ -301,10 +316,6 @@ MMT_DEVICE void epilogue_block(const GemmParams& p, const OutMaps& tmC, uint32_t
     }
     const int colg = col_tile0 + g * 64;
     if (p.dbg & 8) continue;                        // measurement only: drain the accumulator, store nothing
-    if (tma_out) {
-      if (lane == 0) tma_store_wait_read();        // this warp's previous store has read the slab
-      __syncwarp();
-    }
     if (colg < p.N && (row_ok || tma_out)) {
 #pragma unroll
       for (int j8 = 0; j8 < 8; ++j8) {
@@ -379,13 +390,138 @@ MMT_DEVICE void epilogue_block(const GemmParams& p, const OutMaps& tmC, uint32_t
         }
       }
     }
+    MMT_TRACE_STAMP(30 + g);
     if (tma_out) {
+      // The warp's 32 x 64 slab leaves as full 128-byte row segments: lane l copies 16 bytes of row (l >> 3) of
+      // every group of four rows, so each store instruction of the warp writes four complete lines.  Plain
+      // stores on purpose: a bulk (TMA) store would queue behind the operand loads that the producer warp has
+      // already issued for the next tile, and the warp would wait for that queue before it may refill its slab.
+      __syncwarp();
+      if (colg < p.N && !(p.dbg & 4)) {
+        const int chunk = lane & 7;
+        const int col = colg + chunk * 8;
+        if (col < p.N) {
+#pragma unroll
+          for (int it = 0; it < 8; ++it) {
+            const int row = it * 4 + (lane >> 3);
+            const long gr = (long)srow0 + row;
+            if (gr < p.M) {
+              const uint4 val = *reinterpret_cast<const uint4*>(slab + store_box_offset(row, chunk * 8));
+              __nv_bfloat16* dst;
+              if (p.rs_rows) {
+                const int owner = (int)(gr / p.rs_rows);
+                dst = reinterpret_cast<__nv_bfloat16*>(p.rs_base[owner]) +
+                      ((long)p.rs_self * p.rs_rows + (gr - (long)owner * p.rs_rows)) * p.ldc + col;
+              } else {
+                dst = reinterpret_cast<__nv_bfloat16*>(p.C) + gr * p.ldc + col;
+              }
+              *reinterpret_cast<uint4*>(dst) = val;
+            }
+          }
+        }
+      }
+      __syncwarp();                                  // the slab may be refilled
+    }
+    MMT_TRACE_STAMP(40 + g);
+  }
+}
+
+// The common case of epilogue_block as straight-line code: alpha == 1, no activation, bf16 output that overwrites C,
+// no stream-K partial sums; bias and residual are compile-time options.  Every linear layer's forward, input-gradient
+// and (first) weight-gradient GEMM ends here; epilogue_block keeps the general arithmetic.
+// Releases an accumulator to the MMA warp.  Within one CTA a CTA-scope arrive is enough (tensor-memory accesses are
+// ordered by the tcgen05 fences); the cluster-scope release that a barrier in the partner CTA needs would first wait
+// until this thread's earlier global stores are visible cluster-wide, i.e. for their round trip to L2.
+MMT_DEVICE void release_acc(uint32_t release_bar, bool remote) {
+  if (remote) mbar_arrive_cluster(release_bar);
+  else asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(release_bar) : "memory");
+}
+
+template <int BN, bool kBias, bool kResid>
+MMT_DEVICE void epilogue_fast(const GemmParams& p, const OutMaps& tmC, uint32_t tmem_acc, int row0, int col_tile0,
+                              int q, int half, int lane, uint8_t* slab, uint32_t release_bar, bool remote) {
+  constexpr int kGroups = BN / 64;
+  const int srow0 = row0 + q * 32;
+  const long grow = (long)srow0 + lane;
+  const bool row_ok = grow < p.M;
+  const uint32_t taddr0 = tmem_acc + ((uint32_t)(q * 32) << 16);
+  const int N = p.N;
+  const int chunk = lane & 7, sub = lane >> 3;
+  constexpr int last_g_of[2] = {((kGroups - 1) & ~1), ((kGroups - 2) | 1)};
+  const int last_g = kGroups == 1 ? (half == 0 ? 0 : -1) : last_g_of[half];
+  if (last_g < 0 || half >= kGroups) {
+    __syncwarp();
+    if (lane == 0) release_acc(release_bar, remote);
+    return;
+  }
+  // bulk (TMA) stores: the warp hands its slab to the copy engine and goes on; the burst of all CTAs' results then
+  // drains into L2 behind the next tile's main loop instead of stalling the epilogue warps on store back-pressure
+  const bool bulk = p.tma_store == 2;
+#pragma unroll 1
+  for (int g = half; g < kGroups; g += 2) {
+    uint32_t r0[32], r1[32];
+    tmem_ld_32x32b_x32(taddr0 + (uint32_t)(g * 64), r0);
+    tmem_ld_32x32b_x32(taddr0 + (uint32_t)(g * 64 + 32), r1);
+    tmem_wait_ld();
+    MMT_TRACE_STAMP(10 + g);
+    if (g == last_g) {
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) release_acc(release_bar, remote);
+    }
+    MMT_TRACE_STAMP(20 + g);
+    const int colg = col_tile0 + g * 64;
+    if (colg >= N) continue;
+    uint4 o[8];
+#pragma unroll
+    for (int j8 = 0; j8 < 8; ++j8) {
+      const int col = colg + j8 * 8;
+      float v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(j8 < 4 ? r0[j8 * 8 + j] : r1[(j8 - 4) * 8 + j]);
+      if (kBias || kResid) {
+        if (col < N) {
+          if (kBias) {
+            const uint4 bv = __ldg(reinterpret_cast<const uint4*>(p.bias + col));
+            const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 f = unpack_bf16x2(bw[j]);
+              v[2 * j] += f.x;
+              v[2 * j + 1] += f.y;
+            }
+          }
+          if (kResid && row_ok) {
+            const uint4 rv = *reinterpret_cast<const uint4*>(p.residual + grow * p.ldr + col);
+            const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 f = unpack_bf16x2(rw[j]);
+              v[2 * j] += f.x;
+              v[2 * j + 1] += f.y;
+            }
+          }
+        }
+      }
+      o[j8].x = pack_bf16x2(v[0], v[1]);
+      o[j8].y = pack_bf16x2(v[2], v[3]);
+      o[j8].z = pack_bf16x2(v[4], v[5]);
+      o[j8].w = pack_bf16x2(v[6], v[7]);
+    }
+    if (bulk) {
+      if (lane == 0) tma_store_wait_read();          // the previous bulk store has read the slab
+      __syncwarp();
+    }
+#pragma unroll
+    for (int j8 = 0; j8 < 8; ++j8) *reinterpret_cast<uint4*>(slab + store_box_offset(lane, j8 * 8)) = o[j8];
+    MMT_TRACE_STAMP(30 + g);
+    if (bulk) {
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) {
-        if (colg < p.N && srow0 < p.M && !(p.dbg & 4)) {   // dbg bit 2: everything but the TMA store itself
+        if (srow0 < p.M) {
           if (p.rs_rows) {
-            const int owner = srow0 / p.rs_rows;
+            const int owner = srow0 / p.rs_rows;      // rs_rows is a multiple of 32: a slab has one owner
             tma_store_2d(&tmC.m[owner], slab, colg, srow0 - owner * p.rs_rows);
           } else {
             tma_store_2d(&tmC.m[0], slab, colg, srow0);
@@ -393,7 +529,49 @@ MMT_DEVICE void epilogue_block(const GemmParams& p, const OutMaps& tmC, uint32_t
         }
         tma_store_commit();
       }
+      MMT_TRACE_STAMP(40 + g);
+      continue;
     }
+    __syncwarp();
+    const int col = colg + chunk * 8;
+    if (col < N) {
+#pragma unroll
+      for (int it = 0; it < 8; ++it) {
+        const int row = it * 4 + sub;
+        const long gr = (long)srow0 + row;
+        if (gr < p.M) {
+          const uint4 val = *reinterpret_cast<const uint4*>(slab + store_box_offset(row, chunk * 8));
+          __nv_bfloat16* dst;
+          if (p.rs_rows) {
+            const int owner = (int)(gr / p.rs_rows);
+            dst = reinterpret_cast<__nv_bfloat16*>(p.rs_base[owner]) +
+                  ((long)p.rs_self * p.rs_rows + (gr - (long)owner * p.rs_rows)) * p.ldc + col;
+          } else {
+            dst = reinterpret_cast<__nv_bfloat16*>(p.C) + gr * p.ldc + col;
+          }
+          *reinterpret_cast<uint4*>(dst) = val;
+        }
+      }
+    }
+    __syncwarp();
+    MMT_TRACE_STAMP(40 + g);
+  }
+}
+
+// Picks the straight-line epilogue when the GEMM's options allow it.
+template <int BN>
+MMT_DEVICE void epilogue_any(const GemmParams& p, const OutMaps& tmC, bool remote, uint32_t tmem_acc, int row0,
+                             int col_tile0, int q, int half, int lane, uint8_t* slab, uint32_t release_bar,
+                             const float* sk_part = nullptr, int sk_n = 0, long sk_stride = 0) {
+  const bool fast = p.alpha == 1.0f && p.act == 0 && !p.accumulate && !p.out_f32 && sk_n == 0 && !(p.dbg & 12);
+  if (!fast) {
+    epilogue_block<BN>(p, tmem_acc, row0, col_tile0, q, half, lane, slab, release_bar, sk_part, sk_n, sk_stride);
+  } else if (p.bias) {
+    if (p.residual) epilogue_fast<BN, true, true>(p, tmC, tmem_acc, row0, col_tile0, q, half, lane, slab, release_bar, remote);
+    else epilogue_fast<BN, true, false>(p, tmC, tmem_acc, row0, col_tile0, q, half, lane, slab, release_bar, remote);
+  } else {
+    if (p.residual) epilogue_fast<BN, false, true>(p, tmC, tmem_acc, row0, col_tile0, q, half, lane, slab, release_bar, remote);
+    else epilogue_fast<BN, false, false>(p, tmC, tmem_acc, row0, col_tile0, q, half, lane, slab, release_bar, remote);
   }
 }
 
@@ -612,7 +790,9 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 #pragma unroll 1
       for (int h = 0; h < MT; ++h) {
         const int slot = MT == 2 ? h : acc;
+        MMT_TRACE_STAMP(1);
         ok = mbar_wait(&tfull[slot], acc_ph, p.ew, 300);
+        MMT_TRACE_STAMP(2);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
@@ -624,7 +804,7 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           epilogue_partial<BN>(tmem_base + (uint32_t)(slot * BN), p.sk_ws + (long)blockIdx.x * kSlot + (long)h * BM * BN,
                                q, half, lane, smem_u32(&tempty[slot]));
         } else {
-          epilogue_block<BN>(p, tmC, tmem_base + (uint32_t)(slot * BN), tm * BMT + h * BM, tn * BN, q, half, lane, slab,
+          epilogue_any<BN>(p, tmC, false, tmem_base + (uint32_t)(slot * BN), tm * BMT + h * BM, tn * BN, q, half, lane, slab,
                              smem_u32(&tempty[slot]), p.sk_ws + (long)w.first_contrib * kSlot + (long)h * BM * BN,
                              n_contrib, kSlot);
         }
@@ -643,12 +823,12 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         acc_ph ^= 1;
       }
     }
-    if (lane == 0) {
-      tma_store_wait_all();                                  // every store of this warp has been written out
-      asm volatile("fence.proxy.async;" ::: "memory");
-    }
   }
 
+  if (warp >= 2 && lane == 0) {
+    tma_store_wait_all();                       // every bulk store of this warp has been written out
+    asm volatile("fence.proxy.async;" ::: "memory");
+  }
   if (p.rs_rows) __threadfence_system();   // this thread's peer stores are visible system-wide
   tc_fence_before();
   __syncthreads();
@@ -859,14 +1039,10 @@ gemm_bf16_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_con
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      epilogue_block<BN>(p, tmC, tmem_base + (uint32_t)(acc * BN), tm * BMT + (int)rank * BM, tn * BN, q, half, lane,
+      epilogue_any<BN>(p, tmC, true, tmem_base + (uint32_t)(acc * BN), tm * BMT + (int)rank * BM, tn * BN, q, half, lane,
                          slab, map_to_cta(smem_u32(&tempty[acc]), 0));
       acc ^= 1;
       if (acc == 0) acc_ph ^= 1;
-    }
-    if (lane == 0) {
-      tma_store_wait_all();
-      asm volatile("fence.proxy.async;" ::: "memory");
     }
   }
 
@@ -1009,6 +1185,46 @@ extern "C" int mmt_make_tmap_2d(CUtensorMap* out, const void* ptr, uint64_t inne
   return (int)r;
 }
 
+// Encoded tensor maps are kept per (address, extents, row stride, box): a training step issues the same few hundred
+// GEMMs on the same buffers every iteration, and encoding three maps per launch is host time on the launch path.
+namespace {
+struct TmapKey {
+  uint64_t ptr, inner, outer, ld, box;
+  int promo;
+  bool operator==(const TmapKey& o) const {
+    return ptr == o.ptr && inner == o.inner && outer == o.outer && ld == o.ld && box == o.box && promo == o.promo;
+  }
+};
+struct TmapSlot {
+  TmapKey key;
+  CUtensorMap map;
+  bool used;
+};
+constexpr int kTmapSlots = 1 << 13;
+thread_local TmapSlot* g_tmap_cache = nullptr;
+
+int cached_tmap_2d(CUtensorMap* out, const void* ptr, uint64_t inner, uint64_t outer, uint64_t ld, uint32_t box_inner,
+                   uint32_t box_outer) {
+  if (!g_tmap_cache) g_tmap_cache = static_cast<TmapSlot*>(calloc(kTmapSlots, sizeof(TmapSlot)));
+  const TmapKey k{reinterpret_cast<uint64_t>(ptr), inner, outer, ld, ((uint64_t)box_inner << 32) | box_outer, g_l2promo};
+  if (!g_tmap_cache) return mmt_make_tmap_2d(out, ptr, inner, outer, ld, box_inner, box_outer);
+  uint64_t h = k.ptr * 0x9E3779B97F4A7C15ull ^ (k.inner * 0xC2B2AE3D27D4EB4Full) ^ (k.outer << 17) ^ (k.ld << 7) ^ k.box;
+  h ^= h >> 29;
+  TmapSlot& slot = g_tmap_cache[h & (kTmapSlots - 1)];
+  if (slot.used && slot.key == k) {
+    *out = slot.map;
+    return 0;
+  }
+  const int r = mmt_make_tmap_2d(out, ptr, inner, outer, ld, box_inner, box_outer);
+  if (r == 0) {
+    slot.key = k;
+    slot.map = *out;
+    slot.used = true;
+  }
+  return r;
+}
+}  // namespace
+
 // Tuning knob: 0 = choose per call, 1 = 128-row tiles, 2 = 256-row tiles in one CTA, 3 = 2-CTA kernel.
 extern "C" void mmt_gemm_force_mt(int mt) { g_force_mt = mt; }
 // Raster band height in m-tiles (0 = choose, -1 = one band: m-fastest over the whole matrix).
@@ -1055,7 +1271,11 @@ extern "C" void mmt_gemm_set_comm(const MmtGemmComm* c) { g_comm = c; }
 extern "C" int mmt_gemm_bf16(const void* A, const void* B, void* C, const void* bias, const void* residual, int M,
                              int N, int K, int lda, int ldb, int ldc, int ldr, int a_mn, int b_mn, int act,
                              int accumulate, int out_f32, float alpha, int bn, void* stream) {
-  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  // collective roles belong to THIS call only: take them before any early return, so that a call that fails its
+  // argument checks cannot leave them behind for an unrelated GEMM
+  const MmtGemmComm* comm = g_comm;
+  g_comm = nullptr;
+  if (M <= 0 || N <= 0 || K <= 0) return comm ? -9 : 0;     // peers would wait for flags that an empty GEMM never sets
   if (mmt_ensure_context(A)) return -7;
   if ((lda & 7) || (ldb & 7) || (ldc & 7) || (N & 7) || (residual && (ldr & 7))) return -2;
   if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) ||
@@ -1076,7 +1296,7 @@ extern "C" int mmt_gemm_bf16(const void* A, const void* B, void* C, const void* 
     const int tn = (N + 255) / 256;
     const long kb = (K + BK - 1) / BK;
     // waves of 128-row / 256-row tiles; a partial last wave that stream-K spreads over all CTAs counts as a fraction
-    const bool plain = g_comm == nullptr;
+    const bool plain = comm == nullptr;
     read_env_once();
     auto waves = [&](long tiles, int m) {
       const long full = tiles / sms, rem = tiles % sms;
@@ -1096,11 +1316,11 @@ extern "C" int mmt_gemm_bf16(const void* A, const void* B, void* C, const void* 
   const int bbox = mt == 3 ? 128 : bn;                 // rows per TMA box of B
   CUtensorMap ta, tb;
   int r;
-  if (!a_mn) r = mmt_make_tmap_2d(&ta, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BK, (uint32_t)bmt);
-  else       r = mmt_make_tmap_2d(&ta, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, 64, BK);
+  if (!a_mn) r = cached_tmap_2d(&ta, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BK, (uint32_t)bmt);
+  else       r = cached_tmap_2d(&ta, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, 64, BK);
   if (r) return 1000 + r;
-  if (!b_mn) r = mmt_make_tmap_2d(&tb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BK, (uint32_t)bbox);
-  else       r = mmt_make_tmap_2d(&tb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, 64, BK);
+  if (!b_mn) r = cached_tmap_2d(&tb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BK, (uint32_t)bbox);
+  else       r = cached_tmap_2d(&tb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, 64, BK);
   if (r) return 2000 + r;
 
   GemmParams p;
@@ -1123,15 +1343,16 @@ extern "C" int mmt_gemm_bf16(const void* A, const void* B, void* C, const void* 
   p.ag_epoch = p.ag_rows = p.ag_self = 0;
   p.rs_rows = p.rs_self = p.rs_ranks = p.rs_epoch = 0;
   p.rs_counter = nullptr;
-  if (g_comm) {
-    const MmtGemmComm* c = g_comm;
-    g_comm = nullptr;
+  if (comm) {
+    const MmtGemmComm* c = comm;
     p.ag_flags = c->ag_flags; p.ag_epoch = c->ag_epoch; p.ag_rows = c->ag_rows; p.ag_self = c->ag_self;
     p.rs_rows = c->rs_rows; p.rs_self = c->rs_self; p.rs_ranks = c->rs_ranks; p.rs_epoch = c->rs_epoch;
     p.rs_counter = c->rs_counter;
     for (int i = 0; i < 8; ++i) { p.rs_base[i] = c->rs_base[i]; p.rs_flag[i] = c->rs_flag[i]; }
     if (p.ag_flags && (p.ag_rows <= 0 || a_mn)) return -5;
     if (p.rs_rows && (out_f32 || p.rs_ranks > 8 || p.rs_ranks < 1)) return -6;
+    // every row needs an owner among the rs_ranks peers: a longer M would index past the peer table
+    if (p.rs_rows && (long)M > (long)p.rs_rows * p.rs_ranks) return -8;
   }
   // stream-K for a partial last wave (plain GEMMs on the 1-CTA kernels only)
   p.sk_tiles = 0;
@@ -1150,24 +1371,28 @@ extern "C" int mmt_gemm_bf16(const void* A, const void* B, void* C, const void* 
       sk_on = true;
     }
   }
-  // output tensor maps for the TMA-store epilogue
+  // bf16 results leave through the epilogue warps' shared-memory slabs as full 128-byte row segments
+  // bf16 results leave through the epilogue warps' shared-memory slabs: as bulk stores of [32 x 64] boxes
+  // (tma_store == 2; a reduce-scatter producer needs rows-per-owner to be a multiple of 32 for that, so that a slab
+  // has a single owner) or else as plain 16-byte stores of full row segments (tma_store == 1)
   OutMaps tc;
   memset(&tc, 0, sizeof(tc));
   p.tma_store = 0;
   if (!out_f32) {
+    p.tma_store = 1;
     if (p.rs_rows) {
-      if (p.rs_rows % BM == 0) {
-        p.tma_store = 1;
+      if (p.rs_rows % 32 == 0) {
+        p.tma_store = 2;
         for (int i = 0; i < p.rs_ranks; ++i) {
           const __nv_bfloat16* base = reinterpret_cast<const __nv_bfloat16*>(p.rs_base[i]) +
                                       (long)p.rs_self * p.rs_rows * ldc;
-          r = mmt_make_tmap_2d(&tc.m[i], base, (uint64_t)N, (uint64_t)p.rs_rows, (uint64_t)ldc, 64, 32);
+          r = cached_tmap_2d(&tc.m[i], base, (uint64_t)N, (uint64_t)p.rs_rows, (uint64_t)ldc, 64, 32);
           if (r) return 3000 + r;
         }
       }
     } else {
-      p.tma_store = 1;
-      r = mmt_make_tmap_2d(&tc.m[0], C, (uint64_t)N, (uint64_t)M, (uint64_t)ldc, 64, 32);
+      p.tma_store = 2;
+      r = cached_tmap_2d(&tc.m[0], C, (uint64_t)N, (uint64_t)M, (uint64_t)ldc, 64, 32);
       if (r) return 3000 + r;
     }
   }

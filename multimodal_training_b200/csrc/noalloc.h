@@ -30,8 +30,8 @@ extern "C" {
 // dy, x, dx: bf16 [rows, cols] contiguous; w, dw: bf16 [cols]; rstd: fp32 [rows] (from the forward).
 // All pointers are device pointers supplied by the caller; `stream` is a cudaStream_t (0 = default).
 //
-// Returns 0 on success.  Errors (nothing is launched): -2 cols not a multiple of 8; -5 cols larger
-// than MMT_NOALLOC_MAX_COLS or rows outside [0, 2^31); -6 the scratch address could not be resolved
+// Returns 0 on success.  Errors (nothing is launched): -2 cols not a multiple of 8; -5 cols <= 0 or larger
+// than MMT_NOALLOC_MAX_COLS, or rows outside [0, 2^31); -6 the scratch address could not be resolved
 // on the current device.  A message naming the limit is written to stderr for -5 and -6.
 //
 // Set-up: the first call on each device resolves the device address of the built-in scratch array

@@ -55,6 +55,9 @@ extern "C" int mmt_get_error(int* out) {
   return (int)cudaMemcpy(out, w, sizeof(MmtErrorWord), cudaMemcpyDeviceToHost);
 }
 
+// Device address of the error word (for an asynchronous copy to pinned host memory behind a step).
+extern "C" void* mmt_error_word_address() { return mmt_error_word(); }
+
 extern "C" int mmt_clear_error() {
   MmtErrorWord* w = mmt_error_word();
   if (!w) return -1;

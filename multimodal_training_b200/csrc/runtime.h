@@ -16,6 +16,8 @@ int mmt_ensure_context(const void* ptr);
 extern "C" {
 // Copies the error word to out[4] = {code, where, block, aux}; synchronises the device.
 int mmt_get_error(int* out);
+// Device address of the error word ([4] int32), or nullptr if it could not be allocated.
+void* mmt_error_word_address();
 // Resets the error word to zero.
 int mmt_clear_error();
 // Library build tag, for tests that check the native path is loaded.

@@ -104,9 +104,13 @@ class HeapContext:
 class FusedComm:
     """Activation-side fused exchanges of one process (tensor parallel + handoff)."""
 
-    def __init__(self, mesh, device, heap_bytes: int, checkpointed: bool = True):
+    def __init__(self, mesh, device, heap_bytes: int, checkpointed: bool = True, text_hidden: int = 0,
+                 vision_hidden: int = 0):
         self.mesh = mesh
         self.device = device
+        self.text_hidden, self.vision_hidden = int(text_hidden), int(vision_hidden)
+        self.ulysses = False             # set by the vision trainer when the Ulysses exchange runs over the heap
+        self._sizes = None
         self.ctx = HeapContext(mesh.world_group, heap_bytes, device)
         # results that live in reusable heap regions may be handed out as views only while BOTH halves recompute
         # their activations in backward; otherwise they are cloned (see set_checkpointed)
@@ -122,6 +126,55 @@ class FusedComm:
     def set_checkpointed(self, half: str, on: bool) -> None:
         """Per-step decision of one half of the model ("vision" / "text") on activation recomputation."""
         self._ckpt[half] = bool(on)
+
+    # ------------------------------------------------------------------ region capacities
+    def region_plan(self, sizes) -> list[tuple[str, int]]:
+        """(name, bytes) of every exchange buffer for a step whose largest extents over all ranks are ``sizes``
+        (``trainers.context.StepSizes``).  Row counts are rounded up to quarter-octave buckets so that data sets
+        whose batches vary in length settle after a few steps instead of growing a region every step."""
+        from ..utils.checkpointing import bucket_tokens
+        m, H, C = self.mesh, self.text_hidden, self.vision_hidden
+        plan: list[tuple[str, int]] = []
+        shard = bucket_tokens(max(int(sizes.shard_rows), 1))
+        if m.tp > 1 and H:
+            for role in ("qkv", "mlp", "o_bwd", "down_bwd"):
+                plan.append(("ag_" + role, shard * m.tp * H * 2))
+            for role in ("o", "down", "qkv_bwd", "mlp_bwd"):
+                plan.append(("rs_" + role, shard * m.tp * H * 2))
+        if sizes.has_images and H:
+            plan.append(("handoff_in", shard * H * 2))
+            plan.append(("handoff_grad", bucket_tokens(max(int(sizes.merged_rows), 1)) * H * 2))
+        if self.ulysses and m.sp > 1 and C and sizes.has_images:
+            t_all = bucket_tokens(max(int(sizes.vision_tokens_all), 1))
+            t_loc = bucket_tokens(max(int(sizes.vision_tokens_rank), 1))
+            W = C // m.sp
+            plan += [("ul_heads3", t_all * 3 * W * 2), ("ul_tokens1", t_loc * C * 2),
+                     ("ul_tokens3_bwd", t_loc * 3 * C * 2), ("ul_heads1_bwd", t_all * W * 2)]
+        return plan
+
+    def begin_step(self, sizes) -> None:
+        """Reserve (or grow) every exchange buffer for this step, on every rank, in one fixed order and with sizes
+        that are the same on all ranks -- whether or not this rank will use a given buffer in this step.  That is
+        what keeps a region at the same offset in every rank's heap when batches are ragged: replicas with fewer
+        tokens, or without images, still reserve what the largest replica needs."""
+        if sizes == self._sizes:
+            return
+        self._sizes = sizes
+        for name, nbytes in self.region_plan(sizes):
+            self.ctx.heap.alloc(name, nbytes)
+
+    def end_step(self) -> None:
+        """Collective, main thread: after a step that reserved or moved regions, all ranks compare their tables."""
+        heap = self.ctx.heap
+        if heap.regions.version != heap.verified_version:
+            heap.verify_layout()
+
+    def capacity_rows(self, what: str, rows: int) -> int:
+        """Rows to reserve for a buffer of kind ``what`` that needs ``rows`` now: the step's world-wide maximum."""
+        s = self._sizes
+        if s is None:
+            return rows
+        return max(rows, {"shard": s.shard_rows, "merged": s.merged_rows}.get(what, 0))
 
     # ------------------------------------------------------------------ tensor parallel
     def _region(self, name: str, shape, dtype=torch.bfloat16) -> tuple[int, torch.Tensor]:
@@ -157,6 +210,9 @@ class FusedComm:
         m = self.mesh
         T = a.shape[0]
         N = w.shape[1] if b_mn else w.shape[0]
+        if T % m.tp:
+            raise ValueError(f"GEMM -> reduce-scatter over {m.tp} ranks needs a token count that {m.tp} divides, "
+                             f"got {T} (the row owner would be out of range)")
         rows = T // m.tp
         off, staging = self._region("rs_" + role, (m.tp * rows, N))
         slot = self.ctx.slot("rs_" + role)
@@ -287,7 +343,8 @@ class _FusedHandoffFn(torch.autograd.Function):
         dev = x_shard.device
         d = _dev_plan(plan, dev)
         H = x_shard.shape[1]
-        region = fc.route(leaf.contiguous(), d["dest_rank"], d["dest_row"], "handoff_in", x_shard.shape[0], H)
+        region = fc.route(leaf.contiguous(), d["dest_rank"], d["dest_row"], "handoff_in",
+                          fc.capacity_rows("shard", x_shard.shape[0]), H)
         out = x_shard.clone()
         rows = d["recv_rows"]
         if rows.numel():
@@ -303,7 +360,11 @@ class _FusedHandoffFn(torch.autograd.Function):
         rows = d["recv_rows"]
         H = dout.shape[1]
         g = F.gather_rows_raw(dout, rows) if rows.numel() else dout.new_zeros((0, H))
-        region = fc.route(g, d["recv_src_rank"], d["recv_src_index"], "handoff_grad", max(ctx.n_local, 1), H)
+        # the region is sized by the LARGEST rank's merged-token count (ragged splits give the ranks different
+        # counts): a region has to have the same size on every rank, and rows of a larger peer must pass the
+        # destination bound of a smaller one
+        region = fc.route(g, d["recv_src_rank"], d["recv_src_index"], "handoff_grad",
+                          fc.capacity_rows("merged", max(ctx.n_local, 1)), H)
         dleaf = region[:ctx.n_local].clone()
         dx = dout.clone()
         if rows.numel():
@@ -355,7 +416,10 @@ def try_create(mesh, config):
         if mesh.world > MAX_PEERS:
             return None, None
         heap_mb = int(config.get("symm_heap_mb", 8192))
-        fc = FusedComm(mesh, dev, heap_mb << 20, checkpointed=config.get("activation_checkpointing", True) is True)
+        from ..config.model_configs import get_model_config
+        mc = get_model_config(config.get("model_name", "qwen2_5_vl_7b"))
+        fc = FusedComm(mesh, dev, heap_mb << 20, checkpointed=config.get("activation_checkpointing", True) is True,
+                       text_hidden=mc.text.hidden_size, vision_hidden=mc.vision.hidden_size)
         return fc.ctx, fc
     except Exception as e:  # the NCCL path still works; say why the fused one does not
         log.warning("fused collectives unavailable: %s", e)

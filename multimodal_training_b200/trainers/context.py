@@ -19,6 +19,18 @@ from ..parallel.mesh import Mesh
 from ..parallel.sp import Geometry, VisionPlan, build_vision_plan, compute_geometry
 
 
+@dataclass(frozen=True)
+class StepSizes:
+    """Largest extents of this step over ALL ranks of the job: the same numbers on every rank (each rank knows
+    every replica's geometry), which is what makes the regions of the symmetric heap line up across ranks."""
+
+    shard_rows: int = 0          # rows of a text token shard (packed, padded tokens of a replica / tp)
+    merged_rows: int = 0         # merged vision tokens held by one vision rank
+    vision_tokens_all: int = 0   # patches of all images of one vision replica
+    vision_tokens_rank: int = 0  # patches held by one vision rank
+    has_images: bool = False
+
+
 @dataclass
 class StepContext:
     step: int
@@ -29,6 +41,7 @@ class StepContext:
     handoff: HandoffPlan | None
     n_vision_patches_global: int
     n_text_tokens_global: int
+    sizes: StepSizes = StepSizes()
 
 
 def _slice(n: int, parts: int, i: int) -> range:
@@ -87,8 +100,21 @@ def build_step_context(step: int, samples: list, cfg: VLConfig, mesh: Mesh, *, p
         if gid > 0 else None
     n_patches = sum(t * h * w for s in samples for (t, h, w) in s.grid_thw)
     n_text = sum(s.input_ids.numel() for s in samples)
+    live = [g for g in geoms if g is not None]
+    sizes = StepSizes(
+        shard_rows=max(text_len) // mesh.tp if text_len else 0,
+        merged_rows=max((sum(hi - lo for lo, hi in g.slices[r]) // g.unit for g in live for r in range(mesh.sp)),
+                        default=0),
+        vision_tokens_all=max((g.n_patches for g in live), default=0),
+        vision_tokens_rank=max((sum(hi - lo for lo, hi in g.slices[r]) for g in live for r in range(mesh.sp)),
+                               default=0),
+        has_images=gid > 0)
+    for d, n in enumerate(text_len):
+        if n % mesh.tp:
+            raise ValueError(f"text replica {d} packs {n} tokens, which the tensor-parallel size {mesh.tp} does not "
+                             "divide; set data.pad_multiple to a multiple of it")
     return StepContext(step, samples, list(_slice(B, mesh.vdp, mesh.vdp_rank)), vplan, my_tb, handoff, n_patches,
-                       n_text)
+                       n_text, sizes)
 
 
 def local_pixels(ctx: StepContext, out: torch.Tensor | None = None, plan: VisionPlan | None = None) -> torch.Tensor:

@@ -77,6 +77,20 @@ def test_noalloc_matches_regular_entry_point_twice():
     _case(lib, rows=333, cols=1280, seed=1, accumulate=True)   # second call: other shape, stale scratch in place
 
 
+def test_noalloc_with_capped_partial_rows_and_on_a_side_stream():
+    """cols = 8192 with thousands of rows: the number of per-CTA partial rows is capped by the size of the built-in
+    scratch (2^21 / 8192 = 256 rows of partial sums, fewer than the regular entry point would use), with and without
+    accumulation into dw, and launched on a stream that is not the default one."""
+    lib = _lib()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        _case(lib, rows=2000, cols=8192, seed=2, accumulate=False)
+        _case(lib, rows=2176, cols=8192, seed=3, accumulate=True)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+
+
 def test_noalloc_rejects_sizes_beyond_the_maximum():
     lib = _lib()
     t = torch.zeros(8, device="cuda", dtype=torch.bfloat16)
@@ -84,3 +98,5 @@ def test_noalloc_rejects_sizes_beyond_the_maximum():
     p = t.data_ptr()
     assert lib.mmt_rmsnorm_bwd_noalloc(p, p, p, f.data_ptr(), p, p, 1, 8192 + 8, 0, None) == -5
     assert lib.mmt_rmsnorm_bwd_noalloc(p, p, p, f.data_ptr(), p, p, 1, 12, 0, None) == -2
+    assert lib.mmt_rmsnorm_bwd_noalloc(p, p, p, f.data_ptr(), p, p, 1, 0, 0, None) == -5
+    assert lib.mmt_rmsnorm_bwd_noalloc(p, p, p, f.data_ptr(), p, p, -1, 8, 0, None) == -5
