@@ -1134,7 +1134,7 @@ void read_env_once() {
   }
   if (g_mt2_const < 0.0) {
     const char* e = getenv("MMT_GEMM_MT2_CONST");
-    g_mt2_const = e ? atof(e) : 3.9;
+    g_mt2_const = e ? atof(e) : 5.5;
   }
 }
 cudaEvent_t g_sk_event = nullptr;
@@ -1162,6 +1162,7 @@ int sk_tiles_for(int tiles, long kb, int sms, int mt) {
   return rem;
 }
 
+int g_force_bn = 0;   // 0 = choose, else the tile width (64 / 128 / 192 / 256) of every following GEMM
 int g_force_mt = 0;   // 0 = choose, 1 / 2 = force the number of 128-row accumulators per tile, 3 = 2-CTA kernel
 int g_use_pair = 0;
 int g_group_m = 0;
@@ -1227,6 +1228,8 @@ int cached_tmap_2d(CUtensorMap* out, const void* ptr, uint64_t inner, uint64_t o
 
 // Tuning knob: 0 = choose per call, 1 = 128-row tiles, 2 = 256-row tiles in one CTA, 3 = 2-CTA kernel.
 extern "C" void mmt_gemm_force_mt(int mt) { g_force_mt = mt; }
+// Tuning knob: tile width of every following GEMM (0 = choose per call).
+extern "C" void mmt_gemm_force_bn(int bn) { g_force_bn = bn; }
 // Raster band height in m-tiles (0 = choose, -1 = one band: m-fastest over the whole matrix).
 extern "C" void mmt_gemm_group_m(int g) { g_group_m = g; }
 // Measurement aid: device pointer to two 64-bit words that CTA 0 of every following GEMM fills with the SM
@@ -1282,36 +1285,48 @@ extern "C" int mmt_gemm_bf16(const void* A, const void* B, void* C, const void* 
       (reinterpret_cast<uintptr_t>(C) & 15))
     return -3;
   const int sms = mmt_sm_count();
-  if (bn == 0) {
-    // Measured on B200: the 256-wide tile has the best bytes-per-flop from L2 and wins even when
-    // it leaves a partial last wave; narrower tiles only for narrow outputs.
-    bn = N > 192 ? 256 : (N > 128 ? 192 : (N > 64 ? 128 : 64));
-  }
-  // Tile height.  256-row tiles (two accumulators sharing each B tile) move a third less data per flop, which under
-  // the board's power limit is what sets the clock, but their two accumulators fill tensor memory, so the
-  // epilogue is not hidden behind the next tile.  Cost model fitted to sustained measurements on B200, in units of
-  // one 128 x 256 x 64 step: a 128-row tile costs 0.56 per k-block, a 256-row tile 1.0 per k-block plus 3.9.
+  // Tile shape: rows = 128 (accumulator double buffered in tensor memory, epilogue hidden behind the next tile) or
+  // 256 (two accumulators that share every B tile: the main loop alternates between them, which keeps the tensor pipe
+  // busier than back-to-back MMAs into one accumulator, but the two fill tensor memory and the epilogue is exposed);
+  // width = 192 or 256 columns (narrower only for narrow outputs: a 128-wide MMA is bound by shared-memory reads).
+  // Cost of a candidate = waves x (k-blocks x c + e), in units of one 256 x 256 x 64 step, with c and e fitted to
+  // sustained measurements on B200 (rows x width: 128 x 256 c 0.568 e 2.4; 256 x 256 c 1.03 e 5.5; 128 x 192
+  // c 0.458 e 2.7; 256 x 192 c 0.72 e 8.0).  What it mostly decides is how well the tile count fills the 148 SMs.
+  read_env_once();
   int mt = 1;
-  if (bn == 256) {
-    const int tn = (N + 255) / 256;
-    const long kb = (K + BK - 1) / BK;
-    // waves of 128-row / 256-row tiles; a partial last wave that stream-K spreads over all CTAs counts as a fraction
-    const bool plain = comm == nullptr;
-    read_env_once();
-    auto waves = [&](long tiles, int m) {
-      const long full = tiles / sms, rem = tiles % sms;
-      if (rem == 0) return (double)full;
-      if (plain && sk_tiles_for((int)tiles, kb, sms, m) > 0)
-        return (double)full + (double)rem / sms + (m == 2 ? 16.0 : 8.0) / (double)kb;
-      return (double)full + 1.0;
-    };
-    const double w1 = waves((long)((M + 127) / 128) * tn, 1), w2 = waves((long)((M + 255) / 256) * tn, 2);
-    const double c1 = w1 * 0.5615 * (double)kb, c2 = w2 * ((double)kb + g_mt2_const);
-    if (M >= 256 && c2 < c1) mt = 2;
-    if (g_use_pair && M >= 256) mt = 3;                  // 2-CTA kernel: 256 x 256 tile per CTA pair
-    if (g_force_mt) mt = g_force_mt;
+  const long kb = (K + BK - 1) / BK;
+  const bool plain = comm == nullptr;
+  auto cost = [&](int m, int width) {
+    const long tiles = (long)((M + 128 * m - 1) / (128 * m)) * ((N + width - 1) / width);
+    const long full = tiles / sms, rem = tiles % sms;
+    double waves = (double)full + (rem ? 1.0 : 0.0);
+    if (rem && plain && width == 256 && sk_tiles_for((int)tiles, kb, sms, m) > 0)
+      waves = (double)full + (double)rem / sms + (m == 2 ? 16.0 : 8.0) / (double)kb;
+    double c, e;
+    if (width == 256) { c = m == 2 ? 1.03 : 0.568; e = m == 2 ? g_mt2_const : 2.4; }
+    else              { c = m == 2 ? 0.72 : 0.458; e = m == 2 ? 8.0 : 2.7; }
+    return waves * ((double)kb * c + e);
+  };
+  if (bn == 0 && g_force_bn) bn = g_force_bn;
+  if (bn == 0 && N <= 192) bn = N > 128 ? 192 : (N > 64 ? 128 : 64);
+  if (bn == 0) {
+    double best = 1e30;
+    for (int m = 1; m <= (M >= 256 ? 2 : 1); ++m) {
+      if (g_force_mt == 1 || g_force_mt == 2) m = g_force_mt;
+      for (int width = 192; width <= 256; width += 64) {
+        const double c = cost(m, width);
+        if (c < best) { best = c; mt = m; bn = width; }
+      }
+      if (g_force_mt == 1 || g_force_mt == 2) break;
+    }
     if (M < 256) mt = 1;
+  } else if (bn >= 192) {
+    mt = (M >= 256 && cost(2, bn) < cost(1, bn)) ? 2 : 1;
+    if (g_force_mt == 1 || g_force_mt == 2) mt = M >= 256 ? g_force_mt : 1;
+  } else if (g_force_mt == 2 && M >= 256 && bn == 128) {
+    mt = 2;
   }
+  if (bn == 256 && M >= 256 && (g_force_mt == 3 || (g_use_pair && g_force_mt == 0))) mt = 3;   // 2-CTA kernel
   const int bmt = mt == 3 ? BM : BM * mt;              // rows per TMA box of A
   const int bbox = mt == 3 ? 128 : bn;                 // rows per TMA box of B
   CUtensorMap ta, tb;
@@ -1405,8 +1420,8 @@ extern "C" int mmt_gemm_bf16(const void* A, const void* B, void* C, const void* 
       if (mt == 3) rc = launch_pair(ta, tb, tc, p, sms, st);
       else rc = mt == 2 ? launch<256, 2>(ta, tb, tc, p, sms, st) : launch<256, 1>(ta, tb, tc, p, sms, st);
       break;
-    case 192: rc = launch<192, 1>(ta, tb, tc, p, sms, st); break;
-    case 128: rc = launch<128, 1>(ta, tb, tc, p, sms, st); break;
+    case 192: rc = mt == 2 ? launch<192, 2>(ta, tb, tc, p, sms, st) : launch<192, 1>(ta, tb, tc, p, sms, st); break;
+    case 128: rc = mt == 2 ? launch<128, 2>(ta, tb, tc, p, sms, st) : launch<128, 1>(ta, tb, tc, p, sms, st); break;
     case 64:  rc = launch<64, 1>(ta, tb, tc, p, sms, st); break;
     default:  return -4;
   }
