@@ -76,8 +76,8 @@ DEFAULTS: dict[str, Any] = {
         "trace_file": None,        # with trace: prefix of the per-rank chrome://tracing files (train_spmd)
         "backend": None,           # torch.distributed backend: default nccl on GPU, gloo on CPU
         "runtime": "auto",         # actor runtime: auto | ray | builtin
-        "fused_comm": "auto",      # peer-memory fused collectives: true | false | auto (on for fixed-shape synthetic
-                                   # data; off for data sets, whose varying lengths outgrow first-use heap regions)
+        "fused_comm": "auto",      # peer-memory fused collectives: true | false | auto (on when every GPU can map
+                                   # every other one; heap regions grow with the longest batch seen)
         "overlap_optimizer": False,  # single-GPU engine: text AdamW on a side stream behind the next vision forward
         "symm_heap_mb": 8192,      # size of each GPU's symmetric heap (exchange buffers of the fused collectives)
     },

@@ -52,5 +52,19 @@ def synthetic_sample(cfg: VLConfig, index: int, *, image_size: int, text_tokens:
     return Sample(input_ids, labels, pixels, [(1, side, side)], index)
 
 
-def synthetic_global_batch(cfg: VLConfig, step: int, global_batch: int, **kw) -> list[Sample]:
-    return [synthetic_sample(cfg, step * global_batch + i, **kw) for i in range(global_batch)]
+def synthetic_global_batch(cfg: VLConfig, step: int, global_batch: int, *, image_sizes=None, text_token_choices=None,
+                           **kw) -> list[Sample]:
+    """``global_batch`` samples of step ``step``.  With ``image_sizes`` / ``text_token_choices`` (lists) the samples
+    cycle through those image sides and text lengths, so that consecutive samples and steps differ in shape the way
+    batches of a real data set do (ragged sequence-parallel splits, heap regions that have to grow)."""
+    out = []
+    for i in range(global_batch):
+        index = step * global_batch + i
+        k = dict(kw)
+        if image_sizes:
+            k["image_size"] = int(image_sizes[index % len(image_sizes)])
+        if text_token_choices:
+            k["text_tokens"] = int(text_token_choices[(index // max(len(image_sizes or [1]), 1) + index)
+                                                      % len(text_token_choices)])
+        out.append(synthetic_sample(cfg, index, **k))
+    return out

@@ -19,17 +19,26 @@ from .trainers.vision import VisionTrainer
 from .utils import tracing
 
 
+class DeviceStepError(RuntimeError):
+    """A kernel of the step reported a failure (a bounded wait on a peer ran out, an access was out of range)."""
+
+
 class LossHandle:
-    """Loss of one step on its way to the host (see ``HybridEngine.train_step_async``)."""
+    """Loss of one step on its way to the host (see ``HybridEngine.train_step_async``), together with a copy of the
+    device error word taken behind the step: reading the loss also tells whether the step's kernels all finished
+    their exchanges, without an extra synchronisation."""
 
-    __slots__ = ("host", "event")
+    __slots__ = ("host", "event", "err")
 
-    def __init__(self, host: torch.Tensor, event):
-        self.host, self.event = host, event
+    def __init__(self, host: torch.Tensor, event, err: torch.Tensor | None = None):
+        self.host, self.event, self.err = host, event, err
 
     def value(self) -> float:
         if self.event is not None:
             self.event.synchronize()
+        if self.err is not None and int(self.err[0]) != 0:
+            from .ops.native import format_error
+            raise DeviceStepError(format_error(*[int(x) for x in self.err[:4]]))
         return float(self.host[0])
 
 
@@ -52,6 +61,8 @@ class HybridEngine:
         # pinned host slots for train_step_async (allocated here: the first pinned allocation of a process is slow)
         pin = torch.cuda.is_available()
         self._loss_ring = [torch.zeros(1, dtype=torch.float32, pin_memory=pin) for _ in range(8)]
+        self._err_ring = [torch.zeros(4, dtype=torch.int32, pin_memory=pin) for _ in range(8)]
+        self._err_dev = None
         self._loss_i = 0
         # single-GPU runs hold the whole optimizer state on one device (37 ms of AdamW per 7B step);
         # training.overlap_optimizer puts the text update on a side stream behind the next vision forward.  Off by
@@ -147,6 +158,9 @@ class HybridEngine:
             self._opt_events.append(opt_ev)
         if self.timer is not None:
             self.timer.end_step()
+        fused = process_state().fused
+        if fused is not None:
+            fused.end_step()          # after a step that reserved or moved heap regions: all ranks compare layouts
         self.step_index = step + 1
         return loss
 
@@ -182,13 +196,20 @@ class HybridEngine:
         """
         loss = self.train_step(step)
         host = self._loss_ring[self._loss_i % len(self._loss_ring)]
-        self._loss_i += 1
+        err = None
         host.copy_(loss.detach().float().reshape(1), non_blocking=True)
         event = None
         if loss.is_cuda:
+            from .ops import native as nv
+            if nv.available():
+                if self._err_dev is None:
+                    self._err_dev = nv.error_word_tensor()
+                err = self._err_ring[self._loss_i % len(self._err_ring)]
+                err.copy_(self._err_dev, non_blocking=True)
             event = torch.cuda.Event()
             event.record()
-        return LossHandle(host, event)
+        self._loss_i += 1
+        return LossHandle(host, event, err)
 
     # ------------------------------------------------------------------ checkpoints (same layout as the actor driver)
     def save_checkpoint(self, checkpoint_dir: str, tag, config: dict | None = None, extra_meta: dict | None = None):
@@ -196,6 +217,8 @@ class HybridEngine:
         ``tag``; rank 0 then writes ``metadata.json``, which marks the checkpoint complete."""
         from .checkpoint import write_metadata
         self.synchronize()
+        # a device-side failure (checked inside the trainers' save) raises here, before metadata.json marks the
+        # checkpoint complete
         self.vision.save_checkpoint(checkpoint_dir, tag)
         self.text.save_checkpoint(checkpoint_dir, tag)
         if self.mesh.world > 1:

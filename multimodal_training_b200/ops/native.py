@@ -24,6 +24,7 @@ _SIGS = {
     "mmt_version": (c_char_p, []),
     "mmt_get_error": (c_int, [_P]),
     "mmt_clear_error": (c_int, []),
+    "mmt_error_word_address": (c_void_p, []),
     "mmt_gemm_set_mn_desc": (None, [c_uint32, c_uint32, c_uint32]),
     "mmt_gemm_bf16": (c_int, [_P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                               c_int, c_int, c_int, c_float, c_int, _P]),
@@ -135,8 +136,26 @@ def get_error() -> tuple[int, int, int, int]:
     return tuple(buf)  # type: ignore[return-value]
 
 
+ERROR_NAMES = {1: "an mbarrier wait ran out", 2: "a wait on a peer's flag ran out",
+               3: "an out-of-range access was skipped", 4: "tensor memory could not be allocated"}
+
+
+def format_error(code: int, where: int, block: int, aux: int) -> str:
+    return (f"device-side failure: {ERROR_NAMES.get(code, 'code ' + str(code))} (code={code} site={where} "
+            f"block={block} aux={aux}); results of this step are not valid")
+
+
+def error_word_tensor() -> "torch.Tensor":
+    """The device error word as an int32[4] tensor (for an asynchronous copy to pinned host memory)."""
+    from ..parallel.symm import tensor_from_ptr
+    addr = lib().mmt_error_word_address()
+    if not addr:
+        raise RuntimeError("the kernel library could not allocate its error word")
+    return tensor_from_ptr(addr, (4,), torch.int32, torch.device("cuda", torch.cuda.current_device()))
+
+
 def raise_on_device_error() -> None:
     code, where, block, aux = get_error()
     if code != 0:
         lib().mmt_clear_error()
-        raise RuntimeError(f"device-side bounded wait failed: code={code} site={where} block={block} aux={aux}")
+        raise RuntimeError(format_error(code, where, block, aux))

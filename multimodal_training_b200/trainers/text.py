@@ -59,6 +59,8 @@ class TextTrainer(Trainer):
         cfg = self._model_cfg()
         ctx = self.step_context(iteration)
         dev = self._get_device()
+        if self.state.fused is not None:
+            self.state.fused.begin_step(ctx.sizes)
         tb = ctx.text_batch
         vis = None
         if vision_out is not None:

@@ -84,13 +84,25 @@ def init_distributed_comm(backend: str | None = None, timeout_s: float | None = 
     dist.init_process_group(backend=backend, **kw)
 
 
+def _int_list(v):
+    """``[224, 448]`` or ``"224,448"`` (a dotted command-line override) -> list of ints; None stays None."""
+    if v is None or v == "":
+        return None
+    if isinstance(v, str):
+        return [int(x) for x in v.replace("[", "").replace("]", "").split(",") if x.strip()]
+    if isinstance(v, (int, float)):
+        return [int(v)]
+    return [int(x) for x in v]
+
+
 class SyntheticSource:
     """Deterministic global batches of synthetic samples (see ``data/synthetic.py``)."""
 
     def __init__(self, cfg: VLConfig, global_batch: int, image_size: int, text_tokens: int, seed: int, dtype,
-                 pin: bool = False, with_pixels: bool = True, repeat: int = 0):
+                 pin: bool = False, with_pixels: bool = True, repeat: int = 0, image_sizes=None,
+                 text_token_choices=None):
         self.kw = dict(image_size=image_size, text_tokens=text_tokens, seed=seed, dtype=dtype, pin=pin,
-                       with_pixels=with_pixels)
+                       with_pixels=with_pixels, image_sizes=image_sizes, text_token_choices=text_token_choices)
         self.cfg, self.global_batch, self.repeat = cfg, global_batch, repeat
         self._cache: dict[int, list] = {}
 
@@ -154,18 +166,15 @@ class Trainer(RayActor):
         return st.mesh
 
     def _want_fused_comm(self) -> bool:
-        """``training.fused_comm``: true / false, or auto = on when every step has the same shapes (synthetic data).
-        The regions of the symmetric heap are reserved at first use with the sizes of that step; batches of a data
-        set vary in length, and a later, longer batch would not fit its regions."""
+        """``training.fused_comm``: true / false / auto.  ``auto`` (the default) means on whenever every GPU of the job
+        can address every other one (``parallel.fused.try_create`` checks that and falls back to NCCL otherwise).
+        Batches of a data set vary in length; the regions of the symmetric heap are re-reserved per step from sizes
+        that are identical on all ranks (``FusedComm.begin_step``) and grow when a longer batch arrives."""
         v = self.config.get("fused_comm", "auto")
         if isinstance(v, str):
             if v.lower() != "auto":
                 return v.lower() in ("true", "1", "on", "yes")
-            on = bool(self.config.get("synthetic"))
-            if not on:
-                log.info("fused_comm auto: off for data-set batches of varying length (NCCL collectives are used); "
-                         "set training.fused_comm=true for fixed-shape data")
-            return on
+            return True
         return bool(v)
 
     def _ensure_source(self):
@@ -179,7 +188,9 @@ class Trainer(RayActor):
                 st.source = SyntheticSource(cfg, gb, int(syn.get("image_size", 448)), int(syn.get("text_tokens", 64)),
                                             self.seed, torch.bfloat16 if self._get_device().type == "cuda" else
                                             torch.float32, pin=bool(self.config.get("pin_memory", True)),
-                                            repeat=int(syn.get("repeat", 0)))
+                                            repeat=int(syn.get("repeat", 0)),
+                                            image_sizes=_int_list(syn.get("image_sizes")),
+                                            text_token_choices=_int_list(syn.get("text_token_choices")))
             else:
                 from ..data.dataset import DatasetSource
                 st.source = DatasetSource(self.config, cfg, mesh)
@@ -266,9 +277,25 @@ class Trainer(RayActor):
         lr = self.current_lr()
         self.optimizer.step(lr=lr, grad_scale=scale, shard=shard)
         self.global_step += 1
+        if self.kind == "text" and self.state.fused is not None:
+            # once per step and process, on the driver's calling thread: after a step that reserved or moved
+            # regions of the symmetric heap all ranks compare their layouts (HybridEngine does the same itself)
+            self.state.fused.end_step()
         return lr
 
+    def check_device_errors(self) -> bool:
+        """Raise if a kernel of this process recorded a bounded wait that ran out (or a skipped out-of-range access)
+        since the last check.  Synchronises the device: call it where the host waits anyway."""
+        if self._get_device().type == "cuda":
+            from ..ops import native as nv
+            if nv.available():
+                nv.raise_on_device_error()
+        return True
+
     def get_memory_stats(self) -> dict:
+        # the driver calls this once per step after it has read the losses: the step's kernels have run, so this is
+        # where the actor runtime notices a device-side failure before the next step builds on garbage
+        self.check_device_errors()
         if self._get_device().type == "cuda":
             return {"allocated_mb": torch.cuda.memory_allocated() / 2 ** 20,
                     "peak_mb": torch.cuda.max_memory_allocated() / 2 ** 20}
@@ -310,6 +337,7 @@ class Trainer(RayActor):
         return self.global_step
 
     def save_checkpoint(self, checkpoint_dir: str, epoch) -> str:
+        self.check_device_errors()          # never write weights that a failed exchange may have corrupted
         path = self._ckpt_path(checkpoint_dir, epoch)
         os.makedirs(os.path.dirname(path), exist_ok=True)
         payload = {"model": {k: v.cpu() for k, v in self.model.reference_state_dict().items()}}
@@ -326,24 +354,35 @@ class Trainer(RayActor):
         return path
 
     def load_checkpoint(self, checkpoint_dir: str, epoch) -> bool:
+        """Load this rank's shard; False if it is missing or unreadable.  On failure the weights this trainer had
+        before the call are put back (a partial load must not leave some tensors from the checkpoint and others from
+        the initialisation) and the caller decides for ALL ranks together whether training starts from scratch."""
         path = self._ckpt_path(checkpoint_dir, epoch)
         if not os.path.exists(path):
             log.warning("checkpoint %s not found", path)
             return False
+        backup = {k: v.detach().clone() for k, v in self.model.state_dict().items()}
         try:
-            payload = torch.load(path, map_location="cpu", weights_only=False)
+            payload = torch.load(path, map_location="cpu", weights_only=True)
             self._load_model_state(payload["model"], sharded=True)
             if self.optimizer is not None:
                 self.optimizer.refresh_master_from_params()
                 opath = os.path.join(checkpoint_dir, self._ckpt_name(epoch), self.kind + "_optim",
                                      f"rank_{self.rank}.pt")
                 if os.path.exists(opath):
-                    extra = torch.load(opath, map_location="cpu", weights_only=False)
+                    extra = torch.load(opath, map_location="cpu", weights_only=True)
                     self.optimizer.load_state_dict(extra["optimizer"])
                     self.global_step = int(extra.get("global_step", self.global_step))
+                    if extra.get("rng") is not None:
+                        torch.set_rng_state(extra["rng"].cpu().to(torch.uint8))
             return True
         except Exception as e:  # a broken shard must not kill the run (the driver starts from scratch)
             log.error("failed to load checkpoint %s: %s", path, e)
+            with torch.no_grad():
+                for k, v in self.model.state_dict().items():
+                    v.copy_(backup[k])
+            if self.optimizer is not None:
+                self.optimizer.refresh_master_from_params()
             return False
 
     def _load_model_state(self, sd: dict, sharded: bool) -> None:

@@ -61,6 +61,7 @@ class VisionTrainer(Trainer):
                 and self.config.get("fused_ulysses", True)):
             from ..parallel.fused_ulysses import UlyssesFused
             ulysses = UlyssesFused(self.state.fused)
+            self.state.fused.ulysses = True
         if self.tensor_parallel:
             # the mesh's vision group is the tensor-parallel group; nothing is sequence parallel inside the model
             self.norm_type = "tensor"
@@ -115,6 +116,8 @@ class VisionTrainer(Trainer):
         t0 = self._timer_start()
         ctx = self.step_context(iteration)
         dev = self._get_device()
+        if self.state.fused is not None:
+            self.state.fused.begin_step(ctx.sizes)
         plan, rows = ctx.vision_plan, None
         if plan is None:
             # no image in this replica's share of the batch: nothing to encode, nothing to hand over

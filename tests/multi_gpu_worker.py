@@ -12,7 +12,7 @@ import torch  # noqa: E402
 import torch.distributed as dist  # noqa: E402
 
 
-def run(fused: bool, steps: int, vision: str = "sequence"):
+def run(fused: bool, steps: int, vision: str = "sequence", ragged: bool = False):
     from multimodal_training_b200.config.loader import load_config
     from multimodal_training_b200.engine import HybridEngine
     from multimodal_training_b200.ops import native as nv
@@ -25,11 +25,18 @@ def run(fused: bool, steps: int, vision: str = "sequence"):
         "training.learning_rate=1e-3", "training.warmup_ratio=0", "training.warmup_steps=0",
         "training.lr_scheduler_type=constant", "+data.synthetic.image_size=448", "+data.synthetic.text_tokens=256",
         f"+data.synthetic.global_batch={2 * (world // min(world, 2))}", "+data.synthetic.repeat=1",
-        f"training.fused_comm={'true' if fused else 'false'}"])
+        f"training.fused_comm={'true' if fused else 'false'}"]
+        # images of three sizes and texts of three lengths, new ones every step: ragged sequence-parallel splits
+        # (81 and 225 merged tokens do not divide by 2) and heap regions that have to grow after the first step
+        + (["+data.synthetic.image_sizes=252,448,420", "+data.synthetic.text_token_choices=96,256,40",
+            "+data.synthetic.repeat=0"] if ragged else []))
     reset_process_state()
     eng = HybridEngine.from_config(cfg)
     assert (process_state().fused is not None) == fused
-    losses = [eng.mean_loss(eng.train_step(0)) for _ in range(steps)]
+    losses = [eng.mean_loss(eng.train_step(s if ragged else 0)) for s in range(steps)]
+    if fused and ragged:
+        heap = process_state().fused.ctx.heap
+        assert heap.regions.version == heap.verified_version     # every layout change was compared across ranks
     nv.raise_on_device_error()
     return losses
 
@@ -40,8 +47,11 @@ def main():
     fused = run(True, 4)
     lib = run(False, 4)
     vtp = run(False, 4, vision="tensor")          # tensor-parallel vision encoder (all-reduce per block)
+    rag_fused = run(True, 6, ragged=True)
+    rag_lib = run(False, 6, ragged=True)
     if dist.get_rank() == 0:
-        print("RESULT " + json.dumps({"fused": fused, "lib": lib, "vision_tp": vtp}))
+        print("RESULT " + json.dumps({"fused": fused, "lib": lib, "vision_tp": vtp, "ragged_fused": rag_fused,
+                                      "ragged_lib": rag_lib}))
     dist.barrier()
     dist.destroy_process_group()
 
