@@ -327,6 +327,26 @@ def main() -> int:
             engine.train_step(step0 + s)
         step0 += 2
 
+    # ---- device time per phase of the step (CUDA events, three extra steps after every timed region)
+    phases = None
+    try:
+        from multimodal_training_b200.utils.tracing import PhaseTimer
+        engine.timer = PhaseTimer()
+        for s in range(3):
+            engine.train_step(step0 + s)
+        step0 += 3
+        summ = engine.timer.summary()
+        engine.timer = None
+        names = sorted(summ)
+        pt = torch.tensor([summ[k] for k in names], device="cuda", dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(pt, op=dist.ReduceOp.MAX)
+        phases = {k: float(v) for k, v in zip(names, pt)}
+    except Exception as e:
+        engine.timer = None
+        phases = {"error": f"{type(e).__name__}: {str(e)[:200]}"}
+    barrier()
+
     # ---- device idle time between kernels (host-bound or not), traced, after every timed region
     idle = None
     if not args.no_idle_gaps:
@@ -421,6 +441,7 @@ def main() -> int:
                                  "thousand launches ahead it waits for launch-queue slots, so this approaches the "
                                  "device time from below even when the host is not the limit; device_idle is the "
                                  "measurement that separates the two cases",
+            "phases_ms": phases,
             "device_idle": idle,
             "gpu_launches": int(launches),
             "gpu_launches_per_step": launches / args.steps,

@@ -76,6 +76,7 @@ DEFAULTS: dict[str, Any] = {
         "trace_file": None,        # with trace: prefix of the per-rank chrome://tracing files (train_spmd)
         "backend": None,           # torch.distributed backend: default nccl on GPU, gloo on CPU
         "runtime": "auto",         # actor runtime: auto | ray | builtin
+        "label_smoothing": 0.0,    # cross-entropy label smoothing (python/tensor_parallel/cross_entropy.py:185-202)
         "fused_comm": "auto",      # peer-memory fused collectives: true | false | auto (on when every GPU can map
                                    # every other one; heap regions grow with the longest batch seen)
         "overlap_optimizer": False,  # single-GPU engine: text AdamW on a side stream behind the next vision forward
@@ -163,6 +164,14 @@ def validate(cfg: dict) -> dict:
             raise ConfigError(f"attention_backend must be one of {ATTN_BACKENDS}")
         if sec.get("zero_stage") not in (0, 1, 2, 3, None):
             raise ConfigError("zero_stage must be 0..3")
+        # zero_stage matters only with parallelism: deepspeed (as in the reference, python/ray/text.py:99-106).
+        # Stages 0-2 run as the flat-buffer ZeRO optimizer of parallel/zero.py: gradients are reduce-scattered, so
+        # each rank reduces and keeps only its own partition (what stage 2 adds to stage 1), and optimizer states
+        # are always sharded.  Stage 3 (parameters partitioned, gathered layer by layer) is not implemented:
+        # sequence / tensor parallelism is how this framework splits a model that does not fit one GPU.
+        if sec["parallelism"] == "deepspeed" and sec.get("zero_stage") == 3:
+            raise ConfigError("parallelism: deepspeed with zero_stage: 3 (parameter partitioning) is not supported; "
+                              "use zero_stage 1 or 2, or parallelism: tensor / sequence to shard the model")
     for k in ("batch_size", "num_epochs", "num_iterations", "parallel_size", "dp_size",
               "gradient_accumulation_steps"):
         if not isinstance(tr[k], int) or tr[k] < 1:

@@ -159,12 +159,14 @@ class TextDecoder(nn.Module):
             x = checkpoint(lambda t, L=L: self._layer(t, L, cos, sin, seq), (x,), enabled=ckpt)
         return x
 
-    def loss(self, x_shard: torch.Tensor, shifted_labels: torch.Tensor, chunk_rows: int = 4096) -> torch.Tensor:
+    def loss(self, x_shard: torch.Tensor, shifted_labels: torch.Tensor, chunk_rows: int = 4096,
+             label_smoothing: float = 0.0) -> torch.Tensor:
         """Final norm -> all-gather -> lm_head + vocab-parallel CE (mean over rows with label >= 0)."""
         h = F.rmsnorm(x_shard, self.norm_w, self.cfg.rms_norm_eps)
         hg = comm.all_gather(h, self.tp.group)
         w = self.embed_tokens if self.lm_head is None else self.lm_head
-        return F.lm_head_cross_entropy(hg, w, shifted_labels, self.vocab_lo, self.tp.group, chunk_rows)
+        return F.lm_head_cross_entropy(hg, w, shifted_labels, self.vocab_lo, self.tp.group, chunk_rows,
+                                       label_smoothing=label_smoothing)
 
     def logits(self, x_shard: torch.Tensor) -> torch.Tensor:
         """Local vocab-shard logits [T, V/tp] (tests and evaluation)."""

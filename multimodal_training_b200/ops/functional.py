@@ -413,7 +413,7 @@ class _LMHeadCEFn(torch.autograd.Function):
     """
 
     @staticmethod
-    def forward(ctx, hidden, weight, labels, vocab_lo, group, chunk_rows):
+    def forward(ctx, hidden, weight, labels, vocab_lo, group, chunk_rows, smoothing=0.0, vocab_total=0):
         T, H = hidden.shape
         V = weight.shape[0]
         dev = hidden.device
@@ -448,10 +448,25 @@ class _LMHeadCEFn(torch.autograd.Function):
                 _all_reduce(st[0], ReduceOp.MAX, group)
                 st[1].mul_(torch.exp(lmax - st[0]))
                 _all_reduce(st[1:3], ReduceOp.SUM, group)
-            row_loss = (torch.log(st[1]) + st[0] - st[2]) * valid[c0:c1]
+            if smoothing > 0.0:
+                # label smoothing (rare path, plain tensor ops around the kernels): the loss also needs the mean
+                # logit over the whole vocabulary, the gradient moves `smoothing` of the target's mass to all ids
+                zsum = logits.sum(-1, dtype=torch.float32)
+                _all_reduce(zsum, ReduceOp.SUM, group)
+                row_loss = (torch.log(st[1]) + st[0] - (1.0 - smoothing) * st[2] - smoothing * zsum / vocab_total) \
+                    * valid[c0:c1]
+            else:
+                row_loss = (torch.log(st[1]) + st[0] - st[2]) * valid[c0:c1]
             loss_sum += row_loss.sum()
             nv.call("mmt_ce_grad", logits.data_ptr(), lab.data_ptr(), st[0].data_ptr(), st[1].data_ptr(),
                     inv.data_ptr(), rows, V, logits.stride(0), vocab_lo, nv.stream())
+            if smoothing > 0.0:
+                scale = (inv[0] * valid[c0:c1]).to(logits.dtype)                       # [rows]
+                logits.sub_((smoothing / vocab_total) * scale.unsqueeze(1))
+                local = lab - vocab_lo
+                mine = (local >= 0) & (local < V) & valid[c0:c1]
+                logits.view(-1).index_add_(0, (torch.arange(rows, device=dev) * logits.stride(0)
+                                               + local.clamp(0, V - 1))[mine], (smoothing * scale)[mine])
             gemm(logits, weight, b_mn=True, out=dhidden[c0:c1])
             if need_w:
                 gemm(logits, h, a_mn=True, b_mn=True, out=dw, accumulate=acc0 or c0 > 0)
@@ -468,24 +483,32 @@ class _LMHeadCEFn(torch.autograd.Function):
         dh = dhidden * dloss.to(dhidden.dtype)
         if dw is not None:
             dw = dw * dloss.to(dw.dtype)
-        return dh, dw, None, None, None, None
+        return dh, dw, None, None, None, None, None, None
 
 
 def lm_head_cross_entropy(hidden: torch.Tensor, weight: torch.Tensor, labels: torch.Tensor, vocab_lo: int = 0,
-                          group=None, chunk_rows: int = 4096) -> torch.Tensor:
+                          group=None, chunk_rows: int = 4096, label_smoothing: float = 0.0) -> torch.Tensor:
     """Mean CE over rows with ``labels >= 0``.  ``weight`` is this rank's [V_local, H] vocab shard starting at
     ``vocab_lo``; with a group, max / sum-exp / target logit are reduced over it
     (Megatron-style, reference: python/tensor_parallel/cross_entropy.py:41-236).
 
     ``labels`` are already shifted (row t holds the id to predict at t) and use -100 (any negative) to ignore.
     On the GPU path, the weight gradient assumes ``dloss == 1`` when it is written into ``main_grad``.
+
+    ``label_smoothing`` = a in (0, 1): the target keeps 1 - a of the probability mass and the other ids of the WHOLE
+    vocabulary share a (the reference's option, python/tensor_parallel/cross_entropy.py:185-202,223-230, which takes
+    the mean over the local shard only): with s = a V / (V - 1), loss = (1 - s) nll - s mean_v(log p_v).
     """
+    multi = group is not None and torch.distributed.get_world_size(group) > 1
+    vocab_total = weight.shape[0] * (torch.distributed.get_world_size(group) if multi else 1)
+    if not 0.0 <= label_smoothing < 1.0:
+        raise ValueError("label_smoothing must be in [0, 1)")
+    smoothing = label_smoothing * vocab_total / (vocab_total - 1) if label_smoothing > 0 else 0.0
     if _native(hidden):
-        return _LMHeadCEFn.apply(_c(hidden), weight, labels, vocab_lo, group, chunk_rows)
+        return _LMHeadCEFn.apply(_c(hidden), weight, labels, vocab_lo, group, chunk_rows, smoothing, vocab_total)
     logits = F.linear(hidden, weight).float()
     V = weight.shape[0]
     ReduceOp = torch.distributed.ReduceOp
-    multi = group is not None and torch.distributed.get_world_size(group) > 1
     m = logits.max(dim=-1).values.detach()
     if multi:
         _all_reduce(m, ReduceOp.MAX, group)
@@ -499,7 +522,13 @@ def lm_head_cross_entropy(hidden: torch.Tensor, weight: torch.Tensor, labels: to
         tgt = all_reduce_sum_autograd(tgt, group)
         se = all_reduce_sum_autograd(se, group)
     valid = labels >= 0
-    row = (se.log() - tgt) * valid
+    if smoothing > 0.0:
+        zsum = z.sum(-1)
+        if multi:
+            zsum = all_reduce_sum_autograd(zsum, group)
+        row = (se.log() - (1.0 - smoothing) * tgt - smoothing * zsum / vocab_total) * valid
+    else:
+        row = (se.log() - tgt) * valid
     return row.sum() / valid.sum().clamp(min=1)
 
 

@@ -102,7 +102,8 @@ class TextTrainer(Trainer):
         cos, sin = cos.to(dev, non_blocking=True), sin.to(dev, non_blocking=True)
         seq = SeqInfo.from_list(tb.cu_seqlens, dev)
         h = self.model(x, cos, sin, seq)
-        loss = self.model.loss(h, labels, chunk_rows=int(self.config.get("ce_chunk_rows", 4096)))
+        loss = self.model.loss(h, labels, chunk_rows=int(self.config.get("ce_chunk_rows", 4096)),
+                               label_smoothing=float(self.config.get("label_smoothing", 0.0) or 0.0))
         self._loss = loss
         out = {"loss": loss.detach(), "sample_index": tb.sample_index, "iteration": iteration}
         ms = self._timer_stop(t0)

@@ -220,12 +220,24 @@ def test_token_buckets_bound_the_number_of_checkpointing_decisions():
     assert len(sizes) <= 4 * 7 + 1 and all(bucket_tokens(n) >= n for n in range(1, 70000, 97))
 
 
-def test_fused_comm_auto_is_on_for_fixed_shapes_only():
+def test_fused_comm_auto_is_on_for_data_sets_too():
+    """Heap regions are sized per step and grow, so ``auto`` no longer depends on the batches having one shape."""
     from multimodal_training_b200.trainers.trainer import Trainer
     want = lambda cfg: Trainer(cfg)._want_fused_comm()  # noqa: E731
-    assert want({"synthetic": {"image_size": 448}}) and not want({})
-    assert want({"fused_comm": "auto", "synthetic": {"image_size": 448}}) and not want({"fused_comm": "auto"})
+    assert want({"synthetic": {"image_size": 448}}) and want({})
+    assert want({"fused_comm": "auto", "synthetic": {"image_size": 448}}) and want({"fused_comm": "auto"})
     assert want({"fused_comm": True}) and want({"fused_comm": "true"})
     assert not want({"fused_comm": False, "synthetic": {"image_size": 448}}) and not want({"fused_comm": "false"})
     v, _ = trainer_configs(load_config(None, []))
     assert v["fused_comm"] == "auto"
+
+
+def test_zero_stage_three_is_rejected_only_where_it_would_be_used():
+    """``zero_stage`` is consulted with ``parallelism: deepspeed`` only (as in the reference): stages 0-2 run as the
+    flat-buffer ZeRO optimizer, stage 3 (parameter partitioning) is refused instead of being mapped silently."""
+    load_config(None, ["text.parallelism=tensor", "text.zero_stage=3"])           # ignored in this mode
+    load_config(None, ["text.parallelism=deepspeed", "text.zero_stage=2"])
+    with pytest.raises(ConfigError, match="zero_stage"):
+        load_config(None, ["text.parallelism=deepspeed", "text.zero_stage=3"])
+    with pytest.raises(ConfigError, match="zero_stage"):
+        load_config(None, ["vision.parallelism=deepspeed", "vision.zero_stage=3"])

@@ -176,6 +176,30 @@ def test_lm_head_cross_entropy(T, V, H):
     assert rel_err(w.grad, wf.grad) < 3e-2
 
 
+def test_lm_head_cross_entropy_with_label_smoothing():
+    """The smoothed loss and its gradients against an fp32 evaluation of -sum_v q_v log p_v (q = 1 - a on the target,
+    a / (V - 1) on every other id)."""
+    F, nv = _F()
+    torch.manual_seed(9)
+    T, V, H, a = 300, 4096, 256, 0.1
+    h = torch.randn(T, H, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    w = (torch.randn(V, H, device=DEV, dtype=torch.bfloat16) * 0.05).requires_grad_()
+    labels = torch.randint(0, V, (T,), device=DEV)
+    labels[::5] = -100
+    loss = F.lm_head_cross_entropy(h, w, labels, chunk_rows=128, label_smoothing=a)
+    loss.backward()
+    hf, wf = h.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    logp = torch.log_softmax(hf @ wf.t(), dim=-1)
+    q = torch.full_like(logp, a / (V - 1))
+    q.scatter_(1, labels.clamp(min=0)[:, None], 1.0 - a)
+    valid = labels >= 0
+    lr = (-(q * logp).sum(-1) * valid).sum() / valid.sum()
+    lr.backward()
+    assert abs(loss.item() - lr.item()) < 2e-2 * abs(lr.item())
+    assert rel_err(h.grad, hf.grad) < 3e-2
+    assert rel_err(w.grad, wf.grad) < 3e-2
+
+
 def test_adamw_and_sumsq():
     F, nv = _F()
     torch.manual_seed(8)
