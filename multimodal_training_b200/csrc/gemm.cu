@@ -29,6 +29,17 @@
 #include "common.cuh"
 #include "runtime.h"
 
+// Measurement builds only (-DMMT_GEMM_MEASURE, see csrc/build.py): switches that drop parts of the kernel's work
+// (results are then wrong), the in-kernel clock probe and the descriptor bring-up knob.  In a regular build none of
+// them exists: the tests read MMT_DBG as the constant 0 and the setters are not exported.
+#ifdef MMT_GEMM_MEASURE
+#define MMT_DBG (p.dbg)
+#define MMT_CLK (p.clk)
+#else
+#define MMT_DBG 0
+#define MMT_CLK ((unsigned long long*)nullptr)
+#endif
+
 namespace {
 
 constexpr int BM = 128;
@@ -254,13 +265,13 @@ MMT_DEVICE void tmem_dealloc_pair(uint32_t taddr, uint32_t cols) {
 
 // sk_part / sk_n / sk_stride: stream-K partial sums of this accumulator left by sk_n earlier CTAs (fp32, [128][BN],
 // one slot of sk_stride floats per CTA), added in CTA order before the epilogue arithmetic.
-#ifdef MMT_GEMM_TRACE
-// measurement build: warp 2 of CTA 0 appends SM cycle stamps to p.clk[2..] (see the epilogue loop)
+#if defined(MMT_GEMM_TRACE) && defined(MMT_GEMM_MEASURE)
+// measurement build: warp 2 of CTA 0 appends SM cycle stamps to MMT_CLK[2..] (see the epilogue loop)
 #define MMT_TRACE_STAMP(id)                                                                         \
   do {                                                                                              \
-    if (p.clk && blockIdx.x == 0 && (threadIdx.x >> 5) == 2 && (threadIdx.x & 31) == 0) {            \
-      const unsigned long long n_ = p.clk[2];                                                       \
-      if (n_ < 500) { p.clk[3 + 2 * n_] = (id); p.clk[4 + 2 * n_] = (unsigned long long)clock64(); p.clk[2] = n_ + 1; } \
+    if (MMT_CLK && blockIdx.x == 0 && (threadIdx.x >> 5) == 2 && (threadIdx.x & 31) == 0) {            \
+      const unsigned long long n_ = MMT_CLK[2];                                                       \
+      if (n_ < 500) { MMT_CLK[3 + 2 * n_] = (id); MMT_CLK[4 + 2 * n_] = (unsigned long long)clock64(); MMT_CLK[2] = n_ + 1; } \
     }                                                                                               \
   } while (0)
 #else
@@ -315,7 +326,7 @@ MMT_DEVICE void epilogue_block(const GemmParams& p, uint32_t tmem_acc, int row0,
       }
     }
     const int colg = col_tile0 + g * 64;
-    if (p.dbg & 8) continue;                        // measurement only: drain the accumulator, store nothing
+    if (MMT_DBG & 8) continue;                        // measurement only: drain the accumulator, store nothing
     if (colg < p.N && (row_ok || tma_out)) {
 #pragma unroll
       for (int j8 = 0; j8 < 8; ++j8) {
@@ -397,7 +408,7 @@ MMT_DEVICE void epilogue_block(const GemmParams& p, uint32_t tmem_acc, int row0,
       // stores on purpose: a bulk (TMA) store would queue behind the operand loads that the producer warp has
       // already issued for the next tile, and the warp would wait for that queue before it may refill its slab.
       __syncwarp();
-      if (colg < p.N && !(p.dbg & 4)) {
+      if (colg < p.N && !(MMT_DBG & 4)) {
         const int chunk = lane & 7;
         const int col = colg + chunk * 8;
         if (col < p.N) {
@@ -563,7 +574,7 @@ template <int BN>
 MMT_DEVICE void epilogue_any(const GemmParams& p, const OutMaps& tmC, bool remote, uint32_t tmem_acc, int row0,
                              int col_tile0, int q, int half, int lane, uint8_t* slab, uint32_t release_bar,
                              const float* sk_part = nullptr, int sk_n = 0, long sk_stride = 0) {
-  const bool fast = p.alpha == 1.0f && p.act == 0 && !p.accumulate && !p.out_f32 && sk_n == 0 && !(p.dbg & 12);
+  const bool fast = p.alpha == 1.0f && p.act == 0 && !p.accumulate && !p.out_f32 && sk_n == 0 && !(MMT_DBG & 12);
   if (!fast) {
     epilogue_block<BN>(p, tmem_acc, row0, col_tile0, q, half, lane, slab, release_bar, sk_part, sk_n, sk_stride);
   } else if (p.bias) {
@@ -631,7 +642,7 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   const int lane = threadIdx.x & 31;
   long long clk_c0 = 0;
   unsigned long long clk_t0 = 0;
-  if (p.clk && blockIdx.x == 0 && threadIdx.x == 0) {
+  if (MMT_CLK && blockIdx.x == 0 && threadIdx.x == 0) {
     clk_c0 = clock64();
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(clk_t0));
   }
@@ -685,7 +696,7 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           asm volatile("fence.proxy.async;" ::: "memory");
         }
         for (int kb = w.k0; kb < w.k1; ++kb) {
-          if ((p.dbg & 1) && kcount++ >= kStages) continue;
+          if ((MMT_DBG & 1) && kcount++ >= kStages) continue;
           if (!mbar_wait(&empty[s], ph ^ 1, p.ew, 100)) { ok = false; break; }
           uint8_t* sA = smem + (size_t)s * C_::STAGE_BYTES;
           uint8_t* sB = sA + C_::A_BYTES;
@@ -732,7 +743,7 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         tc_fence_after();
         const uint32_t d0 = tmem_base + (uint32_t)((MT == 2 ? 0 : acc) * BN);
         for (int kb = 0; kb < w.k1 - w.k0; ++kb) {      // kb counts from the start of this run: a fresh accumulator
-          const bool skip = (p.dbg & 1) && kcount++ >= kStages;
+          const bool skip = (MMT_DBG & 1) && kcount++ >= kStages;
           if (!ready && !skip && !mbar_wait(&full[s], ph, p.ew, 201)) { ok = false; break; }
           const uint32_t so = (uint32_t)s * (C_::STAGE_BYTES >> 4);
           int sn = s + 1;
@@ -750,7 +761,7 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             }
             if (k == 0) ready = mbar_test(&full[sn], phn);
           }
-          if (!(p.dbg & 2)) tc_commit(&empty[s]);
+          if (!(MMT_DBG & 2)) tc_commit(&empty[s]);
           s = sn;
           ph = phn;
         }
@@ -779,8 +790,8 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     for (int wi = 0; ok && work_item(p, wi, blockIdx.x, gridDim.x, KB, ntiles, w); ++wi) {
       int tm, tn;
       tile_coords(p, w.tile, tiles_m, BMT, tm, tn);
-      const int n_contrib = (w.kind == 2 && !(p.dbg & 32)) ? (int)blockIdx.x - w.first_contrib : 0;
-      if (w.kind == 2 && !(p.dbg & 16)) {
+      const int n_contrib = (w.kind == 2 && !(MMT_DBG & 32)) ? (int)blockIdx.x - w.first_contrib : 0;
+      if (w.kind == 2 && !(MMT_DBG & 16)) {
         // the CTAs that did the first k-blocks of this tile have left their partial sums
         for (int c = w.first_contrib; c < (int)blockIdx.x && ok; ++c)
           ok = flag_wait_ge(&p.sk_flags[c], p.sk_epoch, MMT_WAIT_NS, p.ew, 310);
@@ -796,7 +807,7 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
-        if (w.kind == 1 && (p.dbg & 64)) {       // measurement only: drop the partial sums
+        if (w.kind == 1 && (MMT_DBG & 64)) {       // measurement only: drop the partial sums
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive_cluster(smem_u32(&tempty[slot]));
@@ -833,11 +844,11 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   tc_fence_before();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_base, C_::TMEM_COLS);
-  if (p.clk && blockIdx.x == 0 && threadIdx.x == 0) {
+  if (MMT_CLK && blockIdx.x == 0 && threadIdx.x == 0) {
     unsigned long long t1;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
-    p.clk[0] = (unsigned long long)(clock64() - clk_c0);
-    p.clk[1] = t1 - clk_t0;
+    MMT_CLK[0] = (unsigned long long)(clock64() - clk_c0);
+    MMT_CLK[1] = t1 - clk_t0;
   }
   if (p.rs_rows && threadIdx.x == 0) {
     // last CTA to finish publishes "my partial sums have landed" to every peer
@@ -895,7 +906,7 @@ gemm_bf16_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_con
   const int lane = threadIdx.x & 31;
   long long clk_c0 = 0;
   unsigned long long clk_t0 = 0;
-  if (p.clk && blockIdx.x == 0 && threadIdx.x == 0) {
+  if (MMT_CLK && blockIdx.x == 0 && threadIdx.x == 0) {
     clk_c0 = clock64();
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(clk_t0));
   }
@@ -955,7 +966,7 @@ gemm_bf16_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_con
           asm volatile("fence.proxy.async;" ::: "memory");
         }
         for (int kb = 0; kb < KB; ++kb) {
-          if ((p.dbg & 1) && kcount++ >= kStages) continue;
+          if ((MMT_DBG & 1) && kcount++ >= kStages) continue;
           if (!mbar_wait(&empty[s], ph ^ 1, p.ew, 121)) { ok = false; break; }
           uint8_t* sA = smem + (size_t)s * C_::STAGE_BYTES;
           uint8_t* sB = sA + C_::A_BYTES;
@@ -998,7 +1009,7 @@ gemm_bf16_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_con
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
         for (int kb = 0; kb < KB; ++kb) {
-          const bool skip = (p.dbg & 1) && kcount++ >= kStages;
+          const bool skip = (MMT_DBG & 1) && kcount++ >= kStages;
           if (!ready && !skip && !mbar_wait(&full[s], ph, p.ew, 221)) { ok = false; break; }
           const uint32_t so = (uint32_t)s * (C_::STAGE_BYTES >> 4);
           int sn = s + 1;
@@ -1011,7 +1022,7 @@ gemm_bf16_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_con
             tc_mma_ss_pair(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
             if (k == 0) ready = mbar_test(&full[sn], phn);
           }
-          if (!(p.dbg & 2)) {
+          if (!(MMT_DBG & 2)) {
             tc_commit_pair(empty0 + (uint32_t)s * 8u);     // the stage is free again in both CTAs
             tc_commit_pair(empty1 + (uint32_t)s * 8u);
           }
@@ -1051,11 +1062,11 @@ gemm_bf16_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_con
   __syncthreads();
   cluster_sync_all();          // nobody leaves (or frees tensor memory) while the peer may still touch it
   if (warp == 1) tmem_dealloc_pair(tmem_base, C_::TMEM_COLS);
-  if (p.clk && blockIdx.x == 0 && threadIdx.x == 0) {
+  if (MMT_CLK && blockIdx.x == 0 && threadIdx.x == 0) {
     unsigned long long t1;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
-    p.clk[0] = (unsigned long long)(clock64() - clk_c0);
-    p.clk[1] = t1 - clk_t0;
+    MMT_CLK[0] = (unsigned long long)(clock64() - clk_c0);
+    MMT_CLK[1] = t1 - clk_t0;
   }
   if (p.rs_rows && threadIdx.x == 0) {
     if (atomicAdd(p.rs_counter, 1) == (int)gridDim.x - 1) {
@@ -1232,22 +1243,28 @@ extern "C" void mmt_gemm_force_mt(int mt) { g_force_mt = mt; }
 extern "C" void mmt_gemm_force_bn(int bn) { g_force_bn = bn; }
 // Raster band height in m-tiles (0 = choose, -1 = one band: m-fastest over the whole matrix).
 extern "C" void mmt_gemm_group_m(int g) { g_group_m = g; }
+#ifdef MMT_GEMM_MEASURE
 // Measurement aid: device pointer to two 64-bit words that CTA 0 of every following GEMM fills with the SM
 // cycles and the nanoseconds it spent in the kernel (nullptr = off).  cycles / ns = SM clock in GHz under load.
 extern "C" void mmt_gemm_set_clock_probe(unsigned long long* p) { g_clk = p; }
+#endif
 // Tuning knob: L2 promotion size of the tensor maps (0 none, 1 64 B, 2 128 B, 3 256 B).
 extern "C" void mmt_gemm_set_l2promo(int v) { g_l2promo = v; }
+#ifdef MMT_GEMM_MEASURE
 // Measurement only (results are wrong): see GemmParams::dbg.
 extern "C" void mmt_gemm_set_dbg(int d) { g_dbg = d; }
+#endif
 // Default kernel for M >= 256 and 256-wide tiles: 1 = the 2-CTA kernel, 0 = the 1-CTA kernels.
 extern "C" void mmt_gemm_use_pair(int on) { g_use_pair = on; }
 
+#ifdef MMT_GEMM_MEASURE
 // Bring-up knob: descriptor constants used for MN-major shared-memory tiles.
 extern "C" void mmt_gemm_set_mn_desc(uint32_t lbo, uint32_t sbo, uint32_t kstep) {
   g_mn_lbo = lbo;
   g_mn_sbo = sbo;
   g_mn_kstep = kstep;
 }
+#endif
 
 // Optional collective roles of a GEMM launch (see GemmParams).
 struct MmtGemmComm {
@@ -1349,7 +1366,7 @@ extern "C" int mmt_gemm_bf16(const void* A, const void* B, void* C, const void* 
   p.mn_lbo = g_mn_lbo; p.mn_sbo = g_mn_sbo; p.mn_kstep = g_mn_kstep;
   p.ew = mmt_error_word();
   p.clk = g_clk;
-  p.dbg = g_dbg;
+  p.dbg = g_dbg;  // read through MMT_DBG only
   p.tiles_n = (N + bn - 1) / bn;
   // raster bands of 2048 rows: a wave of CTAs then covers a roughly square block of C, so the A and B tiles it
   // needs are shared by many CTAs while they are in L2
@@ -1375,7 +1392,7 @@ extern "C" int mmt_gemm_bf16(const void* A, const void* B, void* C, const void* 
   p.sk_flags = nullptr;
   p.sk_epoch = 0;
   bool sk_on = false;
-  if (!p.ag_flags && !p.rs_rows && mt != 3 && !(p.dbg & 1)) {
+  if (!p.ag_flags && !p.rs_rows && mt != 3 && !(MMT_DBG & 1)) {
     const int tiles = ((M + bmt - 1) / bmt) * ((N + bn - 1) / bn);
     const int skt = sk_tiles_for(tiles, (K + BK - 1) / BK, sms, mt);
     if (skt > 0 && sk_ready()) {

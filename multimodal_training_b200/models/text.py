@@ -25,20 +25,38 @@ from ..utils.checkpointing import bucket_tokens, checkpoint
 from ..utils.checkpointing import decide as decide_ckpt
 
 
-def mrope_cos_sin(position_ids: torch.Tensor, head_dim: int, theta: float, mrope_section: list[int]):
+_MROPE_CACHE: dict = {}
+
+
+def mrope_cos_sin(position_ids: torch.Tensor, head_dim: int, theta: float, mrope_section: list[int], device=None):
     """cos/sin [T, head_dim] fp32 from 3-axis position ids [3, T].
 
     The doubled section list picks axis ``i mod 3`` for chunk i of the rotary dims
-    (modeling_qwen2_5_vl.py:1123-1133,1185-1187).
+    (modeling_qwen2_5_vl.py:1123-1133,1185-1187).  With ``device`` the tables are built there from the position ids
+    (one small host->device copy instead of two [T, head_dim] fp32 tables) and kept for batches with the same
+    positions, which is every step of a fixed-shape run.
     """
-    inv_freq = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float32) / head_dim))
-    pos = position_ids.to(torch.float32).cpu()
+    dev = torch.device(device) if device is not None else position_ids.device
+    key = None
+    if dev.type == "cuda":
+        key = (hash(position_ids.cpu().numpy().tobytes()), tuple(position_ids.shape), head_dim, float(theta),
+               tuple(mrope_section), str(dev))
+        hit = _MROPE_CACHE.get(key)
+        if hit is not None:
+            return hit
+    inv_freq = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float32, device=dev) / head_dim))
+    pos = position_ids.to(dev, non_blocking=True).to(torch.float32)
     freqs = pos[:, :, None] * inv_freq[None, None, :]            # [3, T, d/2]
     emb = torch.cat((freqs, freqs), dim=-1)                      # [3, T, d]
     sections = list(mrope_section) * 2
     chunks = emb.split(sections, dim=-1)
     sel = torch.cat([c[i % 3] for i, c in enumerate(chunks)], dim=-1)  # [T, d]
-    return sel.cos().contiguous(), sel.sin().contiguous()
+    out = (sel.cos().contiguous(), sel.sin().contiguous())
+    if key is not None:
+        if len(_MROPE_CACHE) >= 16:
+            _MROPE_CACHE.pop(next(iter(_MROPE_CACHE)))
+        _MROPE_CACHE[key] = out
+    return out
 
 
 class TextDecoder(nn.Module):
@@ -48,6 +66,7 @@ class TextDecoder(nn.Module):
         self.cfg = cfg
         self.tp = tp or TPContext.single()
         self.ckpt = activation_checkpointing
+        self.tp_block = True          # one autograd node per tensor-parallel layer on the fused paths (GPU)
         tpn, tpr = self.tp.size, self.tp.rank
         H, I, d = cfg.hidden_size, cfg.intermediate_size, cfg.head_dim
         if cfg.num_key_value_heads % tpn or cfg.num_attention_heads % tpn:
@@ -154,6 +173,19 @@ class TextDecoder(nn.Module):
                 x = blocks.local_block(x, spec, cos, sin, seq, (L.ln1_w, L.qkv_w, L.qkv_b, L.o_w, None, L.ln2_w,
                                                                 L.gate_up_w, None, L.down_w, None), recompute=ckpt,
                                        keep_elementwise=keep_ew)
+            return x
+        if (self.tp.size > 1 and self.tp.fused is not None and self.tp_block and torch.is_grad_enabled()
+                and blocks.usable(x) and attn_mod.BACKEND == "sm100"):
+            # tensor-parallel layers over the fused peer-memory paths: one autograd node per layer as well
+            # (ops/tp_blocks.py); the per-op graph below stays for NCCL collectives, the CPU and as the oracle
+            from ..ops import tp_blocks
+            d = self.cfg.head_dim
+            spec = blocks.BlockSpec(n_q=self.n_q, n_kv=self.n_kv, head_dim=d, rope_heads=self.n_q + self.n_kv,
+                                    causal=True, eps=self.cfg.rms_norm_eps, scale=1.0 / math.sqrt(d))
+            for L in self.layers:
+                x = tp_blocks.tp_block(x, spec, cos, sin, seq, self.tp.fused,
+                                       (L.ln1_w, L.qkv_w, L.qkv_b, L.o_w, L.ln2_w, L.gate_up_w, L.down_w),
+                                       recompute=ckpt)
             return x
         for L in self.layers:
             x = checkpoint(lambda t, L=L: self._layer(t, L, cos, sin, seq), (x,), enabled=ckpt)

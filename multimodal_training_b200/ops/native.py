@@ -25,7 +25,6 @@ _SIGS = {
     "mmt_get_error": (c_int, [_P]),
     "mmt_clear_error": (c_int, []),
     "mmt_error_word_address": (c_void_p, []),
-    "mmt_gemm_set_mn_desc": (None, [c_uint32, c_uint32, c_uint32]),
     "mmt_gemm_bf16": (c_int, [_P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                               c_int, c_int, c_int, c_float, c_int, _P]),
     "mmt_rmsnorm_fwd": (c_int, [_P, _P, _P, _P, c_long, c_int, c_float, _P]),

@@ -31,6 +31,7 @@ class TextTrainer(Trainer):
         tp = TPContext(mesh.tp_group, mesh.tp, mesh.tp_rank, fused=self.state.fused)
         self.model = TextDecoder(cfg.text, tp, dtype=dt, device=dev, seed=self.seed,
                                  activation_checkpointing=self.config.get("activation_checkpointing", True))
+        self.model.tp_block = bool(self.config.get("tp_block", True))
         pre = self.config.get("pretrained_checkpoint_dir")
         if pre:
             self._load_pretrained(pre)
@@ -69,6 +70,14 @@ class TextTrainer(Trainer):
                     raise RuntimeError(f"vision output is for iteration {vision_out['iteration']}, "
                                        f"text step is {iteration}")
                 vis = vision_out["vision_embeddings"]
+                # the vision half must have encoded exactly the samples that this step's context assigns to its
+                # replica (same guard as the reference's sample-index check, python/ray/text.py:794-807; there both
+                # halves see the whole batch, here the vision replica's share is the expected list)
+                got = vision_out.get("sample_index")
+                want = [ctx.samples[i].sample_index for i in ctx.vision_samples]
+                if got is not None and list(got) != want:
+                    raise RuntimeError(f"vision output covers samples {list(got)[:8]}..., this step expects "
+                                       f"{want[:8]}... (the halves are out of step)")
             else:
                 vis = vision_out
         # ---- guards (host metadata only, no device sync)
@@ -98,8 +107,8 @@ class TextTrainer(Trainer):
             else:
                 recv = exchange_vision_rows(leaf, plan, mesh)
                 x = splice_rows(x, recv, plan.recv_rows.to(dev))
-        cos, sin = mrope_cos_sin(tb.position_ids, cfg.text.head_dim, cfg.text.rope_theta, cfg.text.mrope_section)
-        cos, sin = cos.to(dev, non_blocking=True), sin.to(dev, non_blocking=True)
+        cos, sin = mrope_cos_sin(tb.position_ids, cfg.text.head_dim, cfg.text.rope_theta, cfg.text.mrope_section,
+                                 device=dev)
         seq = SeqInfo.from_list(tb.cu_seqlens, dev)
         h = self.model(x, cos, sin, seq)
         loss = self.model.loss(h, labels, chunk_rows=int(self.config.get("ce_chunk_rows", 4096)),

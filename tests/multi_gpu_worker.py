@@ -12,7 +12,8 @@ import torch  # noqa: E402
 import torch.distributed as dist  # noqa: E402
 
 
-def run(fused: bool, steps: int, vision: str = "sequence", ragged: bool = False):
+def run(fused: bool, steps: int, vision: str = "sequence", ragged: bool = False, tp_block: bool = True,
+        ckpt: str = "true"):
     from multimodal_training_b200.config.loader import load_config
     from multimodal_training_b200.engine import HybridEngine
     from multimodal_training_b200.ops import native as nv
@@ -25,7 +26,8 @@ def run(fused: bool, steps: int, vision: str = "sequence", ragged: bool = False)
         "training.learning_rate=1e-3", "training.warmup_ratio=0", "training.warmup_steps=0",
         "training.lr_scheduler_type=constant", "+data.synthetic.image_size=448", "+data.synthetic.text_tokens=256",
         f"+data.synthetic.global_batch={2 * (world // min(world, 2))}", "+data.synthetic.repeat=1",
-        f"training.fused_comm={'true' if fused else 'false'}"]
+        f"training.fused_comm={'true' if fused else 'false'}", f"+training.tp_block={'true' if tp_block else 'false'}",
+        f"vision.activation_checkpointing={ckpt}", f"text.activation_checkpointing={ckpt}"]
         # images of three sizes and texts of three lengths, new ones every step: ragged sequence-parallel splits
         # (81 and 225 merged tokens do not divide by 2) and heap regions that have to grow after the first step
         + (["+data.synthetic.image_sizes=252,448,420", "+data.synthetic.text_token_choices=96,256,40",
@@ -47,10 +49,12 @@ def main():
     fused = run(True, 4)
     lib = run(False, 4)
     vtp = run(False, 4, vision="tensor")          # tensor-parallel vision encoder (all-reduce per block)
+    per_op = run(True, 4, tp_block=False)         # fused exchanges through the per-op autograd graph
+    keep = run(True, 4, ckpt="false")             # one-node layers that keep their activations
     rag_fused = run(True, 6, ragged=True)
     rag_lib = run(False, 6, ragged=True)
     if dist.get_rank() == 0:
-        print("RESULT " + json.dumps({"fused": fused, "lib": lib, "vision_tp": vtp, "ragged_fused": rag_fused,
+        print("RESULT " + json.dumps({"fused": fused, "lib": lib, "vision_tp": vtp, "fused_per_op": per_op, "fused_keep": keep, "ragged_fused": rag_fused,
                                       "ragged_lib": rag_lib}))
     dist.barrier()
     dist.destroy_process_group()
