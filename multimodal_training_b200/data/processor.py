@@ -10,6 +10,8 @@ run needs nothing but a tokenizer:
 * :class:`Qwen2_5_VLImageProcessor` -- bicubic resize, scale to [0,1], normalise, cut into
   ``[N, 3 * 2 * 14 * 14]`` patch rows in the order the vision encoder expects (2x2 merge blocks contiguous,
   the single frame repeated to fill the temporal patch), plus ``image_grid_thw``;
+* videos: a clip (frames array or list of frames) becomes ``ceil(F / 2)`` temporal patches of the same patch
+  layout, ``video_grid_thw`` and ``second_per_grid_ts``; ``<|video_pad|>`` expands like ``<|image_pad|>``;
 * :class:`Qwen2_5_VLProcessor` -- replaces every ``<|image_pad|>`` by one placeholder per merged vision token
   (``grid.prod() // merge**2``, processing_qwen2_5_vl.py:178-186), tokenises, and renders Qwen's chat template
   (``apply_chat_template``) for LLaVA-style messages;
@@ -26,6 +28,7 @@ import torch
 IMAGE_MEAN = (0.48145466, 0.4578275, 0.40821073)
 IMAGE_STD = (0.26862954, 0.26130258, 0.27577711)
 IMAGE_PAD, VISION_START, VISION_END = "<|image_pad|>", "<|vision_start|>", "<|vision_end|>"
+VIDEO_PAD = "<|video_pad|>"
 IM_START, IM_END = "<|im_start|>", "<|im_end|>"
 
 
@@ -86,6 +89,44 @@ class Qwen2_5_VLImageProcessor:
         # [T, C, gh/m, m, P, gw/m, m, P] -> [gh/m, gw/m, m, m, C, T, P, P]: merge blocks contiguous
         t = frames.reshape(T, 3, gh // m, m, P, gw // m, m, P).permute(2, 5, 3, 6, 1, 0, 4, 7)
         return t.reshape(gh * gw, 3 * T * P * P).contiguous(), (1, gh, gw)
+
+    def preprocess_video(self, frames, min_pixels=None, max_pixels=None):
+        """A clip as [F, H, W, 3] array / tensor or a list of frames -> patch rows [t * gh * gw, 3 * T * P * P] with
+        ``t = ceil(F / T)`` temporal patches (the last frame is repeated to fill the last one) and its grid."""
+        if isinstance(frames, (str, bytes)):
+            # no video decoder ships with this package: clips arrive as decoded frames
+            raise NotImplementedError(f"video '{frames}': pass the decoded frames ([F, H, W, 3] array or a list of "
+                                      "frames); decoding container files is left to the caller")
+        if isinstance(frames, (torch.Tensor, np.ndarray)) and getattr(frames, "ndim", 0) == 4:
+            frames = [frames[i] for i in range(frames.shape[0])]
+        xs = [_to_chw_float(f) for f in frames]
+        if not xs:
+            raise ValueError("a video needs at least one frame")
+        H, W = xs[0].shape[1:]
+        f = self.patch_size * self.merge_size
+        h, w = smart_resize(H, W, f, min_pixels or self.min_pixels, max_pixels or self.max_pixels)
+        x = torch.stack([v.expand(3, -1, -1) if v.shape[0] == 1 else v for v in xs])       # [F, 3, H, W]
+        if (h, w) != (H, W):
+            x = torch.nn.functional.interpolate(x, size=(h, w), mode="bicubic", align_corners=False,
+                                                antialias=True).clamp(0, 1)
+        x = (x - self.mean) / self.std
+        P, T, m = self.patch_size, self.temporal_patch_size, self.merge_size
+        if x.shape[0] % T:
+            x = torch.cat([x, x[-1:].expand(T - x.shape[0] % T, -1, -1, -1)])
+        t, gh, gw = x.shape[0] // T, h // P, w // P
+        # [t, T, C, gh/m, m, P, gw/m, m, P] -> [t, gh/m, gw/m, m, m, C, T, P, P]
+        r = x.reshape(t, T, 3, gh // m, m, P, gw // m, m, P).permute(0, 3, 6, 4, 7, 2, 1, 5, 8)
+        return r.reshape(t * gh * gw, 3 * T * P * P).contiguous(), (t, gh, gw)
+
+    def videos(self, videos, fps: float = 2.0, min_pixels=None, max_pixels=None):
+        rows, grids = [], []
+        for v in videos:
+            r, g = self.preprocess_video(v, min_pixels, max_pixels)
+            rows.append(r)
+            grids.append(g)
+        return {"pixel_values_videos": torch.cat(rows),
+                "video_grid_thw": torch.tensor(grids, dtype=torch.long).reshape(-1, 3),
+                "second_per_grid_ts": [self.temporal_patch_size / float(fps)] * len(grids)}
 
     def __call__(self, images, min_pixels=None, max_pixels=None, **_):
         images = images if isinstance(images, (list, tuple)) else [images]
@@ -179,8 +220,10 @@ class Qwen2_5_VLProcessor:
 
     # ------------------------------------------------------------------ chat template
     def render(self, messages: list[dict], add_generation_prompt: bool = False) -> tuple[str, list]:
-        """Qwen chat format; returns the text (one ``<|image_pad|>`` per image) and the images in order."""
+        """Qwen chat format; returns the text (one ``<|image_pad|>`` per image, one ``<|video_pad|>`` per video), the
+        images in order and, as ``self.last_videos``, the videos in order."""
         parts, images = [], []
+        self.last_videos = []
         if not messages or messages[0].get("role") != "system":
             parts.append(f"{IM_START}system\nYou are a helpful assistant.{IM_END}\n")
         for msg in messages:
@@ -196,9 +239,8 @@ class Qwen2_5_VLProcessor:
                     elif item.get("type") == "text":
                         body.append(item["text"])
                     elif item.get("type") == "video":
-                        # the training pipeline is image-only, like the reference's (its M-RoPE ids cover images:
-                        # python/data/rope_utils.py); dropping the clip silently would train on a wrong prompt
-                        raise NotImplementedError("video content is not supported by the in-tree processor")
+                        self.last_videos.append(item.get("video"))
+                        body.append(f"{VISION_START}{VIDEO_PAD}{VISION_END}")
             parts.append(f"{IM_START}{msg['role']}\n{''.join(body)}{IM_END}\n")
         if add_generation_prompt:
             parts.append(f"{IM_START}assistant\n")
@@ -209,19 +251,24 @@ class Qwen2_5_VLProcessor:
         text, images = self.render(messages, add_generation_prompt)
         if not tokenize:
             return text
-        return self(text=[text], images=images or None, return_tensors=return_tensors, **image_kw)
+        return self(text=[text], images=images or None, videos=self.last_videos or None,
+                    return_tensors=return_tensors, **image_kw)
 
     # ------------------------------------------------------------------ text + images -> model inputs
-    def __call__(self, text=None, images=None, return_tensors=None, **image_kw):
+    def __call__(self, text=None, images=None, videos=None, return_tensors=None, fps: float = 2.0, **image_kw):
         texts = [text] if isinstance(text, str) else list(text or [])
         out = {}
-        grids = []
+        grids, vgrids = [], []
         if images is not None and len(images):
             img = self.image_processor(images, **image_kw)
             out.update(img)
             grids = img["image_grid_thw"].tolist()
+        if videos is not None and len(videos):
+            vid = self.image_processor.videos(videos, fps=fps, **image_kw)
+            out.update(vid)
+            vgrids = vid["video_grid_thw"].tolist()
         unit = self.image_processor.merge_size ** 2
-        k = 0
+        k = kv = 0
         expanded = []
         for t in texts:
             while IMAGE_PAD in t:
@@ -230,9 +277,18 @@ class Qwen2_5_VLProcessor:
                 n = int(np.prod(grids[k])) // unit
                 t = t.replace(IMAGE_PAD, "<|placeholder|>" * n, 1)
                 k += 1
-            expanded.append(t.replace("<|placeholder|>", IMAGE_PAD))
+            t = t.replace("<|placeholder|>", IMAGE_PAD)
+            while VIDEO_PAD in t:
+                if kv >= len(vgrids):
+                    raise ValueError("more <|video_pad|> placeholders than videos")
+                n = int(np.prod(vgrids[kv])) // unit
+                t = t.replace(VIDEO_PAD, "<|placeholder|>" * n, 1)
+                kv += 1
+            expanded.append(t.replace("<|placeholder|>", VIDEO_PAD))
         if k != len(grids):
             raise ValueError(f"{len(grids)} images but {k} <|image_pad|> placeholders")
+        if kv != len(vgrids):
+            raise ValueError(f"{len(vgrids)} videos but {kv} <|video_pad|> placeholders")
         enc = self.tokenizer(expanded)
         ids = enc["input_ids"]
         if return_tensors == "pt":

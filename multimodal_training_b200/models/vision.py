@@ -351,10 +351,13 @@ def prepare_plan(plan: VisionPlan, device) -> VisionPlan:
     plan.sin_dev = plan.local_sin.to(device, non_blocking=True)
     plan.win_seq = SeqInfo.from_list(plan.win_cu, device)
     plan.full_seq = SeqInfo.from_list(plan.full_cu, device)
-    cu = [0]
-    for _, n in plan.per_image_local:
-        if n:
-            cu.append(cu[-1] + n)
+    if plan.sp == 1:
+        cu = list(plan.full_cu)            # whole images are local: one sequence per temporal patch
+    else:
+        cu = [0]
+        for _, n in plan.per_image_local:
+            if n:
+                cu.append(cu[-1] + n)
     plan.local_image_seq = SeqInfo.from_list(cu, device)
     if plan.to_image_major is not None:
         plan.to_image_major_dev = plan.to_image_major.to(device, non_blocking=True)

@@ -50,11 +50,19 @@ class Qwen2_5_VLModel(nn.Module):
         out = torch.empty_like(merged)
         return out.index_copy(0, plan.local_merged_ids.to(dev), merged)
 
-    def get_rope_index(self, input_ids: torch.Tensor, image_grid_thw, attention_mask=None):
-        return get_rope_index_for_images(self.config.vision.spatial_merge_size, input_ids.cpu(), image_grid_thw,
-                                         None if attention_mask is None else attention_mask.cpu(),
-                                         image_token_id=self.config.image_token_id,
-                                         vision_start_token_id=self.config.vision_start_token_id)
+    def get_rope_index(self, input_ids: torch.Tensor, image_grid_thw, attention_mask=None, video_grid_thw=None,
+                       second_per_grid_ts=None):
+        """3-axis M-RoPE ids for images and videos (modeling_qwen2_5_vl.py:1561-1741 in the reference)."""
+        if video_grid_thw is None or len(video_grid_thw) == 0:
+            return get_rope_index_for_images(self.config.vision.spatial_merge_size, input_ids.cpu(), image_grid_thw,
+                                             None if attention_mask is None else attention_mask.cpu(),
+                                             image_token_id=self.config.image_token_id,
+                                             vision_start_token_id=self.config.vision_start_token_id)
+        from ..data.rope_utils import get_rope_index
+        return get_rope_index(self.config.vision.spatial_merge_size, input_ids.cpu(), image_grid_thw, video_grid_thw,
+                              second_per_grid_ts, None if attention_mask is None else attention_mask.cpu(),
+                              image_token_id=self.config.image_token_id, video_token_id=self.config.video_token_id,
+                              vision_start_token_id=self.config.vision_start_token_id)
 
     def _pack(self, input_ids: torch.Tensor, attention_mask):
         """[B, S] (right padded) -> packed ids [T], cu_seqlens, and the per-sample keep masks."""
@@ -69,7 +77,8 @@ class Qwen2_5_VLModel(nn.Module):
             cu.append(cu[-1] + int(n))
         return input_ids[keep], cu, keep
 
-    def hidden_states(self, input_ids, pixel_values=None, image_grid_thw=None, attention_mask=None):
+    def hidden_states(self, input_ids, pixel_values=None, image_grid_thw=None, attention_mask=None,
+                      pixel_values_videos=None, video_grid_thw=None, second_per_grid_ts=None):
         """Packed final hidden states [T, H] (before the last norm), cu_seqlens and the keep mask."""
         cfg = self.config
         ids, cu, keep = self._pack(input_ids, attention_mask)
@@ -81,16 +90,24 @@ class Qwen2_5_VLModel(nn.Module):
             if rows.numel() != vis.shape[0]:
                 raise ValueError(f"{rows.numel()} image placeholder tokens but {vis.shape[0]} merged vision tokens")
             x = x.index_copy(0, rows, vis)
-        pos, _ = self.get_rope_index(input_ids if input_ids.dim() == 2 else input_ids.unsqueeze(0), image_grid_thw,
-                                     attention_mask)
+        if pixel_values_videos is not None and video_grid_thw is not None and len(video_grid_thw):
+            vid = self.encode_images(pixel_values_videos.to(dev), video_grid_thw).to(x.dtype)
+            rows = (ids == cfg.video_token_id).nonzero().flatten().to(dev)
+            if rows.numel() != vid.shape[0]:
+                raise ValueError(f"{rows.numel()} video placeholder tokens but {vid.shape[0]} merged video tokens")
+            x = x.index_copy(0, rows, vid)
+        pos, _ = self.get_rope_index(input_ids if input_ids.dim() == 2 else input_ids.unsqueeze(0),
+                                     image_grid_thw if image_grid_thw is not None else [], attention_mask,
+                                     video_grid_thw, second_per_grid_ts)
         pos = pos[:, keep.cpu()]                                    # [3, T]
         cos, sin = mrope_cos_sin(pos, cfg.text.head_dim, cfg.text.rope_theta, cfg.text.mrope_section)
         h = self.language_model(x, cos.to(dev), sin.to(dev), SeqInfo.from_list(cu, dev))
         return h, cu, keep
 
-    def forward(self, input_ids, pixel_values=None, image_grid_thw=None, attention_mask=None):
-        """Logits of every kept token, packed: [T, vocab]."""
-        h, _, _ = self.hidden_states(input_ids, pixel_values, image_grid_thw, attention_mask)
+    def forward(self, input_ids, pixel_values=None, image_grid_thw=None, attention_mask=None, **video_kw):
+        """Logits of every kept token, packed: [T, vocab].  ``video_kw``: ``pixel_values_videos``, ``video_grid_thw``,
+        ``second_per_grid_ts`` as the processor returns them."""
+        h, _, _ = self.hidden_states(input_ids, pixel_values, image_grid_thw, attention_mask, **video_kw)
         return self.language_model.logits(h)
 
 
@@ -100,9 +117,10 @@ class Qwen2_5_VLForConditionalGeneration(nn.Module):
         self.model = Qwen2_5_VLModel(config, **kw)
         self.config = self.model.config
 
-    def forward(self, input_ids, pixel_values=None, image_grid_thw=None, attention_mask=None, labels=None):
+    def forward(self, input_ids, pixel_values=None, image_grid_thw=None, attention_mask=None, labels=None,
+                **video_kw):
         """Returns ``{"logits": [T, V]}`` and, with labels [B, S], ``"loss"`` (next-token CE, -100 ignored)."""
-        h, cu, keep = self.model.hidden_states(input_ids, pixel_values, image_grid_thw, attention_mask)
+        h, cu, keep = self.model.hidden_states(input_ids, pixel_values, image_grid_thw, attention_mask, **video_kw)
         out = {"logits": self.model.language_model.logits(h)}
         if labels is not None:
             if labels.dim() == 1:

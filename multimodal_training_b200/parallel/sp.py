@@ -263,9 +263,12 @@ def _build_vision_plan(geom: Geometry, sp: int, rank: int, head_dim: int) -> Vis
 
     # exchange order for full attention: rows arrive as (rank s, image b); attention needs (image b, rank s)
     to_img = to_rank = None
+    # one attention sequence per temporal patch of every image / video (a still image has one): window order keeps
+    # the patches of a temporal patch contiguous (modeling_qwen2_5_vl.py:944-952 builds cu_seqlens the same way)
     full_cu = [0]
-    for b in range(len(grid_thw)):
-        full_cu.append(full_cu[-1] + (img_start[b + 1] - img_start[b]))
+    for (t, h, w) in grid_thw:
+        for _ in range(t):
+            full_cu.append(full_cu[-1] + h * w)
     if sp > 1:
         rank_off = [0]
         for r in range(sp):

@@ -64,9 +64,11 @@ def test_llava_sample_through_chat_template_masks_everything_but_the_answer():
     assert enc["pixel_values"].shape[0] == int(enc["image_grid_thw"].prod())
 
 
-def test_video_content_is_refused_not_dropped():
+def test_an_undecoded_video_file_is_refused_not_dropped():
+    """Clips are accepted as decoded frames (tests/test_video_inputs.py); a path to a container file is refused with
+    a message instead of being dropped from the prompt."""
     import pytest
     from multimodal_training_b200.data.processor import Qwen2_5_VLProcessor
-    with pytest.raises(NotImplementedError):
+    with pytest.raises(NotImplementedError, match="decoded frames"):
         Qwen2_5_VLProcessor().apply_chat_template([{"role": "user", "content": [{"type": "video", "video": "clip.mp4"},
                                                                                 {"type": "text", "text": "What happens?"}]}])
