@@ -991,6 +991,9 @@ gemm_bf16_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_con
   } else if (warp == 1) {
     // ------------------------------ MMA issuer (leader CTA only) ------------------------------
     if (lane == 0 && leader) {
+      // One 256 x 256 MMA per k-step.  (Splitting it into two 256 x 128 MMAs on alternating accumulators, to avoid
+      // back-to-back MMAs into one accumulator, was measured and is slower: at N = 128 every CTA reads as many operand
+      // bytes per MMA cycle -- its A rows, its own B rows and the partner's -- as shared memory delivers.)
       const uint32_t idesc = make_idesc_bf16(BMT, BN, p.a_mn, p.b_mn);
       const uint32_t a_hi = smem_desc_hi(p.a_mn ? p.mn_sbo : 1024u), b_hi = smem_desc_hi(p.b_mn ? p.mn_sbo : 1024u);
       const uint32_t a_lo0 = smem_desc_lo(smem_u32(smem), p.a_mn ? p.mn_lbo : 16u);

@@ -39,6 +39,40 @@ def test_gemm_layouts(M, N, K, layout):
     assert nv.get_error()[0] == 0
 
 
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (304, 520, 328), (1000, 1176, 1176), (2048, 3584, 3584),
+                                   (4096, 1288, 1280)])
+@pytest.mark.parametrize("layout", ["kk", "k_mn", "mn_mn"])
+@pytest.mark.parametrize("mt,bn", [(3, 256), (2, 192), (2, 256), (1, 192)])
+def test_gemm_tile_variants(M, N, K, layout, mt, bn):
+    """Every tile variant forced by hand -- the 2-CTA kernel (mt 3: two interleaved 128-wide accumulators per tile),
+    256-row tiles at width 192 and 256, 128-row tiles at width 192 -- in all three operand layouts, with tails in M,
+    N and K, bias and residual in the epilogue, against an fp32 PyTorch product."""
+    F, nv = _F()
+    lib = nv.lib()
+    torch.manual_seed(M + N + K)
+    a_mn = layout == "mn_mn"
+    if a_mn:
+        M = (M + 7) // 8 * 8
+    A = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    B = torch.randn(N, K, device=DEV, dtype=torch.bfloat16) * 0.05
+    bias = torch.randn(N, device=DEV, dtype=torch.bfloat16)
+    res = torch.randn(M, N, device=DEV, dtype=torch.bfloat16)
+    ref = A.float() @ B.float().t()
+    b_mn = layout != "kk"
+    try:
+        lib.mmt_gemm_force_mt(mt)
+        lib.mmt_gemm_force_bn(bn)
+        Aa, Bb = (A.t().contiguous() if a_mn else A), (B.t().contiguous() if b_mn else B)
+        out = F.gemm(Aa, Bb, a_mn=a_mn, b_mn=b_mn)
+        out2 = F.gemm(Aa, Bb, a_mn=a_mn, b_mn=b_mn, bias=bias, residual=res)
+    finally:
+        lib.mmt_gemm_force_mt(0)
+        lib.mmt_gemm_force_bn(0)
+    assert rel_err(out, ref) < 8e-3
+    assert rel_err(out2, ref + bias.float() + res.float()) < 8e-3
+    assert nv.get_error()[0] == 0
+
+
 def test_gemm_epilogue_bias_residual_accumulate_f32():
     F, nv = _F()
     torch.manual_seed(1)
