@@ -47,7 +47,9 @@ constexpr int BK = 64;            // 64 bf16 = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
 constexpr int kEpiWarps = 8;
 constexpr uint32_t kSlabBytes = 32 * 64 * 2;   // one epilogue warp's [32 x 64] bf16 staging slab
-constexpr int kThreads = 64 + kEpiWarps * 32;   // TMA warp, MMA warp, eight epilogue warps
+constexpr int kPushWarps = 2;                  // warps 10, 11: producer side of an all-gather fused into the GEMM
+constexpr int kThreads = 64 + kEpiWarps * 32 + kPushWarps * 32;   // TMA warp, MMA warp, eight epilogue warps, two push warps
+constexpr int kAgChunks = 64;                  // chunk flags per source rank of a fused all-gather
 
 struct GemmParams {
   int M, N, K;
@@ -80,6 +82,21 @@ struct GemmParams {
   //     are complete once ag_flags[s] >= ag_epoch; this rank's own rows need no wait.  ag_flags == nullptr: off.
   const int* ag_flags;
   int ag_epoch, ag_rows, ag_self;
+  // --- all-gather PRODUCER inside the same kernel (agp_src != nullptr): before their first tile is ready the
+  //     epilogue warps of all CTAs (RMS-normalise and) store this rank's agp_rows rows of agp_src [agp_rows, K] into
+  //     every peer's gathered buffer agp_dst[p] at rows ag_self * ag_rows + r, one warp per row, rows interleaved over
+  //     the CTAs so that the first chunks complete first.  Per chunk of ag_chunk rows a counter collects the finished
+  //     rows; the warp that completes a chunk publishes ag_epoch to flag word [ag_self * kAgChunks + chunk] on every
+  //     peer (agp_flag[p]).  The consumer side then waits per (source rank, chunk) on ag_flags, own rows included.
+  const __nv_bfloat16* agp_src;
+  const __nv_bfloat16* agp_w;       // RMSNorm weight [K] or nullptr (plain copy)
+  float* agp_rstd;                  // [agp_rows] out, or nullptr
+  float agp_eps;
+  unsigned long long agp_dst[8];
+  int* agp_flag[8];
+  int* agp_counter;                 // [kAgChunks] ints, zero between launches
+  int agp_rows, agp_peers, ag_chunk;
+  int agp_only;                     // push this rank's rows and return (no tiles): single-GPU emulation of a peer
   // --- reduce-scatter producer: row r of C belongs to rank r / rs_rows and is stored to that rank's staging
   //     slot `rs_self` ([rs_self*rs_rows + r % rs_rows, :] at rs_base[owner]); when the whole GEMM is done,
   //     rs_flag[p] on every peer receives rs_epoch.  rs_rows == 0: off.
@@ -621,6 +638,112 @@ MMT_DEVICE void epilogue_partial(uint32_t tmem_acc, float* dst, int q, int half,
 
 MMT_DEVICE void epi_bar_sync() { asm volatile("bar.sync 2, 256;" ::: "memory"); }
 
+// Producer half of the fused all-gather (see GemmParams::agp_src), run by the two push warps of every CTA from kernel
+// start until all rows of this rank are out.  Nothing here waits for a peer, so every rank's rows reach the others
+// whatever those are doing, and nothing here delays the epilogue warps.  A row goes to THIS rank's buffer first and
+// counts towards the local chunk flag after a device-scope fence (the rank's own tiles can start within
+// microseconds); the stores to the peers follow, and their chunk flags are raised after a system-scope fence, i.e.
+// once the data has crossed NVLink.  Two rows share one system fence (the fence waits for a round trip).
+MMT_DEVICE void ag_store_row(const GemmParams& p, int r, int lane) {
+  const int nvec = p.K >> 3;
+  const long ld = p.K;
+  const __nv_bfloat16* src = p.agp_src + (long)r * ld;
+  const long dst_row = ((long)p.ag_self * p.ag_rows + r) * ld;
+  float rstd = 1.f;
+  if (p.agp_w) {
+    float ss = 0.f;
+    for (int c = lane; c < nvec; c += 32) {
+      const uint4 u = *reinterpret_cast<const uint4*>(src + c * 8);
+      const uint32_t w4[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = unpack_bf16x2(w4[j]);
+        ss += f.x * f.x + f.y * f.y;
+      }
+    }
+    ss = warp_sum(ss);
+    rstd = rsqrtf(ss / (float)p.K + p.agp_eps);
+    if (lane == 0 && p.agp_rstd) p.agp_rstd[r] = rstd;
+  }
+  __nv_bfloat16* local = reinterpret_cast<__nv_bfloat16*>(p.agp_dst[p.ag_self]) + dst_row;
+  for (int c = lane; c < nvec; c += 32) {
+    uint4 u = *reinterpret_cast<const uint4*>(src + c * 8);
+    if (p.agp_w) {
+      const uint4 wv = __ldg(reinterpret_cast<const uint4*>(p.agp_w + c * 8));
+      const uint32_t x4[4] = {u.x, u.y, u.z, u.w}, w4[4] = {wv.x, wv.y, wv.z, wv.w};
+      uint32_t o4[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 a = unpack_bf16x2(x4[j]), b = unpack_bf16x2(w4[j]);
+        o4[j] = pack_bf16x2(a.x * rstd * b.x, a.y * rstd * b.y);
+      }
+      u = make_uint4(o4[0], o4[1], o4[2], o4[3]);
+    }
+    *reinterpret_cast<uint4*>(local + c * 8) = u;
+    for (int q = 0; q < p.agp_peers; ++q)
+      if (q != p.ag_self) *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.agp_dst[q]) + dst_row + c * 8) = u;
+  }
+}
+
+// Counts row r into its chunk (counter set `set`: 0 = stored locally, 1 = stored to the peers); the warp that
+// completes a chunk raises the chunk's flag on this rank (set 0) or on every peer (set 1).
+MMT_DEVICE void ag_count_row(const GemmParams& p, int r, int set) {
+  const int chunk = r / p.ag_chunk;
+  const int in_chunk = min(p.ag_chunk, p.agp_rows - chunk * p.ag_chunk);
+  int* counter = p.agp_counter + set * kAgChunks + chunk;
+  if (atomicAdd(counter, 1) == in_chunk - 1) {
+    *counter = 0;
+    if (set == 0) {
+      __threadfence();
+      flag_store_release_sys(p.agp_flag[p.ag_self] + p.ag_self * kAgChunks + chunk, p.ag_epoch);
+    } else {
+      __threadfence_system();
+      for (int q = 0; q < p.agp_peers; ++q)
+        if (q != p.ag_self) flag_store_release_sys(p.agp_flag[q] + p.ag_self * kAgChunks + chunk, p.ag_epoch);
+    }
+  }
+}
+
+MMT_DEVICE void ag_push_rows(const GemmParams& p, int push_warp, int lane) {
+  const int step = (int)gridDim.x * kPushWarps;
+  for (int r = (int)blockIdx.x * kPushWarps + push_warp; r < p.agp_rows; r += 2 * step) {
+    const int r2 = r + step;
+    ag_store_row(p, r, lane);
+    if (r2 < p.agp_rows) ag_store_row(p, r2, lane);
+    __threadfence();                     // device scope: this rank's copies are readable by its own TMA loads
+    __syncwarp();
+    if (lane == 0) {
+      ag_count_row(p, r, 0);
+      if (r2 < p.agp_rows) ag_count_row(p, r2, 0);
+    }
+    if (p.agp_peers > 1) {
+      __threadfence_system();            // system scope: the peers' copies have landed
+      __syncwarp();
+      if (lane == 0) {
+        ag_count_row(p, r, 1);
+        if (r2 < p.agp_rows) ag_count_row(p, r2, 1);
+      }
+    }
+  }
+}
+
+// Consumer half: rows [r0, r1] of the gathered A are complete once the chunk flags of their (source rank, chunk)
+// pairs carry this launch's epoch.  `seen` remembers the pairs this thread has already waited for.
+MMT_DEVICE bool ag_wait_chunks(const GemmParams& p, int r0, int r1, uint32_t (&seen)[16]) {
+  for (int row = r0; row <= r1;) {
+    const int src = row / p.ag_rows;
+    const int c = (row - src * p.ag_rows) / p.ag_chunk;
+    const int idx = src * kAgChunks + c;
+    if (!((seen[idx >> 5] >> (idx & 31)) & 1u)) {
+      if (!flag_wait_ge(&p.ag_flags[idx], p.ag_epoch, MMT_WAIT_NS, p.ew, 111)) return false;
+      seen[idx >> 5] |= 1u << (idx & 31);
+    }
+    row = src * p.ag_rows + (c + 1) * p.ag_chunk;      // first row of the next chunk (or of the next rank)
+    if (row > (src + 1) * p.ag_rows) row = (src + 1) * p.ag_rows;
+  }
+  return true;
+}
+
 template <int BN, int MT>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -648,7 +771,7 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   }
   const int tiles_m = (p.M + BMT - 1) / BMT;
   const int tiles_n = (p.N + BN - 1) / BN;
-  const int ntiles = tiles_m * tiles_n;
+  const int ntiles = p.agp_only ? 0 : tiles_m * tiles_n;
   const int KB = (p.K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
@@ -680,6 +803,7 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       uint32_t ph = 0;
       bool ok = true;
       uint32_t ag_seen = p.ag_flags ? (1u << p.ag_self) : 0u;
+      uint32_t ag_chunk_seen[16] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
       int kcount = 0;
       WorkItem w;
       for (int wi = 0; ok && work_item(p, wi, blockIdx.x, gridDim.x, KB, ntiles, w); ++wi) {
@@ -687,10 +811,14 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         tile_coords(p, w.tile, tiles_m, BMT, tm, tn);
         if (p.ag_flags) {
           const int r0 = tm * BMT, r1 = min(r0 + BMT, p.M) - 1;
-          for (int src = r0 / p.ag_rows; src <= r1 / p.ag_rows && ok; ++src) {
-            if (ag_seen & (1u << src)) continue;
-            ok = flag_wait_ge(&p.ag_flags[src], p.ag_epoch, MMT_WAIT_NS, p.ew, 110);
-            ag_seen |= 1u << src;
+          if (p.ag_chunk > 0) {
+            ok = ag_wait_chunks(p, r0, r1, ag_chunk_seen);
+          } else {
+            for (int src = r0 / p.ag_rows; src <= r1 / p.ag_rows && ok; ++src) {
+              if (ag_seen & (1u << src)) continue;
+              ok = flag_wait_ge(&p.ag_flags[src], p.ag_epoch, MMT_WAIT_NS, p.ew, 110);
+              ag_seen |= 1u << src;
+            }
           }
           if (!ok) break;
           asm volatile("fence.proxy.async;" ::: "memory");
@@ -777,6 +905,9 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         }
       }
     }
+  } else if (warp >= 2 + kEpiWarps) {
+    // ------------------------------ all-gather producer (2 warps) --------------
+    if (p.agp_src) ag_push_rows(p, warp - 2 - kEpiWarps, lane);
   } else {
     // ------------------------------ epilogue (8 warps) -------------------------
     const int q = warp & 3;              // tensor-memory lane quadrant this warp may read
@@ -836,7 +967,7 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     }
   }
 
-  if (warp >= 2 && lane == 0) {
+  if (warp >= 2 && warp < 2 + kEpiWarps && lane == 0) {
     tma_store_wait_all();                       // every bulk store of this warp has been written out
     asm volatile("fence.proxy.async;" ::: "memory");
   }
@@ -1039,7 +1170,7 @@ gemm_bf16_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_con
         if (acc == 0) acc_ph ^= 1;
       }
     }
-  } else {
+  } else if (warp < 2 + kEpiWarps) {
     // ------------------------------ epilogue (both CTAs, 8 warps each) ------------------------------
     const int q = warp & 3;
     const int half = (warp - 2) >> 2;
@@ -1057,6 +1188,10 @@ gemm_bf16_tcgen05_pair(const __grid_constant__ CUtensorMap tmA, const __grid_con
                          slab, map_to_cta(smem_u32(&tempty[acc]), 0));
       acc ^= 1;
       if (acc == 0) acc_ph ^= 1;
+    }
+    if (lane == 0) {
+      tma_store_wait_all();                     // every bulk store of this warp has been written out
+      asm volatile("fence.proxy.async;" ::: "memory");
     }
   }
 
@@ -1273,6 +1408,15 @@ extern "C" void mmt_gemm_set_mn_desc(uint32_t lbo, uint32_t sbo, uint32_t kstep)
 struct MmtGemmComm {
   const int* ag_flags;
   int ag_epoch, ag_rows, ag_self;
+  // fused producer (agp_src == nullptr: the rows were pushed by an earlier launch)
+  const void* agp_src;
+  const void* agp_w;
+  float* agp_rstd;
+  float agp_eps;
+  unsigned long long agp_dst[8];
+  int* agp_flag[8];
+  int* agp_counter;
+  int agp_rows, agp_peers, ag_chunk, agp_only;
   unsigned long long rs_base[8];
   int* rs_flag[8];
   int* rs_counter;
@@ -1346,7 +1490,8 @@ extern "C" int mmt_gemm_bf16(const void* A, const void* B, void* C, const void* 
   } else if (g_force_mt == 2 && M >= 256 && bn == 128) {
     mt = 2;
   }
-  if (bn == 256 && M >= 256 && (g_force_mt == 3 || (g_use_pair && g_force_mt == 0))) mt = 3;   // 2-CTA kernel
+  if (bn == 256 && M >= 256 && (g_force_mt == 3 || (g_use_pair && g_force_mt == 0)) && !(comm && (comm->agp_src || comm->ag_chunk > 0)))
+    mt = 3;   // 2-CTA kernel
   const int bmt = mt == 3 ? BM : BM * mt;              // rows per TMA box of A
   const int bbox = mt == 3 ? 128 : bn;                 // rows per TMA box of B
   CUtensorMap ta, tb;
@@ -1376,6 +1521,11 @@ extern "C" int mmt_gemm_bf16(const void* A, const void* B, void* C, const void* 
   p.group_m = g_group_m > 0 ? g_group_m : (g_group_m < 0 ? 0 : 2048 / (mt == 1 ? BM : 2 * BM));
   p.ag_flags = nullptr;
   p.ag_epoch = p.ag_rows = p.ag_self = 0;
+  p.agp_src = p.agp_w = nullptr;
+  p.agp_rstd = nullptr;
+  p.agp_counter = nullptr;
+  p.agp_eps = 0.f;
+  p.agp_rows = p.agp_peers = p.ag_chunk = p.agp_only = 0;
   p.rs_rows = p.rs_self = p.rs_ranks = p.rs_epoch = 0;
   p.rs_counter = nullptr;
   if (comm) {
@@ -1384,7 +1534,20 @@ extern "C" int mmt_gemm_bf16(const void* A, const void* B, void* C, const void* 
     p.rs_rows = c->rs_rows; p.rs_self = c->rs_self; p.rs_ranks = c->rs_ranks; p.rs_epoch = c->rs_epoch;
     p.rs_counter = c->rs_counter;
     for (int i = 0; i < 8; ++i) { p.rs_base[i] = c->rs_base[i]; p.rs_flag[i] = c->rs_flag[i]; }
+    p.agp_src = reinterpret_cast<const __nv_bfloat16*>(c->agp_src);
+    p.agp_w = reinterpret_cast<const __nv_bfloat16*>(c->agp_w);
+    p.agp_rstd = c->agp_rstd; p.agp_eps = c->agp_eps; p.agp_counter = c->agp_counter;
+    p.agp_rows = c->agp_rows; p.agp_peers = c->agp_peers; p.ag_chunk = c->ag_chunk; p.agp_only = c->agp_only;
+    for (int i = 0; i < 8; ++i) { p.agp_dst[i] = c->agp_dst[i]; p.agp_flag[i] = c->agp_flag[i]; }
     if (p.ag_flags && (p.ag_rows <= 0 || a_mn)) return -5;
+    if (p.ag_chunk < 0 || (p.ag_chunk > 0 && (long)p.ag_chunk * kAgChunks < p.ag_rows)) return -10;
+    if (p.agp_src) {
+      // fused producer: A is the gathered buffer of this rank ([ranks * ag_rows, K] contiguous), chunk flags required;
+      // the 2-CTA kernel has no producer path
+      if (!p.ag_flags || p.ag_chunk <= 0 || p.agp_peers < 1 || p.agp_peers > 8 || p.agp_rows > p.ag_rows ||
+          lda != K || (K & 7) || !p.agp_counter)
+        return -11;
+    }
     if (p.rs_rows && (out_f32 || p.rs_ranks > 8 || p.rs_ranks < 1)) return -6;
     // every row needs an owner among the rs_ranks peers: a longer M would index past the peer table
     if (p.rs_rows && (long)M > (long)p.rs_rows * p.rs_ranks) return -8;

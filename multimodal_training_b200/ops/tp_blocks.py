@@ -30,18 +30,24 @@ from .blocks import (BlockSpec, _attn_bwd, _attn_fwd, _grad_into, _rmsnorm_bwd, 
 def _col_fwd(fc, x_shard, norm_w, eps, w, b, role, keep: bool):
     """(RMSNorm ->) all-gather -> GEMM.  Returns (y, gathered input, rstd); the gathered input is a private copy
     when it has to outlive the heap region (activations kept for backward)."""
-    rows = x_shard.shape[0]
-    gathered, rstd, flags, epoch = fc.push_gather(x_shard, norm_w, eps, role)
-    y = fc.gemm_gathered(gathered, flags, epoch, rows, w, bias=b)
+    if fc.fused_ag:
+        y, gathered, rstd = fc.ag_gemm(x_shard, norm_w, eps, w, role=role, bias=b)
+    else:
+        rows = x_shard.shape[0]
+        gathered, rstd, flags, epoch = fc.push_gather(x_shard, norm_w, eps, role)
+        y = fc.gemm_gathered(gathered, flags, epoch, rows, w, bias=b)
     return y, (gathered.clone() if keep else gathered), rstd
 
 
 def _row_bwd(fc, dy_shard, a, w, role):
     """Backward of ``reduce_scatter(a @ w^T)``: gather the output gradient, input gradient through the gathered
     GEMM, weight gradient from the same gathered rows."""
-    rows = dy_shard.shape[0]
-    gathered, _, flags, epoch = fc.push_gather(dy_shard, None, 0.0, role + "_bwd")
-    da = fc.gemm_gathered(gathered, flags, epoch, rows, w, b_mn=True)
+    if fc.fused_ag:
+        da, gathered, _ = fc.ag_gemm(dy_shard, None, 0.0, w, role=role + "_bwd", b_mn=True)
+    else:
+        rows = dy_shard.shape[0]
+        gathered, _, flags, epoch = fc.push_gather(dy_shard, None, 0.0, role + "_bwd")
+        da = fc.gemm_gathered(gathered, flags, epoch, rows, w, b_mn=True)
     _grad_into(w, lambda out, acc: F.gemm(gathered, a, a_mn=True, b_mn=True, out=out, accumulate=acc))
     return da
 

@@ -31,6 +31,8 @@ log = logging.getLogger("mmt_b200")
 
 MAX_PEERS = 8
 N_SLOTS = 64
+AG_ROLES = 8          # exchange roles that may use the in-GEMM all-gather (each owns one block of chunk flags)
+AG_CHUNKS = 64        # chunk flags per source rank (csrc/gemm.cu: kAgChunks)
 
 
 class PeerSetC(ctypes.Structure):
@@ -39,7 +41,11 @@ class PeerSetC(ctypes.Structure):
 
 class GemmCommC(ctypes.Structure):
     _fields_ = [("ag_flags", ctypes.c_void_p), ("ag_epoch", ctypes.c_int), ("ag_rows", ctypes.c_int),
-                ("ag_self", ctypes.c_int), ("rs_base", ctypes.c_uint64 * 8), ("rs_flag", ctypes.c_void_p * 8),
+                ("ag_self", ctypes.c_int), ("agp_src", ctypes.c_void_p), ("agp_w", ctypes.c_void_p),
+                ("agp_rstd", ctypes.c_void_p), ("agp_eps", ctypes.c_float), ("agp_dst", ctypes.c_uint64 * 8),
+                ("agp_flag", ctypes.c_uint64 * 8), ("agp_counter", ctypes.c_void_p), ("agp_rows", ctypes.c_int),
+                ("agp_peers", ctypes.c_int), ("ag_chunk", ctypes.c_int), ("agp_only", ctypes.c_int),
+                ("rs_base", ctypes.c_uint64 * 8), ("rs_flag", ctypes.c_void_p * 8),
                 ("rs_counter", ctypes.c_void_p), ("rs_rows", ctypes.c_int), ("rs_self", ctypes.c_int),
                 ("rs_ranks", ctypes.c_int), ("rs_epoch", ctypes.c_int)]
 
@@ -64,10 +70,12 @@ class HeapContext:
     """A symmetric heap plus flag slots: [N_SLOTS, 8] int32 flags and [N_SLOTS] int32 CTA counters per rank."""
 
     def __init__(self, group, nbytes: int, device):
-        self.heap = SymmetricHeap(group, nbytes + 2 * N_SLOTS * 64, device)
+        self.heap = SymmetricHeap(group, nbytes + 2 * N_SLOTS * 64 + AG_ROLES * MAX_PEERS * AG_CHUNKS * 4 + 4096, device)
         self.size, self.rank = self.heap.size, self.heap.rank
         self.flags_off = self.heap.alloc("__flags", N_SLOTS * MAX_PEERS * 4)
         self.counters_off = self.heap.alloc("__counters", N_SLOTS * 4)
+        # chunk flags of the all-gathers fused into GEMMs: [role][source rank][chunk] int32, zero at start
+        self.agflags_off = self.heap.alloc("__agflags", AG_ROLES * MAX_PEERS * AG_CHUNKS * 4)
         self._slots: dict[str, int] = {}
         self._epochs: dict[int, int] = {}
 
@@ -111,6 +119,9 @@ class FusedComm:
         self.text_hidden, self.vision_hidden = int(text_hidden), int(vision_hidden)
         self.ulysses = False             # set by the vision trainer when the Ulysses exchange runs over the heap
         self._sizes = None
+        self.fused_ag = False            # True: all-gather inside the consuming GEMM; False: a push kernel in front of it
+        self._ag_roles: dict[str, int] = {}
+        self._ag_counters: dict[int, torch.Tensor] = {}
         self.ctx = HeapContext(mesh.world_group, heap_bytes, device)
         # results that live in reusable heap regions may be handed out as views only while BOTH halves recompute
         # their activations in backward; otherwise they are cloned (see set_checkpointed)
@@ -198,6 +209,45 @@ class FusedComm:
                 self.ctx.counter_addr(slot), epoch, m.tp_rank * rows, rows, cols, float(eps), nv.stream())
         return gathered, rstd, self.ctx.local_flags(slot), epoch
 
+    def ag_gemm(self, x_shard: torch.Tensor, norm_w, eps: float, w, *, role: str, bias=None, b_mn: bool = False,
+                push_only: bool = False):
+        """(RMSNorm of) a [T/tp, K] shard all-gathered INSIDE the GEMM that consumes it: ``gather(h) @ w^T + bias``.
+
+        One kernel: its epilogue warps first store this rank's (normalised) rows into every peer's gather buffer and
+        raise a flag per 128-row chunk; its TMA producer waits per (source rank, chunk), starting with this rank's own
+        rows, so the tensor cores work on the chunks that have landed while the others are still in flight.
+        Returns ``(y, gathered, rstd)``; ``push_only`` stores the rows and computes nothing (tests emulate a peer
+        with it on one GPU)."""
+        m = self.mesh
+        x_shard = x_shard.contiguous()
+        rows, cols = x_shard.shape
+        off, gathered = self._region("ag_" + role, (rows * m.tp, cols))
+        ridx = self._ag_roles.setdefault(role, len(self._ag_roles))
+        if ridx >= AG_ROLES:
+            raise RuntimeError("too many all-gather roles")
+        slot = self.ctx.slot("agc_" + role)
+        epoch = self.ctx.next_epoch(slot)
+        if ridx not in self._ag_counters:
+            # [0, 64): rows stored locally per chunk; [64, 128): rows stored to the peers per chunk
+            self._ag_counters[ridx] = torch.zeros(2 * AG_CHUNKS, dtype=torch.int32, device=x_shard.device)
+        rstd = torch.empty(rows, device=x_shard.device, dtype=torch.float32) if norm_w is not None else None
+        block = ridx * MAX_PEERS * AG_CHUNKS * 4
+        c = GemmCommC()
+        c.ag_flags = self.ctx.heap.local_ptr + self.ctx.agflags_off + block
+        c.ag_epoch, c.ag_rows, c.ag_self = epoch, rows, m.tp_rank
+        c.agp_src, c.agp_w, c.agp_rstd, c.agp_eps = x_shard.data_ptr(), nv.ptr(norm_w), nv.ptr(rstd), float(eps)
+        for i, r in enumerate(self.tp_ranks):
+            c.agp_dst[i] = self.ctx.heap.ptrs[r] + off
+            c.agp_flag[i] = self.ctx.heap.ptrs[r] + self.ctx.agflags_off + block
+        c.agp_counter = self._ag_counters[ridx].data_ptr()
+        c.agp_rows, c.agp_peers = rows, m.tp
+        c.ag_chunk = 128 * max(1, -(-rows // (128 * AG_CHUNKS)))
+        c.agp_only = int(push_only)
+        c.rs_rows = 0
+        nv.lib().mmt_gemm_set_comm(ctypes.byref(c))
+        y = F.gemm(gathered, w, b_mn=b_mn, bias=bias)
+        return y, gathered, rstd
+
     def gemm_gathered(self, gathered, flags_ptr, epoch, rows_per_rank, w, *, b_mn=False, bias=None):
         c = GemmCommC()
         c.ag_flags, c.ag_epoch, c.ag_rows, c.ag_self = flags_ptr, epoch, rows_per_rank, self.mesh.tp_rank
@@ -273,8 +323,11 @@ class _FusedColLinearFn(torch.autograd.Function):
     def forward(ctx, x_shard, norm_w, w, b, fc: FusedComm, role, eps):
         x_shard = x_shard.contiguous()
         rows = x_shard.shape[0]
-        gathered, rstd, flags, epoch = fc.push_gather(x_shard, norm_w, eps, role)
-        y = fc.gemm_gathered(gathered, flags, epoch, rows, w, bias=b)
+        if fc.fused_ag:
+            y, gathered, rstd = fc.ag_gemm(x_shard, norm_w, eps, w, role=role, bias=b)
+        else:
+            gathered, rstd, flags, epoch = fc.push_gather(x_shard, norm_w, eps, role)
+            y = fc.gemm_gathered(gathered, flags, epoch, rows, w, bias=b)
         if not fc.checkpointed:
             gathered = gathered.clone()
         ctx.save_for_backward(x_shard, norm_w, rstd, w, gathered)
@@ -328,8 +381,11 @@ class _FusedRowLinearFn(torch.autograd.Function):
         fc, role, has_res = ctx.misc
         dy_shard = dy_shard.contiguous()
         rows = dy_shard.shape[0]
-        gathered, _, flags, epoch = fc.push_gather(dy_shard, None, 0.0, role + "_bwd")
-        da = fc.gemm_gathered(gathered, flags, epoch, rows, w, b_mn=True)
+        if fc.fused_ag:
+            da, gathered, _ = fc.ag_gemm(dy_shard, None, 0.0, w, role=role + "_bwd", b_mn=True)
+        else:
+            gathered, _, flags, epoch = fc.push_gather(dy_shard, None, 0.0, role + "_bwd")
+            da = fc.gemm_gathered(gathered, flags, epoch, rows, w, b_mn=True)
         dw = F._write_param_grad(w, lambda out, acc: F.gemm(gathered, a, a_mn=True, b_mn=True, out=out,
                                                            accumulate=acc))
         return da, dw, (dy_shard if has_res else None), None, None

@@ -104,8 +104,11 @@ def bench_tp(fc: FusedComm, args, out) -> None:
             gathered_lib = torch.empty(T, H, device=dev, dtype=torch.bfloat16)
             y_lib = torch.empty(T, n_loc, device=dev, dtype=torch.bfloat16)
 
-            def fused():
-                g, _, flags, epoch = fc.push_gather(x, None, 0.0, f"bench_ag_{T}_{H}")
+            def fused():          # the all-gather inside the GEMM kernel (chunk flags)
+                return fc.ag_gemm(x, None, 0.0, w, role="bench_ag")[0]
+
+            def fused_two_kernels():   # the earlier form: a push kernel in front of the GEMM, one flag per source
+                g, _, flags, epoch = fc.push_gather(x, None, 0.0, "bench_ag2")
                 return fc.gemm_gathered(g, flags, epoch, rows, w)
 
             def lib():
@@ -147,7 +150,11 @@ def bench_tp(fc: FusedComm, args, out) -> None:
         t_l = _timed(lib, args.iters, args.warmup, flush)
         t_g = _timed(gemm_only, args.iters, args.warmup, flush)
         roof = _roof_ms(flops, link)
+        extra = {}
+        if kind == "ag_gemm":
+            extra["push_kernel_then_gemm_ms"] = _timed(fused_two_kernels, args.iters, args.warmup, flush)
         _emit({"path": kind, "gpus": tp, "tokens": T, "hidden": H, "width": W, "fused_ms": t_f, "nccl_cublas_ms": t_l,
+               **extra,
                "own_gemm_alone_ms": t_g, "speedup_vs_lib": t_l / t_f, "roofline_ms": roof,
                "frac_of_roofline": roof / t_f, "tflops_per_gpu": flops / t_f / 1e9, "link_gbs": link / t_f / 1e6,
                "max_rel_err_vs_lib": err, "peaks": peaks()[2]}, out)

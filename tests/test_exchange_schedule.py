@@ -23,6 +23,8 @@ from multimodal_training_b200.ops.blocks import BlockSpec
 class RecorderFC:
     """Stands in for FusedComm: hands out small CPU tensors and records which region/epoch they are views of."""
 
+    fused_ag = True                   # all-gathers run inside the consuming GEMM (one op: store to all, then read)
+
     def __init__(self):
         self.ops = []                 # the program: ("push", role, epoch) / ("read", region, epoch, waits) / ...
         self.epochs = {}
@@ -41,6 +43,11 @@ class RecorderFC:
         self.region_of[id(g)] = (region, e)
         self.keepalive.append(g)
         return g, (torch.ones(x_shard.shape[0]) if norm_w is not None else None), 0, e
+
+    def ag_gemm(self, x_shard, norm_w, eps, w, *, role, bias=None, b_mn=False, push_only=False):
+        g, rstd, _, e = self.push_gather(x_shard, norm_w, eps, role)
+        y = self.gemm_gathered(g, 0, e, x_shard.shape[0], w, b_mn=b_mn, bias=bias)
+        return y, g, rstd
 
     def gemm_gathered(self, gathered, flags, epoch, rows, w, *, b_mn=False, bias=None):
         region, e = self.region_of[id(gathered)]
