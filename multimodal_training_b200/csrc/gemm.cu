@@ -47,8 +47,7 @@ constexpr int BK = 64;            // 64 bf16 = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
 constexpr int kEpiWarps = 8;
 constexpr uint32_t kSlabBytes = 32 * 64 * 2;   // one epilogue warp's [32 x 64] bf16 staging slab
-constexpr int kPushWarps = 2;                  // warps 10, 11: producer side of an all-gather fused into the GEMM
-constexpr int kThreads = 64 + kEpiWarps * 32 + kPushWarps * 32;   // TMA warp, MMA warp, eight epilogue warps, two push warps
+constexpr int kThreads = 64 + kEpiWarps * 32 + 32;   // TMA warp, MMA warp, eight epilogue warps, one forwarder warp
 constexpr int kAgChunks = 64;                  // chunk flags per source rank of a fused all-gather
 
 struct GemmParams {
@@ -82,21 +81,19 @@ struct GemmParams {
   //     are complete once ag_flags[s] >= ag_epoch; this rank's own rows need no wait.  ag_flags == nullptr: off.
   const int* ag_flags;
   int ag_epoch, ag_rows, ag_self;
-  // --- all-gather PRODUCER inside the same kernel (agp_src != nullptr): before their first tile is ready the
-  //     epilogue warps of all CTAs (RMS-normalise and) store this rank's agp_rows rows of agp_src [agp_rows, K] into
-  //     every peer's gathered buffer agp_dst[p] at rows ag_self * ag_rows + r, one warp per row, rows interleaved over
-  //     the CTAs so that the first chunks complete first.  Per chunk of ag_chunk rows a counter collects the finished
-  //     rows; the warp that completes a chunk publishes ag_epoch to flag word [ag_self * kAgChunks + chunk] on every
-  //     peer (agp_flag[p]).  The consumer side then waits per (source rank, chunk) on ag_flags, own rows included.
-  const __nv_bfloat16* agp_src;
-  const __nv_bfloat16* agp_w;       // RMSNorm weight [K] or nullptr (plain copy)
-  float* agp_rstd;                  // [agp_rows] out, or nullptr
-  float agp_eps;
-  unsigned long long agp_dst[8];
-  int* agp_flag[8];
-  int* agp_counter;                 // [kAgChunks] ints, zero between launches
-  int agp_rows, agp_peers, ag_chunk;
-  int agp_only;                     // push this rank's rows and return (no tiles): single-GPU emulation of a peer
+  // --- all-gather FORWARDER inside the same kernel (fwd_peers > 0).  The CTAs that compute the first fwd_split
+  //     column tiles of a block of this rank's own rows also send that block to the peers: of the A stages the TMA
+  //     producer loads for the MMA, column tile tn forwards the k-blocks with kb % fwd_split == tn, storing the stage
+  //     from shared memory into the same place of every destination's gathered buffer (bulk tensor stores over
+  //     NVLink).  The rows cross the link while the tensor core works on them, are read from HBM once, and the work
+  //     is spread over fwd_split CTAs per row block.  Each of those CTAs counts itself into fwd_counter[block] once
+  //     its stores have landed; the last one writes ag_epoch to flag word [ag_self * kAgChunks + block] on every
+  //     peer, and the consumer side waits per (source rank, block) on ag_flags.  ag_chunk = rows per block = rows of
+  //     a tile.  fwd_direct: own rows are loaded from the caller's shard (tensor map 9 of the table) instead of the
+  //     gathered buffer, and this rank's gathered buffer is one more destination (fwd_dsts = fwd_peers + 1).
+  int* fwd_flag[8];                 // flag arrays of the fwd_peers remote peers
+  int* fwd_counter;                 // [kAgChunks] ints, zero between launches
+  int fwd_peers, fwd_dsts, fwd_split, fwd_direct, ag_chunk;
   // --- reduce-scatter producer: row r of C belongs to rank r / rs_rows and is stored to that rank's staging
   //     slot `rs_self` ([rs_self*rs_rows + r % rs_rows, :] at rs_base[owner]); when the whole GEMM is done,
   //     rs_flag[p] on every peer receives rs_epoch.  rs_rows == 0: off.
@@ -203,14 +200,16 @@ struct Cfg {
   static constexpr int kStages = (int)((227u * 1024u - 2048u - STORE_BYTES) / STAGE_BYTES) > 8
                                      ? 8 : (int)((227u * 1024u - 2048u - STORE_BYTES) / STAGE_BYTES);
   static constexpr uint32_t TMEM_COLS = (2 * BN <= 128) ? 128 : (2 * BN <= 256 ? 256 : 512);
-  static constexpr size_t SMEM = 1024 + (size_t)kStages * STAGE_BYTES + STORE_BYTES + (2 * kStages + 4) * 8 + 16;
+  static constexpr size_t SMEM = 1024 + (size_t)kStages * STAGE_BYTES + STORE_BYTES + (4 * kStages + 4) * 8 + 16;
   static_assert(MT == 1 || 2 * BN <= 512, "two accumulators must fit tensor memory");
 };
 
 
-// Output tensor maps ([32 x 64] boxes): index 0 for a plain GEMM; one per owner rank for a reduce-scatter producer.
+// Tensor maps beside A and B.  Output ([32 x 64] boxes): index 0 for a plain GEMM; one per owner rank for a
+// reduce-scatter producer.  All-gather forwarder: 1 .. 8 = the destinations' gathered buffers (boxes of an A stage),
+// 9 = this rank's shard as the source of its own rows.
 struct OutMaps {
-  CUtensorMap m[8];
+  CUtensorMap m[10];
 };
 
 // byte offset of (row, col) in a [rows x 64] bf16 box (1024-byte aligned) with 128-byte rows and the 128B swizzle
@@ -638,93 +637,11 @@ MMT_DEVICE void epilogue_partial(uint32_t tmem_acc, float* dst, int q, int half,
 
 MMT_DEVICE void epi_bar_sync() { asm volatile("bar.sync 2, 256;" ::: "memory"); }
 
-// Producer half of the fused all-gather (see GemmParams::agp_src), run by the two push warps of every CTA from kernel
-// start until all rows of this rank are out.  Nothing here waits for a peer, so every rank's rows reach the others
-// whatever those are doing, and nothing here delays the epilogue warps.  A row goes to THIS rank's buffer first and
-// counts towards the local chunk flag after a device-scope fence (the rank's own tiles can start within
-// microseconds); the stores to the peers follow, and their chunk flags are raised after a system-scope fence, i.e.
-// once the data has crossed NVLink.  Two rows share one system fence (the fence waits for a round trip).
-MMT_DEVICE void ag_store_row(const GemmParams& p, int r, int lane) {
-  const int nvec = p.K >> 3;
-  const long ld = p.K;
-  const __nv_bfloat16* src = p.agp_src + (long)r * ld;
-  const long dst_row = ((long)p.ag_self * p.ag_rows + r) * ld;
-  float rstd = 1.f;
-  if (p.agp_w) {
-    float ss = 0.f;
-    for (int c = lane; c < nvec; c += 32) {
-      const uint4 u = *reinterpret_cast<const uint4*>(src + c * 8);
-      const uint32_t w4[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 f = unpack_bf16x2(w4[j]);
-        ss += f.x * f.x + f.y * f.y;
-      }
-    }
-    ss = warp_sum(ss);
-    rstd = rsqrtf(ss / (float)p.K + p.agp_eps);
-    if (lane == 0 && p.agp_rstd) p.agp_rstd[r] = rstd;
-  }
-  __nv_bfloat16* local = reinterpret_cast<__nv_bfloat16*>(p.agp_dst[p.ag_self]) + dst_row;
-  for (int c = lane; c < nvec; c += 32) {
-    uint4 u = *reinterpret_cast<const uint4*>(src + c * 8);
-    if (p.agp_w) {
-      const uint4 wv = __ldg(reinterpret_cast<const uint4*>(p.agp_w + c * 8));
-      const uint32_t x4[4] = {u.x, u.y, u.z, u.w}, w4[4] = {wv.x, wv.y, wv.z, wv.w};
-      uint32_t o4[4];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 a = unpack_bf16x2(x4[j]), b = unpack_bf16x2(w4[j]);
-        o4[j] = pack_bf16x2(a.x * rstd * b.x, a.y * rstd * b.y);
-      }
-      u = make_uint4(o4[0], o4[1], o4[2], o4[3]);
-    }
-    *reinterpret_cast<uint4*>(local + c * 8) = u;
-    for (int q = 0; q < p.agp_peers; ++q)
-      if (q != p.ag_self) *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.agp_dst[q]) + dst_row + c * 8) = u;
-  }
-}
-
-// Counts row r into its chunk (counter set `set`: 0 = stored locally, 1 = stored to the peers); the warp that
-// completes a chunk raises the chunk's flag on this rank (set 0) or on every peer (set 1).
-MMT_DEVICE void ag_count_row(const GemmParams& p, int r, int set) {
-  const int chunk = r / p.ag_chunk;
-  const int in_chunk = min(p.ag_chunk, p.agp_rows - chunk * p.ag_chunk);
-  int* counter = p.agp_counter + set * kAgChunks + chunk;
-  if (atomicAdd(counter, 1) == in_chunk - 1) {
-    *counter = 0;
-    if (set == 0) {
-      __threadfence();
-      flag_store_release_sys(p.agp_flag[p.ag_self] + p.ag_self * kAgChunks + chunk, p.ag_epoch);
-    } else {
-      __threadfence_system();
-      for (int q = 0; q < p.agp_peers; ++q)
-        if (q != p.ag_self) flag_store_release_sys(p.agp_flag[q] + p.ag_self * kAgChunks + chunk, p.ag_epoch);
-    }
-  }
-}
-
-MMT_DEVICE void ag_push_rows(const GemmParams& p, int push_warp, int lane) {
-  const int step = (int)gridDim.x * kPushWarps;
-  for (int r = (int)blockIdx.x * kPushWarps + push_warp; r < p.agp_rows; r += 2 * step) {
-    const int r2 = r + step;
-    ag_store_row(p, r, lane);
-    if (r2 < p.agp_rows) ag_store_row(p, r2, lane);
-    __threadfence();                     // device scope: this rank's copies are readable by its own TMA loads
-    __syncwarp();
-    if (lane == 0) {
-      ag_count_row(p, r, 0);
-      if (r2 < p.agp_rows) ag_count_row(p, r2, 0);
-    }
-    if (p.agp_peers > 1) {
-      __threadfence_system();            // system scope: the peers' copies have landed
-      __syncwarp();
-      if (lane == 0) {
-        ag_count_row(p, r, 1);
-        if (r2 < p.agp_rows) ag_count_row(p, r2, 1);
-      }
-    }
-  }
+// Does the CTA that computes tile (tm, tn) also forward the tile's rows of A to the peers?  (GemmParams::fwd_peers)
+MMT_DEVICE bool forwards_tile(const GemmParams& p, int tm, int tn, int bmt) {
+  if (p.fwd_peers <= 0 || tn >= p.fwd_split) return false;
+  const int r0 = tm * bmt, own0 = p.ag_self * p.ag_rows;
+  return r0 >= own0 && r0 < own0 + p.ag_rows;
 }
 
 // Consumer half: rows [r0, r1] of the gathered A are complete once the chunk flags of their (source rank, chunk)
@@ -732,6 +649,10 @@ MMT_DEVICE void ag_push_rows(const GemmParams& p, int push_warp, int lane) {
 MMT_DEVICE bool ag_wait_chunks(const GemmParams& p, int r0, int r1, uint32_t (&seen)[16]) {
   for (int row = r0; row <= r1;) {
     const int src = row / p.ag_rows;
+    if (src == p.ag_self) {                            // own rows were written by this stream before the launch
+      row = (src + 1) * p.ag_rows;
+      continue;
+    }
     const int c = (row - src * p.ag_rows) / p.ag_chunk;
     const int idx = src * kAgChunks + c;
     if (!((seen[idx >> 5] >> (idx & 31)) & 1u)) {
@@ -759,7 +680,12 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   uint64_t* empty = bars + kStages;
   uint64_t* tfull = bars + 2 * kStages;   // [2]: accumulator slot filled
   uint64_t* tempty = tfull + 2;           // [2]: accumulator slot drained
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  // all-gather forwarding only: the MMA thread tells the forwarder that a stage of a forwarded tile has landed
+  // (fwd_go), the forwarder tells the TMA producer that its stores have read the stage (fwd_done).  Both rings see
+  // one phase per FORWARDED use of a stage, and each has a single waiter that follows every phase.
+  uint64_t* fwd_go = tempty + 2;          // [kStages]
+  uint64_t* fwd_done = fwd_go + kStages;  // [kStages]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(fwd_done + kStages);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -771,7 +697,7 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   }
   const int tiles_m = (p.M + BMT - 1) / BMT;
   const int tiles_n = (p.N + BN - 1) / BN;
-  const int ntiles = p.agp_only ? 0 : tiles_m * tiles_n;
+  const int ntiles = tiles_m * tiles_n;
   const int KB = (p.K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
@@ -780,6 +706,8 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
+      mbar_init(&fwd_go[s], 1);
+      mbar_init(&fwd_done[s], 1);
     }
     mbar_init(&tfull[0], 1);
     mbar_init(&tfull[1], 1);
@@ -804,11 +732,14 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       bool ok = true;
       uint32_t ag_seen = p.ag_flags ? (1u << p.ag_self) : 0u;
       uint32_t ag_chunk_seen[16] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
+      uint32_t fwd_pending = 0, fwd_parity = 0;   // per stage: last use is being forwarded / parity of that hand-back
       int kcount = 0;
       WorkItem w;
       for (int wi = 0; ok && work_item(p, wi, blockIdx.x, gridDim.x, KB, ntiles, w); ++wi) {
         int tm, tn;
         tile_coords(p, w.tile, tiles_m, BMT, tm, tn);
+        const bool fwd_tile = forwards_tile(p, tm, tn, BMT);
+        const bool own_direct = p.fwd_direct && tm * BMT >= p.ag_self * p.ag_rows && tm * BMT < (p.ag_self + 1) * p.ag_rows;
         if (p.ag_flags) {
           const int r0 = tm * BMT, r1 = min(r0 + BMT, p.M) - 1;
           if (p.ag_chunk > 0) {
@@ -826,10 +757,19 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         for (int kb = w.k0; kb < w.k1; ++kb) {
           if ((MMT_DBG & 1) && kcount++ >= kStages) continue;
           if (!mbar_wait(&empty[s], ph ^ 1, p.ew, 100)) { ok = false; break; }
+          if (fwd_pending & (1u << s)) {
+            // the stage's previous contents also went to the peers: the forwarder's stores must have read them
+            if (!mbar_wait(&fwd_done[s], (fwd_parity >> s) & 1u, p.ew, 101)) { ok = false; break; }
+            fwd_parity ^= 1u << s;
+            fwd_pending &= ~(1u << s);
+          }
+          if (fwd_tile && kb % p.fwd_split == tn) fwd_pending |= 1u << s;
           uint8_t* sA = smem + (size_t)s * C_::STAGE_BYTES;
           uint8_t* sB = sA + C_::A_BYTES;
           mbar_expect_tx(&full[s], C_::STAGE_BYTES);
-          if (!p.a_mn) {
+          if (own_direct) {
+            tma_load_2d(sA, &tmC.m[9], &full[s], kb * BK, tm * BMT - p.ag_self * p.ag_rows);
+          } else if (!p.a_mn) {
             tma_load_2d(sA, &tmA, &full[s], kb * BK, tm * BMT);      // one box of BMT rows
           } else {
 #pragma unroll
@@ -869,6 +809,12 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         if (!mbar_wait(&tempty[MT == 2 ? 0 : acc], acc_ph ^ 1, p.ew, 200)) { ok = false; break; }
         if (MT == 2 && !mbar_wait(&tempty[1], acc_ph ^ 1, p.ew, 202)) { ok = false; break; }
         tc_fence_after();
+        int fwd_tn = -1;                 // >= 0: this tile forwards its k-blocks kb % fwd_split == fwd_tn
+        if (p.fwd_peers > 0) {
+          int tm, tn;
+          tile_coords(p, w.tile, tiles_m, BMT, tm, tn);
+          if (forwards_tile(p, tm, tn, BMT)) fwd_tn = tn;
+        }
         const uint32_t d0 = tmem_base + (uint32_t)((MT == 2 ? 0 : acc) * BN);
         for (int kb = 0; kb < w.k1 - w.k0; ++kb) {      // kb counts from the start of this run: a fresh accumulator
           const bool skip = (MMT_DBG & 1) && kcount++ >= kStages;
@@ -889,6 +835,8 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             }
             if (k == 0) ready = mbar_test(&full[sn], phn);
           }
+          // the stage has landed: the forwarder may send it on
+          if (fwd_tn >= 0 && (w.k0 + kb) % p.fwd_split == fwd_tn) mbar_arrive(&fwd_go[s]);
           if (!(MMT_DBG & 2)) tc_commit(&empty[s]);
           s = sn;
           ph = phn;
@@ -906,8 +854,44 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       }
     }
   } else if (warp >= 2 + kEpiWarps) {
-    // ------------------------------ all-gather producer (2 warps) --------------
-    if (p.agp_src) ag_push_rows(p, warp - 2 - kEpiWarps, lane);
+    // ------------------------------ all-gather forwarder (one thread) ----------
+    if (p.fwd_peers > 0 && lane == 0) {
+      uint32_t use = 0;                  // ring slots handed out so far (the TMA producer counts the same way)
+      uint32_t go_parity = 0;            // per stage: parity of the next fwd_go phase
+      bool ok = true;
+      WorkItem w;
+      for (int wi = 0; ok && work_item(p, wi, blockIdx.x, gridDim.x, KB, ntiles, w); ++wi) {
+        int tm, tn;
+        tile_coords(p, w.tile, tiles_m, BMT, tm, tn);
+        if (!forwards_tile(p, tm, tn, BMT)) {
+          use += (uint32_t)(w.k1 - w.k0);
+          continue;
+        }
+        for (int kb = w.k0; kb < w.k1; ++kb, ++use) {
+          if (kb % p.fwd_split != tn) continue;
+          const uint32_t s = use % (uint32_t)kStages;
+          if (!mbar_wait(&fwd_go[s], (go_parity >> s) & 1u, p.ew, 400)) { ok = false; break; }
+          go_parity ^= 1u << s;
+          const uint8_t* sA = smem + (size_t)s * C_::STAGE_BYTES;
+          for (int q = 0; q < p.fwd_dsts; ++q) tma_store_2d(&tmC.m[1 + q], sA, kb * BK, tm * BMT);
+          tma_store_commit();
+          tma_store_wait_read();         // shared memory has been read; the stage may be refilled
+          mbar_arrive(&fwd_done[s]);
+        }
+        if (!ok) break;
+        tma_store_wait_all();            // this CTA's share of the row block has been written everywhere ...
+        asm volatile("fence.proxy.async;" ::: "memory");
+        __threadfence_system();
+        const int block = (tm * BMT - p.ag_self * p.ag_rows) / BMT;
+        const int parts = min(p.fwd_split, tiles_n);
+        if (atomicAdd(&p.fwd_counter[block], 1) == parts - 1) {
+          p.fwd_counter[block] = 0;      // ready for the next launch
+          __threadfence_system();
+          for (int q = 0; q < p.fwd_peers; ++q)   // ... and the last share announces the block
+            flag_store_release_sys(p.fwd_flag[q] + p.ag_self * kAgChunks + block, p.ag_epoch);
+        }
+      }
+    }
   } else {
     // ------------------------------ epilogue (8 warps) -------------------------
     const int q = warp & 3;              // tensor-memory lane quadrant this warp may read
@@ -1408,15 +1392,16 @@ extern "C" void mmt_gemm_set_mn_desc(uint32_t lbo, uint32_t sbo, uint32_t kstep)
 struct MmtGemmComm {
   const int* ag_flags;
   int ag_epoch, ag_rows, ag_self;
-  // fused producer (agp_src == nullptr: the rows were pushed by an earlier launch)
-  const void* agp_src;
-  const void* agp_w;
-  float* agp_rstd;
-  float agp_eps;
-  unsigned long long agp_dst[8];
-  int* agp_flag[8];
-  int* agp_counter;
-  int agp_rows, agp_peers, ag_chunk, agp_only;
+  // forwarder (fwd_peers == 0: the rows were pushed by an earlier launch): gathered buffers ([ranks * ag_rows, K],
+  // row stride lda) and flag arrays of the remote peers
+  unsigned long long fwd_dst[8];
+  int* fwd_flag[8];
+  int fwd_peers;
+  // fwd_src != nullptr: this rank's rows are read from here ([ag_rows, K], row stride fwd_src_ld) and also stored to
+  // its own gathered buffer A; nullptr: they are in A already
+  const void* fwd_src;
+  int fwd_src_ld;
+  int* fwd_counter;                 // [64] ints, zero between launches
   unsigned long long rs_base[8];
   int* rs_flag[8];
   int* rs_counter;
@@ -1490,7 +1475,7 @@ extern "C" int mmt_gemm_bf16(const void* A, const void* B, void* C, const void* 
   } else if (g_force_mt == 2 && M >= 256 && bn == 128) {
     mt = 2;
   }
-  if (bn == 256 && M >= 256 && (g_force_mt == 3 || (g_use_pair && g_force_mt == 0)) && !(comm && (comm->agp_src || comm->ag_chunk > 0)))
+  if (bn == 256 && M >= 256 && (g_force_mt == 3 || (g_use_pair && g_force_mt == 0)) && !(comm && comm->fwd_peers > 0))
     mt = 3;   // 2-CTA kernel
   const int bmt = mt == 3 ? BM : BM * mt;              // rows per TMA box of A
   const int bbox = mt == 3 ? 128 : bn;                 // rows per TMA box of B
@@ -1521,11 +1506,9 @@ extern "C" int mmt_gemm_bf16(const void* A, const void* B, void* C, const void* 
   p.group_m = g_group_m > 0 ? g_group_m : (g_group_m < 0 ? 0 : 2048 / (mt == 1 ? BM : 2 * BM));
   p.ag_flags = nullptr;
   p.ag_epoch = p.ag_rows = p.ag_self = 0;
-  p.agp_src = p.agp_w = nullptr;
-  p.agp_rstd = nullptr;
-  p.agp_counter = nullptr;
-  p.agp_eps = 0.f;
-  p.agp_rows = p.agp_peers = p.ag_chunk = p.agp_only = 0;
+  p.fwd_peers = p.fwd_dsts = p.fwd_split = p.fwd_direct = p.ag_chunk = 0;
+  p.fwd_counter = nullptr;
+  for (int i = 0; i < 8; ++i) p.fwd_flag[i] = nullptr;
   p.rs_rows = p.rs_self = p.rs_ranks = p.rs_epoch = 0;
   p.rs_counter = nullptr;
   if (comm) {
@@ -1534,19 +1517,27 @@ extern "C" int mmt_gemm_bf16(const void* A, const void* B, void* C, const void* 
     p.rs_rows = c->rs_rows; p.rs_self = c->rs_self; p.rs_ranks = c->rs_ranks; p.rs_epoch = c->rs_epoch;
     p.rs_counter = c->rs_counter;
     for (int i = 0; i < 8; ++i) { p.rs_base[i] = c->rs_base[i]; p.rs_flag[i] = c->rs_flag[i]; }
-    p.agp_src = reinterpret_cast<const __nv_bfloat16*>(c->agp_src);
-    p.agp_w = reinterpret_cast<const __nv_bfloat16*>(c->agp_w);
-    p.agp_rstd = c->agp_rstd; p.agp_eps = c->agp_eps; p.agp_counter = c->agp_counter;
-    p.agp_rows = c->agp_rows; p.agp_peers = c->agp_peers; p.ag_chunk = c->ag_chunk; p.agp_only = c->agp_only;
-    for (int i = 0; i < 8; ++i) { p.agp_dst[i] = c->agp_dst[i]; p.agp_flag[i] = c->agp_flag[i]; }
     if (p.ag_flags && (p.ag_rows <= 0 || a_mn)) return -5;
-    if (p.ag_chunk < 0 || (p.ag_chunk > 0 && (long)p.ag_chunk * kAgChunks < p.ag_rows)) return -10;
-    if (p.agp_src) {
-      // fused producer: A is the gathered buffer of this rank ([ranks * ag_rows, K] contiguous), chunk flags required;
-      // the 2-CTA kernel has no producer path
-      if (!p.ag_flags || p.ag_chunk <= 0 || p.agp_peers < 1 || p.agp_peers > 8 || p.agp_rows > p.ag_rows ||
-          lda != K || (K & 7) || !p.agp_counter)
+    if (c->fwd_peers) {
+      // forwarder: chunk flags per tile-high block of rows, so the blocks must tile every rank's rows exactly; the
+      // gathered buffers are [ranks * ag_rows, K] on every rank; the reduce-scatter role uses the same map table
+      if (!p.ag_flags || c->fwd_peers < 0 || c->fwd_peers > 7 || mt == 3 || p.rs_rows || out_f32 ||
+          p.ag_rows % bmt != 0 || p.ag_rows / bmt > kAgChunks || (long)M > (long)p.ag_rows * (c->fwd_peers + 1))
+        return -10;
+      if (!c->fwd_counter || (c->fwd_src && ((c->fwd_src_ld & 7) || (reinterpret_cast<uintptr_t>(c->fwd_src) & 15))))
         return -11;
+      p.fwd_peers = c->fwd_peers;
+      p.fwd_direct = c->fwd_src ? 1 : 0;
+      p.fwd_dsts = p.fwd_peers + p.fwd_direct;
+      p.fwd_counter = c->fwd_counter;
+      // k-blocks of a row block are dealt out to (up to) eight column tiles: small enough shares that the CTAs which
+      // forward are not late for their next tile, and all of them in the first wave of a raster band
+      p.fwd_split = std::max(1, std::min(std::min(8, (N + bn - 1) / bn), (int)kb));
+      p.ag_chunk = bmt;
+      for (int i = 0; i < p.fwd_peers; ++i) {
+        if (!c->fwd_dst[i] || !c->fwd_flag[i]) return -11;
+        p.fwd_flag[i] = c->fwd_flag[i];
+      }
     }
     if (p.rs_rows && (out_f32 || p.rs_ranks > 8 || p.rs_ranks < 1)) return -6;
     // every row needs an owner among the rs_ranks peers: a longer M would index past the peer table
@@ -1593,6 +1584,16 @@ extern "C" int mmt_gemm_bf16(const void* A, const void* B, void* C, const void* 
       r = cached_tmap_2d(&tc.m[0], C, (uint64_t)N, (uint64_t)M, (uint64_t)ldc, 64, 32);
       if (r) return 3000 + r;
     }
+  }
+  for (int i = 0; i < p.fwd_dsts; ++i) {
+    const void* dst = i < p.fwd_peers ? reinterpret_cast<const void*>(comm->fwd_dst[i]) : A;
+    r = cached_tmap_2d(&tc.m[1 + i], dst, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BK, (uint32_t)bmt);
+    if (r) return 4000 + r;
+  }
+  if (p.fwd_direct) {
+    r = cached_tmap_2d(&tc.m[9], comm->fwd_src, (uint64_t)K, (uint64_t)p.ag_rows, (uint64_t)comm->fwd_src_ld, BK,
+                       (uint32_t)bmt);
+    if (r) return 4000 + r;
   }
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   // the stream-K workspace is shared: a launch on another stream than the previous user waits for that one

@@ -20,6 +20,7 @@ from __future__ import annotations
 
 import ctypes
 import logging
+import os
 
 import torch
 
@@ -41,10 +42,9 @@ class PeerSetC(ctypes.Structure):
 
 class GemmCommC(ctypes.Structure):
     _fields_ = [("ag_flags", ctypes.c_void_p), ("ag_epoch", ctypes.c_int), ("ag_rows", ctypes.c_int),
-                ("ag_self", ctypes.c_int), ("agp_src", ctypes.c_void_p), ("agp_w", ctypes.c_void_p),
-                ("agp_rstd", ctypes.c_void_p), ("agp_eps", ctypes.c_float), ("agp_dst", ctypes.c_uint64 * 8),
-                ("agp_flag", ctypes.c_uint64 * 8), ("agp_counter", ctypes.c_void_p), ("agp_rows", ctypes.c_int),
-                ("agp_peers", ctypes.c_int), ("ag_chunk", ctypes.c_int), ("agp_only", ctypes.c_int),
+                ("ag_self", ctypes.c_int), ("fwd_dst", ctypes.c_uint64 * 8), ("fwd_flag", ctypes.c_uint64 * 8),
+                ("fwd_peers", ctypes.c_int), ("fwd_src", ctypes.c_void_p), ("fwd_src_ld", ctypes.c_int),
+                ("fwd_counter", ctypes.c_void_p),
                 ("rs_base", ctypes.c_uint64 * 8), ("rs_flag", ctypes.c_void_p * 8),
                 ("rs_counter", ctypes.c_void_p), ("rs_rows", ctypes.c_int), ("rs_self", ctypes.c_int),
                 ("rs_ranks", ctypes.c_int), ("rs_epoch", ctypes.c_int)]
@@ -119,9 +119,10 @@ class FusedComm:
         self.text_hidden, self.vision_hidden = int(text_hidden), int(vision_hidden)
         self.ulysses = False             # set by the vision trainer when the Ulysses exchange runs over the heap
         self._sizes = None
-        self.fused_ag = False            # True: all-gather inside the consuming GEMM; False: a push kernel in front of it
+        # True: all-gather inside the consuming GEMM (ag_gemm); False: a push kernel in front of it (push_gather)
+        self.fused_ag = os.environ.get("MMT_FUSED_AG", "1") == "1"
         self._ag_roles: dict[str, int] = {}
-        self._ag_counters: dict[int, torch.Tensor] = {}
+        self._ag_counter = None          # [AG_ROLES, AG_CHUNKS] int32: shares of a row block that have been forwarded
         self.ctx = HeapContext(mesh.world_group, heap_bytes, device)
         # results that live in reusable heap regions may be handed out as views only while BOTH halves recompute
         # their activations in backward; otherwise they are cloned (see set_checkpointed)
@@ -209,40 +210,49 @@ class FusedComm:
                 self.ctx.counter_addr(slot), epoch, m.tp_rank * rows, rows, cols, float(eps), nv.stream())
         return gathered, rstd, self.ctx.local_flags(slot), epoch
 
-    def ag_gemm(self, x_shard: torch.Tensor, norm_w, eps: float, w, *, role: str, bias=None, b_mn: bool = False,
-                push_only: bool = False):
+    def ag_gemm(self, x_shard: torch.Tensor, norm_w, eps: float, w, *, role: str, bias=None, b_mn: bool = False):
         """(RMSNorm of) a [T/tp, K] shard all-gathered INSIDE the GEMM that consumes it: ``gather(h) @ w^T + bias``.
 
-        One kernel: its epilogue warps first store this rank's (normalised) rows into every peer's gather buffer and
-        raise a flag per 128-row chunk; its TMA producer waits per (source rank, chunk), starting with this rank's own
-        rows, so the tensor cores work on the chunks that have landed while the others are still in flight.
-        Returns ``(y, gathered, rstd)``; ``push_only`` stores the rows and computes nothing (tests emulate a peer
-        with it on one GPU)."""
+        The GEMM starts on this rank's own rows; the CTAs that compute the first few column tiles of those rows
+        forward the A tiles they load -- from shared memory, as bulk stores over NVLink -- to the same place of every
+        peer's gather buffer and raise a flag per row block; the GEMM's TMA producer waits per (source rank, row
+        block) before it reads a peer's rows.  The rows cross the link while the tensor cores work and are read from
+        HBM once.  With a norm, a small kernel first leaves the normalised rows in this rank's own gather buffer;
+        without one the GEMM reads them from ``x_shard`` directly and fills its own buffer on the way.  Falls back to
+        the push kernel in front of the GEMM when the shard does not split into whole 256-row blocks.
+        Returns ``(y, gathered, rstd)``."""
         m = self.mesh
         x_shard = x_shard.contiguous()
         rows, cols = x_shard.shape
+        if rows % 256 or rows > 128 * AG_CHUNKS or m.tp > MAX_PEERS:
+            gathered, rstd, flags, epoch = self.push_gather(x_shard, norm_w, eps, role)
+            return self.gemm_gathered(gathered, flags, epoch, rows, w, b_mn=b_mn, bias=bias), gathered, rstd
         off, gathered = self._region("ag_" + role, (rows * m.tp, cols))
         ridx = self._ag_roles.setdefault(role, len(self._ag_roles))
         if ridx >= AG_ROLES:
             raise RuntimeError("too many all-gather roles")
         slot = self.ctx.slot("agc_" + role)
         epoch = self.ctx.next_epoch(slot)
-        if ridx not in self._ag_counters:
-            # [0, 64): rows stored locally per chunk; [64, 128): rows stored to the peers per chunk
-            self._ag_counters[ridx] = torch.zeros(2 * AG_CHUNKS, dtype=torch.int32, device=x_shard.device)
         rstd = torch.empty(rows, device=x_shard.device, dtype=torch.float32) if norm_w is not None else None
-        block = ridx * MAX_PEERS * AG_CHUNKS * 4
+        if norm_w is not None:
+            # normalised own rows -> own buffer (the flag this raises is not read by anyone)
+            me = self.ctx.peerset(off, [self.tp_ranks[m.tp_rank]], slot, m.tp_rank)
+            nv.call("mmt_rmsnorm_push", x_shard.data_ptr(), nv.ptr(norm_w), nv.ptr(rstd), ctypes.byref(me),
+                    self.ctx.counter_addr(slot), epoch, m.tp_rank * rows, rows, cols, float(eps), nv.stream())
+        if self._ag_counter is None:
+            self._ag_counter = torch.zeros(AG_ROLES * AG_CHUNKS, dtype=torch.int32, device=x_shard.device)
+        block = self.ctx.agflags_off + ridx * MAX_PEERS * AG_CHUNKS * 4
         c = GemmCommC()
-        c.ag_flags = self.ctx.heap.local_ptr + self.ctx.agflags_off + block
+        c.ag_flags = self.ctx.heap.local_ptr + block
         c.ag_epoch, c.ag_rows, c.ag_self = epoch, rows, m.tp_rank
-        c.agp_src, c.agp_w, c.agp_rstd, c.agp_eps = x_shard.data_ptr(), nv.ptr(norm_w), nv.ptr(rstd), float(eps)
-        for i, r in enumerate(self.tp_ranks):
-            c.agp_dst[i] = self.ctx.heap.ptrs[r] + off
-            c.agp_flag[i] = self.ctx.heap.ptrs[r] + self.ctx.agflags_off + block
-        c.agp_counter = self._ag_counters[ridx].data_ptr()
-        c.agp_rows, c.agp_peers = rows, m.tp
-        c.ag_chunk = 128 * max(1, -(-rows // (128 * AG_CHUNKS)))
-        c.agp_only = int(push_only)
+        peers = [r for i, r in enumerate(self.tp_ranks) if i != m.tp_rank]
+        for i, r in enumerate(peers):
+            c.fwd_dst[i] = self.ctx.heap.ptrs[r] + off
+            c.fwd_flag[i] = self.ctx.heap.ptrs[r] + block
+        c.fwd_peers = len(peers)
+        if norm_w is None:
+            c.fwd_src, c.fwd_src_ld = x_shard.data_ptr(), cols
+        c.fwd_counter = self._ag_counter.data_ptr() + ridx * AG_CHUNKS * 4
         c.rs_rows = 0
         nv.lib().mmt_gemm_set_comm(ctypes.byref(c))
         y = F.gemm(gathered, w, b_mn=b_mn, bias=bias)

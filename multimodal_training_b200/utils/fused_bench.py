@@ -43,24 +43,29 @@ LINK_BPS = 770e9
 
 
 def _timed(fn, iters: int, warmup: int, flush: torch.Tensor | None) -> float:
-    """Median device milliseconds of fn over ``iters`` launches, max over ranks."""
+    """Median device milliseconds of fn over ``iters`` launches, max over ranks.
+
+    The launches are queued behind a short device-side delay, each between its own pair of events, so that the host
+    stays ahead of the device: the time between a pair of events is device time of fn alone (what it costs inside a
+    training step, where the host also runs ahead), not the host's time to issue fn's second kernel.  Before every
+    timed launch the L2 is flushed and a one-element all-reduce on the same stream lines the ranks up."""
     for _ in range(warmup):
         fn()
         dist.barrier()
     torch.cuda.synchronize()
     dist.barrier()
-    ts = []
-    for _ in range(iters):
+    tick = torch.zeros(1, device="cuda")
+    pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(iters)]
+    torch.cuda._sleep(3_000_000)               # ~1.5 ms at 1.9 GHz
+    for e0, e1 in pairs:
         if flush is not None:
             flush.zero_()
-        dist.barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        dist.all_reduce(tick)
         e0.record()
         fn()
         e1.record()
-        torch.cuda.synchronize()
-        ts.append(e0.elapsed_time(e1))
-    ts.sort()
+    torch.cuda.synchronize()
+    ts = sorted(e0.elapsed_time(e1) for e0, e1 in pairs)
     t = torch.tensor([ts[len(ts) // 2]], device="cuda")
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     return float(t.item())

@@ -44,7 +44,7 @@ class RecorderFC:
         self.keepalive.append(g)
         return g, (torch.ones(x_shard.shape[0]) if norm_w is not None else None), 0, e
 
-    def ag_gemm(self, x_shard, norm_w, eps, w, *, role, bias=None, b_mn=False, push_only=False):
+    def ag_gemm(self, x_shard, norm_w, eps, w, *, role, bias=None, b_mn=False):
         g, rstd, _, e = self.push_gather(x_shard, norm_w, eps, role)
         y = self.gemm_gathered(g, 0, e, x_shard.shape[0], w, b_mn=b_mn, bias=bias)
         return y, g, rstd

@@ -61,53 +61,54 @@ def test_allgather_gemm_with_fused_rmsnorm():
     assert nv.get_error()[0] == 0
 
 
-@pytest.mark.parametrize("tp,rows,K,N,norm", [(2, 300, 512, 384, True), (4, 1000, 1280, 640, False),
-                                               (2, 2048, 3584, 1152, True)])
-def test_allgather_inside_the_gemm(tp, rows, K, N, norm):
-    """The all-gather fused INTO the consuming GEMM: its epilogue warps push this rank's (normalised) rows into every
-    peer's buffer with one flag per 128-row chunk, its TMA producer waits per (source, chunk).  Ranks are emulated on
-    one GPU: every rank first runs the kernel in push-only mode (so that nobody ever waits for rows that have not
-    been stored), then the full kernel, which pushes again and consumes."""
+@pytest.mark.parametrize("direct", [False, True])
+@pytest.mark.parametrize("tp,rows,K,N", [(2, 512, 512, 384), (4, 1024, 1280, 640), (2, 2048, 3584, 1152),
+                                          (2, 2048, 3584, 9472), (2, 4096, 512, 5376), (4, 2048, 256, 5120)])
+def test_allgather_inside_the_gemm(tp, rows, K, N, direct):
+    """The all-gather fused INTO the consuming GEMM: the CTAs that compute the first column tile of this rank's own
+    rows forward every A tile they load to the peers' gather buffers (bulk stores from shared memory) and raise one
+    flag per row block; the TMA producer waits per (source rank, row block) before reading a peer's rows.  Ranks are
+    emulated on one GPU one after the other: the rows and flags a rank waits for are put in place by the host before
+    its launch (no launch ever waits for another), and what it forwards lands in separate buffers that are checked
+    afterwards.  ``direct``: own rows are read from the shard itself and also stored to the rank's own gather buffer."""
     F, nv, fused = _mods()
     torch.manual_seed(rows + K)
-    x = [torch.randn(rows, K, device=DEV, dtype=torch.bfloat16) for _ in range(tp)]
-    nw = (1 + 0.1 * torch.randn(K, device=DEV)).to(torch.bfloat16) if norm else None
+    counter = torch.zeros(64, device=DEV, dtype=torch.int32)
+    h = torch.randn(tp * rows, K, device=DEV, dtype=torch.bfloat16)
     w = [torch.randn(N, K, device=DEV, dtype=torch.bfloat16) * 0.05 for _ in range(tp)]
-    gather = [torch.full((tp * rows, K), float("nan"), device=DEV, dtype=torch.bfloat16) for _ in range(tp)]
-    flags = [torch.zeros(8 * 64, device=DEV, dtype=torch.int32) for _ in range(tp)]
-    counters = [torch.zeros(128, device=DEV, dtype=torch.int32) for _ in range(tp)]
-    rstd = [torch.empty(rows, device=DEV, dtype=torch.float32) for _ in range(tp)]
-    xf = torch.cat(x).float()
-    href = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-6) * nw.float() if norm else xf
-
-    def launch(r, push_only):
+    land = [torch.full((tp * rows, K), float("nan"), device=DEV, dtype=torch.bfloat16) for _ in range(tp)]
+    landflags = [torch.zeros(8 * 64, device=DEV, dtype=torch.int32) for _ in range(tp)]
+    for r in range(tp):
+        gathered = h.clone()
+        flags = torch.ones(8 * 64, device=DEV, dtype=torch.int32)          # every peer's blocks have "arrived"
         c = fused.GemmCommC()
-        c.ag_flags, c.ag_epoch, c.ag_rows, c.ag_self = flags[r].data_ptr(), 1, rows, r
-        c.agp_src, c.agp_w = x[r].data_ptr(), (nw.data_ptr() if norm else None)
-        c.agp_rstd, c.agp_eps = (rstd[r].data_ptr() if norm else None), 1e-6
-        for i in range(tp):
-            c.agp_dst[i] = gather[i].data_ptr()
-            c.agp_flag[i] = flags[i].data_ptr()
-        c.agp_counter, c.agp_rows, c.agp_peers = counters[r].data_ptr(), rows, tp
-        c.ag_chunk, c.agp_only, c.rs_rows = 128, int(push_only), 0
+        c.ag_flags, c.ag_epoch, c.ag_rows, c.ag_self, c.rs_rows = flags.data_ptr(), 1, rows, r, 0
+        peers = [q for q in range(tp) if q != r]
+        for i, q in enumerate(peers):
+            c.fwd_dst[i] = land[q].data_ptr()
+            c.fwd_flag[i] = landflags[q].data_ptr()
+        c.fwd_peers = len(peers)
+        c.fwd_counter = counter.data_ptr()
+        shard = h[r * rows:(r + 1) * rows].clone()
+        if direct:
+            gathered[r * rows:(r + 1) * rows] = float("nan")               # filled by the kernel itself
+            c.fwd_src, c.fwd_src_ld = shard.data_ptr(), K
         nv.lib().mmt_gemm_set_comm(ctypes.byref(c))
-        return F.gemm(gather[r], w[r])
-
-    for r in range(tp):
-        launch(r, True)
-    torch.cuda.synchronize()
-    n_chunks = -(-rows // 128)
-    for r in range(tp):
-        got = flags[r].view(8, 64)[:tp, :n_chunks]
-        assert bool((got == 1).all()) and int(flags[r].sum()) == tp * n_chunks      # exactly the chunks that exist
-        assert int(counters[r].abs().sum()) == 0                                   # counters are back at zero
-        assert rel(gather[r], href) < 1e-2                                         # every row of every rank landed
-    for r in range(tp):
-        y = launch(r, False)
-        assert rel(y, href @ w[r].float().t()) < 1e-2
-        if norm:
-            ref_rstd = torch.rsqrt(x[r].float().pow(2).mean(-1) + 1e-6)
-            assert rel(rstd[r], ref_rstd) < 1e-3
+        y = F.gemm(gathered, w[r])
+        torch.cuda.synchronize()
+        assert rel(y, h.float() @ w[r].float().t()) < 1e-2
+        assert torch.equal(gathered, h) and int(counter.abs().sum()) == 0
+    for q in range(tp):
+        got = landflags[q].view(8, 64)
+        for r in range(tp):
+            mine = land[q][r * rows:(r + 1) * rows]
+            if r == q:
+                assert bool(torch.isnan(mine).all()) and int(got[r].sum()) == 0      # nobody forwards to itself
+                continue
+            assert torch.equal(mine, h[r * rows:(r + 1) * rows])                    # bit-exact copies of the rows
+            n = int(got[r].sum())
+            assert n in (rows // 128, rows // 256) and bool((got[r, :n] == 1).all())  # one flag per tile-high block
+        assert int(got[tp:].sum()) == 0
     assert nv.get_error()[0] == 0
 
 
