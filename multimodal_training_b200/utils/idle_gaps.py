@@ -42,7 +42,23 @@ def summarize(intervals: list[tuple[float, float]], steps: int, gap_floor_us: fl
             "largest_gaps_us": [round(g, 1) for g in big[:5]]}
 
 
-def measure(step_fn, steps: int = 2, ready=None) -> dict:
+def short_name(name: str) -> str:
+    """Kernel name without its return type, namespaces' template arguments and parameter list."""
+    name = name.replace("(anonymous namespace)::", "").split("(")[0]
+    if name.startswith("void "):
+        name = name[5:]
+    depth, out = 0, []
+    for ch in name:                   # drop everything inside <...>
+        if ch == "<":
+            depth += 1
+        elif ch == ">":
+            depth -= 1
+        elif depth == 0:
+            out.append(ch)
+    return "".join(out).strip()[:80]
+
+
+def measure(step_fn, steps: int = 2, ready=None, top_kernels: int = 16) -> dict:
     """Run ``step_fn()`` ``steps`` times under a CUDA activity trace and summarise the device timeline.
 
     ``ready`` is called once the trace is recording and before the first step: in a multi-rank run pass a barrier,
@@ -59,11 +75,18 @@ def measure(step_fn, steps: int = 2, ready=None) -> dict:
             step_fn()
         torch.cuda.synchronize()
     iv = []
+    by_name: dict[str, list[float]] = {}
     for e in prof.events():
         if e.device_type == DeviceType.CUDA:
             r = e.time_range
             iv.append((float(r.start), float(r.end)))
+            acc = by_name.setdefault(short_name(e.name), [0.0, 0.0])
+            acc[0] += 1
+            acc[1] += float(r.end) - float(r.start)
     out = summarize(iv, steps)
+    top = sorted(by_name.items(), key=lambda kv: -kv[1][1])[:top_kernels]
+    out["top_kernels"] = [{"kernel": k, "launches_per_step": round(v[0] / steps, 1),
+                           "ms_per_step": round(v[1] / 1e3 / steps, 3)} for k, v in top]
     out["note"] = ("device timeline of this rank recorded with CUPTI activity tracing in a phase of its own after all "
                    "timed regions; tracing slows the host's launches, so the idle share is an upper bound")
     return out
