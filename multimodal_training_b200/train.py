@@ -121,23 +121,66 @@ def _run(cfg, vision_group, text_group, num_actors, parallel_size, dp_size) -> d
         text_group.execute_all("set_global_step", global_step)
     measured, measured_time, losses = 0, 0.0, []
     stop = False
+    # Steps whose losses have not been read yet.  Reading a loss makes the driver wait for the devices, so with
+    # training.log_interval > 1 it is done at the logging points only (and before checkpoints and at the end): in
+    # between, the actors' hosts run ahead of their GPUs and the launch latency of a step hides behind the previous
+    # step's kernels.  With log_interval = 1 every step is read at once, as in the reference's loop.
+    pending: list[dict] = []
+    t_mark = time.perf_counter()
+
+    def flush(log_line: bool) -> None:
+        nonlocal measured, measured_time, t_mark
+        if not pending:
+            return
+        outs = [[get(refs) for refs in p["text_refs"]] for p in pending]       # waits for the newest step
+        vmem = get(vision_group.execute_all_async("get_memory_stats"))
+        tmem = get(text_group.execute_all_async("get_memory_stats"))
+        dt = (time.perf_counter() - t_mark) / len(pending)
+        for p, micro_outs in zip(pending, outs):
+            loss = 0.0
+            for text_out in micro_outs:
+                step_losses = [float(o["loss"]) for o in text_out]
+                loss += sum(step_losses) / len(step_losses) / accum
+            p["loss"], p["text_out"] = loss, micro_outs[-1]
+            losses.append(loss)
+            if not p["is_warmup"]:
+                measured += 1
+                measured_time += dt
+            for refs in p["text_refs"]:
+                text_group.free(refs)
+        p = pending[-1]
+        if log_line:
+            avg = lambda xs, k: sum(x[k] for x in xs) / len(xs)  # noqa: E731
+            line = (f"Epoch {p['epoch'] + 1}/{num_epochs}, Iter {p['iteration'] + 1}/{num_iterations} "
+                    f"({'warmup' if p['is_warmup'] else 'training'}) - Loss: {p['loss']:.4f}, "
+                    f"Iteration time: {dt:.3f}s")
+            if profile_time:
+                line += (f", Vision fwd: {avg(p['vision_fwd'], 'forward_time_ms'):.1f}ms, "
+                         f"Vision bwd: {avg(p['vision_bwd'], 'backward_time_ms'):.1f}ms, "
+                         f"Text fwd: {avg(p['text_out'], 'forward_time_ms'):.1f}ms, "
+                         f"Text bwd: {avg(p['text_bwd'], 'backward_time_ms'):.1f}ms")
+            if p["global_norm"] is not None:
+                line += f", Grad norm: {p['global_norm']:.4f}"
+            line += (f", Vision mem: {avg(vmem, 'allocated_mb'):.0f} MB (peak {avg(vmem, 'peak_mb'):.0f}), "
+                     f"Text mem: {avg(tmem, 'allocated_mb'):.0f} MB (peak {avg(tmem, 'peak_mb'):.0f})")
+            log.info(line)
+        pending.clear()
+        t_mark = time.perf_counter()
+
     for epoch in range(start_epoch, num_epochs):
         for iteration in range(start_iteration if epoch == start_epoch else 0, num_iterations):
             is_warmup = global_step < warmup_steps
-            t0 = time.perf_counter()
             vision_group.execute_all("zero_grad")
             text_group.execute_all("zero_grad")
-            loss = 0.0
+            kept_text_refs = []
             for micro in range(accum):
                 if micro:
                     vision_group.free(vision_refs + vision_bwd_refs)
-                    text_group.free(text_refs + text_bwd_refs)
+                    text_group.free(text_bwd_refs)
                 idx = global_step * accum + micro
                 vision_refs = vision_group.execute_all_async("forward_step", idx)
                 text_refs = text_group.execute_all_async("forward_step", vision_refs, [idx] * num_actors)
-                text_out = get(text_refs)
-                step_losses = [float(o["loss"]) for o in text_out]
-                loss += sum(step_losses) / len(step_losses) / accum
+                kept_text_refs.append(text_refs)
                 text_bwd_refs = text_group.execute_all_async("backward_step")
                 vision_bwd_refs = vision_group.execute_all_async("backward_step", text_bwd_refs)
                 text_bwd, vision_bwd = get(text_bwd_refs), get(vision_bwd_refs)
@@ -148,39 +191,28 @@ def _run(cfg, vision_group, text_group, num_actors, parallel_size, dp_size) -> d
                 global_norm = aggregate_grad_norms(vn, tn, dp_size, parallel_size)
             text_group.execute_all("optimizer_step", global_norm)
             vision_group.execute_all("optimizer_step", global_norm)
-            vmem = get(vision_group.execute_all_async("get_memory_stats"))
-            tmem = get(text_group.execute_all_async("get_memory_stats"))
-            dt = time.perf_counter() - t0
-            if not is_warmup:
-                measured += 1
-                measured_time += dt
-            losses.append(loss)
-            if iteration % log_interval == 0:
-                avg = lambda xs, k: sum(x[k] for x in xs) / len(xs)  # noqa: E731
-                line = (f"Epoch {epoch + 1}/{num_epochs}, Iter {iteration + 1}/{num_iterations} "
-                        f"({'warmup' if is_warmup else 'training'}) - Loss: {loss:.4f}, Iteration time: {dt:.3f}s")
-                if profile_time:
-                    vf = avg(get(vision_refs), "forward_time_ms")
-                    line += (f", Vision fwd: {vf:.1f}ms, Vision bwd: {avg(vision_bwd, 'backward_time_ms'):.1f}ms, "
-                             f"Text fwd: {avg(text_out, 'forward_time_ms'):.1f}ms, "
-                             f"Text bwd: {avg(text_bwd, 'backward_time_ms'):.1f}ms")
-                if global_norm is not None:
-                    line += f", Grad norm: {global_norm:.4f}"
-                line += (f", Vision mem: {avg(vmem, 'allocated_mb'):.0f} MB (peak {avg(vmem, 'peak_mb'):.0f}), "
-                         f"Text mem: {avg(tmem, 'allocated_mb'):.0f} MB (peak {avg(tmem, 'peak_mb'):.0f})")
-                log.info(line)
+            log_now = iteration % log_interval == 0
+            pending.append({"epoch": epoch, "iteration": iteration, "is_warmup": is_warmup, "text_refs": kept_text_refs,
+                            "global_norm": global_norm, "text_bwd": text_bwd, "vision_bwd": vision_bwd,
+                            "vision_fwd": get(vision_refs) if (profile_time and log_now) else None})
+            if log_now or len(pending) >= 8:
+                flush(log_now)
             vision_group.free(vision_refs + vision_bwd_refs)
-            text_group.free(text_refs + text_bwd_refs)
+            text_group.free(text_bwd_refs)
             global_step += 1
             last_of_epoch = iteration + 1 == num_iterations
             if use_ckpt and save_every and global_step % save_every == 0 and not last_of_epoch:
+                flush(False)
                 save_step_checkpoint(checkpoint_dir, global_step, epoch, iteration + 1, vision_group, text_group, cfg,
                                      keep=keep_steps)
+                t_mark = time.perf_counter()
             if max_steps and global_step >= max_steps:
                 stop = True
                 break
+        flush(False)
         if use_ckpt and global_step == (epoch + 1) * num_iterations:       # the epoch ran to its end
             save_epoch_checkpoint(checkpoint_dir, epoch, vision_group, text_group, cfg)
+            t_mark = time.perf_counter()
         if stop:
             log.info("Stopping after %d steps (training.max_steps)", global_step)
             break
