@@ -121,6 +121,9 @@ def main() -> int:
     ap.add_argument("--model", default="qwen2_5_vl_7b")
     ap.add_argument("--image-size", type=int, default=896)
     ap.add_argument("--text-tokens", type=int, default=1024)
+    ap.add_argument("--image-sizes", default="", help="comma-separated image sizes drawn per sample, new ones every "
+                    "step (ragged run: no two steps have the same shapes; the library arm is skipped)")
+    ap.add_argument("--text-token-choices", default="", help="comma-separated text lengths drawn per sample")
     ap.add_argument("--per-gpu-batch", type=int, default=1)
     ap.add_argument("--global-batch", type=int, default=0, help="overrides --per-gpu-batch x N (other configs)")
     ap.add_argument("--tp", type=int, default=0, help="text tensor-parallel size (default min(N, 4))")
@@ -176,7 +179,7 @@ def main() -> int:
 
     # ------------------------------------------------------------------ library baseline (this arm only, or first)
     lib = None
-    if args.impl == "lib" or not args.no_lib_arm:
+    if args.impl == "lib" or not (args.no_lib_arm or args.image_sizes or args.text_token_choices):
         lib_steps = args.steps if args.impl == "lib" else (args.lib_steps or min(args.steps, 10))
         sampler, fh = (None, None)
         if rank == 0 and args.impl == "lib":
@@ -236,6 +239,13 @@ def main() -> int:
         f"+data.synthetic.global_batch={global_batch}", "+data.synthetic.repeat=2",
         f"training.fused_comm={'false' if args.no_fused_comm else 'true'}",
     ]
+    ragged = bool(args.image_sizes or args.text_token_choices)
+    if ragged:
+        ov += ["+data.synthetic.repeat=0"]
+        if args.image_sizes:
+            ov.append(f"+data.synthetic.image_sizes={args.image_sizes}")
+        if args.text_token_choices:
+            ov.append(f"+data.synthetic.text_token_choices={args.text_token_choices}")
     ckpt = {"auto": "auto", "on": "true", "off": "false"}[args.activation_checkpointing]
     ov += [f"vision.activation_checkpointing={ckpt}", f"text.activation_checkpointing={ckpt}"]
     if args.symm_heap_mb:
@@ -385,6 +395,11 @@ def main() -> int:
         ctx = engine.vision.step_context(0)
         patches = ctx.n_vision_patches_global
         llm_tokens = ctx.n_text_tokens_global
+        if ragged:
+            # shapes differ from step to step: the mean over the steps of the device-timed region
+            ctxs = [engine.vision.step_context(args.warmup + s) for s in range(args.steps)]
+            patches = sum(c.n_vision_patches_global for c in ctxs) / len(ctxs)
+            llm_tokens = sum(c.n_text_tokens_global for c in ctxs) / len(ctxs)
         ms_per_step = dev_ms / args.steps
         value = patches / (ms_per_step / 1e3)
         e2e_value = patches / (e2e_ms / args.steps / 1e3)
@@ -414,8 +429,10 @@ def main() -> int:
                               "states, N GPUs hold 1/N each, so this part shrinks with N under weak scaling",
             "config": {
                 "model": args.model, "global_batch": global_batch, "seq_len": args.text_tokens + patches // global_batch // 4,
-                "image": f"{args.image_size}x{args.image_size}", "vision_patches_per_sample": patches // global_batch,
-                "text_tokens_per_sample": args.text_tokens, "parallelism": par,
+                "image": (f"{args.image_size}x{args.image_size}" if not args.image_sizes
+                          else f"square, side drawn per sample from {{{args.image_sizes}}}, new shapes every step"),
+                "vision_patches_per_sample": patches // global_batch,
+                "text_tokens_per_sample": args.text_token_choices or args.text_tokens, "parallelism": par,
                 "optimizer": "AdamW fp32 master+moments, ZeRO-1",
                 "activation_checkpointing": {
                     "setting": args.activation_checkpointing,

@@ -148,6 +148,11 @@ def _run(cfg, vision_group, text_group, num_actors, parallel_size, dp_size) -> d
                 measured_time += dt
             for refs in p["text_refs"]:
                 text_group.free(refs)
+            for group, refs in p["acks"]:
+                get(refs)
+                group.free(refs)
+            for group, refs in p["late_free"]:
+                group.free(refs)
         p = pending[-1]
         if log_line:
             avg = lambda xs, k: sum(x[k] for x in xs) / len(xs)  # noqa: E731
@@ -170,9 +175,12 @@ def _run(cfg, vision_group, text_group, num_actors, parallel_size, dp_size) -> d
     for epoch in range(start_epoch, num_epochs):
         for iteration in range(start_iteration if epoch == start_epoch else 0, num_iterations):
             is_warmup = global_step < warmup_steps
-            vision_group.execute_all("zero_grad")
-            text_group.execute_all("zero_grad")
+            # calls whose results the driver does not need are only queued (the hosts execute an actor's calls in
+            # order); their acknowledgements are collected at the next logging point, where a failure would surface
+            acks = [(vision_group, vision_group.execute_all_async("zero_grad")),
+                    (text_group, text_group.execute_all_async("zero_grad"))]
             kept_text_refs = []
+            log_now = iteration % log_interval == 0
             for micro in range(accum):
                 if micro:
                     vision_group.free(vision_refs + vision_bwd_refs)
@@ -183,22 +191,27 @@ def _run(cfg, vision_group, text_group, num_actors, parallel_size, dp_size) -> d
                 kept_text_refs.append(text_refs)
                 text_bwd_refs = text_group.execute_all_async("backward_step")
                 vision_bwd_refs = vision_group.execute_all_async("backward_step", text_bwd_refs)
-                text_bwd, vision_bwd = get(text_bwd_refs), get(vision_bwd_refs)
+                # the text half's result carries the gradient for the vision half: it stays in the actors' object
+                # table (fetching it would copy it to the driver); waiting for the vision half covers both
+                vision_bwd = get(vision_bwd_refs) if (log_now or clip or micro + 1 < accum) else None
+                text_bwd = get(text_bwd_refs) if (profile_time and log_now) else None
             global_norm = None
             if clip:
                 vn = vision_group.execute_all("compute_grad_norm_contribution")
                 tn = text_group.execute_all("compute_grad_norm_contribution")
                 global_norm = aggregate_grad_norms(vn, tn, dp_size, parallel_size)
-            text_group.execute_all("optimizer_step", global_norm)
-            vision_group.execute_all("optimizer_step", global_norm)
-            log_now = iteration % log_interval == 0
+            acks.append((text_group, text_group.execute_all_async("optimizer_step", global_norm)))
+            acks.append((vision_group, vision_group.execute_all_async("optimizer_step", global_norm)))
             pending.append({"epoch": epoch, "iteration": iteration, "is_warmup": is_warmup, "text_refs": kept_text_refs,
+                            "acks": acks, "late_free": [] if vision_bwd is not None else
+                            [(vision_group, vision_refs + vision_bwd_refs), (text_group, text_bwd_refs)],
                             "global_norm": global_norm, "text_bwd": text_bwd, "vision_bwd": vision_bwd,
                             "vision_fwd": get(vision_refs) if (profile_time and log_now) else None})
             if log_now or len(pending) >= 8:
                 flush(log_now)
-            vision_group.free(vision_refs + vision_bwd_refs)
-            text_group.free(text_bwd_refs)
+            if vision_bwd is not None:            # otherwise freed at the next logging point, once the calls have run
+                vision_group.free(vision_refs + vision_bwd_refs)
+                text_group.free(text_bwd_refs)
             global_step += 1
             last_of_epoch = iteration + 1 == num_iterations
             if use_ckpt and save_every and global_step % save_every == 0 and not last_of_epoch:
