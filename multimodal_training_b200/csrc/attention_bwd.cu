@@ -2,19 +2,15 @@
 //
 // Three launches, no atomics, deterministic:
 //   1. delta[h, t] = sum_d out[t,h,d] * dout[t,h,d]
-//   2. dK/dV: one CTA per (128-row KV tile, kv head).  For every q head of the GQA group and every
-//      128-row query tile that can see the KV tile:
-//         S  = Q K^T,  dP = dO V^T                (tcgen05, operands K-major, results in tensor memory)
-//         P  = exp(S*scale - lse),  dS = P * (dP - delta) * scale      (one thread per query row)
-//         dV += P^T dO,  dK += dS^T Q             (P/dS in shared memory as MN-major A operands,
-//                                                  dO/Q as MN-major B operands; accumulators stay in
-//                                                  tensor memory across the whole loop)
-//   3. dQ: one CTA per (128-row query tile, q head), looping over KV tiles:
-//         S, dP, P, dS as above;  dQ += dS K      (dS K-major A operand, K MN-major B operand)
-// Every tile is two 64-column TMA boxes, usable as a K-major or an MN-major operand, so Q, K, V and
-// dO are fetched once per use with no transposes.
-// Steps 2 and 3 exist in two generations; the second (2b, 3b below: transposed scores, P^T / dS^T / dS as
-// tensor-memory operands, double-buffered score tiles, eight softmax warps) is the default.
+//   2. dK/dV: one CTA per (128-row KV tile, kv head), looping over the q heads of the GQA group and over blocks
+//      of 64 queries that can see the KV tile; transposed scores S^T = K Q^T and dP^T = V dO^T in tensor memory,
+//      P^T and dS^T written back over them as packed bf16 and used as tensor-memory A operands of
+//      dV += P^T dO and dK += dS^T Q, whose accumulators stay in tensor memory across the whole loop
+//   3. dQ: one CTA per (128-row query tile, q head), looping over KV tiles with the same pipeline
+//      (dQ += dS K, dS as a tensor-memory operand)
+// P = exp(S * scale - lse) and dS = P * (dP - delta) * scale are recomputed from the saved log-sum-exp.
+// Every tile is fetched as 64-column TMA boxes that serve as K-major or MN-major operands, so Q, K, V and dO
+// need no transposes.  Details at the kernels.
 #include "attention_common.cuh"
 
 namespace {
@@ -68,209 +64,6 @@ MMT_DEVICE void store_chunk(uint8_t* tile, int row, int c, const uint32_t (&pk)[
         make_uint4(pk[g * 4], pk[g * 4 + 1], pk[g * 4 + 2], pk[g * 4 + 3]);
 }
 
-// ----------------------------------------------------------------------------------------------
-// 2. dK / dV
-// ----------------------------------------------------------------------------------------------
-template <int DIM>
-__global__ void __launch_bounds__(kThreads, 1)
-attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant__ CUtensorMap tm_do,
-                     const AttnParams p) {
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* sK = smem;
-  uint8_t* sV = sK + 2 * CHUNK;
-  uint8_t* sQ = sV + 2 * CHUNK;
-  uint8_t* sDO = sQ + 2 * CHUNK;
-  uint8_t* sP = sDO + 2 * CHUNK;
-  uint8_t* sDS = sP + 2 * CHUNK;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sDS + 2 * CHUNK);
-  uint64_t* kv_full = bars;        // K and V landed
-  uint64_t* qdo_full = bars + 1;   // Q_i and dO_i landed
-  uint64_t* sdp_full = bars + 2;   // S and dP are in tensor memory
-  uint64_t* sdp_empty = bars + 3;  // softmax threads have read S and dP (4 warps)
-  uint64_t* pds_full = bars + 4;   // P and dS are in shared memory (4 warps)
-  uint64_t* mma2_done = bars + 5;  // dV / dK MMAs of the iteration finished: Q, dO, P, dS reusable
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6);
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int kv0 = blockIdx.x * BKV;
-  // grid.y = kv heads, each CTA looping over the q heads of its group; or, with a partial-sum workspace,
-  // grid.y = q heads (group times more CTAs for short sequences), each CTA writing its own fp32 partial
-  const bool split = p.ws_dk != nullptr;
-  const int full_group = p.n_q / p.n_kv;
-  const int kv_head = split ? (int)blockIdx.y / full_group : (int)blockIdx.y;
-  const int head0 = split ? (int)blockIdx.y : kv_head * full_group;
-  const int group = split ? 1 : full_group;
-  const int kv_last = min(kv0 + BKV, p.T) - 1;
-  const int q_lo = p.causal ? kv0 : p.seq_lo[kv0];
-  const int q_hi = p.seq_hi[kv_last];
-  const int n_qt = (q_hi - q_lo + BQ - 1) / BQ;
-  const int n_iter = n_qt * group;
-  const int xk = (p.n_q + kv_head) * DIM, xv = (p.n_q + p.n_kv + kv_head) * DIM;
-
-  if (threadIdx.x == 0) {
-    tma_prefetch_desc(&tm_qkv);
-    tma_prefetch_desc(&tm_do);
-    mbar_init(kv_full, 1);
-    mbar_init(qdo_full, 1);
-    mbar_init(sdp_full, 1);
-    mbar_init(sdp_empty, 4);
-    mbar_init(pds_full, 4);
-    mbar_init(mma2_done, 1);
-    mbar_fence_init();
-  }
-  if (warp == 5) {
-    tmem_alloc(tmem_slot, 512);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
-  const uint32_t t_s = tmem_base, t_dp = tmem_base + 128, t_dv = tmem_base + 256, t_dk = tmem_base + 384;
-
-  if (warp == 4) {
-    if (lane == 0) {
-      mbar_expect_tx(kv_full, 4 * CHUNK);
-      tma_load_2d(sK, &tm_qkv, kv_full, xk, kv0);
-      tma_load_2d(sK + CHUNK, &tm_qkv, kv_full, xk + 64, kv0);
-      tma_load_2d(sV, &tm_qkv, kv_full, xv, kv0);
-      tma_load_2d(sV + CHUNK, &tm_qkv, kv_full, xv + 64, kv0);
-      for (int it = 0; it < n_iter; ++it) {
-        const int g = it / n_qt, i = it % n_qt;
-        const int head = head0 + g;
-        const int r0 = q_lo + i * BQ;
-        if (!mbar_wait(mma2_done, (it & 1) ^ 1, p.ew, 700)) break;
-        mbar_expect_tx(qdo_full, 4 * CHUNK);
-        tma_load_2d(sQ, &tm_qkv, qdo_full, head * DIM, r0);
-        tma_load_2d(sQ + CHUNK, &tm_qkv, qdo_full, head * DIM + 64, r0);
-        tma_load_2d(sDO, &tm_do, qdo_full, head * DIM, r0);
-        tma_load_2d(sDO + CHUNK, &tm_do, qdo_full, head * DIM + 64, r0);
-      }
-    }
-  } else if (warp == 5) {
-    if (lane == 0) {
-      const uint32_t idesc_s = make_idesc_bf16(BQ, BKV, 0, 0);
-      const uint32_t idesc_t = make_idesc_bf16(BKV, DIM, 1, 1);
-      const uint32_t k_base = smem_u32(sK), v_base = smem_u32(sV), q_base = smem_u32(sQ), do_base = smem_u32(sDO);
-      const uint32_t p_base = smem_u32(sP), ds_base = smem_u32(sDS);
-      bool ok = mbar_wait(kv_full, 0, p.ew, 710);
-      for (int it = 0; it < n_iter && ok; ++it) {
-        const uint32_t ph = it & 1;
-        if (!mbar_wait(qdo_full, ph, p.ew, 711)) break;
-        if (!mbar_wait(sdp_empty, ph ^ 1, p.ew, 712)) break;
-        tc_fence_after();
-#pragma unroll
-        for (int k = 0; k < DIM / 16; ++k)
-          tc_mma_ss(t_s, desc_kmajor(q_base, k), desc_kmajor(k_base, k), idesc_s, k != 0);
-#pragma unroll
-        for (int k = 0; k < DIM / 16; ++k)
-          tc_mma_ss(t_dp, desc_kmajor(do_base, k), desc_kmajor(v_base, k), idesc_s, k != 0);
-        tc_commit(sdp_full);
-        if (!mbar_wait(pds_full, ph, p.ew, 713)) break;
-        tc_fence_after();
-#pragma unroll
-        for (int k = 0; k < BQ / 16; ++k)
-          tc_mma_ss(t_dv, desc_mnmajor(p_base, k), desc_mnmajor(do_base, k), idesc_t, (it | k) != 0);
-#pragma unroll
-        for (int k = 0; k < BQ / 16; ++k)
-          tc_mma_ss(t_dk, desc_mnmajor(ds_base, k), desc_mnmajor(q_base, k), idesc_t, (it | k) != 0);
-        tc_commit(mma2_done);
-      }
-    }
-  } else {
-    const int row = warp * 32 + lane;
-    const uint32_t lane_addr = ((uint32_t)(warp * 32) << 16);
-    const float sl2 = p.scale * LOG2E;
-    bool ok = true;
-    for (int it = 0; it < n_iter; ++it) {
-      const int g = it / n_qt, i = it % n_qt;
-      const int head = head0 + g;
-      const int qrow = q_lo + i * BQ + row;
-      const bool row_ok = qrow < q_hi;
-      int lo = 0, hi = 0;
-      float lse_l2 = 0.f, delta = 0.f;
-      if (row_ok) {
-        lo = p.seq_lo[qrow];
-        hi = p.seq_hi[qrow];
-        if (p.causal) hi = min(hi, qrow + 1);
-        lse_l2 = p.lse[(long)head * p.T + qrow] * LOG2E;
-        delta = p.delta[(long)head * p.T + qrow];
-      }
-      ok = __all_sync(0xffffffffu, mbar_wait(sdp_full, it & 1, p.ew, 720));
-      if (!ok) break;
-      tc_fence_after();
-      // P / dS of the previous iteration must have been consumed before they are overwritten
-      ok = __all_sync(0xffffffffu, mbar_wait(mma2_done, (it & 1) ^ 1, p.ew, 721));
-      if (!ok) break;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r_s[32], r_dp[32], pk_p[16], pk_ds[16];
-        tmem_ld_32x32b_x32(t_s + lane_addr + c * 32, r_s);
-        tmem_ld_32x32b_x32(t_dp + lane_addr + c * 32, r_dp);
-        tmem_wait_ld();
-        p_ds_chunk(r_s, r_dp, kv0 + c * 32, lo, hi, sl2, lse_l2, delta, p.scale, pk_p, pk_ds);
-        store_chunk(sP, row, c, pk_p);
-        store_chunk(sDS, row, c, pk_ds);
-      }
-      tc_fence_before();
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(sdp_empty);
-        mbar_arrive(pds_full);
-      }
-    }
-    // epilogue: thread = kv row
-    if (ok) {
-      if (n_iter > 0) ok = __all_sync(0xffffffffu, mbar_wait(mma2_done, (n_iter - 1) & 1, p.ew, 722));
-      tc_fence_after();
-      const int kvrow = kv0 + row;
-      __nv_bfloat16* dk_dst = p.dqkv + (long)kvrow * p.ld + xk;
-      __nv_bfloat16* dv_dst = p.dqkv + (long)kvrow * p.ld + xv;
-#pragma unroll 1
-      for (int c = 0; c < DIM / 16; ++c) {
-        uint32_t rk[16], rv[16];
-        if (n_iter > 0 && ok) {
-          tmem_ld_32x32b_x16(t_dk + lane_addr + c * 16, rk);
-          tmem_ld_32x32b_x16(t_dv + lane_addr + c * 16, rv);
-          tmem_wait_ld();
-        } else {
-#pragma unroll
-          for (int i = 0; i < 16; ++i) rk[i] = rv[i] = 0u;
-        }
-        if (kvrow < p.T && split) {
-          float* wk = p.ws_dk + ((long)head0 * p.T + kvrow) * DIM + c * 16;
-          float* wv = p.ws_dv + ((long)head0 * p.T + kvrow) * DIM + c * 16;
-#pragma unroll
-          for (int i = 0; i < 16; i += 4) {
-            *reinterpret_cast<uint4*>(wk + i) = make_uint4(rk[i], rk[i + 1], rk[i + 2], rk[i + 3]);
-            *reinterpret_cast<uint4*>(wv + i) = make_uint4(rv[i], rv[i + 1], rv[i + 2], rv[i + 3]);
-          }
-        } else if (kvrow < p.T) {
-#pragma unroll
-          for (int h2 = 0; h2 < 2; ++h2) {
-            uint4 a, b;
-            a.x = pack_bf16x2(__uint_as_float(rk[h2 * 8 + 0]), __uint_as_float(rk[h2 * 8 + 1]));
-            a.y = pack_bf16x2(__uint_as_float(rk[h2 * 8 + 2]), __uint_as_float(rk[h2 * 8 + 3]));
-            a.z = pack_bf16x2(__uint_as_float(rk[h2 * 8 + 4]), __uint_as_float(rk[h2 * 8 + 5]));
-            a.w = pack_bf16x2(__uint_as_float(rk[h2 * 8 + 6]), __uint_as_float(rk[h2 * 8 + 7]));
-            b.x = pack_bf16x2(__uint_as_float(rv[h2 * 8 + 0]), __uint_as_float(rv[h2 * 8 + 1]));
-            b.y = pack_bf16x2(__uint_as_float(rv[h2 * 8 + 2]), __uint_as_float(rv[h2 * 8 + 3]));
-            b.z = pack_bf16x2(__uint_as_float(rv[h2 * 8 + 4]), __uint_as_float(rv[h2 * 8 + 5]));
-            b.w = pack_bf16x2(__uint_as_float(rv[h2 * 8 + 6]), __uint_as_float(rv[h2 * 8 + 7]));
-            *reinterpret_cast<uint4*>(dk_dst + c * 16 + h2 * 8) = a;
-            *reinterpret_cast<uint4*>(dv_dst + c * 16 + h2 * 8) = b;
-          }
-        }
-      }
-    }
-  }
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 5) tmem_dealloc(tmem_base, 512);
-}
-
 // dK / dV of a GQA group = sum of its q heads' fp32 partials, in head order (deterministic), rounded once.
 __global__ void attn_group_reduce_kernel(const float* __restrict__ ws_dk, const float* __restrict__ ws_dv,
                                          __nv_bfloat16* __restrict__ dqkv, int T, int n_q, int n_kv, int dim, long ld) {
@@ -297,197 +90,11 @@ __global__ void attn_group_reduce_kernel(const float* __restrict__ ws_dk, const 
 }
 
 // ----------------------------------------------------------------------------------------------
-// 3. dQ
-// ----------------------------------------------------------------------------------------------
-template <int DIM>
-__global__ void __launch_bounds__(kThreads, 1)
-attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant__ CUtensorMap tm_do,
-                   const AttnParams p) {
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* sQ = smem;
-  uint8_t* sDO = sQ + 2 * CHUNK;
-  uint8_t* sK = sDO + 2 * CHUNK;    // 2 stages
-  uint8_t* sV = sK + 4 * CHUNK;     // 1 stage (12 boxes in total: the shared-memory budget of the launch)
-  uint8_t* sDS = sV + 2 * CHUNK;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sDS + 2 * CHUNK);
-  uint64_t* qdo_full = bars;       // 1
-  uint64_t* k_full = bars + 1;     // 2
-  uint64_t* k_empty = bars + 3;    // 2
-  uint64_t* v_full = bars + 5;     // 1 (bars + 6 unused)
-  uint64_t* v_empty = bars + 7;    // 1 (bars + 8 unused)
-  uint64_t* sdp_full = bars + 9;
-  uint64_t* sdp_empty = bars + 10;
-  uint64_t* ds_full = bars + 11;
-  uint64_t* dq_done = bars + 12;   // dQ MMA of the iteration finished: dS reusable
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int q0 = blockIdx.x * BQ;
-  const int head = blockIdx.y;
-  const int kv_head = head / (p.n_q / p.n_kv);
-  const int q_last = min(q0 + BQ, p.T) - 1;
-  const int kv_lo = p.seq_lo[q0];
-  const int kv_hi = p.causal ? min(p.seq_hi[q_last], q_last + 1) : p.seq_hi[q_last];
-  const int n_tiles = (kv_hi - kv_lo + BKV - 1) / BKV;
-  const int xq = head * DIM, xk = (p.n_q + kv_head) * DIM, xv = (p.n_q + p.n_kv + kv_head) * DIM;
-
-  if (threadIdx.x == 0) {
-    tma_prefetch_desc(&tm_qkv);
-    tma_prefetch_desc(&tm_do);
-    mbar_init(qdo_full, 1);
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&k_full[i], 1);
-      mbar_init(&k_empty[i], 1);
-    }
-    mbar_init(v_full, 1);
-    mbar_init(v_empty, 1);
-    mbar_init(sdp_full, 1);
-    mbar_init(sdp_empty, 4);
-    mbar_init(ds_full, 4);
-    mbar_init(dq_done, 1);
-    mbar_fence_init();
-  }
-  if (warp == 5) {
-    tmem_alloc(tmem_slot, 512);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
-  const uint32_t t_s = tmem_base, t_dp = tmem_base + 128, t_dq = tmem_base + 256;
-
-  if (warp == 4) {
-    if (lane == 0) {
-      mbar_expect_tx(qdo_full, 4 * CHUNK);
-      tma_load_2d(sQ, &tm_qkv, qdo_full, xq, q0);
-      tma_load_2d(sQ + CHUNK, &tm_qkv, qdo_full, xq + 64, q0);
-      tma_load_2d(sDO, &tm_do, qdo_full, xq, q0);
-      tma_load_2d(sDO + CHUNK, &tm_do, qdo_full, xq + 64, q0);
-      for (int j = 0; j < n_tiles; ++j) {
-        const int s = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        const int r0 = kv_lo + j * BKV;
-        if (!mbar_wait(&k_empty[s], ph ^ 1, p.ew, 800)) break;
-        mbar_expect_tx(&k_full[s], 2 * CHUNK);
-        tma_load_2d(sK + s * 2 * CHUNK, &tm_qkv, &k_full[s], xk, r0);
-        tma_load_2d(sK + s * 2 * CHUNK + CHUNK, &tm_qkv, &k_full[s], xk + 64, r0);
-        if (!mbar_wait(v_empty, (j & 1) ^ 1, p.ew, 801)) break;
-        mbar_expect_tx(v_full, 2 * CHUNK);
-        tma_load_2d(sV, &tm_qkv, v_full, xv, r0);
-        tma_load_2d(sV + CHUNK, &tm_qkv, v_full, xv + 64, r0);
-      }
-    }
-  } else if (warp == 5) {
-    if (lane == 0) {
-      const uint32_t idesc_s = make_idesc_bf16(BQ, BKV, 0, 0);
-      const uint32_t idesc_dq = make_idesc_bf16(BQ, DIM, 0, 1);
-      const uint32_t q_base = smem_u32(sQ), do_base = smem_u32(sDO), ds_base = smem_u32(sDS);
-      bool ok = mbar_wait(qdo_full, 0, p.ew, 810);
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        const int s = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        const uint32_t k_base = smem_u32(sK + s * 2 * CHUNK), v_base = smem_u32(sV);
-        if (!mbar_wait(&k_full[s], ph, p.ew, 811)) break;
-        if (!mbar_wait(v_full, j & 1, p.ew, 812)) break;
-        if (!mbar_wait(sdp_empty, (j & 1) ^ 1, p.ew, 813)) break;
-        tc_fence_after();
-#pragma unroll
-        for (int k = 0; k < DIM / 16; ++k)
-          tc_mma_ss(t_s, desc_kmajor(q_base, k), desc_kmajor(k_base, k), idesc_s, k != 0);
-#pragma unroll
-        for (int k = 0; k < DIM / 16; ++k)
-          tc_mma_ss(t_dp, desc_kmajor(do_base, k), desc_kmajor(v_base, k), idesc_s, k != 0);
-        tc_commit(sdp_full);
-        tc_commit(v_empty);
-        if (!mbar_wait(ds_full, j & 1, p.ew, 814)) break;
-        tc_fence_after();
-#pragma unroll
-        for (int k = 0; k < BKV / 16; ++k)
-          tc_mma_ss(t_dq, desc_kmajor(ds_base, k), desc_mnmajor(k_base, k), idesc_dq, (j | k) != 0);
-        tc_commit(dq_done);
-        tc_commit(&k_empty[s]);
-      }
-    }
-  } else {
-    const int row = warp * 32 + lane;
-    const int qrow = q0 + row;
-    const bool row_ok = qrow < p.T;
-    const uint32_t lane_addr = ((uint32_t)(warp * 32) << 16);
-    const float sl2 = p.scale * LOG2E;
-    int lo = 0, hi = 0;
-    float lse_l2 = 0.f, delta = 0.f;
-    if (row_ok) {
-      lo = p.seq_lo[qrow];
-      hi = p.seq_hi[qrow];
-      if (p.causal) hi = min(hi, qrow + 1);
-      lse_l2 = p.lse[(long)head * p.T + qrow] * LOG2E;
-      delta = p.delta[(long)head * p.T + qrow];
-    }
-    bool ok = true;
-    for (int j = 0; j < n_tiles; ++j) {
-      const int kv0 = kv_lo + j * BKV;
-      ok = __all_sync(0xffffffffu, mbar_wait(sdp_full, j & 1, p.ew, 820));
-      if (!ok) break;
-      tc_fence_after();
-      ok = __all_sync(0xffffffffu, mbar_wait(dq_done, (j & 1) ^ 1, p.ew, 821));
-      if (!ok) break;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r_s[32], r_dp[32], pk_p[16], pk_ds[16];
-        tmem_ld_32x32b_x32(t_s + lane_addr + c * 32, r_s);
-        tmem_ld_32x32b_x32(t_dp + lane_addr + c * 32, r_dp);
-        tmem_wait_ld();
-        p_ds_chunk(r_s, r_dp, kv0 + c * 32, lo, hi, sl2, lse_l2, delta, p.scale, pk_p, pk_ds);
-        store_chunk(sDS, row, c, pk_ds);
-      }
-      tc_fence_before();
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(sdp_empty);
-        mbar_arrive(ds_full);
-      }
-    }
-    if (ok) {
-      if (n_tiles > 0) ok = __all_sync(0xffffffffu, mbar_wait(dq_done, (n_tiles - 1) & 1, p.ew, 822));
-      tc_fence_after();
-      __nv_bfloat16* dst = p.dqkv + (long)qrow * p.ld + xq;
-#pragma unroll 1
-      for (int c = 0; c < DIM / 16; ++c) {
-        uint32_t r[16];
-        if (n_tiles > 0 && ok) {
-          tmem_ld_32x32b_x16(t_dq + lane_addr + c * 16, r);
-          tmem_wait_ld();
-        } else {
-#pragma unroll
-          for (int i = 0; i < 16; ++i) r[i] = 0u;
-        }
-        if (row_ok) {
-#pragma unroll
-          for (int h2 = 0; h2 < 2; ++h2) {
-            uint4 a;
-            a.x = pack_bf16x2(__uint_as_float(r[h2 * 8 + 0]), __uint_as_float(r[h2 * 8 + 1]));
-            a.y = pack_bf16x2(__uint_as_float(r[h2 * 8 + 2]), __uint_as_float(r[h2 * 8 + 3]));
-            a.z = pack_bf16x2(__uint_as_float(r[h2 * 8 + 4]), __uint_as_float(r[h2 * 8 + 5]));
-            a.w = pack_bf16x2(__uint_as_float(r[h2 * 8 + 6]), __uint_as_float(r[h2 * 8 + 7]));
-            *reinterpret_cast<uint4*>(dst + c * 16 + h2 * 8) = a;
-          }
-        }
-      }
-    }
-  }
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 5) tmem_dealloc(tmem_base, 512);
-}
-
-// ----------------------------------------------------------------------------------------------
-// 2b. dK / dV, second generation: transposed scores, P^T / dS^T as tensor-memory operands, pipelined.
+// 2. dK / dV: transposed scores, P^T / dS^T as tensor-memory operands, pipelined.
 //
-// The first-generation kernel above runs its four stages (TMA, S/dP MMAs, softmax, dV/dK MMAs) strictly one
-// after the other and moves P and dS through shared memory.  Here one CTA still owns a 128-row KV tile, but
+// A kernel that runs its four stages (TMA, S/dP MMAs, softmax, dV/dK MMAs) strictly one after the other and moves
+// P and dS through shared memory leaves the tensor core idle most of the time.  Here one CTA owns a 128-row KV
+// tile, and
 //   * it computes the TRANSPOSED tiles S^T = K Q^T and dP^T = V dO^T for blocks of 64 queries, so the KV rows
 //     are the tensor-memory lanes and P^T, dS^T can be written back (packed bf16, tcgen05.st) over the columns
 //     they were computed from and fed to dV += P^T dO and dK += dS^T Q as tensor-memory A operands: no P/dS in
@@ -770,7 +377,7 @@ attn_bwd_dkdv2_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_co
 constexpr size_t kBwd2Smem = 1024 + 4 * CHUNK + kRing * 4 * QBOX + 2 * 4 * BQ2 * 4 + 16 + (2 + 2 * kRing + 5) * 8 + 16;
 
 // ----------------------------------------------------------------------------------------------
-// 3b. dQ, second generation: same pipeline as the dK/dV kernel above with the roles of Q and KV exchanged.
+// 3. dQ: same pipeline as the dK/dV kernel above with the roles of Q and KV exchanged.
 // One CTA owns a 128-row query tile of one head and walks the visible KV range in blocks of 64 rows:
 //   S = Q K_blk^T, dP = dO V_blk^T   (query rows are the tensor-memory lanes, 64 + 64 columns, double buffered)
 //   dS = exp2(S*scale*log2e - lse*log2e) * (dP - delta) * scale   (eight softmax warps; per-row values in registers)
@@ -991,56 +598,30 @@ attn_bwd_dq2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 
 constexpr size_t kDq2Smem = 1024 + 4 * CHUNK + kRing * 4 * QBOX + (2 + 2 * kRing + 5) * 8 + 16;
 
-constexpr size_t kBwdSmem = 1024 + 12 * CHUNK + 16 * 8 + 16;
-
-int g_bwd_version = 2;
-
 template <int DIM>
 int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tdo, const CUtensorMap& tq64, const CUtensorMap& tdo64,
                const AttnParams& p, cudaStream_t st) {
   static bool attr = false;
   if (!attr) {
-    cudaError_t e = cudaFuncSetAttribute(attn_bwd_dkdv_kernel<DIM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)kBwdSmem);
+    cudaError_t e = cudaFuncSetAttribute(attn_bwd_dkdv2_kernel<DIM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)kBwd2Smem);
     if (e != cudaSuccess) return (int)e;
-    e = cudaFuncSetAttribute(attn_bwd_dq_kernel<DIM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kBwdSmem);
+    e = cudaFuncSetAttribute(attn_bwd_dq2_kernel<DIM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kDq2Smem);
     if (e != cudaSuccess) return (int)e;
     attr = true;
   }
   const int tiles = (p.T + BQ - 1) / BQ;
-  if (g_bwd_version == 2) {
-    static bool attr2 = false;
-    if (!attr2) {
-      cudaError_t e = cudaFuncSetAttribute(attn_bwd_dkdv2_kernel<DIM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           (int)kBwd2Smem);
-      if (e != cudaSuccess) return (int)e;
-      e = cudaFuncSetAttribute(attn_bwd_dq2_kernel<DIM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kDq2Smem);
-      if (e != cudaSuccess) return (int)e;
-      attr2 = true;
-    }
-    attn_bwd_dkdv2_kernel<DIM><<<dim3(tiles, p.ws_dk ? p.n_q : p.n_kv), kBwd2Threads, kBwd2Smem, st>>>(tq, tq64, tdo64, p);
-    if (p.ws_dk) {
-      const long items = (long)p.T * (p.n_kv * DIM / 4) * 2;
-      attn_group_reduce_kernel<<<(unsigned)((items + 255) / 256), 256, 0, st>>>(p.ws_dk, p.ws_dv, p.dqkv, p.T, p.n_q,
-                                                                               p.n_kv, DIM, p.ld);
-    }
-    attn_bwd_dq2_kernel<DIM><<<dim3(tiles, p.n_q), kBwd2Threads, kDq2Smem, st>>>(tq, tdo, tq64, p);
-    return (int)cudaGetLastError();
-  }
-  attn_bwd_dkdv_kernel<DIM><<<dim3(tiles, p.ws_dk ? p.n_q : p.n_kv), kThreads, kBwdSmem, st>>>(tq, tdo, p);
+  attn_bwd_dkdv2_kernel<DIM><<<dim3(tiles, p.ws_dk ? p.n_q : p.n_kv), kBwd2Threads, kBwd2Smem, st>>>(tq, tq64, tdo64, p);
   if (p.ws_dk) {
     const long items = (long)p.T * (p.n_kv * DIM / 4) * 2;
     attn_group_reduce_kernel<<<(unsigned)((items + 255) / 256), 256, 0, st>>>(p.ws_dk, p.ws_dv, p.dqkv, p.T, p.n_q,
                                                                              p.n_kv, DIM, p.ld);
   }
-  attn_bwd_dq_kernel<DIM><<<dim3(tiles, p.n_q), kThreads, kBwdSmem, st>>>(tq, tdo, p);
+  attn_bwd_dq2_kernel<DIM><<<dim3(tiles, p.n_q), kBwd2Threads, kDq2Smem, st>>>(tq, tdo, tq64, p);
   return (int)cudaGetLastError();
 }
 
 }  // namespace
-
-// Backward kernel generation: 2 = pipelined kernels with tensor-memory P / dS operands, 1 = first generation.
-extern "C" void mmt_attn_set_bwd_version(int v) { g_bwd_version = v; }
 
 // dqkv [T, ld] receives dq | dk | dv in the layout of qkv.  delta is fp32 scratch [n_q, T].  ws is optional fp32
 // scratch of 2 * n_q * T * dim floats: with it (and n_q > n_kv) dK/dV run one CTA per q head and are summed over

@@ -192,8 +192,6 @@ def main(argv=None) -> int:
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--no-flush", action="store_true")
-    ap.add_argument("--fwd-version", type=int, default=0, help="attention forward: 2 = ping-pong kernel, 1 = first one")
-    ap.add_argument("--bwd-version", type=int, default=0, help="attention backward: 2 = pipelined kernels, 1 = first ones")
     ap.add_argument("--stream-k", type=int, default=-1, help="GEMM: 1 = stream-K for partial last waves, 0 = off (default)")
     ap.add_argument("--pair", type=int, default=-1, help="GEMM: 1 = 2-CTA kernel, 0 = 1-CTA kernels, -1 = default")
     ap.add_argument("--sustain", type=float, default=0.5, help="gemm_shapes: seconds of back-to-back launches per case")
@@ -201,10 +199,6 @@ def main(argv=None) -> int:
     dev = "cuda"
     nv.lib()
     flush = not a.no_flush
-    if a.fwd_version:
-        nv.lib().mmt_attn_set_fwd_version(a.fwd_version)
-    if a.bwd_version:
-        nv.lib().mmt_attn_set_bwd_version(a.bwd_version)
     if a.kernel == "gemm_shapes":
         if a.pair >= 0:
             nv.lib().mmt_gemm_use_pair(a.pair)
