@@ -130,6 +130,10 @@ def main() -> int:
     ap.add_argument("--no-fused-comm", action="store_true")
     ap.add_argument("--activation-checkpointing", default="auto", choices=["auto", "on", "off"],
                     help="auto (default): keep activations when they fit in HBM, recompute them otherwise")
+    ap.add_argument("--optimizer-states", default="fp32", choices=["fp32", "bf16"],
+                    help="fp32 (default): AdamW on fp32 master weights with fp32 moments; bf16: AdamW directly on the "
+                         "bf16 parameters with bf16 moments, the precision of the reference's (and the library arm's) "
+                         "optimizer")
     ap.add_argument("--symm-heap-mb", type=int, default=0, help="size of the symmetric heap (default: the config's)")
     ap.add_argument("--no-lib-arm", action="store_true",
                     help="do not time the library baseline in front of the sm100 arm (vs_baseline is then null)")
@@ -246,6 +250,8 @@ def main() -> int:
             ov.append(f"+data.synthetic.image_sizes={args.image_sizes}")
         if args.text_token_choices:
             ov.append(f"+data.synthetic.text_token_choices={args.text_token_choices}")
+    if args.optimizer_states == "bf16":
+        ov.append("training.optimizer_master_weights=false")
     ckpt = {"auto": "auto", "on": "true", "off": "false"}[args.activation_checkpointing]
     ov += [f"vision.activation_checkpointing={ckpt}", f"text.activation_checkpointing={ckpt}"]
     if args.symm_heap_mb:
@@ -433,7 +439,8 @@ def main() -> int:
                           else f"square, side drawn per sample from {{{args.image_sizes}}}, new shapes every step"),
                 "vision_patches_per_sample": patches // global_batch,
                 "text_tokens_per_sample": args.text_token_choices or args.text_tokens, "parallelism": par,
-                "optimizer": "AdamW fp32 master+moments, ZeRO-1",
+                "optimizer": ("AdamW fp32 master+moments, ZeRO-1" if args.optimizer_states == "fp32" else
+                              "AdamW on bf16 parameters with bf16 moments (no master copy), ZeRO-1"),
                 "activation_checkpointing": {
                     "setting": args.activation_checkpointing,
                     "recompute_in_this_run": policy,

@@ -79,6 +79,10 @@ DEFAULTS: dict[str, Any] = {
         "label_smoothing": 0.0,    # cross-entropy label smoothing (python/tensor_parallel/cross_entropy.py:185-202)
         "fused_comm": "auto",      # peer-memory fused collectives: true | false | auto (on when every GPU can map
                                    # every other one; heap regions grow with the longest batch seen)
+        # true: AdamW on fp32 master weights with fp32 moments; false: AdamW directly on the bf16 parameters with bf16
+        # moments, as torch.optim.AdamW on a bf16 model (the reference's optimizer): half the optimizer's memory
+        # traffic, a third of its memory, every update rounded to bf16
+        "optimizer_master_weights": True,
         "overlap_optimizer": False,  # single-GPU engine: text AdamW on a side stream behind the next vision forward
         "symm_heap_mb": 8192,      # size of each GPU's symmetric heap (exchange buffers of the fused collectives)
     },

@@ -630,6 +630,37 @@ __global__ void adamw_kernel(bf16* __restrict__ p, const bf16* __restrict__ g, f
   }
 }
 
+// AdamW with the states of an optimizer that runs directly on bf16 parameters (what torch.optim.AdamW does on a
+// bf16 model, the reference's setting: python/ray/trainer.py:503-572): no fp32 master copy, moments in bf16.  The
+// arithmetic of an element is fp32; weight, m and v are rounded to bf16 when stored.  14 bytes of traffic per
+// parameter instead of 28.
+__global__ void adamw_bf16_kernel(bf16* __restrict__ p, const bf16* __restrict__ g, bf16* __restrict__ m,
+                                  bf16* __restrict__ v, long n, long n_decay, float lr, float b1, float b2, float eps,
+                                  float wd, float bc1, float bc2, const float* __restrict__ gscale_ptr) {
+  const float gs = gscale_ptr ? *gscale_ptr : 1.f;
+  const long n8 = n >> 3;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n8; i += (long)gridDim.x * blockDim.x) {
+    const long e = i * 8;
+    float gv[8], wv[8], mv[8], vv[8];
+    load8(g + e, gv);
+    load8(p + e, wv);
+    load8(m + e, mv);
+    load8(v + e, vv);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float gj = gv[j] * gs;
+      mv[j] = b1 * mv[j] + (1.f - b1) * gj;
+      vv[j] = b2 * vv[j] + (1.f - b2) * gj * gj;
+      const float upd = (mv[j] / bc1) / (sqrtf(vv[j] / bc2) + eps);
+      const float decay = (e + j < n_decay) ? wd : 0.f;
+      wv[j] = wv[j] - lr * (upd + decay * wv[j]);
+    }
+    store8(m + e, mv);
+    store8(v + e, vv);
+    store8(p + e, wv);
+  }
+}
+
 // out[0] += sum(x^2)   (fp32 atomic; caller zeroes out)
 __global__ void sumsq_kernel(const bf16* __restrict__ x, long n8, float* __restrict__ out) {
   __shared__ float red[32];
@@ -847,6 +878,17 @@ int mmt_adamw(void* p, const void* g, float* master, float* m, float* v, long n,
   const float bc1 = 1.f - powf(b1, (float)step), bc2 = 1.f - powf(b2, (float)step);
   adamw_kernel<<<grid_for(n / 8, 256, mmt_sm_count() * 16), 256, 0, ST(stream)>>>(
       BF(p), CBF(g), master, m, v, n, n_decay, lr, b1, b2, eps, wd, bc1, bc2, gscale_ptr);
+  return (int)cudaGetLastError();
+}
+
+// AdamW on bf16 parameters with bf16 moments and no master copy (see adamw_bf16_kernel).
+int mmt_adamw_bf16(void* p, const void* g, void* m, void* v, long n, long n_decay, float lr, float b1, float b2,
+                   float eps, float wd, int step, const float* gscale_ptr, void* stream) {
+  if (n % 8) return -2;
+  if (n == 0) return 0;
+  const float bc1 = 1.f - powf(b1, (float)step), bc2 = 1.f - powf(b2, (float)step);
+  adamw_bf16_kernel<<<grid_for(n / 8, 256, mmt_sm_count() * 16), 256, 0, ST(stream)>>>(
+      BF(p), CBF(g), BF(m), BF(v), n, n_decay, lr, b1, b2, eps, wd, bc1, bc2, gscale_ptr);
   return (int)cudaGetLastError();
 }
 

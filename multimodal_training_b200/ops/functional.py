@@ -537,17 +537,37 @@ def lm_head_cross_entropy(hidden: torch.Tensor, weight: torch.Tensor, labels: to
 # --------------------------------------------------------------------------------------
 def adamw_step(p, g, master, m, v, *, n_decay: int, lr: float, beta1: float, beta2: float, eps: float,
                weight_decay: float, step: int, grad_scale: torch.Tensor | None = None) -> None:
-    """Fused AdamW over flat buffers (bf16 param/grad, fp32 master/m/v); elements [0, n_decay) get weight decay."""
+    """Fused AdamW over flat buffers; elements [0, n_decay) get weight decay.
+
+    With ``master`` (fp32 copy of the weights) the moments are fp32 too and ``p`` receives the rounded master.
+    ``master=None`` is the optimizer of a bf16 model without a master copy (what ``torch.optim.AdamW`` does on bf16
+    parameters, the reference's setting): the moments have ``p``'s dtype, an element is updated in fp32 and weight
+    and moments are rounded when stored."""
     if p.is_cuda:
+        if master is None:
+            nv.call("mmt_adamw_bf16", p.data_ptr(), g.data_ptr(), m.data_ptr(), v.data_ptr(), p.numel(), n_decay, lr,
+                    beta1, beta2, eps, weight_decay, step, nv.ptr(grad_scale), nv.stream())
+            return
         nv.call("mmt_adamw", p.data_ptr(), g.data_ptr(), master.data_ptr(), m.data_ptr(), v.data_ptr(), p.numel(),
                 n_decay, lr, beta1, beta2, eps, weight_decay, step, nv.ptr(grad_scale), nv.stream())
         return
     gf = g.float()
     if grad_scale is not None:
         gf = gf * grad_scale
+    bc1, bc2 = 1 - beta1 ** step, 1 - beta2 ** step
+    if master is None:
+        mf = m.float().mul_(beta1).add_(gf, alpha=1 - beta1)
+        vf = v.float().mul_(beta2).addcmul_(gf, gf, value=1 - beta2)
+        upd = (mf / bc1) / ((vf / bc2).sqrt() + eps)
+        w = p.float()
+        wd = torch.zeros_like(w)
+        wd[:n_decay] = weight_decay
+        p.copy_((w - lr * (upd + wd * w)).to(p.dtype))
+        m.copy_(mf.to(m.dtype))
+        v.copy_(vf.to(v.dtype))
+        return
     m.mul_(beta1).add_(gf, alpha=1 - beta1)
     v.mul_(beta2).addcmul_(gf, gf, value=1 - beta2)
-    bc1, bc2 = 1 - beta1 ** step, 1 - beta2 ** step
     upd = (m / bc1) / ((v / bc2).sqrt() + eps)
     wd = torch.zeros_like(master)
     wd[:n_decay] = weight_decay

@@ -45,6 +45,7 @@ _SIGS = {
     "mmt_ce_grad": (c_int, [_P, _P, _P, _P, _P, c_long, c_int, c_long, c_long, _P]),
     "mmt_adamw": (c_int, [_P, _P, _P, _P, _P, c_long, c_long, c_float, c_float, c_float, c_float, c_float, c_int, _P,
                           _P]),
+    "mmt_adamw_bf16": (c_int, [_P, _P, _P, _P, c_long, c_long, c_float, c_float, c_float, c_float, c_float, c_int, _P, _P]),
     "mmt_sumsq": (c_int, [_P, c_long, _P, _P]),
     "mmt_clip_coef": (c_int, [_P, c_float, c_float, _P, _P]),
 }

@@ -39,7 +39,7 @@ def default_no_decay(name: str) -> bool:
 class ZeroAdamW:
     def __init__(self, named_params, *, group=None, lr: float = 1e-4, betas=(0.9, 0.999), eps: float = 1e-8,
                  weight_decay: float = 0.0, no_decay_fn=default_no_decay, grad_divisor: float = 1.0,
-                 partial_grad_group=None, fused=None):
+                 partial_grad_group=None, fused=None, master_weights: bool = True):
         named = [(n, p) for n, p in named_params if p.requires_grad]
         seen, uniq = set(), []
         for n, p in named:
@@ -54,6 +54,9 @@ class ZeroAdamW:
         self.partial_grad_group = partial_grad_group
         self.fused = fused
         self.step_count = 0
+        # False: no fp32 master copy, moments in the parameters' dtype (torch.optim.AdamW on a bf16 model, the
+        # reference's optimizer: half the optimizer traffic and a third of its memory, bf16 rounding of every update)
+        self.master_weights = bool(master_weights)
 
         def replicated(p):
             return getattr(p, "sequence_parallel", False) or getattr(p, "tensor_replicated", False)
@@ -90,7 +93,7 @@ class ZeroAdamW:
         self.native = p0.is_cuda
 
         self.fz = None
-        if fused is not None and self.native and self.gsize > 1 and self.gsize <= 8:
+        if fused is not None and self.native and self.gsize > 1 and self.gsize <= 8 and self.master_weights:
             from .fused import FusedZero
             self.fz = FusedZero(group, self.total, self.device)
             self.flat_param, self.flat_grad = self.fz.flat_param, self.fz.flat_grad
@@ -109,9 +112,14 @@ class ZeroAdamW:
                 p.grad = gview
         lo = self.grank * self.shard
         self.shard_lo = lo
-        self.master = self.flat_param[lo:lo + self.shard].to(torch.float32, copy=True)
-        self.exp_avg = torch.zeros_like(self.master)
-        self.exp_avg_sq = torch.zeros_like(self.master)
+        if self.master_weights:
+            self.master = self.flat_param[lo:lo + self.shard].to(torch.float32, copy=True)
+            self.exp_avg = torch.zeros_like(self.master)
+            self.exp_avg_sq = torch.zeros_like(self.master)
+        else:
+            self.master = None
+            self.exp_avg = torch.zeros(self.shard, dtype=self.dtype, device=self.device)
+            self.exp_avg_sq = torch.zeros(self.shard, dtype=self.dtype, device=self.device)
         self._normsq = torch.zeros(1, dtype=torch.float32, device=self.device)
         self._coef = torch.ones(1, dtype=torch.float32, device=self.device)
 
@@ -211,7 +219,8 @@ class ZeroAdamW:
 
     # ------------------------------------------------------------------ (de)serialisation of the optimizer shard
     def state_dict(self) -> dict:
-        return {"step": self.step_count, "master": self.master.cpu(), "exp_avg": self.exp_avg.cpu(),
+        return {"step": self.step_count, "master": None if self.master is None else self.master.cpu(),
+                "exp_avg": self.exp_avg.cpu(),
                 "exp_avg_sq": self.exp_avg_sq.cpu(), "shard_lo": self.shard_lo, "total": self.total,
                 "names": list(self.names)}
 
@@ -219,14 +228,18 @@ class ZeroAdamW:
         if sd["total"] != self.total or sd["shard_lo"] != self.shard_lo:
             raise ValueError("optimizer shard layout does not match the checkpoint")
         self.step_count = int(sd["step"])
-        self.master.copy_(sd["master"])
+        if (sd.get("master") is None) != (self.master is None):
+            raise ValueError("the checkpoint's optimizer was saved with a different training.optimizer_master_weights")
+        if self.master is not None:
+            self.master.copy_(sd["master"])
         self.exp_avg.copy_(sd["exp_avg"])
         self.exp_avg_sq.copy_(sd["exp_avg_sq"])
 
     def refresh_master_from_params(self) -> None:
         """After loading model weights into the parameter views."""
         lo = self.shard_lo
-        self.master.copy_(self.flat_param[lo:lo + self.shard].float())
+        if self.master is not None:
+            self.master.copy_(self.flat_param[lo:lo + self.shard].float())
 
 
 def lr_at(step: int, *, base_lr: float, total_steps: int, warmup_steps: int = 0, kind: str = "cosine",

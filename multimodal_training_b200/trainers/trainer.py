@@ -231,7 +231,8 @@ class Trainer(RayActor):
                                    betas=(float(c.get("adam_beta1", 0.9)), float(c.get("adam_beta2", 0.999))),
                                    eps=float(c.get("adam_eps", 1e-8)), weight_decay=float(c.get("weight_decay", 0.0)),
                                    grad_divisor=grad_divisor, partial_grad_group=partial_grad_group,
-                                   fused=self.state.fused)
+                                   fused=self.state.fused,
+                                   master_weights=bool(c.get("optimizer_master_weights", True)))
         return self.optimizer
 
     def _total_steps(self) -> int:

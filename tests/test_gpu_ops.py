@@ -262,6 +262,33 @@ def test_adamw_and_sumsq():
     assert abs(out.item() - g.float().pow(2).sum().item()) < 1e-3 * out.item()
 
 
+def test_adamw_without_master_weights():
+    """AdamW directly on bf16 parameters with bf16 moments (the reference's optimizer precision): the kernel against
+    the CPU path of the same function and against torch's fused AdamW on a bf16 tensor."""
+    F, nv = _F()
+    torch.manual_seed(9)
+    n = 8 * 4321
+    p0 = torch.randn(n, dtype=torch.bfloat16) * 0.2
+    p, pc = p0.to(DEV), p0.clone()
+    m, v = torch.zeros(n, device=DEV, dtype=torch.bfloat16), torch.zeros(n, device=DEV, dtype=torch.bfloat16)
+    mc, vc = torch.zeros(n, dtype=torch.bfloat16), torch.zeros(n, dtype=torch.bfloat16)
+    q = torch.nn.Parameter(p0.to(DEV).clone())
+    topt = torch.optim.AdamW([q], lr=1e-2, weight_decay=0.1, fused=True)
+    for step in (1, 2, 3):
+        g = (torch.randn(n) * 0.1).to(torch.bfloat16)
+        F.adamw_step(p, g.to(DEV), None, m, v, n_decay=n, lr=1e-2, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.1,
+                     step=step)
+        F.adamw_step(pc, g, None, mc, vc, n_decay=n, lr=1e-2, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.1,
+                     step=step)
+        q.grad = g.to(DEV)
+        topt.step()
+    for want in (pc.float(), q.detach().cpu().float()):
+        got = p.cpu().float()
+        assert (got != want).float().mean().item() < 2e-2            # rounding flips of single elements only
+        assert ((got - want).abs() <= want.abs() * 2.0 ** -6 + 1e-30).all()
+    assert rel_err(m.cpu().float(), mc.float()) < 1e-2 and rel_err(v.cpu().float(), vc.float()) < 1e-2
+
+
 def test_native_library_is_loaded():
     import ctypes
     F, nv = _F()
