@@ -101,6 +101,19 @@ struct GemmParams {
   int* rs_flag[8];
   int* rs_counter;
   int rs_rows, rs_self, rs_ranks, rs_epoch;
+  // --- column scatter (Ulysses sequence -> heads exchange as the epilogue of the QKV projection): the output is
+  //     `parts` blocks of sc_part columns; inside every block, columns [r * sc_w, (r + 1) * sc_w) belong to rank r
+  //     and go to row sc_row[row] of that rank's buffer rs_base[r] ([*, sc_ld], sc_ld = parts * sc_w) at column
+  //     part * sc_w + (column inside the owner's range).  A [32 x 64] slab with one owner and 32 consecutive
+  //     destination rows leaves as one bulk store (tensor map r of the table); anything else as 16-byte stores.
+  //     When the whole GEMM is done, rs_flag[r] on every rank receives rs_epoch.  C is not written.  nullptr: off.
+  const int* sc_row;
+  int sc_part, sc_w, sc_ld;
+  // --- K-slice consumer (Ulysses heads -> sequence exchange as the prologue of the output projection): columns
+  //     [s * kf_w, (s + 1) * kf_w) of A were written by rank s and are complete once kf_flags[s] >= kf_epoch.  The
+  //     k-blocks are walked starting with this rank's own slice (kf_self), which needs no wait.  nullptr: off.
+  const int* kf_flags;
+  int kf_epoch, kf_w, kf_self, kf_ranks;
 };
 
 // tile index -> (tile_m, tile_n); with an all-gather consumer the m tiles are rotated so that the CTA wave
@@ -545,7 +558,18 @@ MMT_DEVICE void epilogue_fast(const GemmParams& p, const OutMaps& tmC, uint32_t 
     if (bulk) {
       fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) {
+      bool stored = true;
+      if (p.sc_row) {
+        // one owner, one column block and 32 consecutive destination rows, or else plain stores below
+        const int part = colg / p.sc_part, within = colg - part * p.sc_part, owner = within / p.sc_w;
+        const int in_owner = within - owner * p.sc_w;
+        stored = srow0 + 32 <= p.M && colg + 64 <= N && within + 64 <= p.sc_part && in_owner + 64 <= p.sc_w &&
+                 p.sc_row[srow0 + 31] - p.sc_row[srow0] == 31;
+        if (stored && lane == 0) {
+          tma_store_2d(&tmC.m[owner], slab, part * p.sc_w + in_owner, p.sc_row[srow0]);
+          tma_store_commit();
+        }
+      } else if (lane == 0) {
         if (srow0 < p.M) {
           if (p.rs_rows) {
             const int owner = srow0 / p.rs_rows;      // rs_rows is a multiple of 32: a slab has one owner
@@ -556,12 +580,28 @@ MMT_DEVICE void epilogue_fast(const GemmParams& p, const OutMaps& tmC, uint32_t 
         }
         tma_store_commit();
       }
-      MMT_TRACE_STAMP(40 + g);
-      continue;
+      if (stored) {
+        MMT_TRACE_STAMP(40 + g);
+        continue;
+      }
     }
     __syncwarp();
     const int col = colg + chunk * 8;
-    if (col < N) {
+    if (p.sc_row) {
+      if (col < N) {
+        const int part = col / p.sc_part, within = col - part * p.sc_part, owner = within / p.sc_w;
+        const long dcol = (long)part * p.sc_w + (within - owner * p.sc_w);
+        __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(p.rs_base[owner]);
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+          const int row = it * 4 + sub;
+          const long gr = (long)srow0 + row;
+          if (gr < p.M)
+            *reinterpret_cast<uint4*>(base + (long)p.sc_row[gr] * p.sc_ld + dcol) =
+                *reinterpret_cast<const uint4*>(slab + store_box_offset(row, chunk * 8));
+        }
+      }
+    } else if (col < N) {
 #pragma unroll
       for (int it = 0; it < 8; ++it) {
         const int row = it * 4 + sub;
@@ -733,6 +773,7 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       uint32_t ag_seen = p.ag_flags ? (1u << p.ag_self) : 0u;
       uint32_t ag_chunk_seen[16] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
       uint32_t fwd_pending = 0, fwd_parity = 0;   // per stage: last use is being forwarded / parity of that hand-back
+      uint32_t kf_seen = 0;                       // K-slice consumer: source ranks already waited for
       int kcount = 0;
       WorkItem w;
       for (int wi = 0; ok && work_item(p, wi, blockIdx.x, gridDim.x, KB, ntiles, w); ++wi) {
@@ -754,7 +795,23 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           if (!ok) break;
           asm volatile("fence.proxy.async;" ::: "memory");
         }
-        for (int kb = w.k0; kb < w.k1; ++kb) {
+        for (int kb0 = w.k0; kb0 < w.k1; ++kb0) {
+          int kb = kb0;
+          if (p.kf_flags) {
+            // K-slice consumer: start with this rank's own columns of A, wait for a peer's slice when it is reached
+            kb = kb0 + (p.kf_self * p.kf_w) / BK;
+            if (kb >= KB) kb -= KB;
+            const int s0 = (kb * BK) / p.kf_w, s1 = min((kb * BK + BK - 1) / p.kf_w, p.kf_ranks - 1);
+            bool waited = false;
+            for (int src = s0; src <= s1 && ok; ++src) {
+              if (src == p.kf_self || (kf_seen & (1u << src))) continue;
+              ok = flag_wait_ge(&p.kf_flags[src], p.kf_epoch, MMT_WAIT_NS, p.ew, 112);
+              kf_seen |= 1u << src;
+              waited = true;
+            }
+            if (!ok) break;
+            if (waited) asm volatile("fence.proxy.async;" ::: "memory");
+          }
           if ((MMT_DBG & 1) && kcount++ >= kStages) continue;
           if (!mbar_wait(&empty[s], ph ^ 1, p.ew, 100)) { ok = false; break; }
           if (fwd_pending & (1u << s)) {
@@ -955,7 +1012,7 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     tma_store_wait_all();                       // every bulk store of this warp has been written out
     asm volatile("fence.proxy.async;" ::: "memory");
   }
-  if (p.rs_rows) __threadfence_system();   // this thread's peer stores are visible system-wide
+  if (p.rs_rows || p.sc_row) __threadfence_system();   // this thread's peer stores are visible system-wide
   tc_fence_before();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_base, C_::TMEM_COLS);
@@ -965,7 +1022,7 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     MMT_CLK[0] = (unsigned long long)(clock64() - clk_c0);
     MMT_CLK[1] = t1 - clk_t0;
   }
-  if (p.rs_rows && threadIdx.x == 0) {
+  if ((p.rs_rows || p.sc_row) && threadIdx.x == 0) {
     // last CTA to finish publishes "my partial sums have landed" to every peer
     if (atomicAdd(p.rs_counter, 1) == (int)gridDim.x - 1) {
       *p.rs_counter = 0;
@@ -1406,6 +1463,13 @@ struct MmtGemmComm {
   int* rs_flag[8];
   int* rs_counter;
   int rs_rows, rs_self, rs_ranks, rs_epoch;
+  // column scatter (see GemmParams::sc_row): destinations rs_base[r] ([sc_rows_dst, sc_ld]), flags rs_flag / rs_epoch /
+  // rs_counter, rs_ranks owners
+  const int* sc_row;
+  int sc_part, sc_w, sc_ld, sc_rows_dst;
+  // K-slice consumer (see GemmParams::kf_flags)
+  const int* kf_flags;
+  int kf_epoch, kf_w, kf_self, kf_ranks;
 };
 
 namespace {
@@ -1475,7 +1539,7 @@ extern "C" int mmt_gemm_bf16(const void* A, const void* B, void* C, const void* 
   } else if (g_force_mt == 2 && M >= 256 && bn == 128) {
     mt = 2;
   }
-  if (bn == 256 && M >= 256 && (g_force_mt == 3 || (g_use_pair && g_force_mt == 0)) && !(comm && comm->fwd_peers > 0))
+  if (bn == 256 && M >= 256 && (g_force_mt == 3 || (g_use_pair && g_force_mt == 0)) && !(comm && (comm->fwd_peers > 0 || comm->sc_row || comm->kf_flags)))
     mt = 3;   // 2-CTA kernel
   const int bmt = mt == 3 ? BM : BM * mt;              // rows per TMA box of A
   const int bbox = mt == 3 ? 128 : bn;                 // rows per TMA box of B
@@ -1511,6 +1575,10 @@ extern "C" int mmt_gemm_bf16(const void* A, const void* B, void* C, const void* 
   for (int i = 0; i < 8; ++i) p.fwd_flag[i] = nullptr;
   p.rs_rows = p.rs_self = p.rs_ranks = p.rs_epoch = 0;
   p.rs_counter = nullptr;
+  p.sc_row = nullptr;
+  p.sc_part = p.sc_w = p.sc_ld = 0;
+  p.kf_flags = nullptr;
+  p.kf_epoch = p.kf_w = p.kf_self = p.kf_ranks = 0;
   if (comm) {
     const MmtGemmComm* c = comm;
     p.ag_flags = c->ag_flags; p.ag_epoch = c->ag_epoch; p.ag_rows = c->ag_rows; p.ag_self = c->ag_self;
@@ -1539,6 +1607,21 @@ extern "C" int mmt_gemm_bf16(const void* A, const void* B, void* C, const void* 
         p.fwd_flag[i] = c->fwd_flag[i];
       }
     }
+    if (c->sc_row) {
+      // the scatter lives in the straight-line epilogue of the 1-CTA kernels; 16-byte pieces must not straddle owners
+      if (p.rs_rows || p.ag_flags || out_f32 || accumulate || act || alpha != 1.0f || mt == 3 || p.rs_ranks < 1 ||
+          p.rs_ranks > 8 || c->sc_w <= 0 || (c->sc_w & 7) || c->sc_part != c->sc_w * p.rs_ranks || N % c->sc_part ||
+          c->sc_ld != (N / c->sc_part) * c->sc_w || !p.rs_counter || c->sc_rows_dst <= 0)
+        return -12;
+      p.sc_row = c->sc_row; p.sc_part = c->sc_part; p.sc_w = c->sc_w; p.sc_ld = c->sc_ld;
+    }
+    if (c->kf_flags) {
+      if (a_mn || c->kf_w <= 0 || c->kf_ranks < 1 || c->kf_ranks > 8 || c->kf_self < 0 || c->kf_self >= c->kf_ranks ||
+          (long)c->kf_w * c->kf_ranks != K || mt == 3)
+        return -13;
+      p.kf_flags = c->kf_flags; p.kf_epoch = c->kf_epoch; p.kf_w = c->kf_w; p.kf_self = c->kf_self;
+      p.kf_ranks = c->kf_ranks;
+    }
     if (p.rs_rows && (out_f32 || p.rs_ranks > 8 || p.rs_ranks < 1)) return -6;
     // every row needs an owner among the rs_ranks peers: a longer M would index past the peer table
     if (p.rs_rows && (long)M > (long)p.rs_rows * p.rs_ranks) return -8;
@@ -1549,7 +1632,7 @@ extern "C" int mmt_gemm_bf16(const void* A, const void* B, void* C, const void* 
   p.sk_flags = nullptr;
   p.sk_epoch = 0;
   bool sk_on = false;
-  if (!p.ag_flags && !p.rs_rows && mt != 3 && !(MMT_DBG & 1)) {
+  if (!comm && mt != 3 && !(MMT_DBG & 1)) {
     const int tiles = ((M + bmt - 1) / bmt) * ((N + bn - 1) / bn);
     const int skt = sk_tiles_for(tiles, (K + BK - 1) / BK, sms, mt);
     if (skt > 0 && sk_ready()) {
@@ -1569,7 +1652,14 @@ extern "C" int mmt_gemm_bf16(const void* A, const void* B, void* C, const void* 
   p.tma_store = 0;
   if (!out_f32) {
     p.tma_store = 1;
-    if (p.rs_rows) {
+    if (p.sc_row) {
+      p.tma_store = 2;
+      for (int i = 0; i < p.rs_ranks; ++i) {
+        r = cached_tmap_2d(&tc.m[i], reinterpret_cast<const void*>(p.rs_base[i]), (uint64_t)p.sc_ld,
+                           (uint64_t)comm->sc_rows_dst, (uint64_t)p.sc_ld, 64, 32);
+        if (r) return 3000 + r;
+      }
+    } else if (p.rs_rows) {
       if (p.rs_rows % 32 == 0) {
         p.tma_store = 2;
         for (int i = 0; i < p.rs_ranks; ++i) {

@@ -35,6 +35,7 @@ from ..config.model_configs import VisionConfig
 from ..ops import attention as attn_mod
 from ..ops import blocks
 from ..ops import functional as F
+from ..ops import ulysses_block
 from ..ops.attention import SeqInfo
 from ..parallel import comm
 from ..parallel.sp import VisionPlan
@@ -225,6 +226,12 @@ class VisionEncoder(nn.Module):
                 x = blocks.local_block(x, spec, cos, sin, full_seq if is_full else win_seq,
                                        (B.norm1_w, B.qkv_w, B.qkv_b, B.proj_w, B.proj_b, B.norm2_w, B.gate_up_w,
                                         B.gate_up_b, B.down_w, B.down_b), recompute=ckpt, keep_elementwise=keep_ew)
+                continue
+            if one_node and is_full and getattr(self.sp.fused, "one_node", False):
+                # full attention across ranks: one node with the Ulysses exchanges inside the GEMMs
+                x = ulysses_block.ulysses_block(x, spec, plan, full_seq, self.sp.fused,
+                                                (B.norm1_w, B.qkv_w, B.qkv_b, B.proj_w, B.proj_b, B.norm2_w,
+                                                 B.gate_up_w, B.gate_up_b, B.down_w, B.down_b), recompute=ckpt)
                 continue
             x = checkpoint(lambda t, B=B, f=is_full: self._block(t, B, cos, sin, plan, win_seq, full_seq, f), (x,),
                            enabled=ckpt)

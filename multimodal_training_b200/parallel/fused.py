@@ -47,7 +47,13 @@ class GemmCommC(ctypes.Structure):
                 ("fwd_counter", ctypes.c_void_p),
                 ("rs_base", ctypes.c_uint64 * 8), ("rs_flag", ctypes.c_void_p * 8),
                 ("rs_counter", ctypes.c_void_p), ("rs_rows", ctypes.c_int), ("rs_self", ctypes.c_int),
-                ("rs_ranks", ctypes.c_int), ("rs_epoch", ctypes.c_int)]
+                ("rs_ranks", ctypes.c_int), ("rs_epoch", ctypes.c_int),
+                # column scatter of the output (Ulysses sequence -> heads in the QKV epilogue)
+                ("sc_row", ctypes.c_void_p), ("sc_part", ctypes.c_int), ("sc_w", ctypes.c_int),
+                ("sc_ld", ctypes.c_int), ("sc_rows_dst", ctypes.c_int),
+                # K-slice consumer (Ulysses heads -> sequence in front of the output projection)
+                ("kf_flags", ctypes.c_void_p), ("kf_epoch", ctypes.c_int), ("kf_w", ctypes.c_int),
+                ("kf_self", ctypes.c_int), ("kf_ranks", ctypes.c_int)]
 
 
 class ZeroPeersC(ctypes.Structure):

@@ -11,13 +11,14 @@ neither cos/sin nor masks travel.
 from __future__ import annotations
 
 import ctypes
+import os
 
 import numpy as np
 import torch
 
 from ..ops import functional as F
 from ..ops import native as nv
-from .fused import FusedComm, PeerSetC
+from .fused import FusedComm, GemmCommC, PeerSetC
 
 _P, _I, _L = ctypes.c_void_p, ctypes.c_int, ctypes.c_long
 nv.declare("mmt_ulysses_to_heads", _I, [_P, _P, ctypes.POINTER(PeerSetC), _P, _I, _L, _I, _I, _I, _P])
@@ -30,6 +31,9 @@ class UlyssesFused:
         m = fc.mesh
         self.sp, self.sp_rank = m.sp, m.sp_rank
         self.ranks = [m.vdp_rank * m.sp + i for i in range(m.sp)]     # heap ranks of my sequence-parallel group
+        self._dummies: dict[int, torch.Tensor] = {}
+        # full-attention layers as one autograd node with the exchanges inside the GEMMs (ops/ulysses_block.py)
+        self.one_node = os.environ.get("MMT_ULYSSES_BLOCK", "0") == "1"
 
     def _routes(self, plan, device):
         r = getattr(plan, "_ulysses", None)
@@ -46,6 +50,68 @@ class UlyssesFused:
                  "t_loc_max": int(max(plan.rank_tokens))}
             plan._ulysses = r
         return r
+
+    def rope_tables(self, plan, device):
+        """cos / sin [T_all, head_dim] of every row of the gathered sequence (image-major order = window order of all
+        patches): the head owner rotates rows that the QKV epilogue delivered un-rotated."""
+        t = getattr(plan, "_ulysses_rope", None)
+        if t is None:
+            from .sp import rope_table
+            cos, sin = rope_table(plan.all_pos, plan.head_dim)
+            t = (cos.to(device), sin.to(device))
+            plan._ulysses_rope = t
+        return t
+
+    # ------------------------------------------------------------------ exchanges fused into GEMMs
+    def gemm_scatter(self, a: torch.Tensor, w: torch.Tensor, bias, parts: int, routes, name: str, b_mn: bool = False):
+        """``a @ w^T (+ bias)`` whose epilogue stores column block r of each of the ``parts`` output blocks straight
+        into rank r's [T_all, parts * W] buffer at the row's image-major position (sequence -> heads exchange inside
+        the GEMM).  Returns this rank's buffer once every peer's rows have landed."""
+        fc, ctx = self.fc, self.fc.ctx
+        N = w.shape[1] if b_mn else w.shape[0]
+        C = N // parts
+        W = C // self.sp
+        off, local = fc._region(name, (routes["t_all"], parts * W))
+        slot = ctx.slot(name)
+        epoch = ctx.next_epoch(slot)
+        c = GemmCommC()
+        c.rs_rows, c.rs_self, c.rs_ranks, c.rs_epoch = 0, self.sp_rank, self.sp, epoch
+        c.rs_counter = ctx.counter_addr(slot)
+        for i, r in enumerate(self.ranks):
+            c.rs_base[i] = ctx.heap.ptrs[r] + off
+            c.rs_flag[i] = ctx.flag_addr(r, slot, self.sp_rank)
+        c.sc_row, c.sc_part, c.sc_w = routes["dst_row"].data_ptr(), C, W
+        c.sc_ld, c.sc_rows_dst = parts * W, routes["t_all"]
+        dummy = self._dummies.get(N)
+        if dummy is None:
+            dummy = self._dummies[N] = torch.empty(8, N, device=a.device, dtype=torch.bfloat16)
+        nv.lib().mmt_gemm_set_comm(ctypes.byref(c))
+        F.gemm(a, w, b_mn=b_mn, bias=bias, out=dummy)          # C itself is not written
+        nv.call("mmt_wait_flags", ctx.local_flags(slot), self.sp, -1, epoch, nv.stream())
+        return local
+
+    def to_tokens_nowait(self, src: torch.Tensor, W: int, routes, name: str):
+        """heads -> sequence exchange of [T_all, W] rows without the wait: returns (this rank's [T_loc_max, sp * W]
+        buffer, flag words, epoch) for a GEMM that consumes the buffer's K slices behind the flags."""
+        fc, ctx = self.fc, self.fc.ctx
+        off, local = fc._region(name, (routes["t_loc_max"], W * self.sp))
+        slot = ctx.slot(name)
+        epoch = ctx.next_epoch(slot)
+        ps = ctx.peerset(off, self.ranks, slot, self.sp_rank)
+        src = src.contiguous()
+        nv.call("mmt_ulysses_to_tokens", src.data_ptr(), routes["owner"].data_ptr(), routes["row_local"].data_ptr(),
+                ctypes.byref(ps), ctx.counter_addr(slot), epoch, src.shape[0], 1, self.sp, self.sp_rank, W, nv.stream())
+        return local, ctx.local_flags(slot), epoch
+
+    def gemm_k_slices(self, a: torch.Tensor, w: torch.Tensor, bias, residual, flags_ptr: int, epoch: int, W: int):
+        """``a @ w^T (+ bias + residual)`` where columns [s * W, (s + 1) * W) of ``a`` were written by rank s: the GEMM
+        starts on its own slice and waits per source before it loads a peer's (heads -> sequence exchange as the
+        GEMM's prologue)."""
+        c = GemmCommC()
+        c.rs_rows = 0
+        c.kf_flags, c.kf_epoch, c.kf_w, c.kf_self, c.kf_ranks = flags_ptr, epoch, W, self.sp_rank, self.sp
+        nv.lib().mmt_gemm_set_comm(ctypes.byref(c))
+        return F.gemm(a, w, bias=bias, residual=residual)
 
     def _exchange(self, kind: str, src: torch.Tensor, parts: int, W: int, routes, name: str) -> torch.Tensor:
         fc, ctx = self.fc, self.fc.ctx

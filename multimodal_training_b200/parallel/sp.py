@@ -135,6 +135,10 @@ class VisionPlan:
     local_merged_ids: torch.Tensor      # [T_loc / unit]
     local_merged_image: torch.Tensor    # [T_loc / unit] image id
     per_image_local: list[tuple[int, int]] = field(default_factory=list)  # (start, length) of image b in local pack
+    # (h, w) position of EVERY patch in window order (= the image-major order of the gathered sequence) and the
+    # rotary width: what a head owner needs to rotate rows that arrived un-rotated (shared with the geometry, no copy)
+    all_pos: "np.ndarray | None" = None
+    head_dim: int = 0
 
     @property
     def local_tokens(self) -> int:
@@ -298,6 +302,7 @@ def _build_vision_plan(geom: Geometry, sp: int, rank: int, head_dim: int) -> Vis
         local_cos=cos, local_sin=sin, win_cu=win_cu, rank_tokens=rank_tokens, full_cu=full_cu,
         to_image_major=to_img, to_rank_major=to_rank,
         local_merged_ids=torch.from_numpy(merged_ids), local_merged_image=torch.from_numpy(merged_image),
+        all_pos=pos, head_dim=head_dim,
         per_image_local=per_image_local)
 
 

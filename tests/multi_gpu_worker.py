@@ -13,7 +13,7 @@ import torch.distributed as dist  # noqa: E402
 
 
 def run(fused: bool, steps: int, vision: str = "sequence", ragged: bool = False, tp_block: bool = True,
-        ckpt: str = "true"):
+        ckpt: str = "true", ul_block: bool = False):
     from multimodal_training_b200.config.loader import load_config
     from multimodal_training_b200.engine import HybridEngine
     from multimodal_training_b200.ops import native as nv
@@ -33,6 +33,7 @@ def run(fused: bool, steps: int, vision: str = "sequence", ragged: bool = False,
         + (["+data.synthetic.image_sizes=252,448,420", "+data.synthetic.text_token_choices=96,256,40",
             "+data.synthetic.repeat=0"] if ragged else []))
     reset_process_state()
+    os.environ["MMT_ULYSSES_BLOCK"] = "1" if ul_block else "0"
     eng = HybridEngine.from_config(cfg)
     assert (process_state().fused is not None) == fused
     losses = [eng.mean_loss(eng.train_step(s if ragged else 0)) for s in range(steps)]
@@ -51,10 +52,14 @@ def main():
     vtp = run(False, 4, vision="tensor")          # tensor-parallel vision encoder (all-reduce per block)
     per_op = run(True, 4, tp_block=False)         # fused exchanges through the per-op autograd graph
     keep = run(True, 4, ckpt="false")             # one-node layers that keep their activations
+    ul = run(True, 4, ul_block=True)                # full-attention layers as one node, exchanges inside the GEMMs
+    ul_keep = run(True, 4, ul_block=True, ckpt="false")
+    rag_ul = run(True, 6, ragged=True, ul_block=True)
     rag_fused = run(True, 6, ragged=True)
     rag_lib = run(False, 6, ragged=True)
     if dist.get_rank() == 0:
-        print("RESULT " + json.dumps({"fused": fused, "lib": lib, "vision_tp": vtp, "fused_per_op": per_op, "fused_keep": keep, "ragged_fused": rag_fused,
+        print("RESULT " + json.dumps({"fused": fused, "lib": lib, "vision_tp": vtp, "fused_per_op": per_op, "fused_keep": keep, "ulysses_block": ul, "ulysses_block_keep": ul_keep, "ragged_ulysses_block": rag_ul,
+                                      "ragged_fused": rag_fused,
                                       "ragged_lib": rag_lib}))
     dist.barrier()
     dist.destroy_process_group()

@@ -112,6 +112,83 @@ def test_allgather_inside_the_gemm(tp, rows, K, N, direct):
     assert nv.get_error()[0] == 0
 
 
+def _piecewise_rows(n_rows, total, pieces, gen):
+    """``n_rows`` destination rows inside [0, total) made of ``pieces`` runs of consecutive rows (how a rank's rows of
+    several images sit in the image-major order)."""
+    cuts = sorted(torch.randperm(n_rows - 1, generator=gen)[:pieces - 1].add(1).tolist()) if pieces > 1 else []
+    lens = [b - a for a, b in zip([0] + cuts, cuts + [n_rows])]
+    gaps = total - n_rows
+    starts, pos = [], 0
+    for i, ln in enumerate(lens):
+        pos += int(torch.randint(0, gaps // len(lens) + 1, (1,), generator=gen))
+        starts.append(pos)
+        pos += ln
+    return torch.cat([torch.arange(s0, s0 + ln) for s0, ln in zip(starts, lens)]).to(torch.int32)
+
+
+@pytest.mark.parametrize("sp,C,rows,pieces", [(2, 1280, 1024, 1), (4, 1280, 1000, 3), (8, 1280, 777, 4), (2, 128, 300, 2)])
+def test_qkv_gemm_scatters_heads_to_their_owners(sp, C, rows, pieces):
+    """Ulysses sequence -> heads exchange as the epilogue of the QKV projection: column block r of q, k and v goes to
+    rank r's [T_all, 3 * W] buffer at the row's position in the image-major order.  Slabs with one owner and 32
+    consecutive destination rows leave as bulk stores, the rest (ragged pieces, W = 160) as 16-byte stores.  Ranks are
+    emulated one after the other on one GPU."""
+    F, nv, fused = _mods()
+    gen = torch.Generator().manual_seed(sp * 1000 + rows)
+    W, K = C // sp, 256
+    t_all = rows * sp + 64
+    w = (torch.randn(3 * C, K, generator=gen) * 0.05).to(DEV, torch.bfloat16)
+    b = (torch.randn(3 * C, generator=gen) * 0.1).to(DEV, torch.bfloat16)
+    dst = [torch.full((t_all, 3 * W), float("nan"), device=DEV, dtype=torch.bfloat16) for _ in range(sp)]
+    flags = [torch.zeros(8, device=DEV, dtype=torch.int32) for _ in range(sp)]
+    counter = torch.zeros(1, device=DEV, dtype=torch.int32)
+    want = [torch.full((t_all, 3 * W), float("nan")) for _ in range(sp)]
+    band = t_all // sp
+    for r in range(sp):
+        h = (torch.randn(rows, K, generator=gen)).to(DEV, torch.bfloat16)
+        row_map = (_piecewise_rows(rows, band, pieces, gen) + r * band).to(DEV)
+        c = fused.GemmCommC()
+        c.rs_rows, c.rs_self, c.rs_ranks, c.rs_epoch = 0, r, sp, 1
+        c.rs_counter = counter.data_ptr()
+        for i in range(sp):
+            c.rs_base[i] = dst[i].data_ptr()
+            c.rs_flag[i] = flags[i].data_ptr() + 4 * r
+        c.sc_row, c.sc_part, c.sc_w, c.sc_ld, c.sc_rows_dst = row_map.data_ptr(), C, W, 3 * W, t_all
+        nv.lib().mmt_gemm_set_comm(ctypes.byref(c))
+        F.gemm(h, w, bias=b, out=torch.empty(8, 3 * C, device=DEV, dtype=torch.bfloat16))
+        torch.cuda.synchronize()
+        ref = (h.float() @ w.float().t() + b.float()).cpu().view(rows, 3, sp, W)
+        for g in range(sp):
+            want[g][row_map.cpu().long()] = ref[:, :, g, :].reshape(rows, 3 * W)
+    for g in range(sp):
+        got = dst[g].cpu().float()
+        assert torch.equal(torch.isnan(got), torch.isnan(want[g]))               # exactly the rows that were sent
+        ok = ~torch.isnan(want[g])
+        assert rel(got[ok], want[g][ok]) < 1e-2
+        assert flags[g][:sp].tolist() == [1] * sp and int(counter.item()) == 0
+    assert nv.get_error()[0] == 0
+
+
+@pytest.mark.parametrize("sp,C,self_rank", [(2, 1280, 1), (4, 1280, 2), (8, 1280, 5), (2, 256, 0)])
+def test_out_projection_reads_k_slices_behind_flags(sp, C, self_rank):
+    """Ulysses heads -> sequence exchange in front of the output projection: columns [s * W, (s + 1) * W) of A come
+    from rank s; the GEMM walks its k-blocks starting with its own slice and waits per source (flags are set by the
+    host here).  The result is the plain GEMM's."""
+    F, nv, fused = _mods()
+    torch.manual_seed(sp + C)
+    rows, N = 900, 320
+    a = torch.randn(rows, C, device=DEV, dtype=torch.bfloat16)
+    w = torch.randn(N, C, device=DEV, dtype=torch.bfloat16) * 0.05
+    res = torch.randn(rows, N, device=DEV, dtype=torch.bfloat16)
+    flags = torch.full((8,), 3, device=DEV, dtype=torch.int32)
+    c = fused.GemmCommC()
+    c.kf_flags, c.kf_epoch, c.kf_w, c.kf_self, c.kf_ranks = flags.data_ptr(), 3, C // sp, self_rank, sp
+    c.rs_rows = 0
+    nv.lib().mmt_gemm_set_comm(ctypes.byref(c))
+    y = F.gemm(a, w, residual=res)
+    assert rel(y, a.float() @ w.float().t() + res.float()) < 1e-2
+    assert nv.get_error()[0] == 0
+
+
 def test_gemm_reduce_scatter_with_residual():
     F, nv, fused = _mods()
     torch.manual_seed(1)

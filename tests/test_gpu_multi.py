@@ -28,11 +28,13 @@ def test_fused_collectives_match_nccl_on_two_gpus():
         assert abs(a - b) < 3e-2 * abs(b), res
     # the one-node tensor-parallel layers (default) against the per-op graph on the same fused exchanges, with
     # recomputation and with kept activations
-    for key in ("fused_per_op", "fused_keep"):
+    for key in ("fused_per_op", "fused_keep", "ulysses_block", "ulysses_block_keep"):
         for a, b in zip(res[key], res["fused"]):
             assert abs(a - b) < 2e-2 * abs(b), (key, res)
     # six steps on images of three sizes and texts of three lengths (new shapes every step): the peer-memory paths,
     # whose heap regions are sized per step and grow, give the NCCL path's losses
     assert len(res["ragged_fused"]) == 6
     for a, b in zip(res["ragged_fused"], res["ragged_lib"]):
+        assert abs(a - b) < 3e-2 * abs(b), res
+    for a, b in zip(res["ragged_ulysses_block"], res["ragged_lib"]):
         assert abs(a - b) < 3e-2 * abs(b), res

@@ -98,3 +98,22 @@ def test_plan_partitions_tokens_and_exchange_is_a_permutation(grids, sp):
 def test_rank_without_tokens_is_an_error():
     with pytest.raises(ValueError):
         build_vision_plan([(1, 8, 8)], sp=8, rank=0, head_dim=32)
+
+
+def test_image_major_order_is_the_window_order_of_all_patches():
+    """A head owner rotates rows that arrive un-rotated from all ranks, using tables built from the positions of ALL
+    patches in window order (VisionPlan.all_pos).  That is only right if the image-major order of the gathered
+    sequence IS the window order: every rank's local tables must be rows of the global tables at the rank's
+    image-major positions."""
+    import numpy as np
+    from multimodal_training_b200.parallel.sp import build_vision_plan, rope_table
+    grids = [(1, 18, 26), (1, 8, 12), (2, 10, 6)]
+    for sp in (2, 4):
+        plans = [build_vision_plan(grids, sp=sp, rank=r, spatial_merge_size=2, window_size=112, patch_size=14,
+                                   head_dim=16) for r in range(sp)]
+        cos_all, sin_all = rope_table(plans[0].all_pos, 16)
+        off = np.concatenate([[0], np.cumsum(plans[0].rank_tokens)])
+        inv = plans[0].to_rank_major.numpy()
+        for r, p in enumerate(plans):
+            dst = torch.from_numpy(inv[off[r]:off[r + 1]])
+            assert torch.equal(cos_all[dst], p.local_cos) and torch.equal(sin_all[dst], p.local_sin)
