@@ -237,9 +237,12 @@ def bench_ulysses(fc: FusedComm, args, out) -> None:
         splits_in, splits_out = [T] * sp, list(plan.rank_tokens)
         equal = len(set(plan.rank_tokens)) == 1
 
-        def fused_qkv():
+        def fused_qkv():          # the exchange is the GEMM's epilogue (column scatter to the head owners)
+            return uf.gemm_scatter(x, w_qkv, None, 3, routes, f"bench_ul_heads_{seq}")
+
+        def kernel_qkv():         # the earlier form: GEMM, then an exchange kernel over peer memory
             qkv = F.gemm(x, w_qkv)
-            return uf._exchange("heads", qkv, 3, hl * d, routes, f"bench_ul_heads_{seq}")
+            return uf._exchange("heads", qkv, 3, hl * d, routes, f"bench_ul_heads_k_{seq}")
 
         def lib_qkv():
             qkv = torch.matmul(x, w_qkv.t())
@@ -248,8 +251,12 @@ def bench_ulysses(fc: FusedComm, args, out) -> None:
                                    group=m.sp_group)
             return recv.index_select(0, to_img)
 
-        def fused_out():
-            a = uf._exchange("tokens", attn_out, 1, hl * d, routes, f"bench_ul_tokens_{seq}")[:T]
+        def fused_out():          # rows go back without a wait; the GEMM waits per source before that K slice
+            a, flags, epoch = uf.to_tokens_nowait(attn_out, hl * d, routes, f"bench_ul_tokens_{seq}")
+            return uf.gemm_k_slices(a[:T], w_o, None, None, flags, epoch, hl * d)
+
+        def kernel_out():
+            a = uf._exchange("tokens", attn_out, 1, hl * d, routes, f"bench_ul_tokens_k_{seq}")[:T]
             return F.gemm(a, w_o)
 
         def lib_out():
@@ -264,13 +271,15 @@ def bench_ulysses(fc: FusedComm, args, out) -> None:
         e1 = float((fused_qkv().float() - lib_qkv().float()).abs().max())
         e2 = float((fused_out().float() - lib_out().float()).abs().max())
         flush = torch.empty(256 << 20, device=dev, dtype=torch.uint8)
-        for name, ff, lf, flops, link, err in (
-                ("ulysses_qkv", fused_qkv, lib_qkv, 2.0 * T * 3 * C * C, (sp - 1) / sp * T * 3 * C * 2, e1),
-                ("ulysses_out", fused_out, lib_out, 2.0 * T * C * C, (sp - 1) / sp * T * C * 2, e2)):
+        for name, ff, kf, lf, flops, link, err in (
+                ("ulysses_qkv", fused_qkv, kernel_qkv, lib_qkv, 2.0 * T * 3 * C * C, (sp - 1) / sp * T * 3 * C * 2, e1),
+                ("ulysses_out", fused_out, kernel_out, lib_out, 2.0 * T * C * C, (sp - 1) / sp * T * C * 2, e2)):
             t_f = _timed(ff, args.iters, args.warmup, flush)
+            t_k = _timed(kf, args.iters, args.warmup, flush)
             t_l = _timed(lf, args.iters, args.warmup, flush)
             roof = _roof_ms(flops, link)
-            _emit({"path": name, "gpus": sp, "seq": seq, "rows_per_rank": T, "fused_ms": t_f, "nccl_cublas_ms": t_l,
+            _emit({"path": name, "gpus": sp, "seq": seq, "rows_per_rank": T, "fused_ms": t_f,
+                   "gemm_and_exchange_kernel_ms": t_k, "nccl_cublas_ms": t_l,
                    "speedup_vs_lib": t_l / t_f, "roofline_ms": roof, "frac_of_roofline": roof / t_f,
                    "link_gbs": link / t_f / 1e6, "max_abs_err_vs_lib": err}, out)
         del flush

@@ -285,7 +285,8 @@ def test_adamw_without_master_weights():
     for want in (pc.float(), q.detach().cpu().float()):
         got = p.cpu().float()
         assert (got != want).float().mean().item() < 2e-2            # rounding flips of single elements only
-        assert ((got - want).abs() <= want.abs() * 2.0 ** -6 + 1e-30).all()
+        # one bf16 step at the magnitude of the operands (weights up to ~0.5, updates of ~lr = 1e-2)
+        assert ((got - want).abs() <= want.abs() * 2.0 ** -6 + 2e-4).all()
     assert rel_err(m.cpu().float(), mc.float()) < 1e-2 and rel_err(v.cpu().float(), vc.float()) < 1e-2
 
 
