@@ -33,7 +33,7 @@ class UlyssesFused:
         self.ranks = [m.vdp_rank * m.sp + i for i in range(m.sp)]     # heap ranks of my sequence-parallel group
         self._dummies: dict[int, torch.Tensor] = {}
         # full-attention layers as one autograd node with the exchanges inside the GEMMs (ops/ulysses_block.py)
-        self.one_node = os.environ.get("MMT_ULYSSES_BLOCK", "0") == "1"
+        self.one_node = os.environ.get("MMT_ULYSSES_BLOCK", "1") == "1"
 
     def _routes(self, plan, device):
         r = getattr(plan, "_ulysses", None)
