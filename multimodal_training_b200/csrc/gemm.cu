@@ -497,6 +497,14 @@ MMT_DEVICE void epilogue_fast(const GemmParams& p, const OutMaps& tmC, uint32_t 
   // bulk (TMA) stores: the warp hands its slab to the copy engine and goes on; the burst of all CTAs' results then
   // drains into L2 behind the next tile's main loop instead of stalling the epilogue warps on store back-pressure
   const bool bulk = p.tma_store == 2;
+  // column scatter: destination rows of the slab's first and last row, fetched now so that the loads are in flight
+  // while the accumulator is read; 32 consecutive rows can leave as one box
+  int sc_first = 0;
+  bool sc_rows_in_a_run = false;
+  if (p.sc_row && srow0 + 32 <= p.M) {
+    sc_first = p.sc_row[srow0];
+    sc_rows_in_a_run = p.sc_row[srow0 + 31] - sc_first == 31;
+  }
 #pragma unroll 1
   for (int g = half; g < kGroups; g += 2) {
     uint32_t r0[32], r1[32];
@@ -563,10 +571,9 @@ MMT_DEVICE void epilogue_fast(const GemmParams& p, const OutMaps& tmC, uint32_t 
         // one owner, one column block and 32 consecutive destination rows, or else plain stores below
         const int part = colg / p.sc_part, within = colg - part * p.sc_part, owner = within / p.sc_w;
         const int in_owner = within - owner * p.sc_w;
-        stored = srow0 + 32 <= p.M && colg + 64 <= N && within + 64 <= p.sc_part && in_owner + 64 <= p.sc_w &&
-                 p.sc_row[srow0 + 31] - p.sc_row[srow0] == 31;
+        stored = sc_rows_in_a_run && colg + 64 <= N && within + 64 <= p.sc_part && in_owner + 64 <= p.sc_w;
         if (stored && lane == 0) {
-          tma_store_2d(&tmC.m[owner], slab, part * p.sc_w + in_owner, p.sc_row[srow0]);
+          tma_store_2d(&tmC.m[owner], slab, part * p.sc_w + in_owner, sc_first);
           tma_store_commit();
         }
       } else if (lane == 0) {
@@ -773,7 +780,10 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       uint32_t ag_seen = p.ag_flags ? (1u << p.ag_self) : 0u;
       uint32_t ag_chunk_seen[16] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
       uint32_t fwd_pending = 0, fwd_parity = 0;   // per stage: last use is being forwarded / parity of that hand-back
-      uint32_t kf_seen = 0;                       // K-slice consumer: source ranks already waited for
+      // K-slice consumer: source ranks already waited for (own slice needs no wait), all of them, first k-block
+      uint32_t kf_seen = p.kf_flags ? (1u << p.kf_self) : 0u;
+      const uint32_t kf_all = p.kf_flags ? ((1u << p.kf_ranks) - 1u) : 0u;
+      const int kf_kb0 = p.kf_flags ? (p.kf_self * p.kf_w) / BK : 0;
       int kcount = 0;
       WorkItem w;
       for (int wi = 0; ok && work_item(p, wi, blockIdx.x, gridDim.x, KB, ntiles, w); ++wi) {
@@ -795,16 +805,19 @@ gemm_bf16_tcgen05(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           if (!ok) break;
           asm volatile("fence.proxy.async;" ::: "memory");
         }
+        // K-slice consumer: only until every source has been seen once (normally the CTA's first tile); after that
+        // the k-blocks are walked in plain order with no per-block work in this thread
+        const bool kf_tile = p.kf_flags && kf_seen != kf_all;
         for (int kb0 = w.k0; kb0 < w.k1; ++kb0) {
           int kb = kb0;
-          if (p.kf_flags) {
-            // K-slice consumer: start with this rank's own columns of A, wait for a peer's slice when it is reached
-            kb = kb0 + (p.kf_self * p.kf_w) / BK;
+          if (kf_tile) {
+            // start with this rank's own columns of A, wait for a peer's slice when it is reached
+            kb = kb0 + kf_kb0;
             if (kb >= KB) kb -= KB;
             const int s0 = (kb * BK) / p.kf_w, s1 = min((kb * BK + BK - 1) / p.kf_w, p.kf_ranks - 1);
             bool waited = false;
             for (int src = s0; src <= s1 && ok; ++src) {
-              if (src == p.kf_self || (kf_seen & (1u << src))) continue;
+              if (kf_seen & (1u << src)) continue;
               ok = flag_wait_ge(&p.kf_flags[src], p.kf_epoch, MMT_WAIT_NS, p.ew, 112);
               kf_seen |= 1u << src;
               waited = true;

@@ -172,9 +172,113 @@ def gemm_shapes(a) -> int:
     return 0
 
 
+def gemm_roles(a) -> int:
+    """The GEMM's collective roles on ONE GPU, with local buffers standing in for the peers' (the kernel and its
+    instruction stream are the ones that run across GPUs; only the destination addresses are local): what each role
+    costs over the plain GEMM of the same shape, and a small case to capture under a profiler.
+
+    * forwarder: rank 0 of 2 computes gathered [2 x rows, K] x [N, K]^T and forwards its own rows to the "peer"
+    * scatter:   [rows, K] x [3C, K]^T whose epilogue scatters column blocks to 2 "ranks" at mapped rows
+    * k_slices:  [rows, C] x [C, C]^T that waits per K slice (flags already set)"""
+    import ctypes
+
+    from ..parallel.fused import GemmCommC
+    dev = "cuda"
+    rows, K, N = a.m // 2, a.k, a.n
+    torch.manual_seed(0)
+    gathered = torch.randn(2 * rows, K, device=dev, dtype=torch.bfloat16)
+    w = torch.randn(N, K, device=dev, dtype=torch.bfloat16) * 0.02
+    peer = torch.empty_like(gathered)
+    flags = torch.ones(8 * 64, device=dev, dtype=torch.int32)
+    peer_flags = torch.zeros(8 * 64, device=dev, dtype=torch.int32)
+    counter = torch.zeros(64, device=dev, dtype=torch.int32)
+    out = torch.empty(2 * rows, N, device=dev, dtype=torch.bfloat16)
+
+    def forwarder():
+        c = GemmCommC()
+        c.ag_flags, c.ag_epoch, c.ag_rows, c.ag_self, c.rs_rows = flags.data_ptr(), 1, rows, 0, 0
+        c.fwd_dst[0], c.fwd_flag[0], c.fwd_peers = peer.data_ptr(), peer_flags.data_ptr(), 1
+        c.fwd_counter = counter.data_ptr()
+        nv.lib().mmt_gemm_set_comm(ctypes.byref(c))
+        F.gemm(gathered, w, out=out)
+
+    def back_to_back(fn, n=40):
+        """Seconds per launch with the launches queued back to back (no host gap between them, warm L2)."""
+        for _ in range(3):
+            fn()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e-3 / n
+
+    t_plain = timed(lambda: F.gemm(gathered, w, out=out), a.iters, a.warmup, not a.no_flush)
+    t_fwd = timed(forwarder, a.iters, a.warmup, not a.no_flush)
+    b_plain, b_fwd = back_to_back(lambda: F.gemm(gathered, w, out=out)), back_to_back(forwarder)
+    ok = bool(torch.equal(peer[:rows], gathered[:rows]))
+    fl = 2.0 * 2 * rows * N * K
+    print(json.dumps({"role": "all-gather forwarder", "shape": [2 * rows, N, K], "plain_ms": t_plain * 1e3,
+                      "with_role_ms": t_fwd * 1e3, "tflops_with_role": fl / t_fwd / 1e12, "rows_forwarded_intact": ok,
+                      "back_to_back_plain_ms": b_plain * 1e3, "back_to_back_with_role_ms": b_fwd * 1e3}))
+    # scatter (vision QKV shapes)
+    C, sp, T = 1280, 2, a.tokens
+    W = C // sp
+    h = torch.randn(T, C, device=dev, dtype=torch.bfloat16)
+    wq = torch.randn(3 * C, C, device=dev, dtype=torch.bfloat16) * 0.02
+    dst = [torch.empty(2 * T, 3 * W, device=dev, dtype=torch.bfloat16) for _ in range(sp)]
+    row_map = torch.arange(T, device=dev, dtype=torch.int32)
+    sflags = torch.zeros(8, device=dev, dtype=torch.int32)
+    dummy = torch.empty(8, 3 * C, device=dev, dtype=torch.bfloat16)
+    qkv = torch.empty(T, 3 * C, device=dev, dtype=torch.bfloat16)
+
+    def scatter():
+        c = GemmCommC()
+        c.rs_rows, c.rs_self, c.rs_ranks, c.rs_epoch, c.rs_counter = 0, 0, sp, 1, counter.data_ptr()
+        for i in range(sp):
+            c.rs_base[i], c.rs_flag[i] = dst[i].data_ptr(), sflags.data_ptr()
+        c.sc_row, c.sc_part, c.sc_w, c.sc_ld, c.sc_rows_dst = row_map.data_ptr(), C, W, 3 * W, 2 * T
+        nv.lib().mmt_gemm_set_comm(ctypes.byref(c))
+        F.gemm(h, wq, out=dummy)
+
+    t_plain = timed(lambda: F.gemm(h, wq, out=qkv), a.iters, a.warmup, not a.no_flush)
+    t_sc = timed(scatter, a.iters, a.warmup, not a.no_flush)
+    b_plain, b_sc = back_to_back(lambda: F.gemm(h, wq, out=qkv)), back_to_back(scatter)
+    ref = qkv.view(T, 3, sp, W)
+    ok = all(bool(torch.equal(dst[g][:T], ref[:, :, g, :].reshape(T, 3 * W))) for g in range(sp))
+    print(json.dumps({"role": "column scatter (Ulysses QKV epilogue)", "shape": [T, 3 * C, C], "plain_ms": t_plain * 1e3,
+                      "with_role_ms": t_sc * 1e3, "scattered_equals_plain": ok, "back_to_back_plain_ms": b_plain * 1e3,
+                      "back_to_back_with_role_ms": b_sc * 1e3}))
+    # K-slice consumer (vision output projection)
+    a_tok = torch.randn(T, C, device=dev, dtype=torch.bfloat16)
+    wo = torch.randn(C, C, device=dev, dtype=torch.bfloat16) * 0.02
+    y = torch.empty(T, C, device=dev, dtype=torch.bfloat16)
+
+    def k_slices():
+        c = GemmCommC()
+        c.rs_rows = 0
+        c.kf_flags, c.kf_epoch, c.kf_w, c.kf_self, c.kf_ranks = flags.data_ptr(), 1, W, a.self_rank % sp, sp
+        nv.lib().mmt_gemm_set_comm(ctypes.byref(c))
+        F.gemm(a_tok, wo, out=y)
+
+    t_plain = timed(lambda: F.gemm(a_tok, wo, out=y), a.iters, a.warmup, not a.no_flush)
+    t_kf = timed(k_slices, a.iters, a.warmup, not a.no_flush)
+    b_plain, b_kf = back_to_back(lambda: F.gemm(a_tok, wo, out=y)), back_to_back(k_slices)
+    print(json.dumps({"role": "K-slice consumer (Ulysses output projection)", "shape": [T, C, C],
+                      "plain_ms": t_plain * 1e3, "with_role_ms": t_kf * 1e3, "back_to_back_plain_ms": b_plain * 1e3,
+                      "back_to_back_with_role_ms": b_kf * 1e3}))
+    code = nv.get_error()
+    if code[0]:
+        print(json.dumps({"device_error": code}))
+        return 1
+    return 0
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["gemm_shapes", "gemm", "attention", "attention_bwd", "rmsnorm", "rmsnorm_bwd", "rope", "swiglu",
+    ap.add_argument("kernel", choices=["gemm_shapes", "gemm_roles", "gemm", "attention", "attention_bwd", "rmsnorm", "rmsnorm_bwd", "rope", "swiglu",
                                       "adamw", "ce"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8192)
@@ -194,6 +298,7 @@ def main(argv=None) -> int:
     ap.add_argument("--no-flush", action="store_true")
     ap.add_argument("--stream-k", type=int, default=-1, help="GEMM: 1 = stream-K for partial last waves, 0 = off (default)")
     ap.add_argument("--pair", type=int, default=-1, help="GEMM: 1 = 2-CTA kernel, 0 = 1-CTA kernels, -1 = default")
+    ap.add_argument("--self-rank", type=int, default=1, help="gemm_roles: rank that the K-slice consumer plays")
     ap.add_argument("--sustain", type=float, default=0.5, help="gemm_shapes: seconds of back-to-back launches per case")
     a = ap.parse_args(argv)
     dev = "cuda"
@@ -208,6 +313,8 @@ def main(argv=None) -> int:
             print(json.dumps({"device_error": code}))
             return 1
         return rc
+    if a.kernel == "gemm_roles":
+        return gemm_roles(a)
     if a.kernel == "gemm":
         if a.pair >= 0:
             nv.lib().mmt_gemm_use_pair(a.pair)
