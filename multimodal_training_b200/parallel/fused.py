@@ -128,6 +128,7 @@ class FusedComm:
         # True: all-gather inside the consuming GEMM (ag_gemm); False: a push kernel in front of it (push_gather)
         self.fused_ag = os.environ.get("MMT_FUSED_AG", "1") == "1"
         self._ag_roles: dict[str, int] = {}
+        self._views: dict = {}           # (region, shape, dtype) -> (offset, tensor view of this rank's buffer)
         self._ag_counter = None          # [AG_ROLES, AG_CHUNKS] int32: shares of a row block that have been forwarded
         self.ctx = HeapContext(mesh.world_group, heap_bytes, device)
         # results that live in reusable heap regions may be handed out as views only while BOTH halves recompute
@@ -200,7 +201,17 @@ class FusedComm:
         for s in shape:
             n *= int(s)
         off = self.ctx.heap.alloc(name, n * 2)
-        return off, self.ctx.heap.tensor(off, shape, dtype)
+        # wrapping a raw device pointer in a tensor costs tens of microseconds of host time, and a step asks for the
+        # same few regions hundreds of times: keep the view while the region stays where it is
+        key = (name, tuple(int(s) for s in shape), dtype)
+        hit = self._views.get(key)
+        if hit is not None and hit[0] == off:
+            return off, hit[1]
+        view = self.ctx.heap.tensor(off, shape, dtype)
+        if len(self._views) > 256:
+            self._views.clear()
+        self._views[key] = (off, view)
+        return off, view
 
     def push_gather(self, x_shard: torch.Tensor, norm_w, eps: float, role: str):
         """(RMSNorm of) a [T/tp, K] shard into every TP peer's [T, K] gather buffer.

@@ -175,3 +175,122 @@ def test_the_checker_catches_an_unsafe_order(monkeypatch):
     with pytest.raises(AssertionError, match="has not run yet"):
         for seed in range(60):
             _replay(bad, 2, random.Random(seed), laggard=0)
+
+
+# ------------------------------------------------------------------------------------------------------------------
+# The same check for the vision encoder's full-attention layers (ops/ulysses_block.py): four regions
+# (ul_heads3, ul_tokens1, ul_heads1_bwd, ul_tokens3_bwd), each reused by every full-attention layer.
+# ------------------------------------------------------------------------------------------------------------------
+class RecorderUF:
+    """Stands in for UlyssesFused: records writes into every peer's region and reads of this rank's region."""
+
+    sp, sp_rank = 2, 0
+
+    def __init__(self):
+        self.ops, self.epochs, self.region_of, self.keepalive = [], {}, {}, []
+
+    def _new(self, region, rows, cols):
+        self.epochs[region] = self.epochs.get(region, 0) + 1
+        e = self.epochs[region]
+        self.ops.append(("write_all", region, e))
+        t = torch.zeros(rows, cols)
+        self.region_of[id(t)] = (region, e)
+        self.keepalive.append(t)
+        return t, e
+
+    def _routes(self, plan, device):
+        return {"t_all": 4, "t_loc_max": 2}
+
+    def rope_tables(self, plan, device):
+        return torch.zeros(1), torch.zeros(1)
+
+    def gemm_scatter(self, a, w, bias, parts, routes, name, b_mn=False):
+        self.note_reads(a, w)
+        t, e = self._new(name, 4, parts * 4)
+        self.ops.append(("read", name, e, True))                   # the wait behind the GEMM
+        return t
+
+    def to_tokens_nowait(self, src, W, routes, name):
+        self.note_reads(src)
+        t, e = self._new(name, 2, 8)
+        return t, name, e
+
+    def gemm_k_slices(self, a, w, bias, residual, flags, epoch, W):
+        self.ops.append(("read", flags, epoch, True))              # waits per source inside the GEMM
+        return torch.zeros(a.shape[0], 8)
+
+    def _exchange(self, kind, src, parts, W, routes, name):
+        self.note_reads(src)
+        t, e = self._new(name, 2, parts * 8)
+        self.ops.append(("read", name, e, True))
+        return t
+
+    def note_reads(self, *tensors):
+        for t in tensors:
+            base = t if id(t) in self.region_of else getattr(t, "_base", None)
+            hit = self.region_of.get(id(base)) if base is not None else None
+            if hit is not None:
+                self.ops.append(("read", hit[0], hit[1], False))
+
+
+def _ulysses_program(layers: int, recompute: bool, monkeypatch):
+    from multimodal_training_b200.ops import ulysses_block as ub
+    uf = RecorderUF()
+    C = 8
+    z = lambda *s: torch.zeros(*s)  # noqa: E731
+    monkeypatch.setattr(ub, "_rope_", lambda t, *a, **k: uf.note_reads(t))
+    monkeypatch.setattr(ub, "_rmsnorm_fwd", lambda x, w, eps: (z(*x.shape), z(x.shape[0])))
+    monkeypatch.setattr(ub, "_rmsnorm_bwd", lambda dy, x, w, rstd, extra: z(*x.shape))
+    monkeypatch.setattr(ub, "_swiglu_fwd", lambda gu: z(gu.shape[0], gu.shape[1] // 2))
+    monkeypatch.setattr(ub, "_swiglu_bwd", lambda dm, gu: z(*gu.shape))
+    monkeypatch.setattr(ub, "_grad_into", lambda p, compute: compute(z(*p.shape), False))
+
+    def attn_fwd(qkv, s, seq):
+        uf.note_reads(qkv)
+        return z(qkv.shape[0], 4), z(1, qkv.shape[0])
+
+    def attn_bwd(qkv, a, da, lse, s, seq):
+        uf.note_reads(qkv, a, da)
+        return z(*qkv.shape)
+
+    def linear_bwd(dy, x, w, b):
+        uf.note_reads(dy, x)
+        return z(dy.shape[0], w.shape[1])
+    monkeypatch.setattr(ub, "_attn_fwd", attn_fwd)
+    monkeypatch.setattr(ub, "_attn_bwd", attn_bwd)
+    monkeypatch.setattr(ub, "_linear_bwd", linear_bwd)
+
+    def fake_gemm(a, b, **kw):
+        uf.note_reads(a, b)
+        n = b.shape[1] if kw.get("b_mn") else b.shape[0]
+        return kw.get("out", z(a.shape[0], n))
+    monkeypatch.setattr(ub.F, "gemm", fake_gemm)
+    monkeypatch.setattr(ub.F, "colsum", lambda x, **kw: None)
+    spec = BlockSpec(n_q=2, n_kv=2, head_dim=4, rope_heads=4, causal=False, eps=1e-6, scale=1.0)
+    spec_h = BlockSpec(n_q=1, n_kv=1, head_dim=4, rope_heads=2, causal=False, eps=1e-6, scale=1.0)
+    P = (z(C), z(3 * C, C), z(3 * C), z(C, C), z(C), z(C), z(4 * C, C), z(4 * C), z(C, 2 * C), z(C))
+    ctxs, x = [], z(2, C)
+    for _ in range(layers):
+        ctx = FakeCtx()
+        x = ub._UlyssesBlockFn.forward(ctx, x, spec, spec_h, None, None, recompute, uf, *P)
+        ctxs.append(ctx)
+    dy = z(2, C)
+    for ctx in reversed(ctxs):
+        dy = ub._UlyssesBlockFn.backward(ctx, dy)[0]
+    return uf.ops
+
+
+@pytest.mark.parametrize("recompute", [True, False])
+def test_ulysses_layer_region_reuse_is_safe_under_any_interleaving(monkeypatch, recompute):
+    program = _ulysses_program(layers=3, recompute=recompute, monkeypatch=monkeypatch)
+    regions = {op[1] for op in program}
+    assert {"ul_heads3", "ul_tokens1", "ul_heads1_bwd", "ul_tokens3_bwd"} <= regions
+    if recompute:
+        # backward reads the heap views that its own recomputation produced (no private copies in this mode)
+        assert any(op[0] == "read" and not op[3] and op[1] == "ul_heads3" for op in program)
+        assert any(op[0] == "read" and not op[3] and op[1] == "ul_tokens1" for op in program)
+    for n_ranks in (2, 4):
+        for seed in range(40):
+            _replay(program, n_ranks, random.Random(seed))
+        for lag in range(n_ranks):
+            _replay(program, n_ranks, random.Random(200 + lag), laggard=lag)
