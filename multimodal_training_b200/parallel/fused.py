@@ -3,18 +3,23 @@
 The kernels live in ``csrc/fused.cu`` and ``csrc/gemm.cu``; this module owns the symmetric heap, the
 epoch counters of every flag slot and the autograd functions that replace the NCCL versions of
 
-* tensor-parallel ``all-gather -> GEMM`` (the RMSNorm in front of the GEMM stores its rows into every
-  peer's gather buffer; the GEMM's TMA producer waits per source rank) and ``GEMM -> reduce-scatter``
-  (the GEMM epilogue stores partial tiles into the owner's staging slot; the owner sums them with the
-  residual) -- forward and backward of the attention and MLP projections of the text decoder;
+* tensor-parallel ``all-gather -> GEMM`` (``ag_gemm``: the GEMM forwards the shared-memory stages of its own rows
+  to the peers while it computes on them and waits per (source rank, row block) before it reads a peer's rows;
+  ``push_gather`` + ``gemm_gathered``: the earlier form with a push kernel in front of the GEMM, still used for
+  shards that do not split into 256-row blocks) and ``GEMM -> reduce-scatter`` (the GEMM epilogue stores partial
+  tiles into the owner's staging slot; the owner sums them with the residual) -- forward and backward of the
+  attention and MLP projections of the text decoder (one autograd node per layer: ``ops/tp_blocks.py``);
+* the vision encoder's Ulysses exchanges inside the QKV and output projections (``fused_ulysses.py``,
+  ``ops/ulysses_block.py``);
 * the vision -> text handoff (merged tokens stored straight into the text ranks' rows) and its gradient;
 * ZeRO-1: gradient reduce-scatter + AdamW + parameter all-gather as one kernel (``FusedZero``).
 
 Buffer reuse needs no extra barriers: every region has one role, two uses of a role are separated by
 at least one other exchange that every rank can only finish after all peers have started it, flags
 count epochs upward, and the backward pass computes weight gradients (which read gathered inputs)
-before it pushes anything that lets a peer run ahead.  Every wait is bounded on the device; the host
-checks the error word at step boundaries (``ops.native.raise_on_device_error``).
+before it pushes anything that lets a peer run ahead (``tests/test_exchange_schedule.py`` replays the layers' real
+exchange order under arbitrary rank skew).  Every wait is bounded on the device; the host checks the error word
+where it synchronises anyway (``LossHandle.value``, ``Trainer.check_device_errors``).
 """
 from __future__ import annotations
 

@@ -47,3 +47,28 @@ def test_checkpointing_settings_agree():
         got, _ = _run(2, 1, 3, mode)
         for a, b in zip(ref, got):
             assert abs(a - b) < 1e-3 * abs(a), (mode, ref, got)
+
+
+def test_tensor_transfer_over_cuda_ipc(tmp_path):
+    """runtime/tensor_transfer.py, "ipc" transport: a second process on the same GPU maps the producer's memory from
+    the request (CUDA IPC handle + interprocess event), reads it and writes into it."""
+    import os
+    import pickle
+    import subprocess
+    import sys
+    from multimodal_training_b200.runtime.tensor_transfer import prepare_tensor_for_transfer
+    from multimodal_training_b200.runtime.utils import get_physical_gpu_id
+    t = torch.arange(1 << 16, device="cuda", dtype=torch.float32).reshape(256, 256)
+    want = float(t.double().sum())
+    req = prepare_tensor_for_transfer(t, receiver_gpu_ids=[get_physical_gpu_id()], same_process=False)
+    assert req.transport == "ipc"
+    path = tmp_path / "req.pkl"
+    pickle.dump(req.to_dict(), open(path, "wb"))
+    here = os.path.dirname(os.path.abspath(__file__))
+    out = subprocess.run([sys.executable, os.path.join(here, "ipc_receiver.py"), str(path), os.path.dirname(here)],
+                         capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-2000:]
+    got = float([ln for ln in out.stdout.splitlines() if ln.startswith("SUM ")][-1][4:])
+    assert got == want
+    torch.cuda.synchronize()
+    assert float(t.double().sum()) == 2 * want            # the receiver's in-place update landed in this tensor
