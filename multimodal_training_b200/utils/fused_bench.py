@@ -94,6 +94,8 @@ def bench_tp(fc: FusedComm, args, out) -> None:
     for hidden, inter in ((3584, 18944), (5120, 27648)):
         for tokens in args.tokens:
             shapes.append(("ag_gemm", tokens, hidden, 3 * hidden))       # column-parallel, N = 3 x hidden
+            if hidden == 3584:
+                shapes.append(("ag_gemm", tokens, hidden, 4608))         # the 7B model's q|k|v width (28 + 2 x 4 heads)
             shapes.append(("ag_gemm", tokens, hidden, 2 * inter))        # gate + up
             shapes.append(("gemm_rs", tokens, hidden, hidden))           # row-parallel o_proj: K = hidden
             shapes.append(("gemm_rs", tokens, hidden, inter))            # down_proj: K = MLP width
