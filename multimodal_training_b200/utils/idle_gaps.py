@@ -27,17 +27,28 @@ def merge_intervals(intervals: list[tuple[float, float]]) -> list[tuple[float, f
 
 
 def summarize(intervals: list[tuple[float, float]], steps: int, gap_floor_us: float = 2.0) -> dict:
-    """``intervals`` in microseconds -> per-step busy / idle milliseconds and gap statistics."""
+    """``intervals`` in microseconds -> per-step busy / idle milliseconds and gap statistics.
+
+    The trace begins with a start-up gap that steady-state training does not have (the first traced step starts
+    with an empty launch queue: the device waits while the host prepares the step, and in a multi-rank run also for
+    the slowest rank's tracer).  A gap in the first 15 % of the timeline that is larger than a millisecond is
+    therefore reported on its own (``startup_gap_ms``) and left out of the idle time."""
     merged = merge_intervals(intervals)
     if not merged:
         return {"kernels": 0}
-    span = merged[-1][1] - merged[0][0]
+    t0, t1 = merged[0][0], merged[-1][1]
+    gaps = [(merged[i + 1][0] - merged[i][1], merged[i][1]) for i in range(len(merged) - 1)]
+    startup = 0.0
+    early = [(g, at) for g, at in gaps if at - t0 < 0.15 * (t1 - t0) and g > 1000.0]
+    if early:
+        startup = max(g for g, _ in early)
+    span = (t1 - t0) - startup
     busy = sum(b - a for a, b in merged)
-    gaps = [merged[i + 1][0] - merged[i][1] for i in range(len(merged) - 1)]
-    big = sorted((g for g in gaps if g > gap_floor_us), reverse=True)
+    big = sorted((g for g, _ in gaps if g > gap_floor_us and g != startup), reverse=True)
     return {"kernels": len(intervals), "steps": steps,
             "span_ms_per_step": span / 1e3 / steps, "busy_ms_per_step": busy / 1e3 / steps,
             "idle_ms_per_step": (span - busy) / 1e3 / steps, "idle_share": (span - busy) / span if span else 0.0,
+            "startup_gap_ms": startup / 1e3,
             "gaps_over_floor_per_step": len(big) / steps, "gap_floor_us": gap_floor_us,
             "largest_gaps_us": [round(g, 1) for g in big[:5]]}
 

@@ -241,3 +241,15 @@ def test_zero_stage_three_is_rejected_only_where_it_would_be_used():
         load_config(None, ["text.parallelism=deepspeed", "text.zero_stage=3"])
     with pytest.raises(ConfigError, match="zero_stage"):
         load_config(None, ["vision.parallelism=deepspeed", "vision.zero_stage=3"])
+
+
+def test_idle_gap_summary_merges_streams_and_sets_the_startup_gap_aside():
+    from multimodal_training_b200.utils.idle_gaps import merge_intervals, short_name, summarize
+    assert merge_intervals([(5, 9), (0, 3), (2, 4), (9, 10)]) == [(0, 4), (5, 10)]
+    # two streams overlapping, a 5 ms hole right after the first kernel (empty launch queue at trace start), then
+    # 2000 kernels of 18 us every 20 us
+    iv = [(0, 10), (5000, 5010)] + [(5010 + i * 20, 5010 + i * 20 + 18) for i in range(2000)] + [(6000, 6015)]
+    out = summarize(iv, steps=2)
+    assert abs(out["startup_gap_ms"] - 4.99) < 1e-6
+    assert abs(out["idle_ms_per_step"] - 2.0) < 0.01 and abs(out["idle_share"] - 0.1) < 0.002
+    assert short_name("void (anonymous namespace)::gemm_bf16_tcgen05<256, 2>(CUtensorMap_st, int)") == "gemm_bf16_tcgen05"
