@@ -103,6 +103,19 @@ def _run_lib_arm(args, global_batch: int, tp: int, steps: int, warmup: int) -> d
                        global_batch=global_batch, tp=tp, steps=steps, warmup=warmup)
 
 
+def _native_so_loaded() -> list[str]:
+    """Shared libraries from this repository that are mapped into this process right now."""
+    found = set()
+    try:
+        for line in open("/proc/self/maps"):
+            path = line.rsplit(" ", 1)[-1].strip()
+            if path.endswith(".so") and path.startswith(ROOT):
+                found.add(os.path.relpath(path, ROOT))
+    except OSError:
+        pass
+    return sorted(found)
+
+
 def _lib_best(lib: dict) -> tuple[float, float, str]:
     """(device ms, end-to-end ms, policy) of the faster of the library arm's two activation policies."""
     best = (lib["ms_per_step"], lib["e2e_ms_per_step"], "recompute")
@@ -221,7 +234,8 @@ def main() -> int:
                    "e2e": {"value": patches / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms,
                            "h2d_bytes_per_step": lib["h2d_bytes_per_step"], "d2h_bytes_per_step": 4.0 * N},
                    "gpu_launches": 0,
-                   "gpu_launches_note": "library arm: cuBLAS, flash-attn, ATen and NCCL kernels only"}
+                   "gpu_launches_note": "library arm: cuBLAS, flash-attn, ATen and NCCL kernels only",
+                   "native_so_loaded": _native_so_loaded()}
             print(json.dumps(out))
         if world > 1:
             dist.barrier()
@@ -469,6 +483,7 @@ def main() -> int:
             "device_idle": idle,
             "gpu_launches": int(launches),
             "gpu_launches_per_step": launches / args.steps,
+            "native_so_loaded": _native_so_loaded(),
         }
         print(json.dumps(out))
     if world > 1:
