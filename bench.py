@@ -106,11 +106,12 @@ def _run_lib_arm(args, global_batch: int, tp: int, steps: int, warmup: int) -> d
 def _native_so_loaded() -> list[str]:
     """Shared libraries from this repository that are mapped into this process right now."""
     found = set()
+    root = os.path.realpath(ROOT)
     try:
         for line in open("/proc/self/maps"):
-            path = line.rsplit(" ", 1)[-1].strip()
-            if path.endswith(".so") and path.startswith(ROOT):
-                found.add(os.path.relpath(path, ROOT))
+            path = os.path.realpath(line.rsplit(" ", 1)[-1].strip())
+            if path.endswith(".so") and path.startswith(root + os.sep):
+                found.add(os.path.relpath(path, root))
     except OSError:
         pass
     return sorted(found)
