@@ -54,11 +54,20 @@ class ObjectRef:
 
 
 def _to_cpu(obj):
-    """Make a result picklable for the trip to the driver (device tensors become CPU tensors)."""
+    """Make a result picklable for the trip to the driver (device tensors become CPU tensors).
+
+    A dict that carries a ``loss_async`` handle (``engine.LossHandle``: the loss was copied to pinned host memory
+    behind the step, with an event) is resolved through the handle: waiting for that one event does not drain the
+    launch queue, whereas ``loss.cpu()`` would wait for everything the process has enqueued since."""
     import torch
     if isinstance(obj, torch.Tensor):
         return obj.detach().cpu()
     if isinstance(obj, dict):
+        handle = obj.get("loss_async")
+        if handle is not None and hasattr(handle, "value"):
+            out = {k: _to_cpu(v) for k, v in obj.items() if k not in ("loss", "loss_async")}
+            out["loss"] = torch.tensor(handle.value())
+            return out
         return {k: _to_cpu(v) for k, v in obj.items()}
     if isinstance(obj, (list, tuple)):
         return type(obj)(_to_cpu(v) for v in obj)

@@ -115,10 +115,33 @@ class TextTrainer(Trainer):
                                label_smoothing=float(self.config.get("label_smoothing", 0.0) or 0.0))
         self._loss = loss
         out = {"loss": loss.detach(), "sample_index": tb.sample_index, "iteration": iteration}
+        if loss.is_cuda and bool(self.config.get("async_loss", True)):
+            out["loss_async"] = self._loss_handle(loss)
         ms = self._timer_stop(t0)
         if ms is not None:
             out["forward_time_ms"] = ms
         return out
+
+    def _loss_handle(self, loss: torch.Tensor):
+        """The loss (and the device error word) on their way to pinned host memory, with an event behind the copies:
+        whoever reads the loss later -- the actor runtime when it ships this step's result to the driver -- waits for
+        that event only and learns at the same time whether a kernel reported a failed wait."""
+        from ..engine import LossHandle
+        from ..ops import native as nv
+        ring = getattr(self, "_loss_ring", None)
+        if ring is None:
+            ring = self._loss_ring = [(torch.zeros(1, dtype=torch.float32, pin_memory=True),
+                                       torch.zeros(4, dtype=torch.int32, pin_memory=True)) for _ in range(32)]
+            self._loss_i = 0
+            self._err_dev = nv.error_word_tensor() if nv.available() else None
+        host, err = ring[self._loss_i % len(ring)]
+        self._loss_i += 1
+        host.copy_(loss.detach().float().reshape(1), non_blocking=True)
+        if self._err_dev is not None:
+            err.copy_(self._err_dev, non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        return LossHandle(host, event, err if self._err_dev is not None else None)
 
     def backward_step(self) -> dict:
         t0 = self._timer_start()

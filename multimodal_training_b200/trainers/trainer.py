@@ -294,9 +294,9 @@ class Trainer(RayActor):
         return True
 
     def get_memory_stats(self) -> dict:
-        # the driver calls this once per step after it has read the losses: the step's kernels have run, so this is
-        # where the actor runtime notices a device-side failure before the next step builds on garbage
-        self.check_device_errors()
+        # no device synchronisation here: the driver calls this at its logging points between steps that are still
+        # in flight.  Device-side failures reach the driver with the loss (TextTrainer._loss_handle copies the error
+        # word behind every forward) and are checked with a synchronisation before every checkpoint.
         if self._get_device().type == "cuda":
             return {"allocated_mb": torch.cuda.memory_allocated() / 2 ** 20,
                     "peak_mb": torch.cuda.max_memory_allocated() / 2 ** 20}
