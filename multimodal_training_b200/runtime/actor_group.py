@@ -267,8 +267,9 @@ def get(refs, timeout_s: float | None = None):
 class ActorGroup:
     def __init__(self, config: dict, actor_cls, num_actors: int, collocate: bool = False,
                  placement_group_handle: HostPool | None = None, backend: str | None = None,
-                 rpc_timeout_s: float | None = None, env: dict | None = None):
+                 rpc_timeout_s: float | None = None, env: dict | None = None, gpu_offset: int = 0):
         self.config = config
+        self.gpu_offset = int(gpu_offset)      # actor i drives GPU i + gpu_offset (a group on GPUs of its own)
         self.actor_cls = actor_cls
         self.num_actors = num_actors
         self.collocate = collocate
@@ -310,7 +311,7 @@ class ActorGroup:
             return
         ips = self.execute_all("get_node_ip_addr")
         ports = self.execute_all("get_free_port")
-        cfgs = [TorchDistributedConfig(rank=i, local_rank=i, world_size=self.num_actors,
+        cfgs = [TorchDistributedConfig(rank=i, local_rank=i + self.gpu_offset, world_size=self.num_actors,
                                        local_world_size=self.num_actors, master_addr=ips[0], master_port=ports[0],
                                        backend=self.backend) for i in range(self.num_actors)]
         self.execute_all("setup_env_variables", cfgs)

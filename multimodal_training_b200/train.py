@@ -73,13 +73,32 @@ def main(cfg: dict) -> dict:
     text_cls = get_text_trainer_class(cfg["text"]["model_type"])
     vision_group = ActorGroup(vision_config, vision_cls, num_actors, collocate=collocate,
                               rpc_timeout_s=tr.get("rpc_timeout_s"))
-    # the halves always share hosts: the handoff is an in-process exchange (see runtime/actor_group.py)
-    text_group = ActorGroup(text_config, text_cls, num_actors, collocate=collocate,
-                            placement_group_handle=vision_group.placement_group_handle)
+    if collocate:
+        # the halves share hosts (one process and one torch.distributed world per GPU): the handoff is an exchange
+        # inside that world, or a peer store
+        text_group = ActorGroup(text_config, text_cls, num_actors, collocate=True,
+                                placement_group_handle=vision_group.placement_group_handle)
+    else:
+        # training.collocate: false -- the text half gets host processes (and, when the node has enough of them,
+        # GPUs) of its own and a world of its own.  Vision actor i's rows travel to text actor i by value through
+        # the driver (ActorGroup._localise), the text group exchanges them among its own ranks, and the gradient
+        # comes back the same way (python/train_ray.py:257-260 moves these tensors with Ray's NCCL transport).
+        offset = 0
+        try:
+            import torch
+            if torch.cuda.is_available() and torch.cuda.device_count() >= 2 * num_actors:
+                offset = num_actors
+        except Exception:  # noqa: BLE001
+            pass
+        text_group = ActorGroup(text_config, text_cls, num_actors, collocate=False,
+                                rpc_timeout_s=tr.get("rpc_timeout_s"), gpu_offset=offset)
+        log.info("Text actors on hosts of their own (GPU offset %d)", offset)
     try:
         return _run(cfg, vision_group, text_group, num_actors, parallel_size, dp_size)
     finally:
         vision_group.shutdown()
+        if not collocate:
+            text_group.shutdown()
 
 
 def _run(cfg, vision_group, text_group, num_actors, parallel_size, dp_size) -> dict:

@@ -99,7 +99,8 @@ class TextTrainer(Trainer):
                 raise RuntimeError("this batch has images but no vision output was passed")
             if vis.shape[0] != sum(plan.send_counts):
                 raise RuntimeError(f"vision rows ({vis.shape[0]}) do not match the plan ({sum(plan.send_counts)})")
-            leaf = vis.detach().to(x.dtype).requires_grad_(True)
+            # rows handed over by value from a vision actor in another process arrive as host tensors
+            leaf = vis.detach().to(device=dev, dtype=x.dtype).requires_grad_(True)
             self._vision_leaf = leaf
             fused = self.state.fused
             if fused is not None and x.is_cuda:

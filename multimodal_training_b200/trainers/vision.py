@@ -158,7 +158,7 @@ class VisionTrainer(Trainer):
             return {}
         if grad.dim() == merged.dim() + 1:
             grad = grad.squeeze(0)
-        merged.backward(gradient=grad.to(merged.dtype))
+        merged.backward(gradient=grad.to(device=merged.device, dtype=merged.dtype))
         out = {}
         ms = self._timer_stop(t0)
         if ms is not None:

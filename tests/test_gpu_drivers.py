@@ -37,3 +37,15 @@ def test_actor_and_spmd_drivers_train_like_the_engine_on_two_gpus():
         assert len(res["losses"]) == 10, (name, res)
         for a, b in zip(res["losses"], engine["losses"]):
             assert abs(a - b) < 2e-2 * abs(b), (name, res["losses"], engine["losses"])
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_non_collocated_placement_on_two_gpus():
+    """``training.collocate: false`` with one actor per half: the vision encoder on GPU 0, the text decoder on GPU 1,
+    rows and gradients handed over by value; the losses are those of the collocated run on one GPU."""
+    base = ["+data.synthetic.global_batch=2"]
+    together = _run([sys.executable, WORKER, "actor", "1"] + base)
+    apart = _run([sys.executable, WORKER, "actor", "1", "training.collocate=false"] + base)
+    assert len(apart["losses"]) == 10 and apart["losses"][-1] < apart["losses"][0]
+    for a, b in zip(apart["losses"], together["losses"]):
+        assert abs(a - b) < 2e-2 * abs(b), (apart["losses"], together["losses"])

@@ -401,3 +401,24 @@ def test_a_rank_that_leaves_between_steps_fails_the_others_next_collective(tmp_p
     import json
     res = json.load(open(tmp_path / "c" / "survivor.json"))
     assert res["error"] is not None and res["waited"] < 120 and res["first"] == res["first"], res
+
+
+def test_non_collocated_groups_train_like_collocated_ones(tmp_path):
+    """``training.collocate: false``: the text actors live in host processes (and a torch.distributed world) of their
+    own; vision rows and their gradients travel between the groups by value through the driver.  Same losses as
+    the collocated run, and the two groups really are different processes."""
+    from multimodal_training_b200 import train
+    from multimodal_training_b200.runtime.actor_group import ActorGroup
+    a = train.main(_cfg(tmp_path / "a", **{"training.no_checkpoint": "true"}))
+    b = train.main(_cfg(tmp_path / "b", **{"training.no_checkpoint": "true", "training.collocate": "false"}))
+    assert len(b["losses"]) == len(a["losses"]) == 3
+    for x, y in zip(a["losses"], b["losses"]):
+        assert abs(x - y) < 1e-6 * abs(x), (a["losses"], b["losses"])
+    g1 = ActorGroup({"tag": "vision", "runtime": "builtin"}, Echo, 2, backend="gloo")
+    g2 = ActorGroup({"tag": "text", "runtime": "builtin"}, Echo, 2, collocate=False, backend="gloo", gpu_offset=2)
+    try:
+        p1, p2 = g1.execute_all("whoami"), g2.execute_all("whoami")
+        assert not {x["pid"] for x in p1} & {x["pid"] for x in p2}
+    finally:
+        g1.shutdown()
+        g2.shutdown()
