@@ -5,6 +5,7 @@
   ``labels`` concatenated along the token axis, ``position_ids`` along their last axis, and
   ``attention_mask`` = cumulative sequence lengths (int32) for varlen attention.
 * :class:`VisionDataCollator` concatenates ``pixel_values`` and ``image_grid_thw``.
+Video clips ride along the same way (``pixel_values_videos`` / ``video_grid_thw``, python/data/collator.py:51-71).
 All carry ``sample_index`` so that the vision and text halves can check that they see the same samples.
 """
 from __future__ import annotations
@@ -29,6 +30,12 @@ def _images(instances):
     return (torch.cat(px, 0) if px else None), (torch.cat(grids, 0) if grids else None)
 
 
+def _videos(instances):
+    px = [i["pixel_values_videos"] for i in instances if i.get("pixel_values_videos") is not None]
+    grids = [i["video_grid_thw"] for i in instances if i.get("video_grid_thw") is not None]
+    return (torch.cat(px, 0) if px else None), (torch.cat(grids, 0) if grids else None)
+
+
 def _sample_index(instances):
     return torch.cat([torch.as_tensor(i["sample_index"]).reshape(-1) for i in instances], dim=0)
 
@@ -48,8 +55,10 @@ class DataCollatorForSupervisedDataset:
         lens = torch.tensor([min(len(x), L) for x in ids])
         mask = torch.arange(input_ids.shape[1])[None, :] < lens[:, None]
         px, grid = _images(instances)
+        vx, vgrid = _videos(instances)
         return {"input_ids": input_ids, "labels": lab, "attention_mask": mask, "position_ids": pos,
-                "pixel_values": px, "image_grid_thw": grid, "sample_index": _sample_index(instances)}
+                "pixel_values": px, "image_grid_thw": grid, "pixel_values_videos": vx, "video_grid_thw": vgrid,
+                "sample_index": _sample_index(instances)}
 
 
 @dataclass
@@ -60,13 +69,17 @@ class FlattenedDataCollatorForSupervisedDataset(DataCollatorForSupervisedDataset
         lens = [0] + [x.shape[1] for x in ids]
         cu = torch.tensor(lens, dtype=torch.int32).cumsum(0).to(torch.int32)
         px, grid = _images(instances)
+        vx, vgrid = _videos(instances)
         return {"input_ids": torch.cat(ids, 1), "labels": torch.cat(labels, 1),
                 "position_ids": torch.cat([i["position_ids"] for i in instances], dim=2), "attention_mask": cu,
-                "pixel_values": px, "image_grid_thw": grid, "sample_index": _sample_index(instances)}
+                "pixel_values": px, "image_grid_thw": grid, "pixel_values_videos": vx, "video_grid_thw": vgrid,
+                "sample_index": _sample_index(instances)}
 
 
 @dataclass
 class VisionDataCollator:
     def __call__(self, instances):
         px, grid = _images(instances)
-        return {"pixel_values": px, "image_grid_thw": grid, "sample_index": _sample_index(instances)}
+        vx, vgrid = _videos(instances)
+        return {"pixel_values": px, "image_grid_thw": grid, "pixel_values_videos": vx, "video_grid_thw": vgrid,
+                "sample_index": _sample_index(instances)}

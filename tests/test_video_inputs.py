@@ -71,3 +71,24 @@ def test_video_attention_stays_inside_a_temporal_patch_and_the_wrapper_trains_on
     assert torch.isfinite(out["loss"])
     out["loss"].backward()
     assert model.model.visual.patch_embed_w.grad.abs().sum() > 0
+
+
+def test_collators_carry_video_clips():
+    """The collators concatenate clips and their grids like images (python/data/collator.py:51-71)."""
+    import torch
+    from multimodal_training_b200.data.collator import (DataCollatorForSupervisedDataset,
+                                                        FlattenedDataCollatorForSupervisedDataset, VisionDataCollator)
+
+    def inst(i, with_video):
+        d = {"input_ids": torch.arange(4 + i)[None], "labels": torch.arange(4 + i)[None],
+             "position_ids": torch.zeros(3, 1, 4 + i, dtype=torch.long), "sample_index": torch.tensor([i])}
+        if with_video:
+            d["pixel_values_videos"] = torch.full((8, 6), float(i))
+            d["video_grid_thw"] = torch.tensor([[2, 2, 2]])
+        return d
+    batch = [inst(0, True), inst(1, False), inst(2, True)]
+    for coll in (DataCollatorForSupervisedDataset(), FlattenedDataCollatorForSupervisedDataset(), VisionDataCollator()):
+        out = coll(batch)
+        assert out["pixel_values_videos"].shape == (16, 6) and out["video_grid_thw"].tolist() == [[2, 2, 2], [2, 2, 2]]
+        assert out["pixel_values"] is None and out["image_grid_thw"] is None
+    assert VisionDataCollator()([inst(1, False)])["pixel_values_videos"] is None
