@@ -1337,7 +1337,7 @@ void read_env_once() {
   }
   if (g_mt2_const < 0.0) {
     const char* e = getenv("MMT_GEMM_MT2_CONST");
-    g_mt2_const = e ? atof(e) : 5.5;
+    g_mt2_const = e ? atof(e) : 4.06;
   }
 }
 cudaEvent_t g_sk_event = nullptr;
@@ -1515,9 +1515,11 @@ extern "C" int mmt_gemm_bf16(const void* A, const void* B, void* C, const void* 
   // 256 (two accumulators that share every B tile: the main loop alternates between them, which keeps the tensor pipe
   // busier than back-to-back MMAs into one accumulator, but the two fill tensor memory and the epilogue is exposed);
   // width = 192 or 256 columns (narrower only for narrow outputs: a 128-wide MMA is bound by shared-memory reads).
-  // Cost of a candidate = waves x (k-blocks x c + e), in units of one 256 x 256 x 64 step, with c and e fitted to
-  // sustained measurements on B200 (rows x width: 128 x 256 c 0.568 e 2.4; 256 x 256 c 1.03 e 5.5; 128 x 192
-  // c 0.458 e 2.7; 256 x 192 c 0.72 e 8.0).  What it mostly decides is how well the tile count fills the 148 SMs.
+  // Cost of a candidate = waves x (k-blocks x c + e), in units of one 256 x 256 x 64 step, with c and e fitted (least
+  // squares over 200 sustained measurements on B200: the step's text shapes, the short-K vision shapes and the
+  // tensor-parallel shards, all layouts) per tile shape (rows x width: 128 x 256 c 0.568 e 0.86; 256 x 256 c 0.824
+  // e 4.06; 128 x 192 c 0.507 e 0.4; 256 x 192 c 0.726 e 2.61).  What it mostly decides is how well the tile count
+  // fills the 148 SMs.
   read_env_once();
   int mt = 1;
   const long kb = (K + BK - 1) / BK;
@@ -1529,8 +1531,8 @@ extern "C" int mmt_gemm_bf16(const void* A, const void* B, void* C, const void* 
     if (rem && plain && width == 256 && sk_tiles_for((int)tiles, kb, sms, m) > 0)
       waves = (double)full + (double)rem / sms + (m == 2 ? 16.0 : 8.0) / (double)kb;
     double c, e;
-    if (width == 256) { c = m == 2 ? 1.03 : 0.568; e = m == 2 ? g_mt2_const : 2.4; }
-    else              { c = m == 2 ? 0.72 : 0.458; e = m == 2 ? 8.0 : 2.7; }
+    if (width == 256) { c = m == 2 ? 0.824 : 0.568; e = m == 2 ? g_mt2_const : 0.86; }
+    else              { c = m == 2 ? 0.726 : 0.507; e = m == 2 ? 2.61 : 0.4; }
     return waves * ((double)kb * c + e);
   };
   if (bn == 0 && g_force_bn) bn = g_force_bn;
