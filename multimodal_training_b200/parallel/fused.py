@@ -193,6 +193,14 @@ class FusedComm:
         if heap.regions.version != heap.verified_version:
             heap.verify_layout()
 
+    def reset_after_error(self) -> None:
+        """A kernel that gave up on a wait may have left a completion counter half way (the CTA that would have
+        published and reset it never came): zero this rank's counters so that a later step does not publish early.
+        Called (after a device synchronisation) when the error word was found set; the step is invalid anyway."""
+        if self._ag_counter is not None:
+            self._ag_counter.zero_()
+        self.ctx.heap.tensor(self.ctx.counters_off, (N_SLOTS,), torch.int32).zero_()
+
     def capacity_rows(self, what: str, rows: int) -> int:
         """Rows to reserve for a buffer of kind ``what`` that needs ``rows`` now: the step's world-wide maximum."""
         s = self._sizes

@@ -290,7 +290,12 @@ class Trainer(RayActor):
         if self._get_device().type == "cuda":
             from ..ops import native as nv
             if nv.available():
-                nv.raise_on_device_error()
+                try:
+                    nv.raise_on_device_error()
+                except RuntimeError:
+                    if self.state.fused is not None:
+                        self.state.fused.reset_after_error()
+                    raise
         return True
 
     def get_memory_stats(self) -> dict:
