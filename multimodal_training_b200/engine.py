@@ -8,7 +8,6 @@ forward, text backward, vision backward, gradient norm, two optimizer steps.  Th
 """
 from __future__ import annotations
 
-import math
 
 import torch
 import torch.distributed as dist

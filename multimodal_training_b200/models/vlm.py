@@ -19,7 +19,6 @@ import torch.nn as nn
 
 from ..config.model_configs import VLConfig, get_model_config
 from ..data.rope_utils import get_rope_index_for_images
-from ..ops import functional as F
 from ..ops.attention import SeqInfo
 from ..parallel.sp import build_vision_plan
 from .text import TextDecoder, mrope_cos_sin

@@ -8,7 +8,7 @@ PyTorch, so a silent non-native path cannot pass the GPU tests.
 from __future__ import annotations
 
 import ctypes
-from ctypes import c_char_p, c_float, c_int, c_long, c_uint32, c_void_p
+from ctypes import c_char_p, c_float, c_int, c_long, c_void_p
 from pathlib import Path
 
 import torch

@@ -14,7 +14,6 @@ from __future__ import annotations
 
 import logging
 import math
-import os
 import sys
 import time
 

@@ -20,7 +20,6 @@ import torch.distributed as dist
 
 from ..config.model_configs import VLConfig, get_model_config
 from ..data.synthetic import synthetic_global_batch
-from ..parallel import comm
 from ..parallel.mesh import Mesh, build_mesh
 from ..parallel.zero import ZeroAdamW, lr_at
 from ..runtime.actor import RayActor

@@ -11,7 +11,6 @@ interleavings (including one rank lagging as far behind as its peers' waits allo
 * no schedule deadlocks (every wait is eventually satisfied).
 """
 import random
-import types
 
 import pytest
 import torch

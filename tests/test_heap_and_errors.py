@@ -1,6 +1,5 @@
 """Host-side rules of the symmetric heap (regions that grow, move and stay aligned across ranks) and of the device
 error word on the training path; no GPU needed."""
-import types
 
 import pytest
 import torch
