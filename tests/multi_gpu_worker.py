@@ -36,7 +36,10 @@ def run(fused: bool, steps: int, vision: str = "sequence", ragged: bool = False,
     os.environ["MMT_ULYSSES_BLOCK"] = "1" if ul_block else "0"
     eng = HybridEngine.from_config(cfg)
     assert (process_state().fused is not None) == fused
-    losses = [eng.mean_loss(eng.train_step(s if ragged else 0)) for s in range(steps)]
+    losses = []
+    for s in range(steps):
+        losses.append(eng.mean_loss(eng.train_step(s if ragged else 0)))
+        nv.raise_on_device_error()        # fail at the first step whose exchanges gave up, not after crawling through all
     if fused and ragged:
         heap = process_state().fused.ctx.heap
         assert heap.regions.version == heap.verified_version     # every layout change was compared across ranks

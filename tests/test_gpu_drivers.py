@@ -16,7 +16,7 @@ WORKER = os.path.join(HERE, "driver_gpu_worker.py")
 
 def _run(cmd):
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1")
-    out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=900)
+    out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
     assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
     line = [ln for ln in out.stdout.splitlines() if ln.startswith("RESULT ")][-1]
     return json.loads(line[len("RESULT "):])
@@ -27,6 +27,7 @@ def _torchrun(mode, port):
             "127.0.0.1", "--master-port", str(port), WORKER, mode]
 
 
+@pytest.mark.timeout(420)
 @pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_actor_and_spmd_drivers_train_like_the_engine_on_two_gpus():
     engine = _run(_torchrun("engine", 29541))
@@ -39,6 +40,7 @@ def test_actor_and_spmd_drivers_train_like_the_engine_on_two_gpus():
             assert abs(a - b) < 2e-2 * abs(b), (name, res["losses"], engine["losses"])
 
 
+@pytest.mark.timeout(420)
 @pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_non_collocated_placement_on_two_gpus():
     """``training.collocate: false`` with one actor per half: the vision encoder on GPU 0, the text decoder on GPU 1,

@@ -12,12 +12,13 @@ pytestmark = pytest.mark.gpu
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
+@pytest.mark.timeout(420)
 @pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_fused_collectives_match_nccl_on_two_gpus():
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
            "127.0.0.1", "--master-port", "29533", os.path.join(HERE, "multi_gpu_worker.py")]
-    out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=400)
     assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
     line = [ln for ln in out.stdout.splitlines() if ln.startswith("RESULT ")][-1]
     res = json.loads(line[len("RESULT "):])
