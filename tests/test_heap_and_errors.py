@@ -111,3 +111,33 @@ def test_a_failed_checkpoint_load_puts_the_old_weights_back(tmp_path):
     torch.save({"model": {"a": torch.full((3,), 7.0)}}, path / "rank_0.pt")
     assert tr.load_checkpoint(str(tmp_path), 0) is False
     assert torch.equal(tr.model.a.detach(), torch.ones(3)) and torch.equal(tr.model.b.detach(), torch.ones(3))
+
+
+def test_region_allocator_invariants_under_random_request_streams():
+    """Property check (hypothesis): whatever the stream of (name, size) requests, live regions never overlap, stay
+    inside the heap and aligned, a request that fits returns the same offset again, and two allocators fed the same
+    stream (two ranks) end with the same table and digest."""
+    from hypothesis import given, settings
+    from hypothesis import strategies as st
+
+    from multimodal_training_b200.parallel.symm import RegionAllocator
+
+    names = st.sampled_from(["ag_qkv", "ag_mlp", "rs_o", "rs_down", "handoff_in", "ul_heads3", "ul_tokens1"])
+    sizes = st.integers(min_value=1, max_value=1 << 20)
+
+    @settings(max_examples=200, deadline=None)
+    @given(st.lists(st.tuples(names, sizes), min_size=1, max_size=60))
+    def check(stream):
+        a, b = RegionAllocator(1 << 26), RegionAllocator(1 << 26)
+        for name, size in stream:
+            off = a.alloc(name, size)
+            assert b.alloc(name, size) == off and off % 1024 == 0
+            assert a.alloc(name, size) == off                        # asking again does not move it
+            live = sorted(a.table(), key=lambda kv: kv[1][0])
+            for (_, (o1, s1)), (_, (o2, _)) in zip(live, live[1:]):
+                assert o1 + s1 <= o2                                 # no overlap
+            assert all(o + s <= 1 << 26 for _, (o, s) in live)
+            assert dict(a.table())[name][1] >= size
+        assert a.digest() == b.digest() and a.table() == b.table()
+
+    check()
