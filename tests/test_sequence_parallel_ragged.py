@@ -117,3 +117,46 @@ def test_image_major_order_is_the_window_order_of_all_patches():
         for r, p in enumerate(plans):
             dst = torch.from_numpy(inv[off[r]:off[r + 1]])
             assert torch.equal(cos_all[dst], p.local_cos) and torch.equal(sin_all[dst], p.local_sin)
+
+
+def test_plan_invariants_for_random_image_sets():
+    """Property check (hypothesis) over random batches of ragged images and sequence-parallel sizes: the ranks' local
+    patches partition all patches; every rank's cut falls on a window boundary and on a merge-unit boundary; the
+    exchange maps are inverse permutations; per-image sequence boundaries add up; the Ulysses routes of all ranks
+    tile the gathered sequence exactly once."""
+    import numpy as np
+    from hypothesis import assume, given, settings
+    from hypothesis import strategies as st
+
+    from multimodal_training_b200.parallel.sp import build_vision_plan
+
+    side = st.integers(min_value=2, max_value=20).map(lambda v: 2 * v)          # even grids (2 x 2 merge)
+    grid = st.tuples(st.sampled_from([1, 1, 1, 2]), side, side)
+
+    @settings(max_examples=60, deadline=None)
+    @given(st.lists(grid, min_size=1, max_size=4), st.sampled_from([1, 2, 4]))
+    def check(grids, sp):
+        total = sum(t * h * w for t, h, w in grids)
+        try:
+            plans = [build_vision_plan(grids, sp=sp, rank=r, spatial_merge_size=2, window_size=112, patch_size=14,
+                                       head_dim=16) for r in range(sp)]
+        except ValueError:
+            assume(False)                       # a split that would leave a rank without tokens is refused
+        assert plans[0].n_patches == total and sum(plans[0].rank_tokens) == total
+        seen = np.concatenate([p.local_patch_index.numpy() for p in plans])
+        assert sorted(seen.tolist()) == list(range(total))                       # a partition of all patches
+        for r, p in enumerate(plans):
+            assert p.local_tokens == p.rank_tokens[r] == int(p.local_patch_index.numel())
+            assert p.local_tokens % 4 == 0 and p.local_merged_ids.numel() == p.local_tokens // 4
+            assert p.win_cu[0] == 0 and p.win_cu[-1] == p.local_tokens and all(b > a for a, b in zip(p.win_cu, p.win_cu[1:]))
+            assert p.full_cu[-1] == total
+        if sp > 1:
+            fwd, inv = plans[0].to_image_major.numpy(), plans[0].to_rank_major.numpy()
+            assert sorted(fwd.tolist()) == list(range(total)) and (inv[fwd] == np.arange(total)).all()
+            off = np.concatenate([[0], np.cumsum(plans[0].rank_tokens)])
+            rows = np.concatenate([inv[off[r]:off[r + 1]] for r in range(sp)])
+            assert sorted(rows.tolist()) == list(range(total))                   # destination rows: each exactly once
+        merged = np.concatenate([p.local_merged_ids.numpy() for p in plans])
+        assert sorted(merged.tolist()) == list(range(total // 4))
+
+    check()
