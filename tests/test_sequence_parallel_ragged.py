@@ -160,3 +160,49 @@ def test_plan_invariants_for_random_image_sets():
         assert sorted(merged.tolist()) == list(range(total // 4))
 
     check()
+
+
+@pytest.mark.parametrize("world,sp,tp", [(2, 2, 2), (4, 2, 2), (4, 4, 2), (8, 8, 4)])
+def test_handoff_routes_are_consistent_across_the_world(world, sp, tp):
+    """The handoff plans of all ranks, built independently from the same batch: what rank a says it sends to rank b
+    is what b expects from a; every merged vision token has exactly one destination row; every image-placeholder row
+    of every text shard receives exactly one token; the peer-memory routes (dest_rank, dest_row) agree with the
+    all-to-all routes."""
+    import numpy as np
+    from multimodal_training_b200.config.model_configs import get_model_config
+    from multimodal_training_b200.data.synthetic import synthetic_global_batch
+    from multimodal_training_b200.parallel.mesh import Mesh
+    from multimodal_training_b200.trainers.context import build_step_context
+
+    cfg = get_model_config("tiny")
+    vdp = world // sp
+    B = 2 * max(vdp, world // tp)
+    samples = synthetic_global_batch(cfg, 0, B, image_size=224, text_tokens=48, seed=9, dtype=torch.float32,
+                                     image_sizes=[224, 252, 336], text_token_choices=[48, 80, 33])
+    ctxs = [build_step_context(0, samples, cfg, Mesh(world=world, rank=r, sp=sp, tp=tp)) for r in range(world)]
+    plans = [c.handoff for c in ctxs]
+    assert all(p is not None for p in plans)
+    for a in range(world):
+        for b in range(world):
+            assert plans[a].send_counts[b] == plans[b].recv_counts[a], (a, b)
+    n_merged = sum(int(t * h * w) // 4 for s in samples for (t, h, w) in s.grid_thw)
+    assert sum(sum(p.send_counts) for p in plans) == n_merged
+    taken = set()
+    for r, p in enumerate(plans):
+        rows = p.recv_rows.numpy()
+        assert len(set(rows.tolist())) == len(rows) and (rows < p.shard_rows).all()      # one token per row
+        taken |= {(r, int(x)) for x in rows}
+        # peer-memory routes: the same pairs, grouped by destination
+        dest = p.dest_rank.numpy()
+        assert np.bincount(dest, minlength=world).tolist() == p.send_counts
+    pairs = set()
+    for p in plans:
+        pairs |= set(zip(p.dest_rank.numpy().tolist(), p.dest_row.numpy().tolist()))
+    assert pairs == taken and len(pairs) == n_merged
+    # the rows that receive a token are exactly the image placeholders of the text shards
+    for r, c in enumerate(ctxs):
+        tb, m = c.text_batch, Mesh(world=world, rank=r, sp=sp, tp=tp)
+        shard = plans[r].shard_rows
+        ph = np.concatenate(tb.image_rows) if tb.image_rows else np.zeros(0, np.int64)
+        mine = ph[(ph // shard) == m.tp_rank] % shard
+        assert sorted(mine.tolist()) == sorted(plans[r].recv_rows.numpy().tolist())
