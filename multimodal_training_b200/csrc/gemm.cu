@@ -26,6 +26,7 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <cstddef>
 #include "common.cuh"
 #include "runtime.h"
 
@@ -1484,6 +1485,24 @@ struct MmtGemmComm {
   const int* kf_flags;
   int kf_epoch, kf_w, kf_self, kf_ranks;
 };
+
+// Layout of MmtGemmComm as this library was compiled: {sizeof, offsets of a few fields}.  The Python binding mirrors
+// the struct with ctypes and compares itself with these numbers when it loads (a mismatch would send peer addresses
+// into the wrong fields).  Returns the number of values written.
+extern "C" int mmt_gemm_comm_layout(int* out, int n) {
+  const int v[] = {(int)sizeof(MmtGemmComm),          (int)offsetof(MmtGemmComm, ag_flags),
+                   (int)offsetof(MmtGemmComm, ag_self),     (int)offsetof(MmtGemmComm, fwd_dst),
+                   (int)offsetof(MmtGemmComm, fwd_flag),    (int)offsetof(MmtGemmComm, fwd_peers),
+                   (int)offsetof(MmtGemmComm, fwd_src),     (int)offsetof(MmtGemmComm, fwd_src_ld),
+                   (int)offsetof(MmtGemmComm, fwd_counter), (int)offsetof(MmtGemmComm, rs_base),
+                   (int)offsetof(MmtGemmComm, rs_flag),     (int)offsetof(MmtGemmComm, rs_counter),
+                   (int)offsetof(MmtGemmComm, rs_rows),     (int)offsetof(MmtGemmComm, rs_epoch),
+                   (int)offsetof(MmtGemmComm, sc_row),      (int)offsetof(MmtGemmComm, sc_rows_dst),
+                   (int)offsetof(MmtGemmComm, kf_flags),    (int)offsetof(MmtGemmComm, kf_ranks)};
+  const int count = (int)(sizeof(v) / sizeof(v[0]));
+  for (int i = 0; i < count && i < n; ++i) out[i] = v[i];
+  return count;
+}
 
 namespace {
 const MmtGemmComm* g_comm = nullptr;

@@ -61,6 +61,21 @@ class GemmCommC(ctypes.Structure):
                 ("kf_self", ctypes.c_int), ("kf_ranks", ctypes.c_int)]
 
 
+def check_gemm_comm_layout() -> None:
+    """Compare the ctypes mirror of the GEMM's collective-role struct with the layout the library was compiled with."""
+    fields = ["ag_flags", "ag_self", "fwd_dst", "fwd_flag", "fwd_peers", "fwd_src", "fwd_src_ld", "fwd_counter",
+              "rs_base", "rs_flag", "rs_counter", "rs_rows", "rs_epoch", "sc_row", "sc_rows_dst", "kf_flags", "kf_ranks"]
+    mine = [ctypes.sizeof(GemmCommC)] + [getattr(GemmCommC, f).offset for f in fields]
+    buf = (ctypes.c_int * 32)()
+    fn = nv.lib().mmt_gemm_comm_layout
+    fn.restype, fn.argtypes = ctypes.c_int, [ctypes.POINTER(ctypes.c_int), ctypes.c_int]
+    n = fn(buf, 32)
+    theirs = list(buf[:n])
+    if theirs != mine:
+        raise RuntimeError(f"GemmCommC does not match the library's MmtGemmComm: {mine} vs {theirs}; rebuild the "
+                           "library (python -m multimodal_training_b200.csrc.build) or fix the binding")
+
+
 class ZeroPeersC(ctypes.Structure):
     _fields_ = [("grad", ctypes.c_uint64 * 8), ("param", ctypes.c_uint64 * 8), ("param_flag", ctypes.c_uint64 * 8),
                 ("n", ctypes.c_int)]
@@ -135,6 +150,7 @@ class FusedComm:
         self._ag_roles: dict[str, int] = {}
         self._views: dict = {}           # (region, shape, dtype) -> (offset, tensor view of this rank's buffer)
         self._ag_counter = None          # [AG_ROLES, AG_CHUNKS] int32: shares of a row block that have been forwarded
+        check_gemm_comm_layout()
         self.ctx = HeapContext(mesh.world_group, heap_bytes, device)
         # results that live in reusable heap regions may be handed out as views only while BOTH halves recompute
         # their activations in backward; otherwise they are cloned (see set_checkpointed)

@@ -1,6 +1,8 @@
 """Host-side rules of the symmetric heap (regions that grow, move and stay aligned across ranks) and of the device
 error word on the training path; no GPU needed."""
 
+import ctypes
+
 import pytest
 import torch
 
@@ -141,3 +143,21 @@ def test_region_allocator_invariants_under_random_request_streams():
         assert a.digest() == b.digest() and a.table() == b.table()
 
     check()
+
+
+def test_ctypes_mirror_of_the_gemm_roles_matches_the_library():
+    """``parallel.fused.GemmCommC`` is a hand-written mirror of a C struct; the library reports its own layout."""
+    from multimodal_training_b200.ops import native as nv
+    from multimodal_training_b200.parallel import fused
+    if not nv.available():
+        pytest.skip("the kernel library is not built")
+    fused.check_gemm_comm_layout()
+    saved = fused.GemmCommC._fields_
+    try:
+        class Shifted(ctypes.Structure):                      # the same fields with one int inserted: must be noticed
+            _fields_ = [("extra", ctypes.c_int)] + list(saved)
+        fused.GemmCommC, real = Shifted, fused.GemmCommC
+        with pytest.raises(RuntimeError, match="does not match"):
+            fused.check_gemm_comm_layout()
+    finally:
+        fused.GemmCommC = real
