@@ -422,3 +422,18 @@ def test_non_collocated_groups_train_like_collocated_ones(tmp_path):
     finally:
         g1.shutdown()
         g2.shutdown()
+
+
+def test_driver_with_accumulation_logging_interval_and_profile_times(tmp_path):
+    """Losses are read at logging points only: with ``log_interval=2``, gradient accumulation and ``profile_time``
+    the driver still returns one loss per optimizer step, equal to a run that logs every step."""
+    from multimodal_training_b200 import train
+    base = {"training.no_checkpoint": "true", "training.num_iterations": 5}
+    every = train.main(_cfg(tmp_path / "a", **base))
+    sparse = train.main(_cfg(tmp_path / "b", **dict(base, **{"training.log_interval": 2, "training.profile_time": "true"})))
+    assert len(every["losses"]) == len(sparse["losses"]) == 5
+    for a, b in zip(every["losses"], sparse["losses"]):
+        assert abs(a - b) < 1e-6 * abs(a)
+    acc = train.main(_cfg(tmp_path / "c", **{"training.no_checkpoint": "true", "training.log_interval": 2,
+                                              "training.gradient_accumulation_steps": 2}))
+    assert acc["steps"] == 3 and len(acc["losses"]) == 3 and acc["losses"][-1] < acc["losses"][0]
