@@ -37,6 +37,9 @@ def main(cfg: dict) -> dict:
     expected = int(tr["parallel_size"]) * int(tr.get("dp_size", 1))
     if world != expected:
         raise RuntimeError(f"launched with {world} ranks but training.parallel_size x dp_size = {expected}")
+    if not bool(tr.get("collocate", True)) and rank == 0:
+        log.warning("training.collocate=false is a placement of the actor driver (python -m multimodal_training_b200."
+                    "train); this launcher runs one process per GPU with both halves in it")
     engine = HybridEngine.from_config(cfg)
 
     num_epochs, num_iterations = int(tr["num_epochs"]), int(tr["num_iterations"])
