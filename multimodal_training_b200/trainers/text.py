@@ -131,8 +131,11 @@ class TextTrainer(Trainer):
         from ..ops import native as nv
         ring = getattr(self, "_loss_ring", None)
         if ring is None:
+            # the actor driver reads losses at logging points, at the latest after 8 optimizer steps; every
+            # micro-batch of those steps holds a slot until then
+            slots = max(32, 16 * int(getattr(self, "accumulation_steps", 1)))
             ring = self._loss_ring = [(torch.zeros(1, dtype=torch.float32, pin_memory=True),
-                                       torch.zeros(4, dtype=torch.int32, pin_memory=True)) for _ in range(32)]
+                                       torch.zeros(4, dtype=torch.int32, pin_memory=True)) for _ in range(slots)]
             self._loss_i = 0
             self._err_dev = nv.error_word_tensor() if nv.available() else None
         host, err = ring[self._loss_i % len(ring)]
